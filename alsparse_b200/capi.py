@@ -1,0 +1,121 @@
+"""ctypes binding of libalphasparse_b200.so: one prototype per declaration in include/alphasparse/*.h.
+
+This is the whole Python <-> C boundary: plain pointers, 32-bit indices, enums as C ints and the
+matrix descriptor passed by value, exactly as a C caller of the reference's <alphasparse.h> sees
+them.  No torch types cross it; a torch tensor is passed as ``tensor.data_ptr()``.
+"""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libalphasparse_b200.so")
+
+# alphasparse_status_t (include/alphasparse/spdef.h)
+SUCCESS, NOT_INITIALIZED, ALLOC_FAILED, INVALID_VALUE, EXECUTION_FAILED = 0, 1, 2, 3, 4
+INTERNAL_ERROR, NOT_SUPPORTED, INVALID_POINTER, INVALID_HANDLE = 5, 6, 7, 8
+STATUS_NAMES = ["SUCCESS", "NOT_INITIALIZED", "ALLOC_FAILED", "INVALID_VALUE", "EXECUTION_FAILED",
+                "INTERNAL_ERROR", "NOT_SUPPORTED", "INVALID_POINTER", "INVALID_HANDLE"]
+# alphasparse_operation_t
+NON_TRANSPOSE, TRANSPOSE, CONJUGATE_TRANSPOSE = 0, 1, 2
+# alphasparse_matrix_type_t
+GENERAL, SYMMETRIC, HERMITIAN, TRIANGULAR, DIAGONAL = 0, 1, 2, 3, 4
+# alphasparse_index_base_t
+BASE_ZERO, BASE_ONE = 0, 1
+# alphasparse_layout_t
+ROW_MAJOR, COLUMN_MAJOR = 0, 1
+# alphasparse_format_t / alphasparse_datatype_t
+FORMAT_COO, FORMAT_CSR = 0, 1
+FLOAT, DOUBLE, FLOAT_COMPLEX, DOUBLE_COMPLEX = 0, 1, 2, 3
+# alphasparse_cuda_alg_t
+ALG_AUTO, ALG_VECTOR, ALG_MERGE = 0, 1, 2
+
+
+class MatrixDescr(C.Structure):
+    """struct alpha_matrix_descr, passed by value."""
+    _fields_ = [("type", C.c_int), ("mode", C.c_int), ("diag", C.c_int)]
+
+
+class Matrix(C.Structure):
+    """alphasparse_matrix: what an alphasparse_matrix_t points at."""
+    _fields_ = [("mat", C.c_void_p), ("format", C.c_int), ("datatype", C.c_int),
+                ("inspector", C.c_void_p), ("dcu_info", C.c_void_p)]
+
+
+class MatInfo(C.Structure):
+    """alphasparse_cuda_mat_info_t"""
+    _fields_ = [("rows", C.c_int64), ("cols", C.c_int64), ("nnz", C.c_int64),
+                ("max_row_nnz", C.c_int64), ("empty_rows", C.c_int64), ("mean_row_nnz", C.c_double),
+                ("algorithm", C.c_int32), ("lanes_per_row", C.c_int32), ("merge_tiles", C.c_int64),
+                ("device_bytes", C.c_int64), ("device", C.c_int32), ("reserved", C.c_int32)]
+
+
+class Complex8(C.Structure):
+    _fields_ = [("real", C.c_float), ("imag", C.c_float)]
+
+
+class Complex16(C.Structure):
+    _fields_ = [("real", C.c_double), ("imag", C.c_double)]
+
+
+_H = C.c_void_p           # alphasparse_matrix_t
+_HP = C.POINTER(C.c_void_p)
+_I = C.c_int32
+_P = C.c_void_p
+
+_REAL = {"s": C.c_float, "d": C.c_double}
+_CPLX = {"c": Complex8, "z": Complex16}
+
+
+def prototypes():
+    """name -> (restype, argtypes) for every exported function the headers declare."""
+    p = {}
+    for k, T in list(_REAL.items()) + list(_CPLX.items()):
+        p[f"alphasparse_{k}_create_coo"] = (C.c_int, [_HP, C.c_int, _I, _I, _I, _P, _P, _P])
+        p[f"alphasparse_{k}_create_csr"] = (C.c_int, [_HP, C.c_int, _I, _I, _P, _P, _P, _P])
+        p[f"alphasparse_{k}_mv"] = (C.c_int, [C.c_int, T, _H, MatrixDescr, _P, T, _P])
+        p[f"alphasparse_{k}_mm"] = (C.c_int, [C.c_int, T, _H, MatrixDescr, C.c_int, _P, _I, _I, T, _P, _I])
+    for k in _REAL:
+        p[f"alphasparse_{k}_export_csr"] = (C.c_int, [_H, C.POINTER(C.c_int), C.POINTER(_I), C.POINTER(_I),
+                                                       _HP, _HP, _HP, _HP])
+    p["alphasparse_destroy"] = (C.c_int, [_H])
+    p["alphasparse_convert_csr"] = (C.c_int, [_H, C.c_int, _HP])
+    p["alphasparse_set_mv_hint"] = (C.c_int, [_H, C.c_int, MatrixDescr, _I])
+    p["alphasparse_optimize"] = (C.c_int, [_H])
+    # include/alphasparse/spapi_cuda.h
+    p["alphasparse_cuda_set_stream"] = (C.c_int, [_P])
+    p["alphasparse_cuda_get_stream"] = (C.c_int, [_HP])
+    p["alphasparse_cuda_synchronize"] = (C.c_int, [])
+    p["alphasparse_cuda_set_algorithm"] = (C.c_int, [C.c_int])
+    p["alphasparse_cuda_get_mat_info"] = (C.c_int, [_H, C.POINTER(MatInfo)])
+    p["alphasparse_cuda_get_device_csr"] = (C.c_int, [_H, _HP, _HP, _HP])
+    p["alphasparse_cuda_launch_count"] = (C.c_int64, [])
+    p["alphasparse_cuda_last_error"] = (C.c_char_p, [])
+    # include/alphasparse/util.h
+    p["alpha_malloc"] = (C.c_void_p, [C.c_size_t])
+    p["alpha_memalign"] = (C.c_void_p, [C.c_size_t, C.c_size_t])
+    p["alpha_free"] = (None, [C.c_void_p])
+    p["alpha_get_core_num"] = (C.c_int, [])
+    p["alpha_set_thread_num"] = (None, [C.c_int])
+    p["alpha_get_thread_num"] = (C.c_int, [])
+    p["alpha_timing_wtime"] = (C.c_double, [])
+    p["lower_bound_int"] = (C.c_int, [_P, _I, _I, _I])
+    p["balanced_partition_row_by_nnz"] = (None, [_P, _I, _I, _P])
+    return p
+
+
+_lib = None
+
+
+def load():
+    """Loads the library (once).  Fails loudly when it has not been built: there is no fallback."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: run `python -m alsparse_b200.build` "
+                              "(the CUDA library is the only compute path)")
+        lib = C.CDLL(LIB_PATH, mode=C.RTLD_LOCAL)
+        for name, (res, args) in prototypes().items():
+            fn = getattr(lib, name)  # AttributeError if a declared symbol is not exported
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib

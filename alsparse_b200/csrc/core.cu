@@ -1,0 +1,733 @@
+// Handle layer and entry points of libalphasparse_b200.so: everything between the C ABI of
+// include/alphasparse/spapi.h and the kernels.  Host code only; the kernels live in spmv.cu
+// and spmm.cu.  There is no CPU compute path in this library: when no CUDA device can be
+// used the create calls fail and mv / mm cannot be reached.
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+#include <new>
+#include <numeric>
+#include <vector>
+
+#include "alphasparse/spapi.h"
+#include "alphasparse/util.h"
+#include "internal.h"
+
+namespace asb {
+
+// ---- process-wide state ---------------------------------------------------------------------
+
+static std::atomic<cudaStream_t> g_stream{nullptr};
+static std::atomic<int> g_alg{-1};
+static std::atomic<long long> g_launches{0};
+static thread_local char t_error[256] = "";
+
+cudaStream_t current_stream() { return g_stream.load(std::memory_order_relaxed); }
+
+alphasparse_cuda_alg_t forced_algorithm() {
+    int a = g_alg.load(std::memory_order_relaxed);
+    if (a < 0) {
+        a = ALPHA_SPARSE_CUDA_ALG_AUTO;
+        if (const char *env = getenv("ALPHASPARSE_CUDA_ALG")) {
+            if (!strcmp(env, "vector")) a = ALPHA_SPARSE_CUDA_ALG_VECTOR;
+            else if (!strcmp(env, "merge")) a = ALPHA_SPARSE_CUDA_ALG_MERGE;
+        }
+        g_alg.store(a, std::memory_order_relaxed);
+    }
+    return (alphasparse_cuda_alg_t)a;
+}
+
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+void record_cuda_error(cudaError_t e, const char *what) {
+    snprintf(t_error, sizeof(t_error), "%s: %s", what, cudaGetErrorString(e));
+    (void)cudaGetLastError();  // clear the sticky-free error so later calls start clean
+}
+
+// ---- device context ----------------------------------------------------------------------------
+
+DeviceCtx *ctx_of(const alphasparse_matrix_t A) {
+    if (!A || !A->dcu_info) return nullptr;
+    DeviceCtx *c = static_cast<DeviceCtx *>(A->dcu_info);
+    return c->magic == kCtxMagic ? c : nullptr;
+}
+
+void ctx_destroy(DeviceCtx *c) {
+    if (!c) return;
+    int prev = -1;
+    cudaGetDevice(&prev);
+    cudaSetDevice(c->device);
+    cudaFree(c->d_row_ptr);
+    cudaFree(c->d_col);
+    cudaFree(c->d_val);
+    cudaFree(c->d_tile);
+    cudaFree(c->d_carry_row);
+    cudaFree(c->d_carry_val);
+    cudaFree(c->d_x_stage);
+    cudaFree(c->d_y_stage);
+    if (prev >= 0) cudaSetDevice(prev);
+    c->magic = 0;
+    delete c;
+}
+
+alphasparse_status_t ctx_create(int datatype, int64_t rows, int64_t cols, const int *ptr,
+                                const int *col, const void *val, DeviceCtx **out) {
+    *out = nullptr;
+    int dev = 0;
+    ASB_CUDA_OR(cudaGetDevice(&dev), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    DeviceCtx *c = new (std::nothrow) DeviceCtx();
+    if (!c) return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    c->device = dev;
+    c->datatype = datatype;
+    c->rows = rows, c->cols = cols;
+    c->nnz = rows > 0 ? (int64_t)ptr[rows] - (int64_t)ptr[0] : 0;
+    const size_t tsz = datatype == ALPHA_SPARSE_DATATYPE_DOUBLE ? 8 : 4;
+    const size_t padded = (size_t)c->nnz + kTailPad;
+    cudaStream_t st = current_stream();
+
+    auto fail = [&](alphasparse_status_t s) {
+        ctx_destroy(c);
+        return s;
+    };
+#define TRY(expr, status)                        \
+    do {                                         \
+        cudaError_t _e = (expr);                 \
+        if (_e != cudaSuccess) {                 \
+            record_cuda_error(_e, #expr);        \
+            return fail(status);                 \
+        }                                        \
+    } while (0)
+
+    TRY(cudaMalloc(&c->d_row_ptr, sizeof(int) * (size_t)(rows + 1)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMalloc(&c->d_col, sizeof(int) * padded), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMalloc(&c->d_val, tsz * padded), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    c->device_bytes = (int64_t)(sizeof(int) * (size_t)(rows + 1) + (sizeof(int) + tsz) * padded);
+
+    if (rows > 0) {
+        TRY(cudaMemcpyAsync(c->d_row_ptr, ptr, sizeof(int) * (size_t)(rows + 1),
+                            cudaMemcpyHostToDevice, st),
+            ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    } else {
+        TRY(cudaMemsetAsync(c->d_row_ptr, 0, sizeof(int), st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    }
+    if (c->nnz > 0) {
+        TRY(cudaMemcpyAsync(c->d_col, col, sizeof(int) * (size_t)c->nnz, cudaMemcpyHostToDevice, st),
+            ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        TRY(cudaMemcpyAsync(c->d_val, val, tsz * (size_t)c->nnz, cudaMemcpyHostToDevice, st),
+            ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    }
+    TRY(cudaMemsetAsync(c->d_col + c->nnz, 0, sizeof(int) * kTailPad, st),
+        ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaMemsetAsync(static_cast<char *>(c->d_val) + tsz * (size_t)c->nnz, 0, tsz * kTailPad, st),
+        ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+#undef TRY
+
+    alphasparse_status_t s = ctx_analyse(c);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return fail(s);
+    *out = c;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+// ---- host copies ---------------------------------------------------------------------------------
+
+template <typename T>
+struct CsrOf;
+template <>
+struct CsrOf<float> {
+    using csr = spmat_csr_s_t;
+    using coo = spmat_coo_s_t;
+    static constexpr alphasparse_datatype_t dt = ALPHA_SPARSE_DATATYPE_FLOAT;
+};
+template <>
+struct CsrOf<double> {
+    using csr = spmat_csr_d_t;
+    using coo = spmat_coo_d_t;
+    static constexpr alphasparse_datatype_t dt = ALPHA_SPARSE_DATATYPE_DOUBLE;
+};
+
+static void *host_alloc(size_t bytes) {
+    void *p = nullptr;
+    if (posix_memalign(&p, 64, bytes ? bytes : 64) != 0) return nullptr;
+    return p;
+}
+
+template <typename T>
+static void free_csr_host(typename CsrOf<T>::csr *m) {
+    if (!m) return;
+    free(m->values);
+    free(m->rows_start);
+    free(m->col_indx);
+    free(m);
+}
+
+// Takes ownership of ptr / col / val (host_alloc'ed, zero-based 3-array CSR) and builds the
+// handle around them: host record for export_csr, device copy and analysis for mv / mm.
+template <typename T>
+static alphasparse_status_t finish_csr_handle(alphasparse_matrix_t *A, int64_t rows, int64_t cols,
+                                              int *ptr, int *col, T *val) {
+    using M = typename CsrOf<T>::csr;
+    alphasparse_matrix *h = static_cast<alphasparse_matrix *>(calloc(1, sizeof(alphasparse_matrix)));
+    M *m = static_cast<M *>(calloc(1, sizeof(M)));
+    if (!h || !m) {
+        free(h), free(m), free(ptr), free(col), free(val);
+        return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+    m->values = val;
+    m->rows_start = ptr;
+    m->rows_end = ptr + 1;
+    m->col_indx = col;
+    m->rows = (ALPHA_INT)rows;
+    m->cols = (ALPHA_INT)cols;
+    m->ordered = false;
+    h->mat = m;
+    h->format = ALPHA_SPARSE_FORMAT_CSR;
+    h->datatype = CsrOf<T>::dt;
+
+    DeviceCtx *c = nullptr;
+    alphasparse_status_t s = ctx_create(CsrOf<T>::dt, rows, cols, ptr, col, val, &c);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) {
+        free_csr_host<T>(m);
+        free(h);
+        return s;
+    }
+    m->d_values = static_cast<T *>(c->d_val);
+    m->d_row_ptr = c->d_row_ptr;
+    m->d_col_indx = c->d_col;
+    h->dcu_info = c;
+    *A = h;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+// Reference semantics (src/core/format/alphasparse_x_create_csr.c:22-55): the element count is
+// rows_end[rows-1] - rows_start[0]; offsets are rows_start[0] followed by rows_end[*]; columns
+// and values are copied from element 0; one-based input loses 1 from every offset and column.
+template <typename T>
+static alphasparse_status_t create_csr(alphasparse_matrix_t *A, alphasparse_index_base_t indexing,
+                                       ALPHA_INT rows, ALPHA_INT cols, const ALPHA_INT *rows_start,
+                                       const ALPHA_INT *rows_end, const ALPHA_INT *col_indx,
+                                       const T *values) {
+    if (!A) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    *A = nullptr;
+    if (rows < 0 || cols < 0) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    if (rows > 0 && (!rows_start || !rows_end)) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    const int shift = indexing == ALPHA_SPARSE_INDEX_BASE_ONE ? 1 : 0;
+    const int64_t nnz = rows > 0 ? (int64_t)rows_end[rows - 1] - (int64_t)rows_start[0] : 0;
+    if (nnz < 0 || nnz > (int64_t)INT32_MAX - 2 * kTailPad) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    if (nnz > 0 && (!col_indx || !values)) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+
+    int *ptr = static_cast<int *>(host_alloc(sizeof(int) * (size_t)(rows + 1)));
+    int *col = static_cast<int *>(host_alloc(sizeof(int) * (size_t)nnz));
+    T *val = static_cast<T *>(host_alloc(sizeof(T) * (size_t)nnz));
+    if (!ptr || !col || !val) {
+        free(ptr), free(col), free(val);
+        return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+    ptr[0] = rows > 0 ? rows_start[0] - shift : 0;
+#pragma omp parallel for schedule(static) if (rows > (1 << 16))
+    for (int64_t i = 0; i < rows; i++) ptr[i + 1] = rows_end[i] - shift;
+#pragma omp parallel for schedule(static) if (nnz > (1 << 16))
+    for (int64_t i = 0; i < nnz; i++) {
+        col[i] = col_indx[i] - shift;
+        val[i] = values[i];
+    }
+    return finish_csr_handle<T>(A, rows, cols, ptr, col, val);
+}
+
+// Reference semantics: src/core/format/alphasparse_x_create_coo.c:16-45 (deep copy, one-based
+// input rebased).  A COO handle never touches the device; it only feeds convert_csr.
+template <typename T>
+static alphasparse_status_t create_coo(alphasparse_matrix_t *A, alphasparse_index_base_t indexing,
+                                       ALPHA_INT rows, ALPHA_INT cols, ALPHA_INT nnz,
+                                       const ALPHA_INT *row_indx, const ALPHA_INT *col_indx,
+                                       const T *values) {
+    using M = typename CsrOf<T>::coo;
+    if (!A) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    *A = nullptr;
+    if (rows < 0 || cols < 0 || nnz < 0) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    if (nnz > 0 && (!row_indx || !col_indx || !values)) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    const int shift = indexing == ALPHA_SPARSE_INDEX_BASE_ONE ? 1 : 0;
+    alphasparse_matrix *h = static_cast<alphasparse_matrix *>(calloc(1, sizeof(alphasparse_matrix)));
+    M *m = static_cast<M *>(calloc(1, sizeof(M)));
+    int *ri = static_cast<int *>(host_alloc(sizeof(int) * (size_t)nnz));
+    int *ci = static_cast<int *>(host_alloc(sizeof(int) * (size_t)nnz));
+    T *v = static_cast<T *>(host_alloc(sizeof(T) * (size_t)nnz));
+    if (!h || !m || !ri || !ci || !v) {
+        free(h), free(m), free(ri), free(ci), free(v);
+        return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+    for (int64_t i = 0; i < nnz; i++) {
+        ri[i] = row_indx[i] - shift;
+        ci[i] = col_indx[i] - shift;
+        v[i] = values[i];
+    }
+    m->values = v, m->row_indx = ri, m->col_indx = ci;
+    m->rows = rows, m->cols = cols, m->nnz = nnz, m->ordered = false;
+    h->mat = m;
+    h->format = ALPHA_SPARSE_FORMAT_COO;
+    h->datatype = CsrOf<T>::dt;
+    *A = h;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+// COO -> CSR with the output the reference produces (src/core/format/convert_csr_x_coo.c:14-81):
+// elements ordered by (row, column), duplicates all kept, offsets by counting.  The reference
+// sorts nnz records with a serial qsort; here a counting pass buckets the elements by row in
+// input order and each row is then sorted by column with a stable sort, in parallel over rows.
+// Equal (row, column) pairs keep their input order (qsort leaves theirs unspecified).
+// With transpose = true rows and columns swap roles (the reference transposes the COO handle
+// first, src/core/op_/alphasparse_convert_csr.c:144-151).
+template <typename T>
+static alphasparse_status_t coo_to_csr(const typename CsrOf<T>::coo *src, bool transpose,
+                                       alphasparse_matrix_t *dest) {
+    const int64_t rows = transpose ? src->cols : src->rows;
+    const int64_t cols = transpose ? src->rows : src->cols;
+    const int64_t nnz = src->nnz;
+    const int *ri = transpose ? src->col_indx : src->row_indx;
+    const int *ci = transpose ? src->row_indx : src->col_indx;
+    for (int64_t i = 0; i < nnz; i++)
+        if (ri[i] < 0 || ri[i] >= rows || ci[i] < 0 || ci[i] >= cols)
+            return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+
+    int *ptr = static_cast<int *>(host_alloc(sizeof(int) * (size_t)(rows + 1)));
+    int *col = static_cast<int *>(host_alloc(sizeof(int) * (size_t)nnz));
+    T *val = static_cast<T *>(host_alloc(sizeof(T) * (size_t)nnz));
+    std::vector<int> fill, order;
+    try {
+        fill.assign((size_t)rows + 1, 0);
+        order.resize((size_t)nnz);
+    } catch (...) {
+        free(ptr), free(col), free(val);
+        return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+    if (!ptr || !col || !val) {
+        free(ptr), free(col), free(val);
+        return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+    for (int64_t i = 0; i < nnz; i++) fill[(size_t)ri[i] + 1]++;
+    ptr[0] = 0;
+    for (int64_t r = 0; r < rows; r++) ptr[r + 1] = ptr[r] + fill[(size_t)r + 1];
+    for (int64_t r = 0; r < rows; r++) fill[(size_t)r] = ptr[r];
+    for (int64_t i = 0; i < nnz; i++) order[(size_t)fill[(size_t)ri[i]]++] = (int)i;
+#pragma omp parallel for schedule(dynamic, 1024)
+    for (int64_t r = 0; r < rows; r++) {
+        int *b = order.data() + ptr[r], *e = order.data() + ptr[r + 1];
+        std::stable_sort(b, e, [&](int p, int q) { return ci[p] < ci[q]; });
+        for (int *it = b; it != e; ++it) {
+            const size_t o = (size_t)(it - order.data());
+            col[o] = ci[*it];
+            val[o] = src->values[*it];
+        }
+    }
+    return finish_csr_handle<T>(dest, rows, cols, ptr, col, val);
+}
+
+// ---- pointer kinds and staging ------------------------------------------------------------------
+
+// true when `p` can be dereferenced by a kernel running on `device`
+static bool is_device_pointer(const void *p, int device) {
+    cudaPointerAttributes at;
+    cudaError_t e = cudaPointerGetAttributes(&at, p);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    if (at.type == cudaMemoryTypeDevice) return true;
+    if (at.type == cudaMemoryTypeManaged) return true;
+    (void)device;
+    return false;  // unregistered or page-locked host memory: staged
+}
+
+static alphasparse_status_t grow(void **buf, size_t *have, size_t want, DeviceCtx *c) {
+    if (*have >= want) return ALPHA_SPARSE_STATUS_SUCCESS;
+    cudaFree(*buf);
+    *buf = nullptr;
+    c->device_bytes -= (int64_t)*have;
+    *have = 0;
+    ASB_CUDA_OR(cudaMalloc(buf, want), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    *have = want;
+    c->device_bytes += (int64_t)want;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int want) {
+        if (cudaGetDevice(&prev) != cudaSuccess) {
+            ok = false;
+            return;
+        }
+        if (prev != want && cudaSetDevice(want) != cudaSuccess) ok = false;
+        if (prev == want) prev = -1;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+// ---- mv / mm -----------------------------------------------------------------------------------------
+
+// Argument checks in the reference's order (src/core/op/level2/alphasparse_x_mv.c:1670-1716,
+// src/core/op/level3/alphasparse_x_mm.c:2317-2338).  Returns SUCCESS when the call is the
+// CSR + GENERAL case this backend serves; every other case the reference would run on its CPU
+// kernels is NOT_SUPPORTED here.
+static alphasparse_status_t check_call(const alphasparse_matrix_t A, const void *x, const void *y,
+                                       alphasparse_datatype_t dt, alphasparse_operation_t op,
+                                       struct alpha_matrix_descr descr) {
+    if (!A || !A->mat || !x || !y) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    if (A->datatype != dt) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    if (op == ALPHA_SPARSE_OPERATION_CONJUGATE_TRANSPOSE) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    if (descr.type == ALPHA_SPARSE_MATRIX_TYPE_SYMMETRIC ||
+        descr.type == ALPHA_SPARSE_MATRIX_TYPE_HERMITIAN) {
+        int64_t r = 0, c = 0;
+        if (A->format == ALPHA_SPARSE_FORMAT_CSR) {
+            const spmat_csr_s_t *m = static_cast<const spmat_csr_s_t *>(A->mat);  // same prefix for d
+            r = m->rows, c = m->cols;
+        } else if (A->format == ALPHA_SPARSE_FORMAT_COO) {
+            const spmat_coo_s_t *m = static_cast<const spmat_coo_s_t *>(A->mat);
+            r = m->rows, c = m->cols;
+        }
+        if (r != c) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    }
+    if (A->format == ALPHA_SPARSE_FORMAT_CSR) {
+        if (descr.type == ALPHA_SPARSE_MATRIX_TYPE_GENERAL) return ALPHA_SPARSE_STATUS_SUCCESS;
+        if (descr.type >= ALPHA_SPARSE_MATRIX_TYPE_SYMMETRIC &&
+            descr.type <= ALPHA_SPARSE_MATRIX_TYPE_DIAGONAL)
+            return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+        return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    }
+    if (A->format == ALPHA_SPARSE_FORMAT_COO ||
+        (A->format >= ALPHA_SPARSE_FORMAT_CSC && A->format <= ALPHA_SPARSE_FORMAT_DIA))
+        return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+}
+
+template <typename T>
+static alphasparse_status_t mv(alphasparse_operation_t op, T alpha, const alphasparse_matrix_t A,
+                               struct alpha_matrix_descr descr, const T *x, T beta, T *y) {
+    alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    if (op != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    DeviceCtx *c = ctx_of(A);
+    if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+    if (c->rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+
+    DeviceGuard guard(c->device);
+    if (!guard.ok) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+    cudaStream_t st = current_stream();
+    const bool x_dev = is_device_pointer(x, c->device), y_dev = is_device_pointer(y, c->device);
+    std::lock_guard<std::mutex> lock(c->mu);
+
+    const T *dx = x;
+    T *dy = y;
+    if (!x_dev) {
+        const size_t bytes = sizeof(T) * (size_t)c->cols;
+        s = grow(&c->d_x_stage, &c->x_stage_bytes, bytes ? bytes : sizeof(T), c);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        if (bytes)
+            ASB_CUDA_OR(cudaMemcpyAsync(c->d_x_stage, x, bytes, cudaMemcpyHostToDevice, st),
+                        ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        dx = static_cast<const T *>(c->d_x_stage);
+    }
+    if (!y_dev) {
+        const size_t bytes = sizeof(T) * (size_t)c->rows;
+        s = grow(&c->d_y_stage, &c->y_stage_bytes, bytes, c);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        if (beta != T(0))
+            ASB_CUDA_OR(cudaMemcpyAsync(c->d_y_stage, y, bytes, cudaMemcpyHostToDevice, st),
+                        ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        dy = static_cast<T *>(c->d_y_stage);
+    }
+    s = launch_spmv<T>(c, alpha, dx, beta, dy, st);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    if (!y_dev) {
+        ASB_CUDA_OR(cudaMemcpyAsync(y, dy, sizeof(T) * (size_t)c->rows, cudaMemcpyDeviceToHost, st),
+                    ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    }
+    if (!y_dev || !x_dev)
+        ASB_CUDA_OR(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+template <typename T>
+static alphasparse_status_t mm(alphasparse_operation_t op, T alpha, const alphasparse_matrix_t A,
+                               struct alpha_matrix_descr descr, alphasparse_layout_t layout,
+                               const T *x, ALPHA_INT columns, ALPHA_INT ldx, T beta, T *y,
+                               ALPHA_INT ldy) {
+    alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    if (op != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    if (layout != ALPHA_SPARSE_LAYOUT_ROW_MAJOR) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    DeviceCtx *c = ctx_of(A);
+    if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+    if (columns < 0 || ldx < columns || ldy < columns) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    if (c->rows == 0 || columns == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+
+    DeviceGuard guard(c->device);
+    if (!guard.ok) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+    cudaStream_t st = current_stream();
+    const bool x_dev = is_device_pointer(x, c->device), y_dev = is_device_pointer(y, c->device);
+    std::lock_guard<std::mutex> lock(c->mu);
+
+    // Dense operands: X is cols x columns (leading dimension ldx), Y is rows x columns (ldy).
+    const size_t xbytes = sizeof(T) * ((size_t)(c->cols > 0 ? c->cols - 1 : 0) * ldx + (c->cols > 0 ? columns : 0));
+    const size_t ybytes = sizeof(T) * ((size_t)(c->rows - 1) * ldy + columns);
+    const T *dx = x;
+    T *dy = y;
+    if (!x_dev) {
+        s = grow(&c->d_x_stage, &c->x_stage_bytes, xbytes ? xbytes : sizeof(T), c);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        if (xbytes)
+            ASB_CUDA_OR(cudaMemcpyAsync(c->d_x_stage, x, xbytes, cudaMemcpyHostToDevice, st),
+                        ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        dx = static_cast<const T *>(c->d_x_stage);
+    }
+    if (!y_dev) {
+        s = grow(&c->d_y_stage, &c->y_stage_bytes, ybytes, c);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        // With ldy > columns the gaps between rows belong to the caller and must survive the
+        // round trip, so the whole block is brought over even when beta == 0.
+        if (beta != T(0) || ldy != columns)
+            ASB_CUDA_OR(cudaMemcpyAsync(c->d_y_stage, y, ybytes, cudaMemcpyHostToDevice, st),
+                        ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        dy = static_cast<T *>(c->d_y_stage);
+    }
+    s = launch_spmm_row<T>(c, alpha, dx, columns, ldx, beta, dy, ldy, st);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    if (!y_dev)
+        ASB_CUDA_OR(cudaMemcpyAsync(y, dy, ybytes, cudaMemcpyDeviceToHost, st),
+                    ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    if (!y_dev || !x_dev)
+        ASB_CUDA_OR(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+}  // namespace asb
+
+// =============================================================================================
+// C ABI
+// =============================================================================================
+using namespace asb;
+
+extern "C" {
+
+alphasparse_status_t alphasparse_s_create_csr(alphasparse_matrix_t *A, const alphasparse_index_base_t indexing,
+                                              const ALPHA_INT rows, const ALPHA_INT cols, ALPHA_INT *rows_start,
+                                              ALPHA_INT *rows_end, ALPHA_INT *col_indx, float *values) {
+    return create_csr<float>(A, indexing, rows, cols, rows_start, rows_end, col_indx, values);
+}
+alphasparse_status_t alphasparse_d_create_csr(alphasparse_matrix_t *A, const alphasparse_index_base_t indexing,
+                                              const ALPHA_INT rows, const ALPHA_INT cols, ALPHA_INT *rows_start,
+                                              ALPHA_INT *rows_end, ALPHA_INT *col_indx, double *values) {
+    return create_csr<double>(A, indexing, rows, cols, rows_start, rows_end, col_indx, values);
+}
+alphasparse_status_t alphasparse_c_create_csr(alphasparse_matrix_t *A, const alphasparse_index_base_t,
+                                              const ALPHA_INT, const ALPHA_INT, ALPHA_INT *, ALPHA_INT *,
+                                              ALPHA_INT *, ALPHA_Complex8 *) {
+    if (A) *A = nullptr;
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+}
+alphasparse_status_t alphasparse_z_create_csr(alphasparse_matrix_t *A, const alphasparse_index_base_t,
+                                              const ALPHA_INT, const ALPHA_INT, ALPHA_INT *, ALPHA_INT *,
+                                              ALPHA_INT *, ALPHA_Complex16 *) {
+    if (A) *A = nullptr;
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+}
+
+alphasparse_status_t alphasparse_s_create_coo(alphasparse_matrix_t *A, const alphasparse_index_base_t indexing,
+                                              const ALPHA_INT rows, const ALPHA_INT cols, const ALPHA_INT nnz,
+                                              ALPHA_INT *row_indx, ALPHA_INT *col_indx, float *values) {
+    return create_coo<float>(A, indexing, rows, cols, nnz, row_indx, col_indx, values);
+}
+alphasparse_status_t alphasparse_d_create_coo(alphasparse_matrix_t *A, const alphasparse_index_base_t indexing,
+                                              const ALPHA_INT rows, const ALPHA_INT cols, const ALPHA_INT nnz,
+                                              ALPHA_INT *row_indx, ALPHA_INT *col_indx, double *values) {
+    return create_coo<double>(A, indexing, rows, cols, nnz, row_indx, col_indx, values);
+}
+alphasparse_status_t alphasparse_c_create_coo(alphasparse_matrix_t *A, const alphasparse_index_base_t,
+                                              const ALPHA_INT, const ALPHA_INT, const ALPHA_INT, ALPHA_INT *,
+                                              ALPHA_INT *, ALPHA_Complex8 *) {
+    if (A) *A = nullptr;
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+}
+alphasparse_status_t alphasparse_z_create_coo(alphasparse_matrix_t *A, const alphasparse_index_base_t,
+                                              const ALPHA_INT, const ALPHA_INT, const ALPHA_INT, ALPHA_INT *,
+                                              ALPHA_INT *, ALPHA_Complex16 *) {
+    if (A) *A = nullptr;
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+}
+
+// Reference: src/core/op_/alphasparse_destroy.c:186-195 (NULL handle is SUCCESS).  Unlike the
+// reference, whose alpha_free releases nothing, host and device storage is really returned.
+alphasparse_status_t alphasparse_destroy(alphasparse_matrix_t A) {
+    if (!A) return ALPHA_SPARSE_STATUS_SUCCESS;
+    ctx_destroy(ctx_of(A));
+    A->dcu_info = nullptr;
+    if (A->mat) {
+        if (A->format == ALPHA_SPARSE_FORMAT_CSR) {
+            if (A->datatype == ALPHA_SPARSE_DATATYPE_FLOAT) free_csr_host<float>(static_cast<spmat_csr_s_t *>(A->mat));
+            else if (A->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE) free_csr_host<double>(static_cast<spmat_csr_d_t *>(A->mat));
+        } else if (A->format == ALPHA_SPARSE_FORMAT_COO) {
+            spmat_coo_s_t *m = static_cast<spmat_coo_s_t *>(A->mat);  // pointer fields first in both precisions
+            free(m->values), free(m->row_indx), free(m->col_indx), free(m);
+        }
+    }
+    free(A);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+// Reference: src/core/op_/alphasparse_convert_csr.c:125-157 (+ :100-123: only a COO source).
+alphasparse_status_t alphasparse_convert_csr(const alphasparse_matrix_t source, const alphasparse_operation_t operation,
+                                             alphasparse_matrix_t *dest) {
+    if (!source || !source->mat) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    if (!dest) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    *dest = nullptr;
+    if (operation == ALPHA_SPARSE_OPERATION_CONJUGATE_TRANSPOSE) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    if (operation != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE && operation != ALPHA_SPARSE_OPERATION_TRANSPOSE)
+        return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    if (source->format != ALPHA_SPARSE_FORMAT_COO) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    const bool tr = operation == ALPHA_SPARSE_OPERATION_TRANSPOSE;
+    if (source->datatype == ALPHA_SPARSE_DATATYPE_FLOAT)
+        return coo_to_csr<float>(static_cast<const spmat_coo_s_t *>(source->mat), tr, dest);
+    if (source->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE)
+        return coo_to_csr<double>(static_cast<const spmat_coo_d_t *>(source->mat), tr, dest);
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+}
+
+// Reference: src/core/format/alphasparse_x_export_csr.c:5-25.
+#define ASB_EXPORT(T, sfx, DT)                                                                              \
+    alphasparse_status_t alphasparse_##sfx##_export_csr(                                                    \
+        const alphasparse_matrix_t source, alphasparse_index_base_t *indexing, ALPHA_INT *rows,             \
+        ALPHA_INT *cols, ALPHA_INT **rows_start, ALPHA_INT **rows_end, ALPHA_INT **col_indx, T **values) {  \
+        if (!source) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;                                            \
+        if (!source->mat) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;                                         \
+        if (source->datatype != DT) return ALPHA_SPARSE_STATUS_INVALID_VALUE;                               \
+        if (source->format != ALPHA_SPARSE_FORMAT_CSR) return ALPHA_SPARSE_STATUS_INVALID_VALUE;            \
+        spmat_csr_##sfx##_t *m = static_cast<spmat_csr_##sfx##_t *>(source->mat);                           \
+        *indexing = ALPHA_SPARSE_INDEX_BASE_ZERO;                                                           \
+        *rows = m->rows, *cols = m->cols;                                                                   \
+        *rows_start = m->rows_start, *rows_end = m->rows_end;                                               \
+        *col_indx = m->col_indx, *values = m->values;                                                       \
+        return ALPHA_SPARSE_STATUS_SUCCESS;                                                                 \
+    }
+ASB_EXPORT(float, s, ALPHA_SPARSE_DATATYPE_FLOAT)
+ASB_EXPORT(double, d, ALPHA_SPARSE_DATATYPE_DOUBLE)
+
+alphasparse_status_t alphasparse_set_mv_hint(const alphasparse_matrix_t A, const alphasparse_operation_t,
+                                             const struct alpha_matrix_descr, const ALPHA_INT) {
+    return A ? ALPHA_SPARSE_STATUS_SUCCESS : ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+}
+
+alphasparse_status_t alphasparse_optimize(alphasparse_matrix_t A) {
+    if (!A || !A->mat) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    DeviceCtx *c = ctx_of(A);
+    if (!c) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    DeviceGuard guard(c->device);
+    if (!guard.ok) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+    std::lock_guard<std::mutex> lock(c->mu);
+    return ctx_analyse(c);
+}
+
+alphasparse_status_t alphasparse_s_mv(const alphasparse_operation_t operation, const float alpha,
+                                      const alphasparse_matrix_t A, const struct alpha_matrix_descr descr,
+                                      const float *x, const float beta, float *y) {
+    return mv<float>(operation, alpha, A, descr, x, beta, y);
+}
+alphasparse_status_t alphasparse_d_mv(const alphasparse_operation_t operation, const double alpha,
+                                      const alphasparse_matrix_t A, const struct alpha_matrix_descr descr,
+                                      const double *x, const double beta, double *y) {
+    return mv<double>(operation, alpha, A, descr, x, beta, y);
+}
+alphasparse_status_t alphasparse_c_mv(const alphasparse_operation_t, const ALPHA_Complex8, const alphasparse_matrix_t A,
+                                      const struct alpha_matrix_descr, const ALPHA_Complex8 *x, const ALPHA_Complex8,
+                                      ALPHA_Complex8 *y) {
+    if (!A || !A->mat || !x || !y) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    if (A->datatype != ALPHA_SPARSE_DATATYPE_FLOAT_COMPLEX) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+}
+alphasparse_status_t alphasparse_z_mv(const alphasparse_operation_t, const ALPHA_Complex16, const alphasparse_matrix_t A,
+                                      const struct alpha_matrix_descr, const ALPHA_Complex16 *x, const ALPHA_Complex16,
+                                      ALPHA_Complex16 *y) {
+    if (!A || !A->mat || !x || !y) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    if (A->datatype != ALPHA_SPARSE_DATATYPE_DOUBLE_COMPLEX) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+}
+
+alphasparse_status_t alphasparse_s_mm(const alphasparse_operation_t operation, const float alpha,
+                                      const alphasparse_matrix_t A, const struct alpha_matrix_descr descr,
+                                      const alphasparse_layout_t layout, const float *x, const ALPHA_INT columns,
+                                      const ALPHA_INT ldx, const float beta, float *y, const ALPHA_INT ldy) {
+    return mm<float>(operation, alpha, A, descr, layout, x, columns, ldx, beta, y, ldy);
+}
+alphasparse_status_t alphasparse_d_mm(const alphasparse_operation_t operation, const double alpha,
+                                      const alphasparse_matrix_t A, const struct alpha_matrix_descr descr,
+                                      const alphasparse_layout_t layout, const double *x, const ALPHA_INT columns,
+                                      const ALPHA_INT ldx, const double beta, double *y, const ALPHA_INT ldy) {
+    return mm<double>(operation, alpha, A, descr, layout, x, columns, ldx, beta, y, ldy);
+}
+alphasparse_status_t alphasparse_c_mm(const alphasparse_operation_t, const ALPHA_Complex8, const alphasparse_matrix_t A,
+                                      const struct alpha_matrix_descr, const alphasparse_layout_t, const ALPHA_Complex8 *x,
+                                      const ALPHA_INT, const ALPHA_INT, const ALPHA_Complex8, ALPHA_Complex8 *y,
+                                      const ALPHA_INT) {
+    if (!A || !A->mat || !x || !y) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    if (A->datatype != ALPHA_SPARSE_DATATYPE_FLOAT_COMPLEX) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+}
+alphasparse_status_t alphasparse_z_mm(const alphasparse_operation_t, const ALPHA_Complex16, const alphasparse_matrix_t A,
+                                      const struct alpha_matrix_descr, const alphasparse_layout_t, const ALPHA_Complex16 *x,
+                                      const ALPHA_INT, const ALPHA_INT, const ALPHA_Complex16, ALPHA_Complex16 *y,
+                                      const ALPHA_INT) {
+    if (!A || !A->mat || !x || !y) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    if (A->datatype != ALPHA_SPARSE_DATATYPE_DOUBLE_COMPLEX) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+}
+
+// ---- additions (include/alphasparse/spapi_cuda.h) ---------------------------------------------
+
+alphasparse_status_t alphasparse_cuda_set_stream(void *stream) {
+    g_stream.store(static_cast<cudaStream_t>(stream), std::memory_order_relaxed);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+alphasparse_status_t alphasparse_cuda_get_stream(void **stream) {
+    if (!stream) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+    *stream = current_stream();
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+alphasparse_status_t alphasparse_cuda_synchronize(void) {
+    ASB_CUDA_OR(cudaStreamSynchronize(current_stream()), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg) {
+    if (alg < ALPHA_SPARSE_CUDA_ALG_AUTO || alg > ALPHA_SPARSE_CUDA_ALG_MERGE) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    g_alg.store((int)alg, std::memory_order_relaxed);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+alphasparse_status_t alphasparse_cuda_get_mat_info(const alphasparse_matrix_t A, alphasparse_cuda_mat_info_t *info) {
+    if (!info) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+    DeviceCtx *c = ctx_of(A);
+    if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+    memset(info, 0, sizeof(*info));
+    info->rows = c->rows, info->cols = c->cols, info->nnz = c->nnz;
+    info->max_row_nnz = c->max_row_nnz, info->empty_rows = c->empty_rows;
+    info->mean_row_nnz = c->mean_row_nnz;
+    info->algorithm = c->algorithm, info->lanes_per_row = c->lanes;
+    info->merge_tiles = c->algorithm == ALPHA_SPARSE_CUDA_ALG_MERGE ? c->merge_tiles : 0;
+    info->device_bytes = c->device_bytes, info->device = c->device;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+alphasparse_status_t alphasparse_cuda_get_device_csr(const alphasparse_matrix_t A, ALPHA_INT **d_row_ptr,
+                                                     ALPHA_INT **d_col_indx, void **d_values) {
+    DeviceCtx *c = ctx_of(A);
+    if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+    if (d_row_ptr) *d_row_ptr = c->d_row_ptr;
+    if (d_col_indx) *d_col_indx = c->d_col;
+    if (d_values) *d_values = c->d_val;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+int64_t alphasparse_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+const char *alphasparse_cuda_last_error(void) { return t_error; }
+
+}  // extern "C"

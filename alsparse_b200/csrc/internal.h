@@ -1,0 +1,104 @@
+// Internal declarations shared by the translation units of libalphasparse_b200.so.
+// Nothing here is part of the C ABI (see include/alphasparse/*.h for that).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "alphasparse/spapi_cuda.h"
+#include "alphasparse/spdef.h"
+#include "alphasparse/spmat.h"
+#include "alphasparse/types.h"
+
+namespace asb {
+
+// ---- process-wide state --------------------------------------------------------------------
+cudaStream_t current_stream();
+alphasparse_cuda_alg_t forced_algorithm();
+void count_launch(int n = 1);
+void record_cuda_error(cudaError_t e, const char *what);
+
+// Maps a failed CUDA call to a status and records its text for alphasparse_cuda_last_error.
+#define ASB_CUDA_OR(expr, status)                          \
+    do {                                                   \
+        cudaError_t _e = (expr);                           \
+        if (_e != cudaSuccess) {                           \
+            ::asb::record_cuda_error(_e, #expr);           \
+            return (status);                               \
+        }                                                  \
+    } while (0)
+
+// ---- per-handle device context, stored in alphasparse_matrix.dcu_info ---------------------
+constexpr uint64_t kCtxMagic = 0x4153423230304358ull;  // guards against foreign pointers
+
+// Elements appended (zero-filled) after the last stored element of the column and value
+// arrays so that aligned 16-byte loads that start inside the array never leave it.
+constexpr int kTailPad = 16;
+
+// Merge-path tile shape: kMergeThreads threads, each consuming kMergeItems (rows+nnz) items.
+constexpr int kMergeThreads = 256;
+constexpr int kMergeItemsS = 9;  // float
+constexpr int kMergeItemsD = 7;  // double
+
+struct MergeCoord {
+    int row;  // rows fully consumed before this point
+    int nz;   // stored elements consumed before this point
+};
+
+struct DeviceCtx {
+    uint64_t magic = kCtxMagic;
+    int device = 0;
+    int datatype = 0;  // alphasparse_datatype_t
+    int64_t rows = 0, cols = 0, nnz = 0;
+
+    int *d_row_ptr = nullptr;  // rows + 1
+    int *d_col = nullptr;      // nnz + kTailPad
+    void *d_val = nullptr;     // nnz + kTailPad
+
+    // analysis results
+    int64_t max_row_nnz = 0;
+    int64_t empty_rows = 0;
+    double mean_row_nnz = 0.0;
+    double mean_row_quads = 0.0;  // aligned 4-element groups a row touches, on average
+    int algorithm = ALPHA_SPARSE_CUDA_ALG_VECTOR;
+    int lanes = 4;
+
+    // merge-path tables (only when algorithm == MERGE)
+    int merge_items = 0;
+    int64_t merge_tiles = 0;
+    MergeCoord *d_tile = nullptr;  // merge_tiles + 1
+    int *d_carry_row = nullptr;    // merge_tiles
+    void *d_carry_val = nullptr;   // merge_tiles
+
+    // staging for calls that pass host vectors (grown on demand, reused)
+    void *d_x_stage = nullptr;
+    size_t x_stage_bytes = 0;
+    void *d_y_stage = nullptr;
+    size_t y_stage_bytes = 0;
+
+    int64_t device_bytes = 0;
+    std::mutex mu;  // serialises calls that share the carry and staging buffers
+};
+
+DeviceCtx *ctx_of(const alphasparse_matrix_t A);
+
+// Upload + analysis.  `ptr` has rows+1 zero-based offsets.  On failure everything allocated
+// so far is released and *out stays null.
+alphasparse_status_t ctx_create(int datatype, int64_t rows, int64_t cols, const int *ptr,
+                                const int *col, const void *val, DeviceCtx **out);
+void ctx_destroy(DeviceCtx *ctx);
+alphasparse_status_t ctx_analyse(DeviceCtx *ctx);
+
+// ---- kernel launchers (device pointers, enqueue only) ---------------------------------------
+template <typename T>
+alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y,
+                                 cudaStream_t stream);
+
+template <typename T>
+alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx,
+                                     T beta, T *Y, int ldy, cudaStream_t stream);
+
+}  // namespace asb

@@ -1,0 +1,493 @@
+// CSR SpMV kernels for sm_100a and the one-time analysis that picks between them.
+//
+// y = alpha * A * x + beta * y for a general CSR matrix, the operation of the reference's
+// gemv_{s,d}_csr (arithmetic defined by src/plain/kernel/level2/mv/gemv/gemv_x_csr_plain.c:4-24
+// of the reference).  SpMV moves ~12 bytes per flop pair, so the kernels are built around
+// HBM traffic, not arithmetic: the value and column streams are read once with 16-byte
+// coalesced loads and a streaming cache policy, x is gathered through the read-only path so
+// that it stays resident in L2, y is written once.  No tensor cores: there is no reuse to
+// feed them.
+//
+// Two kernel families:
+//   vector  a group of LANES (1..32) lanes owns a row; each lane takes whole aligned quads
+//           (4 consecutive stored elements) of the row, so every load is a 16-byte load of
+//           col and of val regardless of where the row starts.  Used when rows are short and
+//           of similar length.
+//   merge   every thread block consumes the same number of (row-end + stored-element) items
+//           of the merge of the row offsets with the element indices, so a 200000-element
+//           row and a run of one-element rows cost the same.  Partial sums that cross a block
+//           boundary go through a small carry array and a second kernel adds them, in a fixed
+//           order: results do not depend on scheduling and no floating-point atomics are used.
+#include <limits.h>
+
+#include "internal.h"
+
+namespace asb {
+
+// ---- streaming loads / stores ------------------------------------------------------------
+// ld.global.cs / st.global.cs: data touched once, first in line for eviction from L1 and L2.
+
+template <typename T>
+struct Quad {
+    T v[4];
+};
+
+__device__ __forceinline__ int4 load_quad_idx(const int *__restrict__ col, int q) {
+    return __ldcs(reinterpret_cast<const int4 *>(col) + q);
+}
+__device__ __forceinline__ Quad<float> load_quad_val(const float *__restrict__ val, int q) {
+    float4 t = __ldcs(reinterpret_cast<const float4 *>(val) + q);
+    Quad<float> r;
+    r.v[0] = t.x, r.v[1] = t.y, r.v[2] = t.z, r.v[3] = t.w;
+    return r;
+}
+__device__ __forceinline__ Quad<double> load_quad_val(const double *__restrict__ val, int q) {
+    double2 a = __ldcs(reinterpret_cast<const double2 *>(val) + 2 * (size_t)q);
+    double2 b = __ldcs(reinterpret_cast<const double2 *>(val) + 2 * (size_t)q + 1);
+    Quad<double> r;
+    r.v[0] = a.x, r.v[1] = a.y, r.v[2] = b.x, r.v[3] = b.y;
+    return r;
+}
+
+// ---- vector kernel -------------------------------------------------------------------------
+
+template <typename T>
+__device__ __forceinline__ T quad_dot(const int4 c, const Quad<T> &v, int base, int s, int e,
+                                      const T *__restrict__ x) {
+    // Elements of the quad outside [s, e) belong to a neighbouring row (or to the zero tail).
+    T acc = T(0);
+    if (base + 0 >= s && base + 0 < e) acc = fma(v.v[0], __ldg(x + c.x), acc);
+    if (base + 1 >= s && base + 1 < e) acc = fma(v.v[1], __ldg(x + c.y), acc);
+    if (base + 2 >= s && base + 2 < e) acc = fma(v.v[2], __ldg(x + c.z), acc);
+    if (base + 3 >= s && base + 3 < e) acc = fma(v.v[3], __ldg(x + c.w), acc);
+    return acc;
+}
+
+// 256 threads; 256/LANES row groups; each group handles RPG rows that are 256/LANES apart so
+// that every load instruction of a warp covers consecutive rows (consecutive memory).  The
+// first quad of all RPG rows is requested before any of them is consumed, which keeps two
+// independent chains (offset -> col/val -> x) in flight per thread.
+template <typename T, int LANES, int RPG, bool HAS_BETA>
+__global__ void __launch_bounds__(256)
+    spmv_vector_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
+                       const T *__restrict__ val, const T *__restrict__ x, T *__restrict__ y,
+                       T alpha, T beta) {
+    constexpr int GROUPS = 256 / LANES;
+    const int lane = threadIdx.x % LANES;
+    const int grp = threadIdx.x / LANES;
+    const long long row0 = (long long)blockIdx.x * (GROUPS * RPG) + grp;
+
+    int s[RPG], e[RPG];
+#pragma unroll
+    for (int u = 0; u < RPG; u++) {
+        const long long r = row0 + (long long)u * GROUPS;
+        s[u] = 0, e[u] = 0;
+        if (r < rows) {
+            s[u] = __ldg(row_ptr + r);
+            e[u] = __ldg(row_ptr + r + 1);
+        }
+    }
+
+    int q[RPG];
+    int4 c[RPG];
+    Quad<T> v[RPG];
+#pragma unroll
+    for (int u = 0; u < RPG; u++) {
+        q[u] = (s[u] >> 2) + lane;
+        if ((q[u] << 2) < e[u]) {
+            c[u] = load_quad_idx(col, q[u]);
+            v[u] = load_quad_val(val, q[u]);
+        }
+    }
+
+    T sum[RPG];
+#pragma unroll
+    for (int u = 0; u < RPG; u++) {
+        sum[u] = T(0);
+        if ((q[u] << 2) < e[u]) sum[u] = quad_dot(c[u], v[u], q[u] << 2, s[u], e[u], x);
+        for (int qq = q[u] + LANES; (qq << 2) < e[u]; qq += LANES) {
+            const int4 cc = load_quad_idx(col, qq);
+            const Quad<T> vv = load_quad_val(val, qq);
+            sum[u] += quad_dot(cc, vv, qq << 2, s[u], e[u], x);
+        }
+    }
+
+#pragma unroll
+    for (int u = 0; u < RPG; u++) {
+#pragma unroll
+        for (int o = LANES / 2; o > 0; o >>= 1) sum[u] += __shfl_xor_sync(0xffffffffu, sum[u], o);
+        const long long r = row0 + (long long)u * GROUPS;
+        if (lane == 0 && r < rows) {
+            T out = alpha * sum[u];
+            if (HAS_BETA) out = fma(beta, y[r], out);
+            __stcs(y + r, out);
+        }
+    }
+}
+
+// ---- merge kernel ----------------------------------------------------------------------------
+
+// One thread block = one tile of NT*IPT merge items.  The tile's start and end coordinates
+// (row, element) were computed once at analysis time.
+template <typename T, int NT, int IPT, bool HAS_BETA>
+__global__ void __launch_bounds__(NT)
+    spmv_merge_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
+                      const T *__restrict__ val, const T *__restrict__ x, T *__restrict__ y,
+                      T alpha, T beta, const MergeCoord *__restrict__ tile,
+                      int *__restrict__ carry_row, T *__restrict__ carry_val) {
+    constexpr int TILE = NT * IPT;
+    constexpr int NW = NT / 32;
+    __shared__ T s_prod[TILE];
+    __shared__ int s_rend[TILE + 1];
+    __shared__ int s_ckey[NT];
+    __shared__ T s_cval[NT];
+    __shared__ int s_wkey[NW];
+    __shared__ T s_wval[NW];
+
+    const int tid = threadIdx.x;
+    const MergeCoord c0 = tile[blockIdx.x], c1 = tile[blockIdx.x + 1];
+    const int r0 = c0.row, j0 = c0.nz;
+    const int tile_rows = c1.row - r0, tile_nnz = c1.nz - j0;
+    const int items = tile_rows + tile_nnz;
+
+    // Row ends relative to the tile's first element; entry tile_rows is the (unfinished) row
+    // the tile stops in, or +inf past the last row.
+    for (int i = tid; i <= tile_rows; i += NT) {
+        const int r = r0 + i;
+        s_rend[i] = (r < rows) ? (__ldg(row_ptr + r + 1) - j0) : INT_MAX;
+    }
+    // All loads of a thread are independent: IPT column/value pairs in flight, then IPT gathers.
+    {
+        int cc[IPT];
+        T vv[IPT];
+#pragma unroll
+        for (int k = 0; k < IPT; k++) {
+            const int i = tid + k * NT;
+            cc[k] = 0, vv[k] = T(0);
+            if (i < tile_nnz) {
+                cc[k] = __ldcs(col + j0 + i);
+                vv[k] = __ldcs(val + j0 + i);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < IPT; k++) {
+            const int i = tid + k * NT;
+            if (i < tile_nnz) s_prod[i] = vv[k] * __ldg(x + cc[k]);
+        }
+    }
+    __syncthreads();
+
+    // This thread's slice of the merge path: items [d, d + IPT).
+    const int d = min(tid * IPT, items);
+    int lo = max(0, d - tile_nnz), hi = min(d, tile_rows);
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (s_rend[mid] <= d - mid - 1) lo = mid + 1;
+        else hi = mid;
+    }
+    int i = lo, j = d - lo;
+
+    T run = T(0);
+    int first_row = -1;  // first row that ends inside this thread; may have started earlier
+    T first_val = T(0);
+#pragma unroll
+    for (int k = 0; k < IPT; k++) {
+        if (d + k < items) {
+            if (j < s_rend[i]) {
+                run += s_prod[j];
+                j++;
+            } else {
+                if (first_row < 0) {
+                    first_row = i;
+                    first_val = run;
+                } else {
+                    const int r = r0 + i;
+                    T out = alpha * run;
+                    if (HAS_BETA) out = fma(beta, y[r], out);
+                    y[r] = out;
+                }
+                run = T(0);
+                i++;
+            }
+        }
+    }
+
+    // Segmented inclusive scan of the per-thread leftovers (key = row the thread stopped in).
+    // Keys are non-decreasing with the thread index, so equal keys are contiguous.
+    const int lane = tid & 31, wid = tid >> 5;
+    int key = i;
+    T acc = run;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int k2 = __shfl_up_sync(0xffffffffu, key, o);
+        const T v2 = __shfl_up_sync(0xffffffffu, acc, o);
+        if (lane >= o && k2 == key) acc += v2;
+    }
+    if (lane == 31) {
+        s_wkey[wid] = key;
+        s_wval[wid] = acc;
+    }
+    __syncthreads();
+    for (int w = wid - 1; w >= 0; w--) {
+        if (s_wkey[w] != key) break;
+        acc += s_wval[w];
+    }
+    s_ckey[tid] = key;
+    s_cval[tid] = acc;
+    __syncthreads();
+
+    if (first_row >= 0) {
+        if (tid > 0 && s_ckey[tid - 1] == first_row) first_val += s_cval[tid - 1];
+        const int r = r0 + first_row;
+        T out = alpha * first_val;
+        if (HAS_BETA) out = fma(beta, y[r], out);
+        y[r] = out;
+    }
+    if (tid == NT - 1) {
+        carry_row[blockIdx.x] = r0 + key;
+        carry_val[blockIdx.x] = acc;
+    }
+}
+
+// Adds the tile leftovers to the rows they belong to.  Consecutive tiles that stopped in the
+// same row form a run; the first thread of a run adds the whole run, front to back.
+template <typename T>
+__global__ void spmv_merge_fixup_kernel(int rows, long long tiles, const int *__restrict__ carry_row,
+                                        const T *__restrict__ carry_val, T *__restrict__ y,
+                                        T alpha) {
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= tiles) return;
+    const int r = carry_row[t];
+    if (r >= rows) return;
+    if (t > 0 && carry_row[t - 1] == r) return;
+    T acc = carry_val[t];
+    for (long long u = t + 1; u < tiles && carry_row[u] == r; u++) acc += carry_val[u];
+    y[r] = fma(alpha, acc, y[r]);
+}
+
+// y = beta * y for a matrix without stored elements (the reference still scales y).
+template <typename T>
+__global__ void scale_kernel(long long n, T *__restrict__ y, T beta) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = (beta == T(0)) ? T(0) : y[i] * beta;
+}
+
+// ---- analysis kernels --------------------------------------------------------------------------
+
+// out[0] = max row length, out[1] = empty rows, out[2] = aligned quads touched (summed over
+// rows), out[3] = rows whose end offset is below their start offset (malformed input).
+__global__ void row_stats_kernel(int rows, const int *__restrict__ row_ptr,
+                                 unsigned long long *__restrict__ out) {
+    unsigned long long mx = 0, empty = 0, quads = 0, bad = 0;
+    for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows;
+         r += (long long)gridDim.x * blockDim.x) {
+        const int s = row_ptr[r], e = row_ptr[r + 1];
+        if (e < s) {
+            bad++;
+            continue;
+        }
+        const unsigned long long len = (unsigned long long)(e - s);
+        mx = len > mx ? len : mx;
+        if (len == 0) empty++;
+        else quads += (unsigned long long)(((e + 3) >> 2) - (s >> 2));
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long m2 = __shfl_xor_sync(0xffffffffu, mx, o);
+        mx = m2 > mx ? m2 : mx;
+        empty += __shfl_xor_sync(0xffffffffu, empty, o);
+        quads += __shfl_xor_sync(0xffffffffu, quads, o);
+        bad += __shfl_xor_sync(0xffffffffu, bad, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicMax(out + 0, mx);
+        if (empty) atomicAdd(out + 1, empty);
+        if (quads) atomicAdd(out + 2, quads);
+        if (bad) atomicAdd(out + 3, bad);
+    }
+}
+
+// out[0] = stored column indices outside [0, cols).  A kernel given such an index would read
+// outside x, so handle creation refuses the matrix instead.
+__global__ void col_range_kernel(long long nnz, int cols, const int *__restrict__ col,
+                                 unsigned long long *__restrict__ out) {
+    unsigned long long bad = 0;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nnz;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int c = col[i];
+        if (c < 0 || c >= cols) bad++;
+    }
+    for (int o = 16; o > 0; o >>= 1) bad += __shfl_xor_sync(0xffffffffu, bad, o);
+    if ((threadIdx.x & 31) == 0 && bad) atomicAdd(out, bad);
+}
+
+// Start coordinate of every merge tile: the point on diagonal t*items of the merge of the row
+// end offsets (row_ptr[1..rows]) with the element indices 0..nnz-1.
+__global__ void merge_tiles_kernel(int rows, int nnz, const int *__restrict__ row_ptr, int items,
+                                   long long tiles, MergeCoord *__restrict__ out) {
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t > tiles) return;
+    long long diag = t * items;
+    const long long total = (long long)rows + nnz;
+    if (diag > total) diag = total;
+    long long lo = diag > nnz ? diag - nnz : 0, hi = diag < rows ? diag : rows;
+    while (lo < hi) {
+        const long long mid = (lo + hi) >> 1;
+        if ((long long)row_ptr[mid + 1] <= diag - mid - 1) lo = mid + 1;
+        else hi = mid;
+    }
+    out[t].row = (int)lo;
+    out[t].nz = (int)(diag - lo);
+}
+
+// ---- analysis (host) ------------------------------------------------------------------------------
+
+static int pick_lanes(double mean_quads) {
+    // Lanes per row = aligned quads an average row touches, rounded to a power of two.
+    int lanes = 1;
+    while (lanes < 32 && (double)lanes < mean_quads * 0.75) lanes <<= 1;
+    return lanes;
+}
+
+alphasparse_status_t ctx_analyse(DeviceCtx *ctx) {
+    cudaStream_t st = current_stream();
+    ctx->algorithm = ALPHA_SPARSE_CUDA_ALG_VECTOR;
+    ctx->lanes = 4;
+    ctx->max_row_nnz = 0, ctx->empty_rows = ctx->rows, ctx->mean_row_nnz = 0.0;
+    if (ctx->rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+
+    unsigned long long *d_out = nullptr, h_out[5] = {0, 0, 0, 0, 0};
+    ASB_CUDA_OR(cudaMalloc(&d_out, sizeof(h_out)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    cudaError_t e = cudaMemsetAsync(d_out, 0, sizeof(h_out), st);
+    if (e == cudaSuccess) {
+        const int threads = 256;
+        long long want = (ctx->rows + threads - 1) / threads;
+        int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+        row_stats_kernel<<<blocks, threads, 0, st>>>((int)ctx->rows, ctx->d_row_ptr, d_out);
+        count_launch();
+        if (ctx->nnz > 0) {
+            want = (ctx->nnz + threads - 1) / threads;
+            blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+            col_range_kernel<<<blocks, threads, 0, st>>>(ctx->nnz, (int)ctx->cols, ctx->d_col,
+                                                         d_out + 4);
+            count_launch();
+        }
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_out, d_out, sizeof(h_out), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(d_out);
+    if (e != cudaSuccess) {
+        record_cuda_error(e, "row analysis");
+        return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+    }
+    if (h_out[3] != 0 || h_out[4] != 0) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+
+    ctx->max_row_nnz = (int64_t)h_out[0];
+    ctx->empty_rows = (int64_t)h_out[1];
+    ctx->mean_row_nnz = (double)ctx->nnz / (double)ctx->rows;
+    ctx->mean_row_quads = (double)h_out[2] / (double)ctx->rows;
+    ctx->lanes = pick_lanes(ctx->mean_row_quads);
+
+    // A row longer than eight passes of its lane group would leave that group running long
+    // after the rest of the grid has drained: switch to equal-work tiles.
+    int alg = forced_algorithm();
+    if (alg == ALPHA_SPARSE_CUDA_ALG_AUTO) {
+        const int64_t comfortable = (int64_t)ctx->lanes * 4 * 8;
+        alg = (ctx->max_row_nnz > comfortable) ? ALPHA_SPARSE_CUDA_ALG_MERGE
+                                                : ALPHA_SPARSE_CUDA_ALG_VECTOR;
+    }
+    ctx->algorithm = alg;
+
+    if (alg == ALPHA_SPARSE_CUDA_ALG_MERGE && ctx->d_tile == nullptr) {
+        const int ipt = (ctx->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE) ? kMergeItemsD : kMergeItemsS;
+        const size_t tsz = (ctx->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE) ? 8 : 4;
+        ctx->merge_items = kMergeThreads * ipt;
+        const int64_t total = ctx->rows + ctx->nnz;
+        ctx->merge_tiles = (total + ctx->merge_items - 1) / ctx->merge_items;
+        ASB_CUDA_OR(cudaMalloc(&ctx->d_tile, sizeof(MergeCoord) * (size_t)(ctx->merge_tiles + 1)),
+                    ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        ASB_CUDA_OR(cudaMalloc(&ctx->d_carry_row, sizeof(int) * (size_t)ctx->merge_tiles),
+                    ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        ASB_CUDA_OR(cudaMalloc(&ctx->d_carry_val, tsz * (size_t)ctx->merge_tiles),
+                    ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        ctx->device_bytes += (int64_t)(sizeof(MergeCoord) * (size_t)(ctx->merge_tiles + 1) +
+                                       (sizeof(int) + tsz) * (size_t)ctx->merge_tiles);
+        const int threads = 256;
+        const int blocks = (int)((ctx->merge_tiles + 1 + threads - 1) / threads);
+        merge_tiles_kernel<<<blocks, threads, 0, st>>>((int)ctx->rows, (int)ctx->nnz, ctx->d_row_ptr,
+                                                       ctx->merge_items, ctx->merge_tiles,
+                                                       ctx->d_tile);
+        count_launch();
+        ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        ASB_CUDA_OR(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    }
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+// ---- launchers -----------------------------------------------------------------------------------
+
+template <typename T, int LANES>
+static void launch_vector(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st) {
+    constexpr int RPG = 2;
+    constexpr int rows_per_block = (256 / LANES) * RPG;
+    const unsigned blocks = (unsigned)((ctx->rows + rows_per_block - 1) / rows_per_block);
+    const T *val = static_cast<const T *>(ctx->d_val);
+    if (beta == T(0))
+        spmv_vector_kernel<T, LANES, RPG, false><<<blocks, 256, 0, st>>>(
+            (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta);
+    else
+        spmv_vector_kernel<T, LANES, RPG, true><<<blocks, 256, 0, st>>>(
+            (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta);
+    count_launch();
+}
+
+template <typename T, int IPT>
+static void launch_merge(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st) {
+    const T *val = static_cast<const T *>(ctx->d_val);
+    T *carry = static_cast<T *>(ctx->d_carry_val);
+    const unsigned blocks = (unsigned)ctx->merge_tiles;
+    if (beta == T(0))
+        spmv_merge_kernel<T, kMergeThreads, IPT, false><<<blocks, kMergeThreads, 0, st>>>(
+            (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta, ctx->d_tile,
+            ctx->d_carry_row, carry);
+    else
+        spmv_merge_kernel<T, kMergeThreads, IPT, true><<<blocks, kMergeThreads, 0, st>>>(
+            (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta, ctx->d_tile,
+            ctx->d_carry_row, carry);
+    const unsigned fblocks = (unsigned)((ctx->merge_tiles + 255) / 256);
+    spmv_merge_fixup_kernel<T><<<fblocks, 256, 0, st>>>((int)ctx->rows, ctx->merge_tiles,
+                                                       ctx->d_carry_row, carry, y, alpha);
+    count_launch(2);
+}
+
+template <typename T>
+alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y,
+                                 cudaStream_t st) {
+    if (ctx->rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+    if (ctx->nnz == 0) {
+        const unsigned blocks = (unsigned)((ctx->rows + 255) / 256);
+        scale_kernel<T><<<blocks, 256, 0, st>>>(ctx->rows, y, beta);
+        count_launch();
+    } else if (ctx->algorithm == ALPHA_SPARSE_CUDA_ALG_MERGE) {
+        constexpr int IPT = sizeof(T) == 8 ? kMergeItemsD : kMergeItemsS;
+        launch_merge<T, IPT>(ctx, alpha, x, beta, y, st);
+    } else {
+        switch (ctx->lanes) {
+            case 1: launch_vector<T, 1>(ctx, alpha, x, beta, y, st); break;
+            case 2: launch_vector<T, 2>(ctx, alpha, x, beta, y, st); break;
+            case 4: launch_vector<T, 4>(ctx, alpha, x, beta, y, st); break;
+            case 8: launch_vector<T, 8>(ctx, alpha, x, beta, y, st); break;
+            case 16: launch_vector<T, 16>(ctx, alpha, x, beta, y, st); break;
+            default: launch_vector<T, 32>(ctx, alpha, x, beta, y, st); break;
+        }
+    }
+    ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+template alphasparse_status_t launch_spmv<float>(DeviceCtx *, float, const float *, float, float *,
+                                                 cudaStream_t);
+template alphasparse_status_t launch_spmv<double>(DeviceCtx *, double, const double *, double,
+                                                  double *, cudaStream_t);
+
+}  // namespace asb

@@ -1,0 +1,65 @@
+#pragma once
+/*
+ * Additions of the sm_100a backend.  Nothing here is needed for drop-in use of the
+ * entry points in spapi.h; a caller that keeps vectors on the device, wants its own
+ * stream, or wants to look at what the one-time analysis decided uses these.  They follow
+ * the precedent of the reference's device API (include/alphasparse/spapi_dcu.h: device
+ * pointers, an explicit stream on the handle, a per-matrix analysis object), not its form.
+ */
+#include "types.h"
+#include "spdef.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Kernels of later mv / mm calls are enqueued on `stream` (a cudaStream_t); NULL restores
+ * the default stream.  Process-wide; set it before the calls it should affect. */
+alphasparse_status_t alphasparse_cuda_set_stream(void *stream);
+alphasparse_status_t alphasparse_cuda_get_stream(void **stream);
+
+/* Blocks until everything enqueued on the library stream has finished. */
+alphasparse_status_t alphasparse_cuda_synchronize(void);
+
+typedef enum {
+    ALPHA_SPARSE_CUDA_ALG_AUTO = 0,   /* chosen per matrix by the analysis */
+    ALPHA_SPARSE_CUDA_ALG_VECTOR = 1, /* a group of 2..32 lanes per row */
+    ALPHA_SPARSE_CUDA_ALG_MERGE = 2   /* merge-path tiles: equal rows+nnz per thread block */
+} alphasparse_cuda_alg_t;
+
+/* Forces the SpMV kernel family for handles analysed after the call (A/B measurements);
+ * the environment variable ALPHASPARSE_CUDA_ALG=auto|vector|merge sets the initial value. */
+alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg);
+
+/* What the analysis at handle creation found and chose. */
+typedef struct {
+    int64_t rows, cols, nnz;
+    int64_t max_row_nnz;
+    int64_t empty_rows;
+    double mean_row_nnz;
+    int32_t algorithm;     /* alphasparse_cuda_alg_t actually used by mv */
+    int32_t lanes_per_row; /* vector kernel: lanes cooperating on one row */
+    int64_t merge_tiles;   /* merge kernel: thread blocks per call */
+    int64_t device_bytes;  /* device memory held by the handle */
+    int32_t device;        /* CUDA device ordinal that owns the device copy */
+    int32_t reserved;
+} alphasparse_cuda_mat_info_t;
+
+alphasparse_status_t alphasparse_cuda_get_mat_info(const alphasparse_matrix_t A,
+                                                   alphasparse_cuda_mat_info_t *info);
+
+/* Borrowed device pointers of the handle's CSR copy (rows+1 offsets, nnz columns, nnz
+ * values of the handle's precision). */
+alphasparse_status_t alphasparse_cuda_get_device_csr(const alphasparse_matrix_t A,
+                                                     ALPHA_INT **d_row_ptr,
+                                                     ALPHA_INT **d_col_indx, void **d_values);
+
+/* Number of kernels this library has launched in this process so far. */
+int64_t alphasparse_cuda_launch_count(void);
+
+/* Text of the last CUDA error the library met in this thread ("" if none). */
+const char *alphasparse_cuda_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,259 @@
+"""CPU checkers for the CSR mv / mm path -- TEST INFRASTRUCTURE ONLY.
+
+Two libraries, both built by ``make -C oracle``:
+
+* ``liboracle.so``  -- the C restatement in ``oracle.c`` (always available);
+* ``_ref/libalpha_ref.so`` -- the reference's own source files for this path compiled in place
+  (plain serial kernels, x86_64 OpenMP kernels, create / convert / partition).  It is built
+  where the reference tree is mounted and travels as a prebuilt file elsewhere.
+
+Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU legs of ``bench.py`` may import this
+module; the product library never does.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_LIB = os.path.join(HERE, "liboracle.so")
+REF_LIB = os.path.join(HERE, "_ref", "libalpha_ref.so")
+_NP = {"s": np.float32, "d": np.float64}
+_CT = {"s": C.c_float, "d": C.c_double}
+_i32, _p = C.c_int32, C.c_void_p
+
+
+def _a(x):
+    return x.ctypes.data
+
+
+def _i(x):
+    return np.ascontiguousarray(x, dtype=np.int32)
+
+
+# ---------------------------------------------------------------------------------------------
+# the C restatement
+# ---------------------------------------------------------------------------------------------
+_oracle = None
+
+
+def lib():
+    global _oracle
+    if _oracle is None:
+        if not os.path.exists(ORACLE_LIB):
+            raise ImportError(f"{ORACLE_LIB} missing: run `make -C oracle`")
+        L = C.CDLL(ORACLE_LIB)
+        for k, T in _CT.items():
+            getattr(L, f"oracle_gemv_csr_{k}").argtypes = [_i32, _p, _p, _p, _p, T, _p, T, _p]
+            getattr(L, f"oracle_gemv_csr_trans_{k}").argtypes = [_i32, _i32, _p, _p, _p, _p, T, _p, T, _p]
+            getattr(L, f"oracle_gemv_csr_omp_{k}").argtypes = [_i32, _p, _p, _p, _p, T, _p, T, _p, _i32]
+            for lay in ("row", "col"):
+                getattr(L, f"oracle_gemm_csr_{lay}_{k}").argtypes = [_i32, _p, _p, _p, _p, T, _p, _i32, _i32, T, _p,
+                                                                      _i32]
+            getattr(L, f"oracle_gemm_csr_row_omp_{k}").argtypes = [_i32, _p, _p, _p, _p, T, _p, _i32, _i32, T, _p,
+                                                                    _i32, _i32]
+            getattr(L, f"oracle_create_csr_{k}").argtypes = [_i32, _i32, _p, _p, _p, _p, _p, _p, _p]
+            getattr(L, f"oracle_create_csr_{k}").restype = _i32
+            getattr(L, f"oracle_coo_to_csr_{k}").argtypes = [_i32, _i32, _i32, _p, _p, _p, _p, _p, _p]
+        L.oracle_partition_rows_by_nnz.argtypes = [_p, _i32, _i32, _p]
+        L.oracle_lower_bound.argtypes = [_p, _i32, _i32, _i32]
+        L.oracle_lower_bound.restype = _i32
+        L.oracle_mv_status.argtypes = [C.c_int] * 9 + [_i32, _i32]
+        L.oracle_mm_status.argtypes = [C.c_int] * 9 + [_i32, _i32]
+        L.oracle_max_threads.restype = C.c_int
+        _oracle = L
+    return _oracle
+
+
+def gemv(kind, rows_start, rows_end, col, val, alpha, x, beta, y, threads=0):
+    """y (modified in place and returned) = beta*y + alpha*A*x; threads>0 uses the OpenMP form."""
+    rs, re_, ci = _i(rows_start), _i(rows_end), _i(col)
+    args = [len(rs), _a(rs), _a(re_), _a(ci), _a(val), alpha, _a(x), beta, _a(y)]
+    if threads:
+        getattr(lib(), f"oracle_gemv_csr_omp_{kind}")(*args, threads)
+    else:
+        getattr(lib(), f"oracle_gemv_csr_{kind}")(*args)
+    return y
+
+
+def gemv_trans(kind, cols, rows_start, rows_end, col, val, alpha, x, beta, y):
+    rs, re_, ci = _i(rows_start), _i(rows_end), _i(col)
+    getattr(lib(), f"oracle_gemv_csr_trans_{kind}")(len(rs), cols, _a(rs), _a(re_), _a(ci), _a(val), alpha, _a(x),
+                                                     beta, _a(y))
+    return y
+
+
+def gemm(kind, layout, rows_start, rows_end, col, val, alpha, X, columns, ldx, beta, Y, ldy, threads=0):
+    rs, re_, ci = _i(rows_start), _i(rows_end), _i(col)
+    args = [len(rs), _a(rs), _a(re_), _a(ci), _a(val), alpha, _a(X), columns, ldx, beta, _a(Y), ldy]
+    if threads:
+        assert layout == "row"
+        getattr(lib(), f"oracle_gemm_csr_row_omp_{kind}")(*args, threads)
+    else:
+        getattr(lib(), f"oracle_gemm_csr_{layout}_{kind}")(*args)
+    return Y
+
+
+def create_csr(kind, base, rows_start, rows_end, col, val):
+    """(offsets[rows+1], col[nnz], val[nnz]) as the reference's create_csr would store them."""
+    rs, re_, ci = _i(rows_start), _i(rows_end), _i(col)
+    v = np.ascontiguousarray(val, dtype=_NP[kind])
+    f = getattr(lib(), f"oracle_create_csr_{kind}")
+    nnz = f(base, len(rs), _a(rs), _a(re_), _a(ci), _a(v), None, None, None)
+    ptr, oc, ov = np.empty(len(rs) + 1, np.int32), np.empty(nnz, np.int32), np.empty(nnz, _NP[kind])
+    f(base, len(rs), _a(rs), _a(re_), _a(ci), _a(v), _a(ptr), _a(oc), _a(ov))
+    return ptr, oc, ov
+
+
+def coo_to_csr(kind, base, rows, row_indx, col_indx, val):
+    ri, ci = _i(row_indx), _i(col_indx)
+    v = np.ascontiguousarray(val, dtype=_NP[kind])
+    ptr, oc, ov = np.empty(rows + 1, np.int32), np.empty(len(ri), np.int32), np.empty(len(ri), _NP[kind])
+    getattr(lib(), f"oracle_coo_to_csr_{kind}")(base, rows, len(ri), _a(ri), _a(ci), _a(v), _a(ptr), _a(oc), _a(ov))
+    return ptr, oc, ov
+
+
+def partition_rows_by_nnz(rows_end, parts):
+    acc = _i(rows_end)
+    out = np.zeros(parts + 1, np.int32)
+    lib().oracle_partition_rows_by_nnz(_a(acc), len(acc), parts, _a(out))
+    return out
+
+
+def mv_status(has_handle=1, has_mat=1, has_x=1, has_y=1, handle_datatype=0, call_datatype=0, operation=0,
+              descr_type=0, fmt=1, rows=1, cols=1):
+    return lib().oracle_mv_status(has_handle, has_mat, has_x, has_y, handle_datatype, call_datatype, operation,
+                                  descr_type, fmt, rows, cols)
+
+
+def max_threads():
+    return lib().oracle_max_threads()
+
+
+# ---------------------------------------------------------------------------------------------
+# the reference's own objects
+# ---------------------------------------------------------------------------------------------
+class _RefHandle(C.Structure):
+    _fields_ = [("mat", C.c_void_p), ("format", C.c_int), ("datatype", C.c_int), ("inspector", C.c_void_p),
+                ("dcu_info", C.c_void_p)]
+
+
+_ref = None
+
+
+def ref_available():
+    return os.path.exists(REF_LIB)
+
+
+def ref():
+    """The reference's objects, loaded RTLD_LOCAL (it exports the same names as the product)."""
+    global _ref
+    if _ref is None:
+        if not ref_available():
+            raise ImportError(f"{REF_LIB} missing (built only where the reference tree is mounted)")
+        L = C.CDLL(REF_LIB, mode=C.RTLD_LOCAL)
+        for k, T in _CT.items():
+            getattr(L, f"alphasparse_{k}_create_csr").argtypes = [_p, C.c_int, _i32, _i32, _p, _p, _p, _p]
+            getattr(L, f"alphasparse_{k}_create_coo").argtypes = [_p, C.c_int, _i32, _i32, _i32, _p, _p, _p]
+            getattr(L, f"convert_csr_{k}_coo").argtypes = [_p, _p]
+            for name in (f"gemv_{k}_csr_plain", f"gemv_{k}_csr", f"gemv_{k}_csr_trans_plain"):
+                getattr(L, name).argtypes = [T, _p, _p, T, _p]
+            for name in (f"gemm_{k}_csr_row_plain", f"gemm_{k}_csr_col_plain", f"gemm_{k}_csr_row",
+                         f"gemm_{k}_csr_col", f"gemm_{k}_csr_row_trans_plain", f"gemm_{k}_csr_col_trans_plain"):
+                getattr(L, name).argtypes = [T, _p, _p, _i32, _i32, T, _p, _i32]
+            getattr(L, f"alphasparse_{k}_export_csr").argtypes = [_p] * 8
+        L.balanced_partition_row_by_nnz.argtypes = [_p, _i32, _i32, _p]
+        L.alpha_set_thread_num.argtypes = [C.c_int]
+        L.alpha_get_core_num.restype = C.c_int
+        _ref = L
+    return _ref
+
+
+class RefCsr:
+    """A CSR handle owned by the reference library.  The reference never frees (its alpha_free is
+    a no-op for non-NULL pointers), so create few of these."""
+
+    def __init__(self, kind, handle):
+        self.kind, self.handle = kind, handle
+        self.mat = C.cast(handle, C.POINTER(_RefHandle)).contents.mat
+
+    @classmethod
+    def from_csr(cls, kind, base, rows, cols, rows_start, rows_end, col, val):
+        rs, re_, ci = _i(rows_start), _i(rows_end), _i(col)
+        v = np.ascontiguousarray(val, dtype=_NP[kind])
+        h = C.c_void_p()
+        st = getattr(ref(), f"alphasparse_{kind}_create_csr")(C.byref(h), base, rows, cols, _a(rs), _a(re_), _a(ci),
+                                                               _a(v))
+        assert st == 0
+        return cls(kind, h)
+
+    @classmethod
+    def from_coo(cls, kind, base, rows, cols, row_indx, col_indx, val):
+        """create_coo then the COO->CSR conversion, as every reference test builds its matrix."""
+        ri, ci = _i(row_indx), _i(col_indx)
+        v = np.ascontiguousarray(val, dtype=_NP[kind])
+        h = C.c_void_p()
+        st = getattr(ref(), f"alphasparse_{kind}_create_coo")(C.byref(h), base, rows, cols, len(ri), _a(ri), _a(ci),
+                                                               _a(v))
+        assert st == 0
+        coo = C.cast(h, C.POINTER(_RefHandle)).contents.mat
+        out = C.c_void_p()
+        st = getattr(ref(), f"convert_csr_{kind}_coo")(coo, C.byref(out))
+        assert st == 0
+        fake = _RefHandle(out.value, 1, 0 if kind == "s" else 1, None, None)
+        obj = cls.__new__(cls)
+        obj.kind, obj._keep, obj.mat = kind, fake, out.value
+        obj.handle = C.cast(C.pointer(fake), C.c_void_p)
+        return obj
+
+    def export(self):
+        base, rows, cols = C.c_int(), C.c_int32(), C.c_int32()
+        rs, re_, ci, v = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_void_p()
+        st = getattr(ref(), f"alphasparse_{self.kind}_export_csr")(self.handle, C.byref(base), C.byref(rows),
+                                                                   C.byref(cols), C.byref(rs), C.byref(re_),
+                                                                   C.byref(ci), C.byref(v))
+        assert st == 0
+        m = rows.value
+        ptr = np.ctypeslib.as_array(C.cast(rs, C.POINTER(C.c_int32)), shape=(m + 1,)).copy()
+        nnz = int(ptr[m] - ptr[0])
+        col = np.ctypeslib.as_array(C.cast(ci, C.POINTER(C.c_int32)), shape=(max(nnz, 1),))[:nnz].copy()
+        val = np.ctypeslib.as_array(C.cast(v, C.POINTER(_CT[self.kind])), shape=(max(nnz, 1),))[:nnz].copy()
+        return ptr, col, val
+
+    def gemv(self, alpha, x, beta, y, omp_threads=0, trans=False):
+        """The reference's plain serial kernel (omp_threads == 0) or its x86_64 OpenMP kernel."""
+        L = ref()
+        if trans:
+            fn = getattr(L, f"gemv_{self.kind}_csr_trans_plain")
+        elif omp_threads:
+            L.alpha_set_thread_num(omp_threads)
+            fn = getattr(L, f"gemv_{self.kind}_csr")
+        else:
+            fn = getattr(L, f"gemv_{self.kind}_csr_plain")
+        st = fn(alpha, self.mat, _a(x), beta, _a(y))
+        assert st == 0
+        return y
+
+    def gemm(self, layout, alpha, X, columns, ldx, beta, Y, ldy, omp_threads=0, trans=False):
+        L = ref()
+        if trans:
+            fn = getattr(L, f"gemm_{self.kind}_csr_{layout}_trans_plain")
+        elif omp_threads:
+            L.alpha_set_thread_num(omp_threads)
+            fn = getattr(L, f"gemm_{self.kind}_csr_{layout}")
+        else:
+            fn = getattr(L, f"gemm_{self.kind}_csr_{layout}_plain")
+        st = fn(alpha, self.mat, _a(X), columns, ldx, beta, _a(Y), ldy)
+        assert st == 0
+        return Y
+
+
+def ref_partition_rows_by_nnz(rows_end, parts):
+    acc = _i(rows_end)
+    out = np.zeros(parts + 1, np.int32)
+    ref().balanced_partition_row_by_nnz(_a(acc), len(acc), parts, _a(out))
+    return out
+
+
+def ref_cores():
+    return ref().alpha_get_core_num()

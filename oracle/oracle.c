@@ -1,0 +1,331 @@
+/*
+ * CPU restatement of the reference's CSR mv / mm path.  TEST INFRASTRUCTURE ONLY: it is the
+ * checker the parity tests and the CPU legs of the benchmark compare against, never part of
+ * the shipped library, which has no CPU path at all.
+ *
+ * Every function names the reference source it follows (paths relative to the reference
+ * tree).  Arrays are passed flat instead of through the reference's structs so the same
+ * functions serve any slice of a matrix.  Built with -ffp-contract=off so that sums are
+ * formed exactly as written: left to right, one rounding per multiply and per add.
+ *
+ * Pinning: tests/test_oracle.py checks these functions against tests/golden/ vectors that
+ * were produced by the reference's own sources (oracle/_ref, see oracle/Makefile), and, when
+ * oracle/_ref/libalpha_ref.so is present, against that library live on the same inputs.
+ */
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+typedef int32_t aint;
+
+/* status codes: include/alphasparse/spdef.h:8-19 */
+enum { ST_SUCCESS = 0, ST_NOT_INITIALIZED = 1, ST_INVALID_VALUE = 3, ST_NOT_SUPPORTED = 6 };
+
+/* ---------------------------------------------------------------------------------------
+ * y = beta*y + alpha*(A x), one row after the other, products added left to right.
+ * src/plain/kernel/level2/mv/gemv/gemv_x_csr_plain.c:4-24: y[r] is scaled by beta first,
+ * the row's dot product is accumulated from zero, then alpha*dot is added.
+ * ------------------------------------------------------------------------------------- */
+#define DEF_GEMV(T, sfx)                                                                      \
+    void oracle_gemv_csr_##sfx(aint rows, const aint *rs, const aint *re, const aint *col,    \
+                               const T *val, T alpha, const T *x, T beta, T *y) {             \
+        for (aint r = 0; r < rows; r++) {                                                     \
+            T out = y[r] * beta;                                                              \
+            T dot = 0;                                                                        \
+            for (aint k = rs[r]; k < re[r]; k++) dot += val[k] * x[col[k]];                   \
+            y[r] = out + alpha * dot;                                                         \
+        }                                                                                     \
+    }
+DEF_GEMV(float, s)
+DEF_GEMV(double, d)
+
+/* ---------------------------------------------------------------------------------------
+ * y = beta*y + alpha*(A^T x): y (length cols) scaled first, then every stored element
+ * scatters (alpha*a)*x[row] into y[col], rows ascending.
+ * src/plain/kernel/level2/mv/gemv/gemv_x_csr_trans_plain.c:4-27.
+ * ------------------------------------------------------------------------------------- */
+#define DEF_GEMV_T(T, sfx)                                                                    \
+    void oracle_gemv_csr_trans_##sfx(aint rows, aint cols, const aint *rs, const aint *re,    \
+                                     const aint *col, const T *val, T alpha, const T *x,      \
+                                     T beta, T *y) {                                          \
+        for (aint c = 0; c < cols; c++) y[c] = y[c] * beta;                                   \
+        for (aint r = 0; r < rows; r++)                                                       \
+            for (aint k = rs[r]; k < re[r]; k++) {                                            \
+                T av = alpha * val[k];                                                        \
+                y[col[k]] += av * x[r];                                                       \
+            }                                                                                 \
+    }
+DEF_GEMV_T(float, s)
+DEF_GEMV_T(double, d)
+
+/* ---------------------------------------------------------------------------------------
+ * Row-major SpMM, Y (rows x columns, leading dimension ldy) = beta*Y + alpha*A*X.
+ * src/plain/kernel/level3/mm/gemm/gemm_x_csr_row_plain.c:4-23: the output row is scaled
+ * by beta, then each stored element adds (alpha*a) * X[col, :] -- alpha is folded into the
+ * element BEFORE the accumulation, unlike the SpMV above.
+ * ------------------------------------------------------------------------------------- */
+#define DEF_GEMM_ROW(T, sfx)                                                                  \
+    void oracle_gemm_csr_row_##sfx(aint rows, const aint *rs, const aint *re,                 \
+                                   const aint *col, const T *val, T alpha, const T *X,        \
+                                   aint columns, aint ldx, T beta, T *Y, aint ldy) {          \
+        for (aint r = 0; r < rows; r++) {                                                     \
+            T *out = Y + (size_t)r * ldy;                                                     \
+            for (aint c = 0; c < columns; c++) out[c] = out[c] * beta;                        \
+            for (aint k = rs[r]; k < re[r]; k++) {                                            \
+                T av = alpha * val[k];                                                        \
+                const T *in = X + (size_t)col[k] * ldx;                                       \
+                for (aint c = 0; c < columns; c++) out[c] += av * in[c];                      \
+            }                                                                                 \
+        }                                                                                     \
+    }
+DEF_GEMM_ROW(float, s)
+DEF_GEMM_ROW(double, d)
+
+/* ---------------------------------------------------------------------------------------
+ * Column-major SpMM: element (r, c) of a dense operand lives at [c*ld + r].
+ * src/plain/kernel/level3/mm/gemm/gemm_x_csr_col_plain.c:4-21: for every dense column and
+ * every sparse row a dot product from zero, then y = y*beta + alpha*dot.
+ * ------------------------------------------------------------------------------------- */
+#define DEF_GEMM_COL(T, sfx)                                                                  \
+    void oracle_gemm_csr_col_##sfx(aint rows, const aint *rs, const aint *re,                 \
+                                   const aint *col, const T *val, T alpha, const T *X,        \
+                                   aint columns, aint ldx, T beta, T *Y, aint ldy) {          \
+        for (aint c = 0; c < columns; c++)                                                    \
+            for (aint r = 0; r < rows; r++) {                                                 \
+                T dot = 0;                                                                    \
+                for (aint k = rs[r]; k < re[r]; k++)                                          \
+                    dot += val[k] * X[(size_t)c * ldx + col[k]];                              \
+                T *o = Y + (size_t)c * ldy + r;                                               \
+                *o = *o * beta;                                                               \
+                *o += alpha * dot;                                                            \
+            }                                                                                 \
+    }
+DEF_GEMM_COL(float, s)
+DEF_GEMM_COL(double, d)
+
+/* ---------------------------------------------------------------------------------------
+ * The OpenMP kernel of the reference's x86_64 tree (the timed CPU baseline when the
+ * reference's own objects are not available): rows are split into one contiguous range
+ * per thread by oracle_partition_rows_by_nnz, each row's dot product uses four partial
+ * sums over elements k, k+1, k+2, k+3 combined as (t0+t1)+(t2+t3), a scalar tail goes to
+ * t0, and then y = y*beta + alpha*dot.
+ * src/kernel/x86_64/level2/mv/gemv/gemv_x_csr.c:129-153 (dot), :155-182 (rows), :184-208.
+ * ------------------------------------------------------------------------------------- */
+void oracle_partition_rows_by_nnz(const aint *acc, aint rows, aint parts, aint *part);
+
+static aint oracle_thread_id(void) {
+#ifdef _OPENMP
+    return (aint)omp_get_thread_num();
+#else
+    return 0;
+#endif
+}
+
+#define DEF_GEMV_OMP(T, sfx)                                                                  \
+    void oracle_gemv_csr_omp_##sfx(aint rows, const aint *rs, const aint *re,                 \
+                                   const aint *col, const T *val, T alpha, const T *x,        \
+                                   T beta, T *y, aint threads) {                              \
+        if (threads < 1) threads = 1;                                                         \
+        aint *part = (aint *)malloc(sizeof(aint) * ((size_t)threads + 1));                    \
+        oracle_partition_rows_by_nnz(re, rows, threads, part);                                \
+        _Pragma("omp parallel num_threads(threads)")                                          \
+        {                                                                                     \
+            const aint t = oracle_thread_id();                                                \
+            for (aint r = part[t]; r < part[t + 1]; r++) {                                    \
+                const aint b = rs[r], n = re[r] - b, n4 = n & ~3;                             \
+                T t0 = 0, t1 = 0, t2 = 0, t3 = 0;                                             \
+                aint k = 0;                                                                   \
+                for (; k < n4; k += 4) {                                                      \
+                    t0 += val[b + k] * x[col[b + k]];                                         \
+                    t1 += val[b + k + 1] * x[col[b + k + 1]];                                 \
+                    t2 += val[b + k + 2] * x[col[b + k + 2]];                                 \
+                    t3 += val[b + k + 3] * x[col[b + k + 3]];                                 \
+                }                                                                             \
+                for (; k < n; k++) t0 += val[b + k] * x[col[b + k]];                          \
+                t0 += t1;                                                                     \
+                t2 += t3;                                                                     \
+                t0 += t2;                                                                     \
+                y[r] = y[r] * beta;                                                           \
+                y[r] += alpha * t0;                                                           \
+            }                                                                                 \
+        }                                                                                     \
+        free(part);                                                                           \
+    }
+
+DEF_GEMV_OMP(float, s)
+DEF_GEMV_OMP(double, d)
+
+/* OpenMP row-major SpMM of the x86_64 tree: a parallel-for over rows around the same
+ * arithmetic as the serial kernel.  src/kernel/x86_64/level3/mm/gemm/gemm_x_csr_row.c:4-27 */
+#define DEF_GEMM_ROW_OMP(T, sfx)                                                              \
+    void oracle_gemm_csr_row_omp_##sfx(aint rows, const aint *rs, const aint *re,             \
+                                       const aint *col, const T *val, T alpha, const T *X,    \
+                                       aint columns, aint ldx, T beta, T *Y, aint ldy,        \
+                                       aint threads) {                                        \
+        if (threads < 1) threads = 1;                                                         \
+        _Pragma("omp parallel for num_threads(threads)")                                      \
+        for (aint r = 0; r < rows; r++) {                                                     \
+            T *out = Y + (size_t)r * ldy;                                                     \
+            for (aint c = 0; c < columns; c++) out[c] = out[c] * beta;                        \
+            for (aint k = rs[r]; k < re[r]; k++) {                                            \
+                T av = alpha * val[k];                                                        \
+                const T *in = X + (size_t)col[k] * ldx;                                       \
+                for (aint c = 0; c < columns; c++) out[c] += av * in[c];                      \
+            }                                                                                 \
+        }                                                                                     \
+    }
+DEF_GEMM_ROW_OMP(float, s)
+DEF_GEMM_ROW_OMP(double, d)
+
+int oracle_max_threads(void) {
+#ifdef _OPENMP
+    return omp_get_num_procs();
+#else
+    return 1;
+#endif
+}
+
+/* ---------------------------------------------------------------------------------------
+ * First index in [lo, hi) whose element is >= value.  src/util/partition.c:46-61.
+ * ------------------------------------------------------------------------------------- */
+aint oracle_lower_bound(const aint *t, aint lo, aint hi, aint value) {
+    while (hi > lo) {
+        aint mid = (lo + hi) / 2;
+        if (t[mid] < value) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo;
+}
+
+/* ---------------------------------------------------------------------------------------
+ * nnz-balanced contiguous row split.  src/util/partition.c:79-92.  `acc` is rows_end, the
+ * inclusive prefix sums of the row lengths.  Quirks kept on purpose: the average is an
+ * integer division; the search range stops at rows-1; a row that crosses a boundary falls
+ * into the following part; parts may be empty.
+ * ------------------------------------------------------------------------------------- */
+void oracle_partition_rows_by_nnz(const aint *acc, aint rows, aint parts, aint *part) {
+    const aint total = acc[rows - 1];
+    const aint share = total / parts;
+    part[0] = 0;
+    for (aint p = 1; p < parts; p++) part[p] = oracle_lower_bound(acc, 0, rows - 1, share * p);
+    part[parts] = rows;
+}
+
+/* ---------------------------------------------------------------------------------------
+ * 4-array user CSR -> owned 3-array CSR.  src/core/format/alphasparse_x_create_csr.c:22-55:
+ * nnz = rows_end[rows-1] - rows_start[0]; offsets[0] = rows_start[0], offsets[i+1] =
+ * rows_end[i]; columns and values are copied from element 0 of the user arrays; with
+ * one-based input one is subtracted from every offset and every column.
+ * out_ptr has rows+1 entries; out_col / out_val have nnz entries.  Returns nnz.
+ * ------------------------------------------------------------------------------------- */
+#define DEF_CREATE(T, sfx)                                                                    \
+    aint oracle_create_csr_##sfx(aint base, aint rows, const aint *rs, const aint *re,        \
+                                 const aint *col, const T *val, aint *out_ptr, aint *out_col, \
+                                 T *out_val) {                                                \
+        const aint nnz = re[rows - 1] - rs[0];                                                \
+        const aint shift = base ? 1 : 0;                                                      \
+        if (out_ptr) {                                                                        \
+            out_ptr[0] = rs[0] - shift;                                                       \
+            for (aint i = 0; i < rows; i++) out_ptr[i + 1] = re[i] - shift;                   \
+        }                                                                                     \
+        if (out_col)                                                                          \
+            for (aint i = 0; i < nnz; i++) {                                                  \
+                out_col[i] = col[i] - shift;                                                  \
+                out_val[i] = val[i];                                                          \
+            }                                                                                 \
+        return nnz;                                                                           \
+    }
+DEF_CREATE(float, s)
+DEF_CREATE(double, d)
+
+/* ---------------------------------------------------------------------------------------
+ * COO -> CSR.  src/core/format/alphasparse_x_create_coo.c:30-45 (one-based input is
+ * rebased) and src/core/format/convert_csr_x_coo.c:14-81: (row, col, value) records are
+ * sorted by row then column, offsets come from one sweep over the sorted rows, columns and
+ * values are copied in sorted order.  Duplicated (row, col) pairs are all kept.  The
+ * reference sorts with qsort, whose order among equal keys is unspecified; this restatement
+ * uses a stable merge sort, so it agrees with any outcome of the reference whenever the
+ * duplicates carry equal values or there are none.
+ * ------------------------------------------------------------------------------------- */
+#define DEF_COO2CSR(T, sfx)                                                                   \
+    typedef struct { aint r, c; T v; } rec_##sfx;                                             \
+    static void msort_##sfx(rec_##sfx *a, rec_##sfx *tmp, size_t n) {                         \
+        if (n < 2) return;                                                                    \
+        size_t h = n / 2;                                                                     \
+        msort_##sfx(a, tmp, h);                                                               \
+        msort_##sfx(a + h, tmp, n - h);                                                       \
+        size_t i = 0, j = h, o = 0;                                                           \
+        while (i < h && j < n) {                                                              \
+            int take_right = (a[j].r < a[i].r) || (a[j].r == a[i].r && a[j].c < a[i].c);      \
+            tmp[o++] = take_right ? a[j++] : a[i++];                                          \
+        }                                                                                     \
+        while (i < h) tmp[o++] = a[i++];                                                      \
+        while (j < n) tmp[o++] = a[j++];                                                      \
+        memcpy(a, tmp, n * sizeof(rec_##sfx));                                                \
+    }                                                                                         \
+    void oracle_coo_to_csr_##sfx(aint base, aint rows, aint nnz, const aint *ri,              \
+                                 const aint *ci, const T *v, aint *out_ptr, aint *out_col,    \
+                                 T *out_val) {                                                \
+        const aint shift = base ? 1 : 0;                                                      \
+        rec_##sfx *a = (rec_##sfx *)malloc(sizeof(rec_##sfx) * (size_t)(nnz > 0 ? nnz : 1));  \
+        rec_##sfx *tmp = (rec_##sfx *)malloc(sizeof(rec_##sfx) * (size_t)(nnz > 0 ? nnz : 1));\
+        for (aint i = 0; i < nnz; i++) {                                                      \
+            a[i].r = ri[i] - shift;                                                           \
+            a[i].c = ci[i] - shift;                                                           \
+            a[i].v = v[i];                                                                    \
+        }                                                                                     \
+        msort_##sfx(a, tmp, (size_t)nnz);                                                     \
+        for (aint r = 0; r <= rows; r++) out_ptr[r] = 0;                                      \
+        for (aint i = 0; i < nnz; i++)                                                        \
+            if (a[i].r >= 0 && a[i].r < rows) out_ptr[a[i].r + 1]++;                          \
+        for (aint r = 0; r < rows; r++) out_ptr[r + 1] += out_ptr[r];                         \
+        for (aint i = 0; i < nnz; i++) {                                                      \
+            out_col[i] = a[i].c;                                                              \
+            out_val[i] = a[i].v;                                                              \
+        }                                                                                     \
+        free(a);                                                                              \
+        free(tmp);                                                                            \
+    }
+DEF_COO2CSR(float, s)
+DEF_COO2CSR(double, d)
+
+/* ---------------------------------------------------------------------------------------
+ * Argument checks of alphasparse_?_mv in the order the reference applies them.
+ * src/core/op/level2/alphasparse_x_mv.c:1670-1716 (real precisions):
+ *   handle / handle->mat / x / y NULL            -> NOT_INITIALIZED
+ *   handle datatype != precision of the call     -> INVALID_VALUE
+ *   CONJUGATE_TRANSPOSE on a real type           -> INVALID_VALUE
+ *   SYMMETRIC or HERMITIAN on a non-square A     -> INVALID_VALUE
+ *   then format CSR + type GENERAL runs gemv; a descriptor type outside 0..4 or an unknown
+ *   format -> INVALID_VALUE.
+ * Returns ST_SUCCESS when the call reaches the CSR/GENERAL kernel, -1 when it reaches some
+ * other kernel of the reference (outside this path), else the error status.
+ * ------------------------------------------------------------------------------------- */
+int oracle_mv_status(int has_handle, int has_mat, int has_x, int has_y, int handle_datatype,
+                     int call_datatype, int operation, int descr_type, int format, aint rows,
+                     aint cols) {
+    if (!has_handle || !has_mat || !has_x || !has_y) return ST_NOT_INITIALIZED;
+    if (handle_datatype != call_datatype) return ST_INVALID_VALUE;
+    if (operation == 2) return ST_INVALID_VALUE;
+    if ((descr_type == 1 || descr_type == 2) && rows != cols) return ST_INVALID_VALUE;
+    if (format == 1 /* CSR */) {
+        if (descr_type == 0) return ST_SUCCESS;
+        if (descr_type >= 1 && descr_type <= 4) return -1;
+        return ST_INVALID_VALUE;
+    }
+    if (format == 0 || (format >= 2 && format <= 5)) return -1;
+    return ST_INVALID_VALUE;
+}
+
+/* alphasparse_?_mm applies the same checks in the same order
+ * (src/core/op/level3/alphasparse_x_mm.c:2317-2338); the kernel is picked by
+ * layout + 2*operation (:47-63). */
+int oracle_mm_status(int has_handle, int has_mat, int has_x, int has_y, int handle_datatype,
+                     int call_datatype, int operation, int descr_type, int format, aint rows,
+                     aint cols) {
+    return oracle_mv_status(has_handle, has_mat, has_x, has_y, handle_datatype, call_datatype,
+                            operation, descr_type, format, rows, cols);
+}
