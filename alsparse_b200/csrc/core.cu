@@ -67,6 +67,8 @@ void ctx_destroy(DeviceCtx *c) {
     cudaFree(c->d_carry_val);
     cudaFree(c->d_x_stage);
     cudaFree(c->d_y_stage);
+    if (c->ev_start) cudaEventDestroy(c->ev_start);
+    if (c->ev_stop) cudaEventDestroy(c->ev_stop);
     if (prev >= 0) cudaSetDevice(prev);
     c->magic = 0;
     delete c;
@@ -725,6 +727,27 @@ alphasparse_status_t alphasparse_cuda_get_device_csr(const alphasparse_matrix_t 
     if (d_row_ptr) *d_row_ptr = c->d_row_ptr;
     if (d_col_indx) *d_col_indx = c->d_col;
     if (d_values) *d_values = c->d_val;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+alphasparse_status_t alphasparse_cuda_profile_kernel(const alphasparse_matrix_t A, int enable) {
+    DeviceCtx *c = ctx_of(A);
+    if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+    DeviceGuard guard(c->device);
+    if (!guard.ok) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+    std::lock_guard<std::mutex> lock(c->mu);
+    if (enable && !c->ev_start) {
+        ASB_CUDA_OR(cudaEventCreate(&c->ev_start), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        ASB_CUDA_OR(cudaEventCreate(&c->ev_stop), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    }
+    c->profile = enable != 0;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+alphasparse_status_t alphasparse_cuda_kernel_ms(const alphasparse_matrix_t A, float *ms) {
+    DeviceCtx *c = ctx_of(A);
+    if (!c || !ms) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+    if (!c->ev_start) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    ASB_CUDA_OR(cudaEventSynchronize(c->ev_stop), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    ASB_CUDA_OR(cudaEventElapsedTime(ms, c->ev_start, c->ev_stop), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 int64_t alphasparse_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

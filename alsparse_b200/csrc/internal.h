@@ -79,6 +79,10 @@ struct DeviceCtx {
     void *d_y_stage = nullptr;
     size_t y_stage_bytes = 0;
 
+    // optional timing of the dominant kernel of each mv / mm call (alphasparse_cuda_profile_kernel)
+    bool profile = false;
+    cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
+
     int64_t device_bytes = 0;
     std::mutex mu;  // serialises calls that share the carry and staging buffers
 };

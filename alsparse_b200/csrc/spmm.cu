@@ -119,12 +119,14 @@ static void launch_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx
                        int ldy, cudaStream_t st) {
     const unsigned blocks = (unsigned)((ctx->rows + 7) / 8);
     const T *val = static_cast<const T *>(ctx->d_val);
+    if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
     if (beta == T(0))
         spmm_row_kernel<T, VEC, false><<<blocks, 256, 0, st>>>(
             (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, X, columns, ldx, Y, ldy, alpha, beta);
     else
         spmm_row_kernel<T, VEC, true><<<blocks, 256, 0, st>>>(
             (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, X, columns, ldx, Y, ldy, alpha, beta);
+    if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
     count_launch();
 }
 

@@ -432,12 +432,14 @@ static void launch_vector(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cud
     constexpr int rows_per_block = (256 / LANES) * RPG;
     const unsigned blocks = (unsigned)((ctx->rows + rows_per_block - 1) / rows_per_block);
     const T *val = static_cast<const T *>(ctx->d_val);
+    if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
     if (beta == T(0))
         spmv_vector_kernel<T, LANES, RPG, false><<<blocks, 256, 0, st>>>(
             (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta);
     else
         spmv_vector_kernel<T, LANES, RPG, true><<<blocks, 256, 0, st>>>(
             (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta);
+    if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
     count_launch();
 }
 
@@ -446,6 +448,7 @@ static void launch_merge(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cuda
     const T *val = static_cast<const T *>(ctx->d_val);
     T *carry = static_cast<T *>(ctx->d_carry_val);
     const unsigned blocks = (unsigned)ctx->merge_tiles;
+    if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
     if (beta == T(0))
         spmv_merge_kernel<T, kMergeThreads, IPT, false><<<blocks, kMergeThreads, 0, st>>>(
             (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta, ctx->d_tile,
@@ -454,6 +457,7 @@ static void launch_merge(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cuda
         spmv_merge_kernel<T, kMergeThreads, IPT, true><<<blocks, kMergeThreads, 0, st>>>(
             (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta, ctx->d_tile,
             ctx->d_carry_row, carry);
+    if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
     const unsigned fblocks = (unsigned)((ctx->merge_tiles + 255) / 256);
     spmv_merge_fixup_kernel<T><<<fblocks, 256, 0, st>>>((int)ctx->rows, ctx->merge_tiles,
                                                        ctx->d_carry_row, carry, y, alpha);

@@ -144,3 +144,15 @@ def partition_rows_by_nnz(rows_end, parts):
     out = np.zeros(parts + 1, dtype=np.int32)
     capi.load().balanced_partition_row_by_nnz(_ptr(acc), len(acc), parts, _ptr(out))
     return out
+
+
+def profile_kernel(A, enable=True):
+    return capi.load().alphasparse_cuda_profile_kernel(A, 1 if enable else 0)
+
+
+def kernel_ms(A):
+    """Duration in ms of the dominant kernel of the last mv / mm call on A (profiling enabled)."""
+    ms = C.c_float()
+    st = capi.load().alphasparse_cuda_kernel_ms(A, C.byref(ms))
+    assert st == SUCCESS, capi.STATUS_NAMES[st]
+    return ms.value

@@ -1,0 +1,423 @@
+"""Benchmark of the CSR SpMV / SpMM path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One "step" is one pass of the hot path over the whole matrix: one alphasparse_?_mv (or _mm) call
+per GPU on its row block.  The metric is effective GB/s = algorithmic bytes / step time, where
+algorithmic bytes = values + col_idx + row_ptr + x + y, each array counted once for the whole
+matrix (also reported: GFLOP/s = 2*nnz[*columns] / step time).
+
+Workloads (seeded synthetic stand-ins for the user-supplied matrix files the reference's tests read):
+  uniform16   fp32, 2^24 x 2^24, exactly 16 distinct uniform columns per row, alpha=1.5, beta=0.5
+              (default: the configuration that is row-partitioned over 1/2/4/8 GPUs)
+  stencil27   fp64, 27-point stencil on a 160^3 grid, alpha=1, beta=0
+  powerlaw    fp64, 2^23 rows, Zipf(1.8) row lengths clipped to [1, 200000], alpha=1, beta=0;
+              with more than one GPU every step ends with the allgather of y into the next x
+  spmm64      fp32, 2^21 rows Poisson(32), times a 2^21 x 64 row-major dense block, alpha=1, beta=0
+
+With N > 1 (launched by torch.distributed.run, one process per GPU) the rows are split by the
+reference's nnz-balanced rule, x is replicated, y stays partitioned: total work is fixed, so the
+scaling is "strong".  `--impl reference` times the reference's own OpenMP CPU kernel instead.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
+# captures summarised under profiles/ (bytes; None where no capture exists yet).
+NCU_TRAFFIC = {"uniform16": None, "stencil27": None, "powerlaw": None, "spmm64": None}
+
+WORKLOADS = {
+    "uniform16": dict(kind="s", rows_log2=24, alpha=1.5, beta=0.5, op="mv"),
+    "stencil27": dict(kind="d", grid=160, alpha=1.0, beta=0.0, op="mv"),
+    "powerlaw": dict(kind="d", rows_log2=23, alpha=1.0, beta=0.0, op="mv"),
+    "spmm64": dict(kind="s", rows_log2=21, alpha=1.0, beta=0.0, op="mm", columns=64),
+}
+TSIZE = {"s": 4, "d": 8}
+
+
+# ------------------------------------------------------------------------------------------------
+# workload construction
+# ------------------------------------------------------------------------------------------------
+def global_row_lengths(name, cfg, seed=0):
+    """Row lengths of the whole matrix (cheap; needed for the nnz-balanced split)."""
+    from alsparse_b200 import synth
+    if name == "stencil27":
+        import ctypes  # noqa: F401
+        n = cfg["grid"]
+        lens = np.empty(n ** 3, dtype=np.int32)
+        synth._load().synth_stencil27_rowlen(n, 0, n ** 3, lens.ctypes.data)
+        return lens
+    rows = 1 << cfg["rows_log2"]
+    if name == "uniform16":
+        return synth.rowlen_fixed(rows, 16)
+    if name == "powerlaw":
+        return synth.rowlen_zipf(seed, rows, 1.8, 1, min(200000, rows))
+    if name == "spmm64":
+        return synth.rowlen_poisson(seed, rows, 32.0, rows)
+    raise ValueError(name)
+
+
+def local_block(name, cfg, lens, r0, r1, seed=0):
+    """Rows [r0, r1) as a CSR piece with local offsets and global columns."""
+    from alsparse_b200 import synth
+    kind = cfg["kind"]
+    if name == "stencil27":
+        return synth.stencil27(kind, cfg["grid"], row0=r0, nrows=r1 - r0)
+    rows = len(lens)
+    return synth._fill_uniform(kind, seed, r0, np.ascontiguousarray(lens[r0:r1]), rows, rows)
+
+
+def algorithmic_bytes(cfg, rows, cols, nnz):
+    t = TSIZE[cfg["kind"]]
+    k = cfg.get("columns", 1)
+    return nnz * t + nnz * 4 + (rows + 1) * 4 + cols * k * t + rows * k * t
+
+
+def flops(cfg, nnz):
+    return 2 * nnz * cfg.get("columns", 1)
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50", "-i",
+                 str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, t0, t1):
+        def parse(rows):
+            out = []
+            for _, line in rows:
+                p = [s.strip() for s in line.split(",")]
+                try:
+                    out.append((float(p[0]), float(p[1]), p[3:7]))
+                except (ValueError, IndexError):
+                    pass
+            return out
+        window = parse([r for r in self.rows if t0 <= r[0] <= t1])
+        scope = "timed region"
+        if len(window) < 3:
+            window, scope = parse(self.rows), "whole measurement phase (timed region shorter than the sampling period)"
+        if not window:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "scope": "nvidia-smi unavailable"}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for _, _, fl in window for i, f in enumerate(fl) if f.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(w[0] for w in window), "sm_max_mhz": window[0][1], "reasons": reasons,
+                "samples": len(window), "scope": scope}
+
+
+# ------------------------------------------------------------------------------------------------
+# the reference arm / CPU baseline
+# ------------------------------------------------------------------------------------------------
+def cpu_reference_run(name, cfg, steps, warmup, sample_rows_log2=22):
+    """The reference's own OpenMP kernel (oracle/_ref) -- or the oracle port of it when those objects
+    are absent -- on a bounded sample: the first 2^sample_rows_log2 rows of the workload's matrix with
+    x at full length, all host threads.  Returns (GB/s, GFLOP/s, ms per step, descriptor dict)."""
+    import oracle
+    from alsparse_b200 import synth
+    kind = cfg["kind"]
+    lens = global_row_lengths(name, cfg)
+    rows, cols = len(lens), len(lens)
+    n = min(rows, 1 << sample_rows_log2)
+    if cfg["op"] == "mm":
+        n = min(n, 1 << 19)
+    m = local_block(name, cfg, lens, 0, n)
+    columns = cfg.get("columns", 1)
+    x = synth.vector(kind, 0, 1, cols * columns, 0.0 if name == "stencil27" else -1.0, 1.0)
+    y = synth.vector(kind, 0, 2, n * columns)
+    use_ref = oracle.ref_available()
+    threads = oracle.ref_cores() if use_ref else oracle.max_threads()
+    A = oracle.RefCsr.from_csr(kind, 0, n, cols, m.rows_start, m.rows_end, m.col, m.val) if use_ref else None
+
+    def step():
+        if cfg["op"] == "mv":
+            if use_ref:
+                A.gemv(cfg["alpha"], x, cfg["beta"], y, omp_threads=threads)
+            else:
+                oracle.gemv(kind, m.rows_start, m.rows_end, m.col, m.val, cfg["alpha"], x, cfg["beta"], y,
+                            threads=threads)
+        else:
+            if use_ref:
+                A.gemm("row", cfg["alpha"], x, columns, columns, cfg["beta"], y, columns, omp_threads=threads)
+            else:
+                oracle.gemm(kind, "row", m.rows_start, m.rows_end, m.col, m.val, cfg["alpha"], x, columns, columns,
+                            cfg["beta"], y, columns, threads=threads)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    nbytes = algorithmic_bytes(cfg, n, cols, m.nnz)
+    desc = {"kind": "reference" if use_ref else "port", "cores": threads,
+            "sample": f"rows [0, {n}) of {rows} ({m.nnz} stored elements), x at full length {cols}"
+                      f"{' x ' + str(columns) if columns > 1 else ''}; {steps} timed calls after {warmup} warm-up"}
+    return nbytes / dt / 1e9, flops(cfg, m.nnz) / dt / 1e9, dt * 1e3, desc
+
+
+def run_reference_arm(args, name, cfg, rank):
+    if rank != 0:
+        return
+    gbs, gfl, ms, desc = cpu_reference_run(name, cfg, args.steps, max(args.warmup, 1))
+    line = {"impl": "reference", "metric": "csr_spmv_effective_gbs" if cfg["op"] == "mv" else "csr_spmm_effective_gbs",
+            "value": gbs, "unit": "GB/s", "gflops": gfl, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": max(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32" if cfg["kind"] == "s" else "f64", "data": "synthetic",
+            "config": {"workload": name}, "cpu_baseline": dict(value=gbs, unit="GB/s", **desc),
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# the GPU arm
+# ------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="uniform16", choices=sorted(WORKLOADS))
+    ap.add_argument("--rows-log2", type=int, default=None, help="shrink the matrix (development only)")
+    ap.add_argument("--grid", type=int, default=None, help="shrink the stencil grid (development only)")
+    ap.add_argument("--alg", default="auto", choices=["auto", "vector", "merge"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    name = args.workload
+    cfg = dict(WORKLOADS[name])
+    reduced = False
+    if args.rows_log2 is not None and "rows_log2" in cfg:
+        reduced, cfg["rows_log2"] = cfg["rows_log2"] != args.rows_log2, args.rows_log2
+    if args.grid is not None and "grid" in cfg:
+        reduced, cfg["grid"] = cfg["grid"] != args.grid, args.grid
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, name, cfg, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from alsparse_b200 import capi, spblas, synth
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device: there is no CPU path"
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
+    kind, alpha, beta, op = cfg["kind"], cfg["alpha"], cfg["beta"], cfg["op"]
+    tdt = torch.float32 if kind == "s" else torch.float64
+    columns = cfg.get("columns", 1)
+    iterate = name == "powerlaw" and world > 1   # y becomes the next x through an allgather
+
+    # ---- build this rank's row block ---------------------------------------------------------------
+    lens = global_row_lengths(name, cfg)
+    rows = cols = len(lens)
+    rows_end = np.cumsum(lens, dtype=np.int64)
+    nnz_total = int(rows_end[-1])
+    assert nnz_total < 2 ** 31
+    part = spblas.partition_rows_by_nnz(rows_end.astype(np.int32), world)
+    r0, r1 = int(part[rank]), int(part[rank + 1])
+    m = local_block(name, cfg, lens, r0, r1)
+    spblas.set_algorithm({"auto": capi.ALG_AUTO, "vector": capi.ALG_VECTOR, "merge": capi.ALG_MERGE}[args.alg])
+    stream = torch.cuda.Stream()
+    spblas.set_stream(stream.cuda_stream)
+    st, A = spblas.create_csr(kind, capi.BASE_ZERO, m.nrows, cols, m.rows_start, m.rows_end, m.col, m.val)
+    assert st == capi.SUCCESS, (capi.STATUS_NAMES[st], spblas.last_error())
+    _, info = spblas.mat_info(A)
+
+    x_lo = 0.0 if name == "stencil27" else -1.0
+    x_h = torch.from_numpy(synth.vector(kind, 0, 1, cols * columns, x_lo, 1.0)).pin_memory()
+    y0_h = torch.from_numpy(synth.vector(kind, 0, 2, rows * columns)[r0 * columns:r1 * columns].copy()).pin_memory()
+    y_h = torch.empty_like(y0_h).pin_memory()
+    x_d = x_h.cuda()
+    y_d = y0_h.cuda()
+    xn_d = torch.empty_like(x_d) if iterate else None
+    descr = spblas.descr()
+
+    def step_device(xd, yd):
+        if op == "mv":
+            s = spblas.mv(kind, 0, alpha, A, descr, xd, beta, yd)
+        else:
+            s = spblas.mm(kind, 0, alpha, A, descr, capi.ROW_MAJOR, xd, columns, columns, beta, yd, columns)
+        assert s == capi.SUCCESS, capi.STATUS_NAMES[s]
+
+    gather_sizes = [int(part[i + 1] - part[i]) for i in range(world)]
+
+    def step():
+        nonlocal x_d, xn_d
+        step_device(x_d, y_d)
+        if iterate:
+            outs = list(torch.split(xn_d, gather_sizes))
+            dist.all_gather(outs, y_d)
+            x_d, xn_d = xn_d, x_d
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            step()
+        barrier()
+        launches0 = spblas.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_wall0 = time.time()
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        e1.synchronize()
+        t_wall1 = time.time()
+        barrier()
+        launches = spblas.launch_count() - launches0
+        ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+
+        # ---- duration of the dominant kernel, launch by launch, same stream -----------------------
+        spblas.profile_kernel(A, True)
+        kms = []
+        for _ in range(args.steps):
+            step()
+            kms.append(spblas.kernel_ms(A))
+        spblas.profile_kernel(A, False)
+        barrier()
+        kernel_ms = max_over_ranks(sum(kms) / len(kms))
+
+        # ---- end to end: host vectors through the same entry point ----------------------------------
+        e2e = None
+        if not args.no_e2e and not iterate:
+            xh, y0h, yh = x_h.numpy(), y0_h.numpy(), y_h.numpy()
+
+            def step_host():
+                if beta != 0.0:
+                    yh[:] = y0h  # the call updates y in place; start every step from the same y0
+                if op == "mv":
+                    s = spblas.mv(kind, 0, alpha, A, descr, xh, beta, yh)
+                else:
+                    s = spblas.mm(kind, 0, alpha, A, descr, capi.ROW_MAJOR, xh, columns, columns, beta, yh, columns)
+                assert s == capi.SUCCESS
+            for _ in range(2):
+                step_host()
+            barrier()
+            n_e2e = max(3, min(args.steps, 10))
+            t0 = time.perf_counter()
+            e0.record(stream)
+            for _ in range(n_e2e):
+                step_host()
+            e1.record(stream)
+            e1.synchronize()
+            wall = (time.perf_counter() - t0) / n_e2e * 1e3
+            barrier()
+            ms_e2e = max_over_ranks(max(e0.elapsed_time(e1) / n_e2e, wall))
+            h2d = x_h.numel() * x_h.element_size() + (y0_h.numel() * y0_h.element_size() if beta != 0.0 else 0)
+            d2h = y_h.numel() * y_h.element_size()
+            e2e = (ms_e2e, h2d, d2h)
+    if sampler:
+        sampler.stop()
+
+    nbytes = algorithmic_bytes(cfg, rows, cols, nnz_total)
+    fl = flops(cfg, nnz_total)
+    # per-launch algorithmic bytes of THIS rank's kernel: its rows' share of A, row_ptr, y plus all of x
+    t = TSIZE[kind]
+    launch_bytes = m.nnz * (t + 4) + (m.nrows + 1) * 4 + cols * columns * t + m.nrows * columns * t
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = FALLBACK_HBM_GBS, "fallback"
+    achieved = launch_bytes / (kernel_ms * 1e-3) / 1e9
+
+    if rank == 0:
+        line = {
+            "metric": "csr_spmv_effective_gbs" if op == "mv" else "csr_spmm_effective_gbs",
+            "value": nbytes / (ms_step * 1e-3) / 1e9, "unit": "GB/s", "gflops": fl / (ms_step * 1e-3) / 1e9,
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32" if kind == "s" else "f64", "data": "synthetic",
+            "config": {"workload": name + (" (REDUCED SIZE: development run)" if reduced else ""), "rows": rows,
+                       "cols": cols, "nnz": nnz_total, "alpha": alpha, "beta": beta, "columns": columns,
+                       "partition": f"nnz-balanced contiguous row blocks over {world} GPU(s), x replicated",
+                       "collective": "allgather of y into the next x each step" if iterate else "none",
+                       "algorithm": ["auto", "vector", "merge"][info.algorithm], "lanes_per_row": info.lanes_per_row,
+                       "l2": f"inputs ({nbytes / 1e6:.0f} MB per step) exceed the 126 MB L2; no flush between steps",
+                       "algorithmic_bytes_per_step": nbytes},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": NCU_TRAFFIC.get(name) if not reduced and world == 1 else None,
+                         "peak_source": peak_src, "kernel_ms": kernel_ms, "bytes_per_launch": launch_bytes},
+            "clocks": sampler.summary(t_wall0, t_wall1) if sampler else None,
+        }
+        if e2e:
+            line["e2e"] = {"value": nbytes / (e2e[0] * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e[0],
+                           "h2d_bytes_per_step": int(e2e[1]), "d2h_bytes_per_step": int(e2e[2])}
+        else:
+            line["e2e"] = None
+        if world == 1 and not args.no_cpu_baseline:
+            gbs, gfl, ms, desc = cpu_reference_run(name, cfg, 3, 1)
+            line["cpu_baseline"] = dict(value=gbs, unit="GB/s", gflops=gfl, ms_per_step=ms, **desc)
+        print(json.dumps(line), flush=True)
+
+    spblas.destroy(A)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -54,6 +54,13 @@ alphasparse_status_t alphasparse_cuda_get_device_csr(const alphasparse_matrix_t 
                                                      ALPHA_INT **d_row_ptr,
                                                      ALPHA_INT **d_col_indx, void **d_values);
 
+/* Kernel timing for benchmarks.  With profiling enabled on a handle, every mv / mm call on it
+ * brackets its dominant kernel (the SpMV or SpMM kernel itself, not the small fix-up or any
+ * copies) with CUDA events on the library stream; alphasparse_cuda_kernel_ms waits for the
+ * last such kernel and returns its duration in milliseconds. */
+alphasparse_status_t alphasparse_cuda_profile_kernel(const alphasparse_matrix_t A, int enable);
+alphasparse_status_t alphasparse_cuda_kernel_ms(const alphasparse_matrix_t A, float *ms);
+
 /* Number of kernels this library has launched in this process so far. */
 int64_t alphasparse_cuda_launch_count(void);
 

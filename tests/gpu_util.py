@@ -1,0 +1,59 @@
+"""Helpers for the GPU parity tests: every call goes through the C ABI (alsparse_b200.spblas)."""
+import ctypes as C
+
+import numpy as np
+import torch
+
+import oracle
+from alsparse_b200 import capi, spblas
+from helpers import NP, assert_rows_close, mm_scale, row_scale
+
+TORCH = {"s": torch.float32, "d": torch.float64}
+
+
+def make_handle(kind, m, base=0):
+    st, A = spblas.create_csr(kind, base, m.nrows, m.cols, m.rows_start + base, m.rows_end + base, m.col + base, m.val)
+    assert st == capi.SUCCESS, (capi.STATUS_NAMES[st], spblas.last_error())
+    return A
+
+
+def download(addr, n, dtype):
+    """n elements of `dtype` from device address `addr` (via a cudaMemcpy issued by torch)."""
+    out = torch.empty(n, dtype=dtype)
+    if n:
+        nbytes = n * out.element_size()
+        cudart = torch.cuda.cudart()
+        err = cudart.cudaMemcpy(out.data_ptr(), addr, nbytes, 2)  # cudaMemcpyDeviceToHost
+        assert int(err) == 0
+    return out.numpy()
+
+
+def check_mv(kind, m, alpha, beta, seed=1, pointers="host", alg=None, A=None):
+    """One mv through the C ABI against the oracle's plain kernel on the same inputs."""
+    from alsparse_b200 import synth
+    x = synth.vector(kind, seed, 1, m.cols)
+    y0 = synth.vector(kind, seed, 2, m.nrows)
+    own = A is None
+    if alg is not None:
+        spblas.set_algorithm(alg)
+    try:
+        if own:
+            A = make_handle(kind, m)
+    finally:
+        if alg is not None:
+            spblas.set_algorithm(capi.ALG_AUTO)
+    y_ref = oracle.gemv(kind, m.rows_start, m.rows_end, m.col, m.val, alpha, x, beta, y0.copy())
+    if pointers == "host":
+        y = y0.copy()
+        st = spblas.mv(kind, capi.NON_TRANSPOSE, alpha, A, spblas.descr(), x, beta, y)
+    else:
+        dx, dy = torch.from_numpy(x).cuda(), torch.from_numpy(y0).cuda()
+        st = spblas.mv(kind, capi.NON_TRANSPOSE, alpha, A, spblas.descr(), dx, beta, dy)
+        torch.cuda.synchronize()
+        y = dy.cpu().numpy()
+    assert st == capi.SUCCESS, (capi.STATUS_NAMES[st], spblas.last_error())
+    assert_rows_close(kind, y, y_ref, row_scale(m.ptr, m.col, m.val, x, alpha, beta, y0),
+                      f"mv {kind} rows={m.nrows} nnz={m.nnz} alg={alg} ptr={pointers}")
+    if own:
+        spblas.destroy(A)
+    return y

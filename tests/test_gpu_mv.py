@@ -1,0 +1,238 @@
+"""Parity of alphasparse_{s,d}_mv on the GPU with the reference's plain kernel (through the oracle),
+against the committed golden vectors and on fresh seeded inputs, including the edge cases."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from alsparse_b200 import capi, spblas, synth
+from gpu_util import TORCH, check_mv, download, make_handle
+from helpers import NP, assert_rows_close, golden, row_scale
+
+pytestmark = pytest.mark.gpu
+ALGS = [capi.ALG_VECTOR, capi.ALG_MERGE]
+
+
+def _csr(g):
+    return synth.Csr(int(g["rows"]), int(g["cols"]), 0, g["ptr"], g["col"], g["val"])
+
+
+def test_kat_3x3_and_index_base():
+    g = golden("kat3x3.npz")
+    for base in (0, 1):
+        st, A = spblas.create_csr("s", base, 3, 3, g["rs"] + base, g["re"] + base, g["col"] + base, g["val"])
+        assert st == capi.SUCCESS
+        y = np.ones(3, np.float32)
+        assert spblas.mv("s", 0, 2.0, A, spblas.descr(), g["x"], 3.0, y) == capi.SUCCESS
+        assert y.tolist() == [405.0, 63.0, 11.0]
+        st, b, rows, cols, rs, re_, col, val = spblas.export_csr("s", A)
+        assert (st, b, rows, cols) == (0, 0, 3, 3)
+        assert rs.tolist() == [0, 2, 3] and re_.tolist() == [2, 3, 4] and col.tolist() == [0, 2, 1, 0]
+        Y = np.zeros(6, np.float32)
+        assert spblas.mm("s", 0, 1.0, A, spblas.descr(), capi.ROW_MAJOR, g["B"], 2, 2, 0.0, Y, 2) == capi.SUCCESS
+        assert Y.tolist() == g["mm_row"].tolist()
+        spblas.destroy(A)
+
+
+@pytest.mark.parametrize("alg", [None] + ALGS)
+@pytest.mark.parametrize("name,kind", [("cfg1_s.npz", "s"), ("zipf_d.npz", "d"), ("stencil8_d.npz", "d")])
+def test_golden_vectors(name, kind, alg):
+    """Known answers produced by the reference's own objects."""
+    g = golden(name)
+    m = _csr(g)
+    if alg is not None:
+        spblas.set_algorithm(alg)
+    A = make_handle(kind, m)
+    spblas.set_algorithm(capi.ALG_AUTO)
+    cases = [(float(g["alpha"]), float(g["beta"]), g["y"])]
+    if name == "cfg1_s.npz":
+        cases.append((1.5, 0.5, g["y_ab"]))
+    for alpha, beta, y_ref in cases:
+        for dev in (False, True):
+            if dev:
+                dx, dy = torch.from_numpy(g["x"]).cuda(), torch.from_numpy(g["y0"]).cuda()
+                assert spblas.mv(kind, 0, alpha, A, spblas.descr(), dx, beta, dy) == capi.SUCCESS
+                y = dy.cpu().numpy()
+            else:
+                y = g["y0"].copy()
+                assert spblas.mv(kind, 0, alpha, A, spblas.descr(), g["x"], beta, y) == capi.SUCCESS
+            assert_rows_close(kind, y, y_ref, row_scale(m.ptr, m.col, m.val, g["x"], alpha, beta, g["y0"]), name)
+    spblas.destroy(A)
+
+
+def test_device_copy_and_coo_conversion_are_bit_exact():
+    """Index handling: device CSR == oracle create_csr; COO->CSR == the reference's conversion."""
+    g = golden("cfg1_s.npz")
+    st, coo = spblas.create_coo("s", capi.BASE_ONE, 1000, 1000, len(g["coo_ri"]), g["coo_ri"] + 1, g["coo_ci"] + 1,
+                                g["coo_v"])
+    assert st == capi.SUCCESS
+    st, A = spblas.convert_csr(coo, capi.NON_TRANSPOSE)
+    assert st == capi.SUCCESS, spblas.last_error()
+    st, base, rows, cols, rs, re_, col, val = spblas.export_csr("s", A)
+    assert (st, base, rows, cols) == (0, 0, 1000, 1000)
+    ptr = np.concatenate([rs[:1], re_])
+    assert np.array_equal(ptr, g["csr_ptr"]) and np.array_equal(col, g["csr_col"])
+    assert np.array_equal(val.view(np.uint32), g["csr_val"].view(np.uint32))
+    st, d_ptr, d_col, d_val = spblas.device_csr(A)
+    assert st == capi.SUCCESS
+    assert np.array_equal(download(d_ptr, 1001, torch.int32), g["csr_ptr"])
+    assert np.array_equal(download(d_col, 5000, torch.int32), g["csr_col"])
+    assert np.array_equal(download(d_val, 5000, torch.float32).view(np.uint32), g["csr_val"].view(np.uint32))
+    y = np.zeros(1000, np.float32)
+    assert spblas.mv("s", 0, 1.0, A, spblas.descr(), g["x"], 0.0, y) == capi.SUCCESS
+    assert_rows_close("s", y, g["y"], row_scale(g["ptr"], g["col"], g["val"], g["x"], 1.0, 0.0, g["y0"]), "coo path")
+    # transposed conversion: A^T built from the COO, checked against the oracle on swapped indices
+    st, At = spblas.convert_csr(coo, capi.TRANSPOSE)
+    assert st == capi.SUCCESS
+    _, _, _, _, trs, tre, tcol, tval = spblas.export_csr("s", At)
+    op, oc, ov = oracle.coo_to_csr("s", 0, 1000, g["coo_ci"], g["coo_ri"], g["coo_v"])
+    assert np.array_equal(np.concatenate([trs[:1], tre]), op) and np.array_equal(tcol, oc) and np.array_equal(tval, ov)
+    for h in (coo, A, At):
+        spblas.destroy(h)
+    # one-based create_csr against the oracle's create_csr
+    m = synth.poisson("d", 2, 700, 900, 7.0)
+    op, oc, ov = oracle.create_csr("d", 1, m.rows_start + 1, m.rows_end + 1, m.col + 1, m.val)
+    A = make_handle("d", m, base=1)
+    _, d_ptr, d_col, d_val = spblas.device_csr(A)
+    assert np.array_equal(download(d_ptr, 701, torch.int32), op)
+    assert np.array_equal(download(d_col, m.nnz, torch.int32), oc)
+    assert np.array_equal(download(d_val, m.nnz, torch.float64), ov)
+    spblas.destroy(A)
+
+
+@pytest.mark.parametrize("kind", ["s", "d"])
+@pytest.mark.parametrize("alg", ALGS)
+@pytest.mark.parametrize("pointers", ["host", "device"])
+def test_shapes_and_scalars(kind, alg, pointers):
+    """Row-length regimes of the benchmark configurations at sizes the oracle finishes instantly."""
+    mats = [synth.uniform_fixed(kind, 1, 20000, 20000, 16), synth.poisson(kind, 2, 9000, 7000, 32.0),
+            synth.stencil27(kind, 14), synth.uniform_fixed(kind, 3, 5000, 300, 1),
+            synth.uniform_fixed(kind, 4, 777, 50, 3)]
+    hi = 200000 if kind == "d" else 1500  # single precision: keep the oracle's own rounding inside tolerance
+    mats.append(synth.zipf(kind, 5, 30000, 250000, 1.8, 1, hi))
+    for m in mats:
+        for alpha, beta in ((1.0, 0.0), (1.5, 0.5), (-2.0, 1.0), (0.0, 3.0)):
+            check_mv(kind, m, alpha, beta, pointers=pointers, alg=alg)
+
+
+@pytest.mark.parametrize("alg", ALGS)
+def test_edge_cases(alg):
+    kind = "d"
+    # empty rows at the front, in runs, at the back; a single row; a single element
+    lens = np.zeros(3000, np.int32)
+    lens[100:200] = 5
+    lens[1500] = 2500
+    lens[2000:2500:3] = 1
+    check_mv(kind, synth.from_lengths(kind, 1, lens, 4000), 2.0, 0.5, alg=alg)
+    check_mv(kind, synth.from_lengths(kind, 2, np.array([7]), 9), 1.0, 0.0, alg=alg)
+    check_mv(kind, synth.from_lengths(kind, 3, np.array([1]), 1), 3.0, 2.0, alg=alg)
+    check_mv(kind, synth.from_lengths(kind, 4, np.array([0, 0, 1, 0]), 5), 3.0, 2.0, alg=alg)
+    # one row of 200000 elements (the clip of the power-law configuration) between short rows
+    lens = np.ones(2001, np.int32)
+    lens[1000] = 200000
+    check_mv(kind, synth.from_lengths(kind, 5, lens, 300000), 1.0, 0.0, alg=alg)
+    # a dense row (every column) and more rows than columns
+    lens = np.full(64, 64, np.int32)
+    check_mv(kind, synth.from_lengths(kind, 6, lens, 64), -1.0, 1.0, alg=alg)
+    # beta == 0 must not read y: NaNs in y0 do not propagate (the oracle computes y*0 = NaN, so compare to a clean run)
+    m = synth.poisson(kind, 7, 500, 500, 6.0)
+    x = synth.vector(kind, 7, 1, 500)
+    spblas.set_algorithm(alg)
+    A = make_handle(kind, m)
+    spblas.set_algorithm(capi.ALG_AUTO)
+    y = np.full(500, np.nan)
+    assert spblas.mv(kind, 0, 1.0, A, spblas.descr(), x, 0.0, y) == capi.SUCCESS
+    y_ref = oracle.gemv(kind, m.rows_start, m.rows_end, m.col, m.val, 1.0, x, 0.0, np.zeros(500))
+    assert_rows_close(kind, y, y_ref, row_scale(m.ptr, m.col, m.val, x, 1.0, 0.0, np.zeros(500)), "beta=0")
+    spblas.destroy(A)
+
+
+def test_no_stored_elements_and_no_rows():
+    # nnz == 0: the CPU kernels still scale y by beta
+    ptr = np.zeros(6, np.int32)
+    st, A = spblas.create_csr("s", 0, 5, 4, ptr[:-1], ptr[1:], np.zeros(0, np.int32), np.zeros(0, np.float32))
+    assert st == capi.SUCCESS
+    y = np.arange(5, dtype=np.float32)
+    assert spblas.mv("s", 0, 1.0, A, spblas.descr(), np.ones(4, np.float32), 2.0, y) == capi.SUCCESS
+    assert y.tolist() == [0, 2, 4, 6, 8]
+    spblas.destroy(A)
+    # rows == 0: success, nothing touched (the reference would read rows_end[-1])
+    st, A = spblas.create_csr("d", 0, 0, 4, None, None, None, None)
+    assert st == capi.SUCCESS
+    y = np.ones(1)
+    assert spblas.mv("d", 0, 1.0, A, spblas.descr(), np.ones(4), 2.0, y) == capi.SUCCESS and y[0] == 1.0
+    spblas.destroy(A)
+
+
+def test_unsorted_columns_and_duplicates():
+    """create_csr does not sort or merge: duplicates are summed by the product, as on the CPU."""
+    rng = np.random.default_rng(3)
+    rows, cols = 400, 60
+    lens = rng.integers(0, 40, rows).astype(np.int32)
+    ptr = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    col = rng.integers(0, cols, ptr[-1]).astype(np.int32)  # unsorted, with repeats
+    val = rng.uniform(-1, 1, ptr[-1])
+    m = synth.Csr(rows, cols, 0, ptr, col, val)
+    for alg in ALGS:
+        check_mv("d", m, 1.25, -0.5, alg=alg)
+
+
+def test_status_codes_on_live_handles():
+    m = synth.poisson("s", 8, 30, 40, 4.0)
+    A = make_handle("s", m)
+    x, y = np.zeros(40, np.float32), np.zeros(30, np.float32)
+    g = spblas.descr()
+    assert spblas.mv("s", 0, 1.0, A, g, None, 0.0, y) == capi.NOT_INITIALIZED
+    assert spblas.mv("s", 0, 1.0, A, g, x, 0.0, None) == capi.NOT_INITIALIZED
+    assert spblas.mv("d", 0, 1.0, A, g, x, 0.0, y) == capi.INVALID_VALUE
+    assert spblas.mv("s", capi.CONJUGATE_TRANSPOSE, 1.0, A, g, x, 0.0, y) == capi.INVALID_VALUE
+    assert spblas.mv("s", 0, 1.0, A, spblas.descr(capi.SYMMETRIC), x, 0.0, y) == capi.INVALID_VALUE  # 30 x 40
+    assert spblas.mv("s", 0, 1.0, A, spblas.descr(7), x, 0.0, y) == capi.INVALID_VALUE
+    assert spblas.mv("s", 0, 1.0, A, spblas.descr(capi.DIAGONAL), x, 0.0, y) == capi.NOT_SUPPORTED
+    # the same precedence the oracle's restatement of the reference's checks gives
+    assert oracle.mv_status(has_x=0) == capi.NOT_INITIALIZED
+    assert oracle.mv_status(handle_datatype=0, call_datatype=1) == capi.INVALID_VALUE
+    assert oracle.mv_status(descr_type=1, rows=30, cols=40) == capi.INVALID_VALUE
+    st, info = spblas.mat_info(A)
+    assert st == capi.SUCCESS and (info.rows, info.cols, info.nnz) == (30, 40, m.nnz)
+    assert info.max_row_nnz == int(np.diff(m.ptr).max()) and info.empty_rows == int((np.diff(m.ptr) == 0).sum())
+    spblas.destroy(A)
+    # out-of-range column index: refused at creation instead of faulting later
+    bad = m.col.copy()
+    bad[3] = 40
+    st, B = spblas.create_csr("s", 0, 30, 40, m.rows_start, m.rows_end, bad, m.val)
+    assert st == capi.INVALID_VALUE and not B.value
+
+
+def test_analysis_picks_by_row_shape():
+    A = make_handle("s", synth.uniform_fixed("s", 1, 4096, 4096, 16))
+    _, info = spblas.mat_info(A)
+    assert info.algorithm == capi.ALG_VECTOR and info.lanes_per_row == 4
+    spblas.destroy(A)
+    A = make_handle("d", synth.zipf("d", 1, 20000, 300000, 1.8, 1, 200000))
+    _, info = spblas.mat_info(A)
+    assert info.algorithm == capi.ALG_MERGE and info.merge_tiles > 0
+    spblas.destroy(A)
+
+
+def test_linearity_and_repeatability():
+    """Size-independent properties: A(ax1 + bx2) = aAx1 + bAx2 within tolerance; identical bits run to run."""
+    kind = "d"
+    m = synth.zipf(kind, 9, 100000, 100000, 1.8, 1, 50000)
+    A = make_handle(kind, m)
+    x1, x2 = (torch.from_numpy(synth.vector(kind, 9, s, m.cols)).cuda() for s in (1, 2))
+    ys = []
+    for x in (x1, x2, 2.0 * x1 - 3.0 * x2, x1):
+        y = torch.zeros(m.nrows, dtype=torch.float64, device="cuda")
+        assert spblas.mv(kind, 0, 1.0, A, spblas.descr(), x, 0.0, y) == capi.SUCCESS
+        ys.append(y)
+    torch.cuda.synchronize()
+    assert torch.equal(ys[0], ys[3])
+    xs = np.abs(synth.vector(kind, 9, 1, m.cols)) * 2 + np.abs(synth.vector(kind, 9, 2, m.cols)) * 3
+    scale = np.bincount(np.repeat(np.arange(m.nrows), np.diff(m.ptr)), weights=np.abs(m.val) * xs[m.col],
+                        minlength=m.nrows)
+    err = (ys[2] - (2.0 * ys[0] - 3.0 * ys[1])).abs().cpu().numpy()
+    assert (err <= 4e-12 * scale + 1e-300).all()
+    spblas.destroy(A)

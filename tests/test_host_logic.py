@@ -1,0 +1,89 @@
+"""Host-side pieces of the library that need no GPU: the row partition, COO handles, generators."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from alsparse_b200 import capi, spblas, synth
+from helpers import golden
+
+
+def test_partition_matches_reference_rule():
+    g = golden("partition.npz")
+    for name in ("tiny", "cfg1", "zipf", "one_row", "flat"):
+        for p in (1, 2, 3, 4, 8):
+            assert np.array_equal(spblas.partition_rows_by_nnz(g[f"{name}_acc"], p), g[f"{name}_p{p}"]), (name, p)
+    rng = np.random.default_rng(1)
+    for _ in range(50):
+        rows = int(rng.integers(1, 400))
+        acc = np.cumsum(rng.integers(0, 40, rows)).astype(np.int32)
+        for p in (2, 4, 8, 16):
+            assert np.array_equal(spblas.partition_rows_by_nnz(acc, p), oracle.partition_rows_by_nnz(acc, p))
+
+
+def test_lower_bound():
+    lib = capi.load()
+    t = np.array([1, 3, 3, 7, 9], np.int32)
+    for v in range(0, 11):
+        assert lib.lower_bound_int(t.ctypes.data, 0, 5, v) == int(np.searchsorted(t, v, "left"))
+
+
+def test_coo_handle_lives_on_the_host():
+    ri, ci = np.array([1, 3, 2], np.int32), np.array([2, 1, 3], np.int32)
+    v = np.array([1.5, 2.5, 3.5])
+    st, A = spblas.create_coo("d", capi.BASE_ONE, 3, 3, 3, ri, ci, v)
+    assert st == capi.SUCCESS and A.value
+    h = C.cast(A, C.POINTER(capi.Matrix)).contents
+    assert h.format == capi.FORMAT_COO and h.datatype == capi.DOUBLE and h.dcu_info is None
+    # not a CSR handle: mv refuses without touching a device
+    assert spblas.mv("d", 0, 1.0, A, spblas.descr(), v, 0.0, v) == capi.NOT_SUPPORTED
+    st, _ = spblas.convert_csr(A, capi.CONJUGATE_TRANSPOSE)
+    assert st == capi.NOT_SUPPORTED
+    assert spblas.destroy(A) == capi.SUCCESS
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-device behaviour")
+def test_no_device_means_failure_not_fallback():
+    m = synth.uniform_fixed("s", 0, 64, 64, 4)
+    st, A = spblas.create_csr("s", 0, 64, 64, m.rows_start, m.rows_end, m.col, m.val)
+    assert st != capi.SUCCESS and not A.value
+    assert spblas.last_error() != ""
+
+
+def test_generators_are_deterministic_and_sliceable():
+    for make in (lambda **k: synth.uniform_fixed("s", 7, 5000, 4000, 16, **k),
+                 lambda **k: synth.poisson("d", 7, 5000, 4000, 9.0, **k),
+                 lambda **k: synth.zipf("d", 7, 5000, 4000, 1.8, 1, 3000, **k),
+                 lambda **k: synth.stencil27("d", 12, **k)):
+        whole, again = make(), make()
+        assert np.array_equal(whole.ptr, again.ptr) and np.array_equal(whole.col, again.col)
+        assert np.array_equal(whole.val, again.val)
+        rows = whole.nrows
+        a, b = rows // 3, rows - rows // 3
+        part = make(row0=a, nrows=b - a)
+        lo, hi = whole.ptr[a], whole.ptr[b]
+        assert np.array_equal(part.ptr, whole.ptr[a:b + 1] - lo)
+        assert np.array_equal(part.col, whole.col[lo:hi]) and np.array_equal(part.val, whole.val[lo:hi])
+        # columns ascending and distinct within every row, inside the matrix
+        d = np.diff(whole.col)
+        starts = whole.ptr[1:-1]
+        inner = np.ones(len(d), bool)
+        inner[starts[(starts > 0) & (starts < whole.nnz)] - 1] = False
+        assert (d[inner] > 0).all() and whole.col.min() >= 0 and whole.col.max() < whole.cols
+
+
+def test_generator_shapes():
+    m = synth.poisson("s", 0, 1000, 1000, 5.0, total=5000)
+    assert m.nnz == 5000 and m.nrows == 1000
+    s = synth.stencil27("d", 10)
+    assert s.nnz == (3 * 10 - 2) ** 3 and np.diff(s.ptr).max() == 27
+    assert set(np.unique(s.val)) == {-1.0, 26.0}
+    lens = synth.rowlen_zipf(0, 200000, 1.8, 1, 200000)
+    assert 0.50 < (lens == 1).mean() < 0.56 and lens.max() > 10000
+    lens = synth.rowlen_poisson(0, 200000, 32.0, 1 << 20)
+    assert abs(lens.mean() - 32.0) < 0.1 and abs(lens.var() - 32.0) < 0.5
+    x = synth.vector("d", 0, 1, 100000, 0.0, 1.0)
+    assert 0.0 <= x.min() and x.max() < 1.0 and abs(x.mean() - 0.5) < 0.01
+    assert np.array_equal(synth.vector("d", 0, 1, 100, 0.0, 1.0, first=50), x[50:150])

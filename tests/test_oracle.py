@@ -1,0 +1,127 @@
+"""Pins the C restatement (oracle/oracle.c) to the reference: against the golden vectors the
+reference's own objects produced, and live against those objects where they are present."""
+import numpy as np
+import pytest
+
+import oracle
+from alsparse_b200 import synth
+from helpers import NP, assert_rows_close, golden, mm_scale, row_scale
+
+# The reference is built with -Ofast (reassociation, FMA contraction); the restatement sums strictly
+# left to right.  Both are one summation order of the same products, so they agree to a few
+# roundings of the row scale -- far inside the parity tolerance, which is what is asserted.
+
+
+def test_kat_3x3():
+    g = golden("kat3x3.npz")
+    y = oracle.gemv("s", g["rs"], g["re"], g["col"], g["val"], 2.0, g["x"], 3.0, np.ones(3, np.float32))
+    assert y.tolist() == [405.0, 63.0, 11.0] == g["y_a2_b3"].tolist() == g["y_base1"].tolist()
+    ptr, col, val = oracle.create_csr("s", 1, g["rs"] + 1, g["re"] + 1, g["col"] + 1, g["val"])
+    assert ptr.tolist() == g["base1_ptr"].tolist() and col.tolist() == g["base1_col"].tolist()
+    Y = oracle.gemm("s", "row", g["rs"], g["re"], g["col"], g["val"], 1.0, g["B"], 2, 2, 0.0, np.zeros(6, np.float32), 2)
+    assert Y.tolist() == g["mm_row"].tolist() == [11, 14, 9, 12, 4, 8]
+    Y = oracle.gemm("s", "col", g["rs"], g["re"], g["col"], g["val"], 1.0, g["B"], 2, 3, 0.0, np.zeros(6, np.float32), 3)
+    assert Y.tolist() == g["mm_col"].tolist()
+
+
+@pytest.mark.parametrize("name,kind", [("cfg1_s.npz", "s"), ("zipf_d.npz", "d"), ("stencil8_d.npz", "d")])
+def test_gemv_golden(name, kind):
+    g = golden(name)
+    ptr, alpha, beta = g["ptr"], float(g["alpha"]), float(g["beta"])
+    scale = row_scale(ptr, g["col"], g["val"], g["x"], alpha, beta, g["y0"])
+    y = oracle.gemv(kind, ptr[:-1], ptr[1:], g["col"], g["val"], alpha, g["x"], beta, g["y0"].copy())
+    assert_rows_close(kind, y, g["y"], scale, name)
+    yo = oracle.gemv(kind, ptr[:-1], ptr[1:], g["col"], g["val"], alpha, g["x"], beta, g["y0"].copy(), threads=3)
+    assert_rows_close(kind, yo, g["y"], scale, name + " (OpenMP form)")
+    if name == "cfg1_s.npz":
+        y = oracle.gemv(kind, ptr[:-1], ptr[1:], g["col"], g["val"], 1.5, g["x"], 0.5, g["y0"].copy())
+        assert_rows_close(kind, y, g["y_ab"], row_scale(ptr, g["col"], g["val"], g["x"], 1.5, 0.5, g["y0"]), "a,b")
+
+
+def test_gemv_trans_golden():
+    g = golden("trans_d.npz")
+    ptr = g["ptr"]
+    y = oracle.gemv_trans("d", int(g["cols"]), ptr[:-1], ptr[1:], g["col"], g["val"], float(g["alpha"]), g["x"],
+                          float(g["beta"]), g["y0"].copy())
+    prod = np.abs(g["val"] * np.repeat(g["x"], np.diff(ptr)))
+    scale = np.abs(g["beta"] * g["y0"]) + abs(g["alpha"]) * np.bincount(g["col"], weights=prod, minlength=len(y))
+    assert_rows_close("d", y, g["y"], scale, "transpose")
+
+
+@pytest.mark.parametrize("kind", ["s", "d"])
+@pytest.mark.parametrize("case", ["w64", "w5"])
+def test_gemm_golden(kind, case):
+    g = golden(f"mm_{kind}.npz")
+    ptr = g["ptr"]
+    columns, ldx, ldy, ldxc, ldyc = (int(v) for v in g[f"{case}_par"][:5])
+    alpha, beta = float(g[f"{case}_par"][5]), float(g[f"{case}_par"][6])
+    Y = oracle.gemm(kind, "row", ptr[:-1], ptr[1:], g["col"], g["val"], alpha, g[f"{case}_X"], columns, ldx, beta,
+                    g[f"{case}_Y0"].copy(), ldy)
+    rows = len(ptr) - 1
+    scale = mm_scale(ptr, g["col"], g["val"], g[f"{case}_X"], columns, ldx, alpha, beta, g[f"{case}_Y0"], ldy)
+    got = Y.reshape(rows, ldy)[:, :columns].reshape(-1)
+    ref = g[f"{case}_row"].reshape(rows, ldy)[:, :columns].reshape(-1)
+    assert_rows_close(kind, got, ref, scale.reshape(-1), f"mm row {case}")
+    # padding between rows is never written
+    assert np.array_equal(Y.reshape(rows, ldy)[:, columns:], g[f"{case}_Y0"].reshape(rows, ldy)[:, columns:])
+    Yc = oracle.gemm(kind, "col", ptr[:-1], ptr[1:], g["col"], g["val"], alpha, g[f"{case}_Xc"], columns, ldxc, beta,
+                     g[f"{case}_Yc0"].copy(), ldyc)
+    # same operation in the other layout: compare with the tolerance of the transposed scale
+    Xc = g[f"{case}_Xc"].reshape(columns, ldxc)[:, : int(g["cols"])].T.copy()
+    Yc0 = g[f"{case}_Yc0"].reshape(columns, ldyc)[:, :rows].T.copy()
+    sc = mm_scale(ptr, g["col"], g["val"], Xc.reshape(-1), columns, columns, alpha, beta, Yc0.reshape(-1), columns)
+    assert_rows_close(kind, Yc.reshape(columns, ldyc)[:, :rows].T.reshape(-1),
+                      g[f"{case}_col"].reshape(columns, ldyc)[:, :rows].T.reshape(-1), sc.reshape(-1), f"mm col {case}")
+
+
+def test_coo_to_csr_golden():
+    g = golden("cfg1_s.npz")
+    ptr, col, val = oracle.coo_to_csr("s", 1, 1000, g["coo_ri"] + 1, g["coo_ci"] + 1, g["coo_v"])
+    assert np.array_equal(ptr, g["csr_ptr"]) and np.array_equal(col, g["csr_col"])
+    assert np.array_equal(val.view(np.uint32), g["csr_val"].view(np.uint32))
+    # and it is the matrix the COO was cut from
+    assert np.array_equal(ptr, g["ptr"]) and np.array_equal(col, g["col"]) and np.array_equal(val, g["val"])
+
+
+def test_partition_golden():
+    g = golden("partition.npz")
+    for name in ("tiny", "cfg1", "zipf", "one_row", "flat"):
+        for p in (1, 2, 3, 4, 8):
+            assert np.array_equal(oracle.partition_rows_by_nnz(g[f"{name}_acc"], p), g[f"{name}_p{p}"]), (name, p)
+    assert g["tiny_p2"].tolist() == [0, 0, 3]  # the crossing row goes to the next part; parts may be empty
+
+
+def test_mv_status_order():
+    S = oracle.mv_status
+    assert S(has_handle=0) == 1 and S(has_mat=0) == 1 and S(has_x=0) == 1 and S(has_y=0) == 1
+    assert S(has_x=0, handle_datatype=1) == 1          # NULL checks come before the datatype check
+    assert S(handle_datatype=1, call_datatype=0) == 3
+    assert S(operation=2) == 3
+    assert S(descr_type=1, rows=3, cols=4) == 3 and S(descr_type=1, rows=3, cols=3) == -1
+    assert S(descr_type=0) == 0 and S(descr_type=6) == 3 and S(fmt=9) == 3 and S(fmt=0) == -1
+
+
+@pytest.mark.skipif(not oracle.ref_available(), reason="reference objects not built on this machine")
+@pytest.mark.parametrize("kind", ["s", "d"])
+def test_live_against_reference_objects(kind):
+    """Fresh seeded inputs through both the restatement and the reference's compiled sources."""
+    lens = synth.rowlen_zipf(11, 4000, 1.8, 1, 900)
+    lens[5::11] = 0
+    m = synth.from_lengths(kind, 11, lens, 3000)
+    x, y0 = synth.vector(kind, 11, 1, 3000), synth.vector(kind, 11, 2, 4000)
+    A = oracle.RefCsr.from_csr(kind, 0, 4000, 3000, m.rows_start, m.rows_end, m.col, m.val)
+    p, c, v = A.export()
+    op, oc, ov = oracle.create_csr(kind, 0, m.rows_start, m.rows_end, m.col, m.val)
+    assert np.array_equal(p, op) and np.array_equal(c, oc) and np.array_equal(v, ov)
+    scale = row_scale(m.ptr, m.col, m.val, x, 0.7, -1.3, y0)
+    y_ref = A.gemv(0.7, x, -1.3, y0.copy())
+    assert_rows_close(kind, oracle.gemv(kind, m.rows_start, m.rows_end, m.col, m.val, 0.7, x, -1.3, y0.copy()), y_ref,
+                      scale, "plain")
+    assert_rows_close(kind, A.gemv(0.7, x, -1.3, y0.copy(), omp_threads=4), y_ref, scale, "reference OpenMP kernel")
+    for parts in (2, 4, 8):
+        assert np.array_equal(oracle.partition_rows_by_nnz(m.rows_end, parts),
+                              oracle.ref_partition_rows_by_nnz(m.rows_end, parts))
+    X, Y0 = synth.vector(kind, 11, 3, 3000 * 8), synth.vector(kind, 11, 4, 4000 * 8)
+    Yr = A.gemm("row", 1.25, X, 8, 8, 0.5, Y0.copy(), 8)
+    Yo = oracle.gemm(kind, "row", m.rows_start, m.rows_end, m.col, m.val, 1.25, X, 8, 8, 0.5, Y0.copy(), 8)
+    assert_rows_close(kind, Yo, Yr, mm_scale(m.ptr, m.col, m.val, X, 8, 8, 1.25, 0.5, Y0, 8).reshape(-1), "mm")
