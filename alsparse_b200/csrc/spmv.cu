@@ -67,8 +67,17 @@ __device__ __forceinline__ T quad_dot(const int4 c, const Quad<T> &v, int base, 
 // that every load instruction of a warp covers consecutive rows (consecutive memory).  The
 // first quad of all RPG rows is requested before any of them is consumed, which keeps two
 // independent chains (offset -> col/val -> x) in flight per thread.
+// Measured on B200: with few lanes per row (random gathers, bound by the L2 request rate) two
+// rows per group at 6 resident blocks per SM is fastest; with 8 or more lanes per row one row
+// per group at full occupancy is.
+template <int LANES>
+struct VectorShape {
+    static constexpr int RPG = LANES <= 4 ? 2 : 1;
+    static constexpr int MIN_BLOCKS = LANES <= 4 ? 6 : 8;
+};
+
 template <typename T, int LANES, int RPG, bool HAS_BETA>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, VectorShape<LANES>::MIN_BLOCKS)
     spmv_vector_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
                        const T *__restrict__ val, const T *__restrict__ x, T *__restrict__ y,
                        T alpha, T beta) {
@@ -129,6 +138,11 @@ __global__ void __launch_bounds__(256)
 
 // One thread block = one tile of NT*IPT merge items.  The tile's start and end coordinates
 // (row, element) were computed once at analysis time.
+//
+// Two paths.  A tile that lies inside a single long row (no row ends in it: about two thirds
+// of the tiles of a power-law matrix) is a plain dot product: strided loads, register sums,
+// one block reduction, nothing staged.  Any other tile stages its products in shared memory
+// in load order and lets every thread walk its IPT consecutive merge items.
 template <typename T, int NT, int IPT, bool HAS_BETA>
 __global__ void __launch_bounds__(NT)
     spmv_merge_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
@@ -145,35 +159,56 @@ __global__ void __launch_bounds__(NT)
     __shared__ T s_wval[NW];
 
     const int tid = threadIdx.x;
+    const int lane = tid & 31, wid = tid >> 5;
     const MergeCoord c0 = tile[blockIdx.x], c1 = tile[blockIdx.x + 1];
     const int r0 = c0.row, j0 = c0.nz;
     const int tile_rows = c1.row - r0, tile_nnz = c1.nz - j0;
-    const int items = tile_rows + tile_nnz;
 
+    // All loads of a thread are independent: IPT column/value pairs in flight, then IPT gathers.
+    int cc[IPT];
+    T vv[IPT];
+#pragma unroll
+    for (int k = 0; k < IPT; k++) {
+        const int i = tid + k * NT;
+        cc[k] = 0, vv[k] = T(0);
+        if (i < tile_nnz) {
+            cc[k] = __ldcs(col + j0 + i);
+            vv[k] = __ldcs(val + j0 + i);
+        }
+    }
+
+    if (tile_rows == 0) {
+        // ---- inside one row: block-wide dot product, leftover goes to the carry array --------
+        T acc = T(0);
+#pragma unroll
+        for (int k = 0; k < IPT; k++)
+            if (tid + k * NT < tile_nnz) acc = fma(vv[k], __ldg(x + cc[k]), acc);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) s_wval[wid] = acc;
+        __syncthreads();
+        if (tid == 0) {
+            T total = s_wval[0];
+#pragma unroll
+            for (int w = 1; w < NW; w++) total += s_wval[w];
+            carry_row[blockIdx.x] = r0;
+            carry_val[blockIdx.x] = total;
+        }
+        return;
+    }
+
+    // ---- general tile ---------------------------------------------------------------------------
+    const int items = tile_rows + tile_nnz;
     // Row ends relative to the tile's first element; entry tile_rows is the (unfinished) row
     // the tile stops in, or +inf past the last row.
     for (int i = tid; i <= tile_rows; i += NT) {
         const int r = r0 + i;
         s_rend[i] = (r < rows) ? (__ldg(row_ptr + r + 1) - j0) : INT_MAX;
     }
-    // All loads of a thread are independent: IPT column/value pairs in flight, then IPT gathers.
-    {
-        int cc[IPT];
-        T vv[IPT];
 #pragma unroll
-        for (int k = 0; k < IPT; k++) {
-            const int i = tid + k * NT;
-            cc[k] = 0, vv[k] = T(0);
-            if (i < tile_nnz) {
-                cc[k] = __ldcs(col + j0 + i);
-                vv[k] = __ldcs(val + j0 + i);
-            }
-        }
-#pragma unroll
-        for (int k = 0; k < IPT; k++) {
-            const int i = tid + k * NT;
-            if (i < tile_nnz) s_prod[i] = vv[k] * __ldg(x + cc[k]);
-        }
+    for (int k = 0; k < IPT; k++) {
+        const int i = tid + k * NT;
+        if (i < tile_nnz) s_prod[i] = vv[k] * __ldg(x + cc[k]);
     }
     __syncthreads();
 
@@ -186,6 +221,7 @@ __global__ void __launch_bounds__(NT)
         else hi = mid;
     }
     int i = lo, j = d - lo;
+    int cur_end = s_rend[i];  // end of the row being accumulated; re-read only when a row ends
 
     T run = T(0);
     int first_row = -1;  // first row that ends inside this thread; may have started earlier
@@ -193,7 +229,7 @@ __global__ void __launch_bounds__(NT)
 #pragma unroll
     for (int k = 0; k < IPT; k++) {
         if (d + k < items) {
-            if (j < s_rend[i]) {
+            if (j < cur_end) {
                 run += s_prod[j];
                 j++;
             } else {
@@ -208,13 +244,13 @@ __global__ void __launch_bounds__(NT)
                 }
                 run = T(0);
                 i++;
+                cur_end = s_rend[i];
             }
         }
     }
 
     // Segmented inclusive scan of the per-thread leftovers (key = row the thread stopped in).
     // Keys are non-decreasing with the thread index, so equal keys are contiguous.
-    const int lane = tid & 31, wid = tid >> 5;
     int key = i;
     T acc = run;
 #pragma unroll
@@ -428,7 +464,7 @@ alphasparse_status_t ctx_analyse(DeviceCtx *ctx) {
 
 template <typename T, int LANES>
 static void launch_vector(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st) {
-    constexpr int RPG = 2;
+    constexpr int RPG = VectorShape<LANES>::RPG;
     constexpr int rows_per_block = (256 / LANES) * RPG;
     const unsigned blocks = (unsigned)((ctx->rows + rows_per_block - 1) / rows_per_block);
     const T *val = static_cast<const T *>(ctx->d_val);
