@@ -88,6 +88,7 @@ def prototypes():
     p["alphasparse_cuda_set_algorithm"] = (C.c_int, [C.c_int])
     p["alphasparse_cuda_get_mat_info"] = (C.c_int, [_H, C.POINTER(MatInfo)])
     p["alphasparse_cuda_get_device_csr"] = (C.c_int, [_H, _HP, _HP, _HP])
+    p["alphasparse_cuda_d_csrmv_noalloc"] = (C.c_int, [_I, _I, _I, C.c_double, _P, _P, _P, _P, C.c_double, _P])
     p["alphasparse_cuda_profile_kernel"] = (C.c_int, [_H, C.c_int])
     p["alphasparse_cuda_kernel_ms"] = (C.c_int, [_H, C.POINTER(C.c_float)])
     p["alphasparse_cuda_launch_count"] = (C.c_int64, [])

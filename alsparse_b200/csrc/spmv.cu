@@ -19,6 +19,7 @@
 //           boundary go through a small carry array and a second kernel adds them, in a fixed
 //           order: results do not depend on scheduling and no floating-point atomics are used.
 #include <limits.h>
+#include <stdio.h>
 
 #include "internal.h"
 
@@ -531,3 +532,118 @@ template alphasparse_status_t launch_spmv<double>(DeviceCtx *, double, const dou
                                                   double *, cudaStream_t);
 
 }  // namespace asb
+
+// =============================================================================================
+// alphasparse_cuda_d_csrmv_noalloc: the merge-path SpMV without any allocation
+// =============================================================================================
+//
+// Everything above keeps its load-balancing tables and carry buffers in memory obtained with
+// cudaMalloc when a handle is created.  Some callers cannot afford that: a solver running
+// inside a framework whose caching pool has already claimed the whole device (a cudaMalloc
+// from a second library then fails although plenty of memory is "free" in the pool), or a
+// service that must never hit the device-wide synchronisation cudaMalloc and cudaFree imply.
+// For them this entry point works on caller-owned device CSR arrays and takes its scratch
+// from one fixed array that is part of the library image.  The array costs kScratchBytes on
+// every GPU that loads the library, for the lifetime of the process.
+
+namespace {
+
+constexpr size_t kScratchBytes = 4u << 20;  // 4 MiB per device
+constexpr int kNoAllocItems = asb::kMergeThreads * asb::kMergeItemsD;
+// per tile: start coordinate (8 bytes) + carry row (4) + carry value (8); one extra coordinate
+constexpr long long kNoAllocMaxTiles = (long long)((kScratchBytes - 64) / 20) - 1;
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a usable address.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+unsigned char *g_noalloc_ptr[kMaxDevices] = {};
+
+// Device address of the scratch array on the CURRENT device, resolved on first use per device.
+alphasparse_status_t noalloc_scratch(unsigned char **out) {
+    int dev = -1;
+    ASB_CUDA_OR(cudaGetDevice(&dev), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    if (dev < 0 || dev >= kMaxDevices) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (!g_noalloc_ptr[dev]) {
+        void *p = nullptr;
+        ASB_CUDA_OR(cudaGetSymbolAddress(&p, g_noalloc_scratch), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        g_noalloc_ptr[dev] = static_cast<unsigned char *>(p);
+    }
+    *out = g_noalloc_ptr[dev];
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+bool on_device(const void *p) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+}
+
+}  // namespace
+
+extern "C" alphasparse_status_t alphasparse_cuda_d_csrmv_noalloc(
+    ALPHA_INT rows, ALPHA_INT cols, ALPHA_INT nnz, double alpha, const ALPHA_INT *d_row_ptr,
+    const ALPHA_INT *d_col_indx, const double *d_values, const double *d_x, double beta, double *d_y) {
+    using namespace asb;
+    (void)cols;
+    if (rows < 0 || nnz < 0) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    if (rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+    if (!d_row_ptr || !d_y || (nnz > 0 && (!d_col_indx || !d_values || !d_x)))
+        return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    if (!on_device(d_row_ptr) || !on_device(d_y) ||
+        (nnz > 0 && (!on_device(d_col_indx) || !on_device(d_values) || !on_device(d_x)))) {
+        record_cuda_error(cudaErrorInvalidValue, "alphasparse_cuda_d_csrmv_noalloc takes device pointers only");
+        return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+    }
+    const long long total = (long long)rows + nnz;
+    const long long tiles = (total + kNoAllocItems - 1) / kNoAllocItems;
+    if (tiles > kNoAllocMaxTiles) {
+        char msg[200];
+        snprintf(msg, sizeof(msg),
+                 "alphasparse_cuda_d_csrmv_noalloc: rows + nnz = %lld exceeds the fixed scratch (limit %lld); "
+                 "create a handle and use alphasparse_d_mv",
+                 total, kNoAllocMaxTiles * kNoAllocItems);
+        record_cuda_error(cudaErrorInvalidValue, msg);
+        return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    }
+    cudaStream_t st = current_stream();
+    if (nnz == 0) {
+        scale_kernel<double><<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(rows, d_y, beta);
+        count_launch();
+        ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        return ALPHA_SPARSE_STATUS_SUCCESS;
+    }
+
+    unsigned char *scratch = nullptr;
+    alphasparse_status_t s = noalloc_scratch(&scratch);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    // Layout inside the scratch array: carry values | tile coordinates | carry rows.
+    double *carry_val = reinterpret_cast<double *>(scratch);
+    MergeCoord *tile = reinterpret_cast<MergeCoord *>(scratch + 8 * (size_t)kNoAllocMaxTiles);
+    int *carry_row = reinterpret_cast<int *>(scratch + 16 * (size_t)(kNoAllocMaxTiles + 1));
+
+    // The array still holds whatever the previous call left.  The tile table is rewritten in
+    // full below; the carries are cleared so that a tile that writes none contributes zero.
+    ASB_CUDA_OR(cudaMemsetAsync(carry_val, 0, sizeof(double) * (size_t)tiles, st),
+                ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    ASB_CUDA_OR(cudaMemsetAsync(carry_row, 0x7f, sizeof(int) * (size_t)tiles, st),
+                ALPHA_SPARSE_STATUS_EXECUTION_FAILED);  // 0x7f7f7f7f: beyond any row, ignored by the fix-up
+    merge_tiles_kernel<<<(unsigned)((tiles + 1 + 255) / 256), 256, 0, st>>>(rows, nnz, d_row_ptr, kNoAllocItems,
+                                                                          tiles, tile);
+    if (beta == 0.0)
+        spmv_merge_kernel<double, kMergeThreads, kMergeItemsD, false><<<(unsigned)tiles, kMergeThreads, 0, st>>>(
+            rows, d_row_ptr, d_col_indx, d_values, d_x, d_y, alpha, beta, tile, carry_row, carry_val);
+    else
+        spmv_merge_kernel<double, kMergeThreads, kMergeItemsD, true><<<(unsigned)tiles, kMergeThreads, 0, st>>>(
+            rows, d_row_ptr, d_col_indx, d_values, d_x, d_y, alpha, beta, tile, carry_row, carry_val);
+    spmv_merge_fixup_kernel<double><<<(unsigned)((tiles + 255) / 256), 256, 0, st>>>(rows, tiles, carry_row,
+                                                                                   carry_val, d_y, alpha);
+    count_launch(3);
+    ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}

@@ -156,3 +156,10 @@ def kernel_ms(A):
     st = capi.load().alphasparse_cuda_kernel_ms(A, C.byref(ms))
     assert st == SUCCESS, capi.STATUS_NAMES[st]
     return ms.value
+
+
+def csrmv_noalloc(rows, cols, nnz, alpha, d_row_ptr, d_col_indx, d_values, d_x, beta, d_y):
+    """alphasparse_cuda_d_csrmv_noalloc: double-precision SpMV on device arrays that never allocates
+    (scratch lives in a fixed 4 MiB array inside the library; rows + nnz <= 375,802,112)."""
+    return capi.load().alphasparse_cuda_d_csrmv_noalloc(rows, cols, nnz, alpha, _ptr(d_row_ptr), _ptr(d_col_indx),
+                                                         _ptr(d_values), _ptr(d_x), beta, _ptr(d_y))

@@ -54,6 +54,34 @@ alphasparse_status_t alphasparse_cuda_get_device_csr(const alphasparse_matrix_t 
                                                      ALPHA_INT **d_row_ptr,
                                                      ALPHA_INT **d_col_indx, void **d_values);
 
+/* y = alpha*A*x + beta*y (double precision, general CSR, non-transposed) on caller-owned
+ * DEVICE arrays, with a guarantee: the call never allocates or frees memory, on the device or
+ * through any library.  No counterpart in the reference; it exists for callers that cannot
+ * allocate at call time -- code running inside a framework whose memory pool already owns the
+ * device (a cudaMalloc from a second library fails there even though the pool has room), or a
+ * service that cannot tolerate the device-wide synchronisation cudaMalloc / cudaFree carry.
+ *
+ * d_row_ptr has rows+1 zero-based offsets, d_col_indx / d_values have nnz entries, d_x has cols
+ * and d_y rows entries; all five live on the current device.  Work is enqueued on the library
+ * stream and the call returns without waiting.
+ *
+ * Scratch (the merge-path tile table and carries that a handle would own) comes from one fixed
+ * 4 MiB array inside the library image, present on every GPU that loads the library until the
+ * process exits.  Consequences:
+ *   - rows + nnz may not exceed 375,802,112; larger problems return
+ *     ALPHA_SPARSE_STATUS_INVALID_VALUE (text via alphasparse_cuda_last_error): create a handle
+ *     and use alphasparse_d_mv instead;
+ *   - all calls share the array and find the previous call's data in it; each call clears what
+ *     it relies on.  Two calls that overlap on the GPU (different streams, different host
+ *     threads without ordering) race on it: keep calls on one device in stream order;
+ *   - the first call on each device looks up the array's device address (no allocation, but a
+ *     runtime query): make that first call before starting any stream capture. */
+alphasparse_status_t alphasparse_cuda_d_csrmv_noalloc(ALPHA_INT rows, ALPHA_INT cols, ALPHA_INT nnz,
+                                                      double alpha, const ALPHA_INT *d_row_ptr,
+                                                      const ALPHA_INT *d_col_indx,
+                                                      const double *d_values, const double *d_x,
+                                                      double beta, double *d_y);
+
 /* Kernel timing for benchmarks.  With profiling enabled on a handle, every mv / mm call on it
  * brackets its dominant kernel (the SpMV or SpMM kernel itself, not the small fix-up or any
  * copies) with CUDA events on the library stream; alphasparse_cuda_kernel_ms waits for the
