@@ -27,7 +27,7 @@ ROW_MAJOR, COLUMN_MAJOR = 0, 1
 FORMAT_COO, FORMAT_CSR = 0, 1
 FLOAT, DOUBLE, FLOAT_COMPLEX, DOUBLE_COMPLEX = 0, 1, 2, 3
 # alphasparse_cuda_alg_t
-ALG_AUTO, ALG_VECTOR, ALG_MERGE = 0, 1, 2
+ALG_AUTO, ALG_VECTOR, ALG_MERGE, ALG_ROWTILE = 0, 1, 2, 3
 
 
 class MatrixDescr(C.Structure):

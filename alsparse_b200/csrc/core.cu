@@ -33,6 +33,7 @@ alphasparse_cuda_alg_t forced_algorithm() {
         if (const char *env = getenv("ALPHASPARSE_CUDA_ALG")) {
             if (!strcmp(env, "vector")) a = ALPHA_SPARSE_CUDA_ALG_VECTOR;
             else if (!strcmp(env, "merge")) a = ALPHA_SPARSE_CUDA_ALG_MERGE;
+            else if (!strcmp(env, "rowtile")) a = ALPHA_SPARSE_CUDA_ALG_ROWTILE;
         }
         g_alg.store(a, std::memory_order_relaxed);
     }
@@ -67,6 +68,7 @@ void ctx_destroy(DeviceCtx *c) {
     cudaFree(c->d_carry_val);
     cudaFree(c->d_x_stage);
     cudaFree(c->d_y_stage);
+    cudaFree(c->d_status);
     if (c->ev_start) cudaEventDestroy(c->ev_start);
     if (c->ev_stop) cudaEventDestroy(c->ev_stop);
     if (prev >= 0) cudaSetDevice(prev);
@@ -102,7 +104,11 @@ alphasparse_status_t ctx_create(int datatype, int64_t rows, int64_t cols, const 
         }                                        \
     } while (0)
 
-    TRY(cudaMalloc(&c->d_row_ptr, sizeof(int) * (size_t)(rows + 1)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    // four spare offsets: the row-tile kernel copies offsets in 16-byte units
+    TRY(cudaMalloc(&c->d_row_ptr, sizeof(int) * (size_t)(rows + 1 + 4)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMalloc(&c->d_status, sizeof(int)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMemsetAsync(c->d_status, 0, sizeof(int), st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaMemsetAsync(c->d_row_ptr + rows + 1, 0, sizeof(int) * 4, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     TRY(cudaMalloc(&c->d_col, sizeof(int) * padded), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
     TRY(cudaMalloc(&c->d_val, tsz * padded), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
     c->device_bytes = (int64_t)(sizeof(int) * (size_t)(rows + 1) + (sizeof(int) + tsz) * padded);
@@ -449,8 +455,14 @@ static alphasparse_status_t mv(alphasparse_operation_t op, T alpha, const alphas
         ASB_CUDA_OR(cudaMemcpyAsync(y, dy, sizeof(T) * (size_t)c->rows, cudaMemcpyDeviceToHost, st),
                     ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     }
-    if (!y_dev || !x_dev)
+    if (!y_dev || !x_dev) {
+        // a synchronous call can also report a kernel whose bounded wait ran out
+        int kernel_status = 0;
+        ASB_CUDA_OR(cudaMemcpyAsync(&kernel_status, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, st),
+                    ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
         ASB_CUDA_OR(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        if (kernel_status != 0) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+    }
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
@@ -703,7 +715,7 @@ alphasparse_status_t alphasparse_cuda_synchronize(void) {
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg) {
-    if (alg < ALPHA_SPARSE_CUDA_ALG_AUTO || alg > ALPHA_SPARSE_CUDA_ALG_MERGE) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    if (alg < ALPHA_SPARSE_CUDA_ALG_AUTO || alg > ALPHA_SPARSE_CUDA_ALG_ROWTILE) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
     g_alg.store((int)alg, std::memory_order_relaxed);
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }

@@ -43,6 +43,11 @@ constexpr int kMergeThreads = 256;
 constexpr int kMergeItemsS = 9;  // float
 constexpr int kMergeItemsD = 7;  // double
 
+// Row-tile kernel: rows per block (= threads per block) and the most shared memory one block may
+// ask for (four blocks per SM must still fit in the 227 KB an SM offers).
+constexpr int kRowTile = 128;
+constexpr size_t kRowTileMaxSmem = 56 * 1024;
+
 struct MergeCoord {
     int row;  // rows fully consumed before this point
     int nz;   // stored elements consumed before this point
@@ -63,6 +68,8 @@ struct DeviceCtx {
     int64_t empty_rows = 0;
     double mean_row_nnz = 0.0;
     double mean_row_quads = 0.0;  // aligned 4-element groups a row touches, on average
+    double shifted_rows = 0.0;    // share of sampled elements whose next-row twin sits one column to the right
+    int64_t max_tile_span = 0;    // largest quad-aligned element span of kRowTile consecutive rows
     int algorithm = ALPHA_SPARSE_CUDA_ALG_VECTOR;
     int lanes = 4;
 
@@ -72,6 +79,8 @@ struct DeviceCtx {
     MergeCoord *d_tile = nullptr;  // merge_tiles + 1
     int *d_carry_row = nullptr;    // merge_tiles
     void *d_carry_val = nullptr;   // merge_tiles
+
+    int *d_status = nullptr;  // error word set by kernels whose bounded waits ran out (0 = fine)
 
     // staging for calls that pass host vectors (grown on demand, reused)
     void *d_x_stage = nullptr;

@@ -39,54 +39,68 @@ __device__ __forceinline__ void load_vec(const T *__restrict__ p, T (&out)[VEC])
     for (int i = 0; i < VEC; i++) out[i] = s[i];
 }
 
+// A group of LPR lanes (a power of two up to 32) owns one sparse row; 32/LPR rows share a warp.
+// Lane g of the group holds VEC consecutive dense columns starting at ct + g*VEC, so one step of
+// the group reads LPR*VEC*sizeof(T) contiguous bytes of an X row (64 fp32 columns: 16 lanes x
+// float4 = 256 bytes, two rows per warp instruction).
 // VEC > 1 requires: columns % VEC == 0, ldx % VEC == 0, ldy % VEC == 0 and X, Y aligned to
 // VEC * sizeof(T); the launcher checks and otherwise uses VEC == 1.
-template <typename T, int VEC, bool HAS_BETA>
-__global__ void __launch_bounds__(256)
+#ifndef ASB_SPMM_UNROLL
+#define ASB_SPMM_UNROLL 4
+#endif
+#ifndef ASB_SPMM_MINBLOCKS
+#define ASB_SPMM_MINBLOCKS 8
+#endif
+template <typename T, int VEC, int LPR, bool HAS_BETA>
+__global__ void __launch_bounds__(256, ASB_SPMM_MINBLOCKS)
     spmm_row_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
                     const T *__restrict__ val, const T *__restrict__ X, int columns,
                     long long ldx, T *__restrict__ Y, long long ldy, T alpha, T beta) {
+    constexpr int UNROLL = ASB_SPMM_UNROLL;
+    constexpr int RPW = 32 / LPR;  // rows per warp
     const int lane = threadIdx.x & 31;
-    const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (row >= rows) return;  // whole warp leaves together
+    const int gl = lane % LPR, grp = lane / LPR;
+    const unsigned gmask = LPR == 32 ? 0xffffffffu : (((1u << LPR) - 1u) << (grp * LPR));
+    const long long row = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * RPW + grp;
+    if (row >= rows) return;  // whole groups leave together; shuffles below name only their group
     const int s = __ldg(row_ptr + row), e = __ldg(row_ptr + row + 1);
 
-    for (int ct = 0; ct < columns; ct += 32 * VEC) {
-        const int c = ct + lane * VEC;
+    for (int ct = 0; ct < columns; ct += LPR * VEC) {
+        const int c = ct + gl * VEC;
         const bool live = c < columns;
         T acc[VEC];
 #pragma unroll
         for (int i = 0; i < VEC; i++) acc[i] = T(0);
 
-        for (int base = s; base < e; base += 32) {
-            const int mine = base + lane;
+        for (int base = s; base < e; base += LPR) {
+            const int mine = base + gl;
             int cj = 0;
             T vj = T(0);
             if (mine < e) {
                 cj = __ldcs(col + mine);
                 vj = alpha * __ldcs(val + mine);
             }
-            const int n = min(32, e - base);
+            const int n = min(LPR, e - base);
             int k = 0;
-            for (; k + 4 <= n; k += 4) {
-                T xv[4][VEC];
-                T av[4];
+            for (; k + UNROLL <= n; k += UNROLL) {
+                T xv[UNROLL][VEC];
+                T av[UNROLL];
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int cc = __shfl_sync(0xffffffffu, cj, k + u);
-                    av[u] = __shfl_sync(0xffffffffu, vj, k + u);
+                for (int u = 0; u < UNROLL; u++) {
+                    const int cc = __shfl_sync(gmask, cj, k + u, LPR);
+                    av[u] = __shfl_sync(gmask, vj, k + u, LPR);
                     if (live) load_vec<T, VEC>(X + (long long)cc * ldx + c, xv[u]);
                 }
                 if (live) {
 #pragma unroll
-                    for (int u = 0; u < 4; u++)
+                    for (int u = 0; u < UNROLL; u++)
 #pragma unroll
                         for (int i = 0; i < VEC; i++) acc[i] = fma(av[u], xv[u][i], acc[i]);
                 }
             }
             for (; k < n; k++) {
-                const int cc = __shfl_sync(0xffffffffu, cj, k);
-                const T a = __shfl_sync(0xffffffffu, vj, k);
+                const int cc = __shfl_sync(gmask, cj, k, LPR);
+                const T a = __shfl_sync(gmask, vj, k, LPR);
                 if (live) {
                     T xv[VEC];
                     load_vec<T, VEC>(X + (long long)cc * ldx + c, xv);
@@ -114,43 +128,50 @@ __global__ void __launch_bounds__(256)
     }
 }
 
-template <typename T, int VEC>
+template <typename T, int VEC, int LPR>
 static void launch_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx, T beta, T *Y,
                        int ldy, cudaStream_t st) {
-    const unsigned blocks = (unsigned)((ctx->rows + 7) / 8);
+    constexpr int rows_per_block = 8 * (32 / LPR);
+    const unsigned blocks = (unsigned)((ctx->rows + rows_per_block - 1) / rows_per_block);
     const T *val = static_cast<const T *>(ctx->d_val);
     if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
     if (beta == T(0))
-        spmm_row_kernel<T, VEC, false><<<blocks, 256, 0, st>>>(
+        spmm_row_kernel<T, VEC, LPR, false><<<blocks, 256, 0, st>>>(
             (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, X, columns, ldx, Y, ldy, alpha, beta);
     else
-        spmm_row_kernel<T, VEC, true><<<blocks, 256, 0, st>>>(
+        spmm_row_kernel<T, VEC, LPR, true><<<blocks, 256, 0, st>>>(
             (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, X, columns, ldx, Y, ldy, alpha, beta);
     if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
     count_launch();
+}
+
+template <typename T, int VEC>
+static void launch_row_lanes(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx, T beta, T *Y,
+                             int ldy, cudaStream_t st) {
+    // smallest group (8, 16 or 32 lanes) whose lanes cover the dense columns in one pass, if any
+    const int need = (columns + VEC - 1) / VEC;
+    if (need <= 8) launch_row<T, VEC, 8>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+    else if (need <= 16) launch_row<T, VEC, 16>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+    else launch_row<T, VEC, 32>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
 }
 
 template <typename T>
 alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx,
                                      T beta, T *Y, int ldy, cudaStream_t st) {
     if (ctx->rows == 0 || columns <= 0) return ALPHA_SPARSE_STATUS_SUCCESS;
-    constexpr int MAXVEC = sizeof(T) == 4 ? 4 : 2;
     auto fits = [&](int vec) {
         const uintptr_t mask = (uintptr_t)(vec * sizeof(T) - 1);
         return columns % vec == 0 && ldx % vec == 0 && ldy % vec == 0 &&
                ((uintptr_t)X & mask) == 0 && ((uintptr_t)Y & mask) == 0;
     };
-    // Widest pack that still gives every lane of the warp a column to work on.
-    int vec = 1;
-    if (MAXVEC >= 4 && columns >= 128 && fits(4)) vec = 4;
-    else if (columns >= 64 && fits(2)) vec = 2;
+    // Widest 16-byte pack the shapes and alignments allow.
     if constexpr (sizeof(T) == 4) {
-        if (vec == 4) launch_row<T, 4>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
-        else if (vec == 2) launch_row<T, 2>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
-        else launch_row<T, 1>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+        if (fits(4)) launch_row_lanes<T, 4>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+        else if (fits(2)) launch_row_lanes<T, 2>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+        else launch_row_lanes<T, 1>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
     } else {
-        if (vec == 2) launch_row<T, 2>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
-        else launch_row<T, 1>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+        if (fits(2)) launch_row_lanes<T, 2>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+        else launch_row_lanes<T, 1>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
     }
     ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     return ALPHA_SPARSE_STATUS_SUCCESS;

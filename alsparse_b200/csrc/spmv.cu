@@ -135,6 +135,106 @@ __global__ void __launch_bounds__(256, VectorShape<LANES>::MIN_BLOCKS)
     }
 }
 
+// ---- row-tile kernel ----------------------------------------------------------------------------
+//
+// One block stages the column indices, values and offsets of kRowTile consecutive rows in
+// shared memory with three bulk asynchronous copies (cp.async.bulk global -> shared, completion
+// counted in bytes on an mbarrier), then every thread walks ONE row out of shared memory.
+// Compared with the vector kernel this turns the x gathers of a banded matrix into coalesced
+// accesses (neighbouring lanes = neighbouring rows = neighbouring columns), which is what the
+// 27-point stencil needs: there the vector kernel is limited by L1 wavefronts, not by HBM.
+// Several blocks are resident per SM, so the copies of one overlap the arithmetic of another.
+//
+// The element range of a tile is widened to multiples of four elements so that source
+// addresses and sizes are multiples of 16 bytes, as the bulk copy requires; the arrays carry a
+// zero tail for that.  The wait on the mbarrier is bounded: if it runs out the block records
+// an error word and leaves without touching y.
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) {
+    return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void bulk_copy_g2s(unsigned dst, const void *src, unsigned bytes, unsigned bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+template <typename T, bool HAS_BETA>
+__global__ void __launch_bounds__(kRowTile)
+    spmv_rowtile_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
+                        const T *__restrict__ val, const T *__restrict__ x, T *__restrict__ y, T alpha,
+                        T beta, int cap, int *__restrict__ status) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    T *s_val = reinterpret_cast<T *>(smem);
+    int *s_col = reinterpret_cast<int *>(smem + (size_t)cap * sizeof(T));
+    int *s_ptr = s_col + cap;
+    unsigned long long *s_bar = reinterpret_cast<unsigned long long *>(s_ptr + kRowTile + 4);
+
+    const int tid = threadIdx.x;
+    const int r0 = blockIdx.x * kRowTile;
+    const int nr = min(kRowTile, rows - r0);
+    const unsigned bar = smem_u32(s_bar);
+
+    if (tid == 0) {
+        const int start = __ldg(row_ptr + r0), end = __ldg(row_ptr + r0 + nr);
+        const int a0 = start & ~3;
+        int n = ((end + 3) & ~3) - a0;
+        if (n > cap) {  // cannot happen for a handle analysed by this library; refuse rather than overrun
+            atomicExch(status, 1);
+            n = 0;
+        }
+        const unsigned ptr_bytes = (unsigned)(((nr + 1 + 3) & ~3) * sizeof(int));
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const unsigned bytes = ptr_bytes + (unsigned)n * (unsigned)(sizeof(int) + sizeof(T));
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+        bulk_copy_g2s(smem_u32(s_ptr), row_ptr + r0, ptr_bytes, bar);
+        if (n > 0) {
+            bulk_copy_g2s(smem_u32(s_col), col + a0, (unsigned)n * sizeof(int), bar);
+            bulk_copy_g2s(smem_u32(s_val), val + a0, (unsigned)n * sizeof(T), bar);
+        }
+    }
+    __syncthreads();
+
+    bool arrived = false;
+    for (int spin = 0; spin < (1 << 22); spin++) {
+        if (mbar_try_wait(bar, 0)) {
+            arrived = true;
+            break;
+        }
+    }
+    if (!arrived) {
+        if (tid == 0) atomicExch(status, 2);
+        return;
+    }
+
+    if (tid < nr) {
+        const int a0 = s_ptr[0] & ~3;
+        int k = s_ptr[tid] - a0;
+        const int e = s_ptr[tid + 1] - a0;
+        if (e > cap) return;  // the oversize case flagged above
+        T acc0 = T(0), acc1 = T(0), acc2 = T(0), acc3 = T(0);
+        for (; k + 4 <= e; k += 4) {
+            const int c0 = s_col[k], c1 = s_col[k + 1], c2 = s_col[k + 2], c3 = s_col[k + 3];
+            const T x0 = __ldg(x + c0), x1 = __ldg(x + c1), x2 = __ldg(x + c2), x3 = __ldg(x + c3);
+            acc0 = fma(s_val[k], x0, acc0);
+            acc1 = fma(s_val[k + 1], x1, acc1);
+            acc2 = fma(s_val[k + 2], x2, acc2);
+            acc3 = fma(s_val[k + 3], x3, acc3);
+        }
+        for (; k < e; k++) acc0 = fma(s_val[k], __ldg(x + s_col[k]), acc0);
+        const int r = r0 + tid;
+        T out = alpha * ((acc0 + acc1) + (acc2 + acc3));
+        if (HAS_BETA) out = fma(beta, y[r], out);
+        __stcs(y + r, out);
+    }
+}
+
 // ---- merge kernel ----------------------------------------------------------------------------
 
 // One thread block = one tile of NT*IPT merge items.  The tile's start and end coordinates
@@ -312,10 +412,11 @@ __global__ void scale_kernel(long long n, T *__restrict__ y, T beta) {
 // ---- analysis kernels --------------------------------------------------------------------------
 
 // out[0] = max row length, out[1] = empty rows, out[2] = aligned quads touched (summed over
-// rows), out[3] = rows whose end offset is below their start offset (malformed input).
+// rows), out[3] = rows whose end offset is below their start offset (malformed input),
+// out[5] = largest quad-aligned element span of a tile of kRowTile consecutive rows.
 __global__ void row_stats_kernel(int rows, const int *__restrict__ row_ptr,
                                  unsigned long long *__restrict__ out) {
-    unsigned long long mx = 0, empty = 0, quads = 0, bad = 0;
+    unsigned long long mx = 0, empty = 0, quads = 0, bad = 0, span = 0;
     for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows;
          r += (long long)gridDim.x * blockDim.x) {
         const int s = row_ptr[r], e = row_ptr[r + 1];
@@ -327,16 +428,27 @@ __global__ void row_stats_kernel(int rows, const int *__restrict__ row_ptr,
         mx = len > mx ? len : mx;
         if (len == 0) empty++;
         else quads += (unsigned long long)(((e + 3) >> 2) - (s >> 2));
+        if (r % kRowTile == 0) {
+            const long long last = r + kRowTile < rows ? r + kRowTile : rows;
+            const int te = row_ptr[last];
+            if (te >= s) {
+                const unsigned long long sp = (unsigned long long)(((te + 3) & ~3) - (s & ~3));
+                span = sp > span ? sp : span;
+            }
+        }
     }
     for (int o = 16; o > 0; o >>= 1) {
         const unsigned long long m2 = __shfl_xor_sync(0xffffffffu, mx, o);
         mx = m2 > mx ? m2 : mx;
+        const unsigned long long s2 = __shfl_xor_sync(0xffffffffu, span, o);
+        span = s2 > span ? s2 : span;
         empty += __shfl_xor_sync(0xffffffffu, empty, o);
         quads += __shfl_xor_sync(0xffffffffu, quads, o);
         bad += __shfl_xor_sync(0xffffffffu, bad, o);
     }
     if ((threadIdx.x & 31) == 0) {
         atomicMax(out + 0, mx);
+        atomicMax(out + 5, span);
         if (empty) atomicAdd(out + 1, empty);
         if (quads) atomicAdd(out + 2, quads);
         if (bad) atomicAdd(out + 3, bad);
@@ -355,6 +467,35 @@ __global__ void col_range_kernel(long long nnz, int cols, const int *__restrict_
     }
     for (int o = 16; o > 0; o >>= 1) bad += __shfl_xor_sync(0xffffffffu, bad, o);
     if ((threadIdx.x & 31) == 0 && bad) atomicAdd(out, bad);
+}
+
+// Shifted-row structure: out[0] counts sampled positions k (first, middle, last element) of rows r
+// for which row r+1 holds column col(r, k) + 1 at the same position, out[1] the positions sampled.
+// Close to 1 for stencils and other banded matrices in natural ordering (neighbouring rows gather
+// neighbouring x elements), close to 0 for unstructured columns.
+__global__ void row_shift_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
+                                 unsigned long long *__restrict__ out) {
+    unsigned long long hit = 0, seen = 0;
+    for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r + 1 < rows;
+         r += (long long)gridDim.x * blockDim.x) {
+        const int s0 = row_ptr[r], s1 = row_ptr[r + 1], e1 = row_ptr[r + 2];
+        const int len0 = s1 - s0, len1 = e1 - s1;
+        if (len0 <= 0 || len1 <= 0) continue;
+        const int ks[3] = {0, len0 / 2, len0 - 1};
+        for (int i = 0; i < 3; i++) {
+            if (i > 0 && ks[i] == ks[i - 1]) continue;
+            seen++;
+            if (ks[i] < len1 && col[s1 + ks[i]] == col[s0 + ks[i]] + 1) hit++;
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        hit += __shfl_xor_sync(0xffffffffu, hit, o);
+        seen += __shfl_xor_sync(0xffffffffu, seen, o);
+    }
+    if ((threadIdx.x & 31) == 0 && seen) {
+        atomicAdd(out + 0, hit);
+        atomicAdd(out + 1, seen);
+    }
 }
 
 // Start coordinate of every merge tile: the point on diagonal t*items of the merge of the row
@@ -378,6 +519,13 @@ __global__ void merge_tiles_kernel(int rows, int nnz, const int *__restrict__ ro
 
 // ---- analysis (host) ------------------------------------------------------------------------------
 
+// Dynamic shared memory of one row-tile block: values | columns | offsets (+4 pad) | mbarrier.
+static size_t rowtile_smem_bytes(const DeviceCtx *ctx) {
+    const size_t cap = (size_t)((ctx->max_tile_span + 3) & ~3ll);
+    const size_t tsz = ctx->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE ? 8 : 4;
+    return cap * (tsz + sizeof(int)) + (kRowTile + 4) * sizeof(int) + 16;
+}
+
 static int pick_lanes(double mean_quads) {
     // Lanes per row = aligned quads an average row touches, rounded to a power of two.
     int lanes = 1;
@@ -392,7 +540,7 @@ alphasparse_status_t ctx_analyse(DeviceCtx *ctx) {
     ctx->max_row_nnz = 0, ctx->empty_rows = ctx->rows, ctx->mean_row_nnz = 0.0;
     if (ctx->rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
 
-    unsigned long long *d_out = nullptr, h_out[5] = {0, 0, 0, 0, 0};
+    unsigned long long *d_out = nullptr, h_out[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     ASB_CUDA_OR(cudaMalloc(&d_out, sizeof(h_out)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
     cudaError_t e = cudaMemsetAsync(d_out, 0, sizeof(h_out), st);
     if (e == cudaSuccess) {
@@ -406,7 +554,11 @@ alphasparse_status_t ctx_analyse(DeviceCtx *ctx) {
             blocks = (int)(want < 148 * 16 ? want : 148 * 16);
             col_range_kernel<<<blocks, threads, 0, st>>>(ctx->nnz, (int)ctx->cols, ctx->d_col,
                                                          d_out + 4);
-            count_launch();
+            want = (ctx->rows + threads - 1) / threads;
+            blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+            row_shift_kernel<<<blocks, threads, 0, st>>>((int)ctx->rows, ctx->d_row_ptr, ctx->d_col,
+                                                         d_out + 6);
+            count_launch(2);
         }
         e = cudaGetLastError();
     }
@@ -423,15 +575,21 @@ alphasparse_status_t ctx_analyse(DeviceCtx *ctx) {
     ctx->empty_rows = (int64_t)h_out[1];
     ctx->mean_row_nnz = (double)ctx->nnz / (double)ctx->rows;
     ctx->mean_row_quads = (double)h_out[2] / (double)ctx->rows;
+    ctx->max_tile_span = (int64_t)h_out[5];
+    ctx->shifted_rows = h_out[7] ? (double)h_out[6] / (double)h_out[7] : 0.0;
     ctx->lanes = pick_lanes(ctx->mean_row_quads);
 
     // A row longer than eight passes of its lane group would leave that group running long
     // after the rest of the grid has drained: switch to equal-work tiles.
     int alg = forced_algorithm();
+    const bool rowtile_fits = rowtile_smem_bytes(ctx) <= kRowTileMaxSmem;
+    if (alg == ALPHA_SPARSE_CUDA_ALG_ROWTILE && !rowtile_fits) alg = ALPHA_SPARSE_CUDA_ALG_AUTO;
     if (alg == ALPHA_SPARSE_CUDA_ALG_AUTO) {
         const int64_t comfortable = (int64_t)ctx->lanes * 4 * 8;
-        alg = (ctx->max_row_nnz > comfortable) ? ALPHA_SPARSE_CUDA_ALG_MERGE
-                                                : ALPHA_SPARSE_CUDA_ALG_VECTOR;
+        if (ctx->max_row_nnz > comfortable) alg = ALPHA_SPARSE_CUDA_ALG_MERGE;
+        else if (rowtile_fits && ctx->shifted_rows >= 0.5)
+            alg = ALPHA_SPARSE_CUDA_ALG_ROWTILE;  // banded: thread-per-row makes the x gathers coalesce
+        else alg = ALPHA_SPARSE_CUDA_ALG_VECTOR;
     }
     ctx->algorithm = alg;
 
@@ -502,6 +660,33 @@ static void launch_merge(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cuda
 }
 
 template <typename T>
+static alphasparse_status_t launch_rowtile(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y,
+                                           cudaStream_t st) {
+    const int cap = (int)((ctx->max_tile_span + 3) & ~3ll);
+    const size_t smem = rowtile_smem_bytes(ctx);
+    const T *val = static_cast<const T *>(ctx->d_val);
+    const unsigned blocks = (unsigned)((ctx->rows + kRowTile - 1) / kRowTile);
+    auto k0 = spmv_rowtile_kernel<T, false>;
+    auto k1 = spmv_rowtile_kernel<T, true>;
+    auto kernel = beta == T(0) ? k0 : k1;
+    // The opt-in limit is a property of the kernel, shared by all handles: only ever raise it.
+    static std::atomic<size_t> granted[2] = {{0}, {0}};
+    const int which = beta == T(0) ? 0 : 1;
+    if (smem > 48 * 1024 && granted[which].load() < smem) {
+        ASB_CUDA_OR(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kRowTileMaxSmem),
+                    ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        granted[which].store(kRowTileMaxSmem);
+    }
+    if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
+    kernel<<<blocks, kRowTile, smem, st>>>((int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha,
+                                           beta, cap, ctx->d_status);
+    if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
+    count_launch();
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+template <typename T>
 alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y,
                                  cudaStream_t st) {
     if (ctx->rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
@@ -512,6 +697,9 @@ alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T 
     } else if (ctx->algorithm == ALPHA_SPARSE_CUDA_ALG_MERGE) {
         constexpr int IPT = sizeof(T) == 8 ? kMergeItemsD : kMergeItemsS;
         launch_merge<T, IPT>(ctx, alpha, x, beta, y, st);
+    } else if (ctx->algorithm == ALPHA_SPARSE_CUDA_ALG_ROWTILE) {
+        alphasparse_status_t s = launch_rowtile<T>(ctx, alpha, x, beta, y, st);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     } else {
         switch (ctx->lanes) {
             case 1: launch_vector<T, 1>(ctx, alpha, x, beta, y, st); break;

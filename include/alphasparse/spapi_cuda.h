@@ -24,11 +24,13 @@ alphasparse_status_t alphasparse_cuda_synchronize(void);
 typedef enum {
     ALPHA_SPARSE_CUDA_ALG_AUTO = 0,   /* chosen per matrix by the analysis */
     ALPHA_SPARSE_CUDA_ALG_VECTOR = 1, /* a group of 2..32 lanes per row */
-    ALPHA_SPARSE_CUDA_ALG_MERGE = 2   /* merge-path tiles: equal rows+nnz per thread block */
+    ALPHA_SPARSE_CUDA_ALG_MERGE = 2,  /* merge-path tiles: equal rows+nnz per thread block */
+    ALPHA_SPARSE_CUDA_ALG_ROWTILE = 3 /* 128-row tiles staged in shared memory by bulk copies,
+                                         one thread per row (falls back when a tile is too large) */
 } alphasparse_cuda_alg_t;
 
 /* Forces the SpMV kernel family for handles analysed after the call (A/B measurements);
- * the environment variable ALPHASPARSE_CUDA_ALG=auto|vector|merge sets the initial value. */
+ * the environment variable ALPHASPARSE_CUDA_ALG=auto|vector|merge|rowtile sets the initial value. */
 alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg);
 
 /* What the analysis at handle creation found and chose. */

@@ -12,7 +12,7 @@ from gpu_util import TORCH, check_mv, download, make_handle
 from helpers import NP, assert_rows_close, golden, row_scale
 
 pytestmark = pytest.mark.gpu
-ALGS = [capi.ALG_VECTOR, capi.ALG_MERGE]
+ALGS = [capi.ALG_VECTOR, capi.ALG_MERGE, capi.ALG_ROWTILE]
 
 
 def _csr(g):
@@ -209,7 +209,11 @@ def test_status_codes_on_live_handles():
 def test_analysis_picks_by_row_shape():
     A = make_handle("s", synth.uniform_fixed("s", 1, 4096, 4096, 16))
     _, info = spblas.mat_info(A)
-    assert info.algorithm == capi.ALG_VECTOR and info.lanes_per_row == 4
+    assert info.algorithm == capi.ALG_VECTOR and info.lanes_per_row == 4   # random columns: no row tiles
+    spblas.destroy(A)
+    A = make_handle("d", synth.stencil27("d", 24))
+    _, info = spblas.mat_info(A)
+    assert info.algorithm == capi.ALG_ROWTILE                               # neighbouring rows, neighbouring columns
     spblas.destroy(A)
     A = make_handle("d", synth.zipf("d", 1, 20000, 300000, 1.8, 1, 200000))
     _, info = spblas.mat_info(A)
