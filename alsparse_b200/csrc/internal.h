@@ -41,7 +41,10 @@ constexpr int kTailPad = 16;
 // Merge-path tile shape: kMergeThreads threads, each consuming kMergeItems (rows+nnz) items.
 constexpr int kMergeThreads = 256;
 constexpr int kMergeItemsS = 9;  // float
-constexpr int kMergeItemsD = 7;  // double
+#ifndef ASB_MERGE_IPT_D
+#define ASB_MERGE_IPT_D 7
+#endif
+constexpr int kMergeItemsD = ASB_MERGE_IPT_D;  // double
 
 // Row-tile kernel: rows per block (= threads per block) and the most shared memory one block may
 // ask for (four blocks per SM must still fit in the 227 KB an SM offers).

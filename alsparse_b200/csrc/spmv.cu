@@ -244,8 +244,11 @@ __global__ void __launch_bounds__(kRowTile)
 // of the tiles of a power-law matrix) is a plain dot product: strided loads, register sums,
 // one block reduction, nothing staged.  Any other tile stages its products in shared memory
 // in load order and lets every thread walk its IPT consecutive merge items.
+#ifndef ASB_MERGE_MINBLOCKS
+#define ASB_MERGE_MINBLOCKS 1
+#endif
 template <typename T, int NT, int IPT, bool HAS_BETA>
-__global__ void __launch_bounds__(NT)
+__global__ void __launch_bounds__(NT, ASB_MERGE_MINBLOCKS)
     spmv_merge_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
                       const T *__restrict__ val, const T *__restrict__ x, T *__restrict__ y,
                       T alpha, T beta, const MergeCoord *__restrict__ tile,
