@@ -244,7 +244,7 @@ def main():
     import torch
     import torch.distributed as dist
 
-    from alsparse_b200 import capi, spblas, synth
+    from alsparse_b200 import capi, multi, spblas, synth
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device: there is no CPU path"
     torch.cuda.set_device(local_rank)
@@ -262,8 +262,8 @@ def main():
     rows_end = np.cumsum(lens, dtype=np.int64)
     nnz_total = int(rows_end[-1])
     assert nnz_total < 2 ** 31
-    part = spblas.partition_rows_by_nnz(rows_end.astype(np.int32), world)
-    r0, r1 = int(part[rank]), int(part[rank + 1])
+    part = multi.row_partition(rows_end, world)
+    r0, r1 = multi.local_rows(part, rank)
     m = local_block(name, cfg, lens, r0, r1)
     spblas.set_algorithm({"auto": capi.ALG_AUTO, "vector": capi.ALG_VECTOR, "merge": capi.ALG_MERGE,
                           "rowtile": capi.ALG_ROWTILE}[args.alg])
@@ -289,14 +289,11 @@ def main():
             s = spblas.mm(kind, 0, alpha, A, descr, capi.ROW_MAJOR, xd, columns, columns, beta, yd, columns)
         assert s == capi.SUCCESS, capi.STATUS_NAMES[s]
 
-    gather_sizes = [int(part[i + 1] - part[i]) for i in range(world)]
-
     def step():
         nonlocal x_d, xn_d
         step_device(x_d, y_d)
         if iterate:
-            outs = list(torch.split(xn_d, gather_sizes))
-            dist.all_gather(outs, y_d)
+            multi.allgather_rows(y_d, xn_d, part)
             x_d, xn_d = xn_d, x_d
 
     def barrier():
