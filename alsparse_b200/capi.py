@@ -89,6 +89,15 @@ def prototypes():
     p["alphasparse_cuda_get_mat_info"] = (C.c_int, [_H, C.POINTER(MatInfo)])
     p["alphasparse_cuda_get_device_csr"] = (C.c_int, [_H, _HP, _HP, _HP])
     p["alphasparse_cuda_d_csrmv_noalloc"] = (C.c_int, [_I, _I, _I, C.c_double, _P, _P, _P, _P, C.c_double, _P])
+    p["alphasparse_cuda_exchange_create"] = (C.c_int, [_HP, C.c_int, C.c_int, C.c_int, _P])
+    p["alphasparse_cuda_exchange_blob_bytes"] = (C.c_size_t, [])
+    p["alphasparse_cuda_exchange_export"] = (C.c_int, [_H, _P])
+    p["alphasparse_cuda_exchange_connect"] = (C.c_int, [_H, _P])
+    p["alphasparse_cuda_exchange_x"] = (C.c_int, [_H, _HP])
+    p["alphasparse_cuda_exchange_status"] = (C.c_int, [_H, C.POINTER(C.c_int)])
+    p["alphasparse_cuda_exchange_destroy"] = (C.c_int, [_H])
+    p["alphasparse_s_mv_exchange"] = (C.c_int, [C.c_float, _H, MatrixDescr, _H, C.c_float, _P])
+    p["alphasparse_d_mv_exchange"] = (C.c_int, [C.c_double, _H, MatrixDescr, _H, C.c_double, _P])
     p["alphasparse_cuda_profile_kernel"] = (C.c_int, [_H, C.c_int])
     p["alphasparse_cuda_kernel_ms"] = (C.c_int, [_H, C.POINTER(C.c_float)])
     p["alphasparse_cuda_launch_count"] = (C.c_int64, [])

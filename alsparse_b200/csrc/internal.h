@@ -51,6 +51,15 @@ constexpr int kMergeItemsD = ASB_MERGE_IPT_D;  // double
 constexpr int kRowTile = 128;
 constexpr size_t kRowTileMaxSmem = 56 * 1024;
 
+// Where a kernel delivers finished y rows besides its own y: the next-x buffer of every GPU of the
+// row partition (peer-mapped device pointers), row r of this block landing at element row_off + r.
+constexpr int kMaxPeers = 8;
+struct PeerPush {
+    void *dst[kMaxPeers];
+    int n;
+    long long row_off;
+};
+
 struct MergeCoord {
     int row;  // rows fully consumed before this point
     int nz;   // stored elements consumed before this point
@@ -111,7 +120,7 @@ alphasparse_status_t ctx_analyse(DeviceCtx *ctx);
 // ---- kernel launchers (device pointers, enqueue only) ---------------------------------------
 template <typename T>
 alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y,
-                                 cudaStream_t stream);
+                                 cudaStream_t stream, const PeerPush *push = nullptr);
 
 template <typename T>
 alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx,

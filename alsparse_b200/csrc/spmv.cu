@@ -164,11 +164,11 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
     return ok != 0;
 }
 
-template <typename T, bool HAS_BETA>
+template <typename T, bool HAS_BETA, bool PUSH>
 __global__ void __launch_bounds__(kRowTile)
     spmv_rowtile_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
                         const T *__restrict__ val, const T *__restrict__ x, T *__restrict__ y, T alpha,
-                        T beta, int cap, int *__restrict__ status) {
+                        T beta, int cap, int *__restrict__ status, PeerPush push) {
     extern __shared__ __align__(128) unsigned char smem[];
     T *s_val = reinterpret_cast<T *>(smem);
     int *s_col = reinterpret_cast<int *>(smem + (size_t)cap * sizeof(T));
@@ -232,7 +232,12 @@ __global__ void __launch_bounds__(kRowTile)
         T out = alpha * ((acc0 + acc1) + (acc2 + acc3));
         if (HAS_BETA) out = fma(beta, y[r], out);
         __stcs(y + r, out);
+        if (PUSH) {  // neighbouring lanes hold neighbouring rows: coalesced stores into every peer's next x
+#pragma unroll 1
+            for (int p = 0; p < push.n; p++) static_cast<T *>(push.dst[p])[push.row_off + r] = out;
+        }
     }
+    if (PUSH) __threadfence_system();
 }
 
 // ---- merge kernel ----------------------------------------------------------------------------
@@ -247,15 +252,23 @@ __global__ void __launch_bounds__(kRowTile)
 #ifndef ASB_MERGE_MINBLOCKS
 #define ASB_MERGE_MINBLOCKS 1
 #endif
-template <typename T, int NT, int IPT, bool HAS_BETA>
+//
+// Finished rows are collected in shared memory and written out together, so y is read (beta) and
+// written with coalesced accesses.  With PUSH the same values also go, in the same coalesced
+// pattern, into the next-x buffer of every peer GPU (plain stores through peer-mapped pointers):
+// the product and its allgather happen in one kernel.  The only row a tile may not push is its
+// first one when that row began in an earlier tile: its value is completed by the fix-up kernel,
+// which pushes it then.
+template <typename T, int NT, int IPT, bool HAS_BETA, bool PUSH>
 __global__ void __launch_bounds__(NT, ASB_MERGE_MINBLOCKS)
     spmv_merge_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
                       const T *__restrict__ val, const T *__restrict__ x, T *__restrict__ y,
                       T alpha, T beta, const MergeCoord *__restrict__ tile,
-                      int *__restrict__ carry_row, T *__restrict__ carry_val) {
+                      int *__restrict__ carry_row, T *__restrict__ carry_val, PeerPush push) {
     constexpr int TILE = NT * IPT;
     constexpr int NW = NT / 32;
     __shared__ T s_prod[TILE];
+    __shared__ T s_out[TILE];
     __shared__ int s_rend[TILE + 1];
     __shared__ int s_ckey[NT];
     __shared__ T s_cval[NT];
@@ -341,10 +354,7 @@ __global__ void __launch_bounds__(NT, ASB_MERGE_MINBLOCKS)
                     first_row = i;
                     first_val = run;
                 } else {
-                    const int r = r0 + i;
-                    T out = alpha * run;
-                    if (HAS_BETA) out = fma(beta, y[r], out);
-                    y[r] = out;
+                    s_out[i] = run;
                 }
                 run = T(0);
                 i++;
@@ -378,23 +388,35 @@ __global__ void __launch_bounds__(NT, ASB_MERGE_MINBLOCKS)
 
     if (first_row >= 0) {
         if (tid > 0 && s_ckey[tid - 1] == first_row) first_val += s_cval[tid - 1];
-        const int r = r0 + first_row;
-        T out = alpha * first_val;
-        if (HAS_BETA) out = fma(beta, y[r], out);
-        y[r] = out;
+        s_out[first_row] = first_val;
     }
     if (tid == NT - 1) {
         carry_row[blockIdx.x] = r0 + key;
         carry_val[blockIdx.x] = acc;
     }
+    __syncthreads();
+
+    // Every row that ended in this tile now has its sum in s_out[0 .. tile_rows).
+    const bool first_began_earlier = PUSH && (j0 > __ldg(row_ptr + r0));
+    for (int o = tid; o < tile_rows; o += NT) {
+        const int r = r0 + o;
+        T out = alpha * s_out[o];
+        if (HAS_BETA) out = fma(beta, y[r], out);
+        y[r] = out;
+        if (PUSH && !(o == 0 && first_began_earlier)) {
+#pragma unroll 1
+            for (int p = 0; p < push.n; p++) static_cast<T *>(push.dst[p])[push.row_off + r] = out;
+        }
+    }
+    if (PUSH) __threadfence_system();
 }
 
 // Adds the tile leftovers to the rows they belong to.  Consecutive tiles that stopped in the
 // same row form a run; the first thread of a run adds the whole run, front to back.
-template <typename T>
+template <typename T, bool PUSH>
 __global__ void spmv_merge_fixup_kernel(int rows, long long tiles, const int *__restrict__ carry_row,
                                         const T *__restrict__ carry_val, T *__restrict__ y,
-                                        T alpha) {
+                                        T alpha, PeerPush push) {
     const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= tiles) return;
     const int r = carry_row[t];
@@ -402,7 +424,24 @@ __global__ void spmv_merge_fixup_kernel(int rows, long long tiles, const int *__
     if (t > 0 && carry_row[t - 1] == r) return;
     T acc = carry_val[t];
     for (long long u = t + 1; u < tiles && carry_row[u] == r; u++) acc += carry_val[u];
-    y[r] = fma(alpha, acc, y[r]);
+    const T out = fma(alpha, acc, y[r]);
+    y[r] = out;
+    if (PUSH) {
+        for (int p = 0; p < push.n; p++) static_cast<T *>(push.dst[p])[push.row_off + r] = out;
+        __threadfence_system();
+    }
+}
+
+// Copies this GPU's finished y block into the next-x buffer of every peer: the exchange step for
+// the kernels that do not push from their own epilogue.
+template <typename T>
+__global__ void push_rows_kernel(long long rows, const T *__restrict__ y, PeerPush push) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < rows;
+         i += (long long)gridDim.x * blockDim.x) {
+        const T v = y[i];
+        for (int p = 0; p < push.n; p++) static_cast<T *>(push.dst[p])[push.row_off + i] = v;
+    }
+    __threadfence_system();
 }
 
 // y = beta * y for a matrix without stored elements (the reference still scales y).
@@ -641,40 +680,51 @@ static void launch_vector(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cud
     count_launch();
 }
 
-template <typename T, int IPT>
-static void launch_merge(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st) {
+template <typename T, int IPT, bool HAS_BETA, bool PUSH>
+static void launch_merge_as(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st,
+                            const PeerPush &push) {
     const T *val = static_cast<const T *>(ctx->d_val);
     T *carry = static_cast<T *>(ctx->d_carry_val);
     const unsigned blocks = (unsigned)ctx->merge_tiles;
     if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
-    if (beta == T(0))
-        spmv_merge_kernel<T, kMergeThreads, IPT, false><<<blocks, kMergeThreads, 0, st>>>(
-            (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta, ctx->d_tile,
-            ctx->d_carry_row, carry);
-    else
-        spmv_merge_kernel<T, kMergeThreads, IPT, true><<<blocks, kMergeThreads, 0, st>>>(
-            (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta, ctx->d_tile,
-            ctx->d_carry_row, carry);
+    spmv_merge_kernel<T, kMergeThreads, IPT, HAS_BETA, PUSH><<<blocks, kMergeThreads, 0, st>>>(
+        (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta, ctx->d_tile, ctx->d_carry_row,
+        carry, push);
     if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
     const unsigned fblocks = (unsigned)((ctx->merge_tiles + 255) / 256);
-    spmv_merge_fixup_kernel<T><<<fblocks, 256, 0, st>>>((int)ctx->rows, ctx->merge_tiles,
-                                                       ctx->d_carry_row, carry, y, alpha);
+    spmv_merge_fixup_kernel<T, PUSH><<<fblocks, 256, 0, st>>>((int)ctx->rows, ctx->merge_tiles,
+                                                             ctx->d_carry_row, carry, y, alpha, push);
     count_launch(2);
+}
+
+template <typename T, int IPT>
+static void launch_merge(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st,
+                         const PeerPush *push) {
+    const PeerPush none{};
+    if (push) {
+        if (beta == T(0)) launch_merge_as<T, IPT, false, true>(ctx, alpha, x, beta, y, st, *push);
+        else launch_merge_as<T, IPT, true, true>(ctx, alpha, x, beta, y, st, *push);
+    } else {
+        if (beta == T(0)) launch_merge_as<T, IPT, false, false>(ctx, alpha, x, beta, y, st, none);
+        else launch_merge_as<T, IPT, true, false>(ctx, alpha, x, beta, y, st, none);
+    }
 }
 
 template <typename T>
 static alphasparse_status_t launch_rowtile(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y,
-                                           cudaStream_t st) {
+                                           cudaStream_t st, const PeerPush *pushp) {
     const int cap = (int)((ctx->max_tile_span + 3) & ~3ll);
     const size_t smem = rowtile_smem_bytes(ctx);
     const T *val = static_cast<const T *>(ctx->d_val);
     const unsigned blocks = (unsigned)((ctx->rows + kRowTile - 1) / kRowTile);
-    auto k0 = spmv_rowtile_kernel<T, false>;
-    auto k1 = spmv_rowtile_kernel<T, true>;
-    auto kernel = beta == T(0) ? k0 : k1;
+    const PeerPush push = pushp ? *pushp : PeerPush{};
+    const int which = (beta == T(0) ? 0 : 1) + (pushp ? 2 : 0);
+    decltype(&spmv_rowtile_kernel<T, false, false>) variants[4] = {
+        spmv_rowtile_kernel<T, false, false>, spmv_rowtile_kernel<T, true, false>,
+        spmv_rowtile_kernel<T, false, true>, spmv_rowtile_kernel<T, true, true>};
+    auto kernel = variants[which];
     // The opt-in limit is a property of the kernel, shared by all handles: only ever raise it.
-    static std::atomic<size_t> granted[2] = {{0}, {0}};
-    const int which = beta == T(0) ? 0 : 1;
+    static std::atomic<size_t> granted[4] = {{0}, {0}, {0}, {0}};
     if (smem > 48 * 1024 && granted[which].load() < smem) {
         ASB_CUDA_OR(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)kRowTileMaxSmem),
@@ -683,7 +733,7 @@ static alphasparse_status_t launch_rowtile(DeviceCtx *ctx, T alpha, const T *x, 
     }
     if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
     kernel<<<blocks, kRowTile, smem, st>>>((int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha,
-                                           beta, cap, ctx->d_status);
+                                           beta, cap, ctx->d_status, push);
     if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
     count_launch();
     return ALPHA_SPARSE_STATUS_SUCCESS;
@@ -691,18 +741,21 @@ static alphasparse_status_t launch_rowtile(DeviceCtx *ctx, T alpha, const T *x, 
 
 template <typename T>
 alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y,
-                                 cudaStream_t st) {
+                                 cudaStream_t st, const PeerPush *push) {
     if (ctx->rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+    bool pushed = false;  // whether the kernel's own epilogue delivered y to the peers
     if (ctx->nnz == 0) {
         const unsigned blocks = (unsigned)((ctx->rows + 255) / 256);
         scale_kernel<T><<<blocks, 256, 0, st>>>(ctx->rows, y, beta);
         count_launch();
     } else if (ctx->algorithm == ALPHA_SPARSE_CUDA_ALG_MERGE) {
         constexpr int IPT = sizeof(T) == 8 ? kMergeItemsD : kMergeItemsS;
-        launch_merge<T, IPT>(ctx, alpha, x, beta, y, st);
+        launch_merge<T, IPT>(ctx, alpha, x, beta, y, st, push);
+        pushed = true;
     } else if (ctx->algorithm == ALPHA_SPARSE_CUDA_ALG_ROWTILE) {
-        alphasparse_status_t s = launch_rowtile<T>(ctx, alpha, x, beta, y, st);
+        alphasparse_status_t s = launch_rowtile<T>(ctx, alpha, x, beta, y, st, push);
         if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        pushed = true;
     } else {
         switch (ctx->lanes) {
             case 1: launch_vector<T, 1>(ctx, alpha, x, beta, y, st); break;
@@ -713,14 +766,18 @@ alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T 
             default: launch_vector<T, 32>(ctx, alpha, x, beta, y, st); break;
         }
     }
+    if (push && !pushed) {
+        push_rows_kernel<T><<<148 * 4, 256, 0, st>>>(ctx->rows, y, *push);
+        count_launch();
+    }
     ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
 template alphasparse_status_t launch_spmv<float>(DeviceCtx *, float, const float *, float, float *,
-                                                 cudaStream_t);
+                                                 cudaStream_t, const PeerPush *);
 template alphasparse_status_t launch_spmv<double>(DeviceCtx *, double, const double *, double,
-                                                  double *, cudaStream_t);
+                                                  double *, cudaStream_t, const PeerPush *);
 
 }  // namespace asb
 
@@ -826,14 +883,17 @@ extern "C" alphasparse_status_t alphasparse_cuda_d_csrmv_noalloc(
                 ALPHA_SPARSE_STATUS_EXECUTION_FAILED);  // 0x7f7f7f7f: beyond any row, ignored by the fix-up
     merge_tiles_kernel<<<(unsigned)((tiles + 1 + 255) / 256), 256, 0, st>>>(rows, nnz, d_row_ptr, kNoAllocItems,
                                                                           tiles, tile);
+    const PeerPush none{};
     if (beta == 0.0)
-        spmv_merge_kernel<double, kMergeThreads, kMergeItemsD, false><<<(unsigned)tiles, kMergeThreads, 0, st>>>(
-            rows, d_row_ptr, d_col_indx, d_values, d_x, d_y, alpha, beta, tile, carry_row, carry_val);
+        spmv_merge_kernel<double, kMergeThreads, kMergeItemsD, false, false>
+            <<<(unsigned)tiles, kMergeThreads, 0, st>>>(rows, d_row_ptr, d_col_indx, d_values, d_x, d_y, alpha,
+                                                        beta, tile, carry_row, carry_val, none);
     else
-        spmv_merge_kernel<double, kMergeThreads, kMergeItemsD, true><<<(unsigned)tiles, kMergeThreads, 0, st>>>(
-            rows, d_row_ptr, d_col_indx, d_values, d_x, d_y, alpha, beta, tile, carry_row, carry_val);
-    spmv_merge_fixup_kernel<double><<<(unsigned)((tiles + 255) / 256), 256, 0, st>>>(rows, tiles, carry_row,
-                                                                                   carry_val, d_y, alpha);
+        spmv_merge_kernel<double, kMergeThreads, kMergeItemsD, true, false>
+            <<<(unsigned)tiles, kMergeThreads, 0, st>>>(rows, d_row_ptr, d_col_indx, d_values, d_x, d_y, alpha,
+                                                        beta, tile, carry_row, carry_val, none);
+    spmv_merge_fixup_kernel<double, false><<<(unsigned)((tiles + 255) / 256), 256, 0, st>>>(
+        rows, tiles, carry_row, carry_val, d_y, alpha, none);
     count_launch(3);
     ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     return ALPHA_SPARSE_STATUS_SUCCESS;

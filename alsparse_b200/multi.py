@@ -10,11 +10,13 @@ next x (iterated SpMV): then every rank's y block is gathered into every rank's 
 Only host-side logic lives here; it runs unchanged over the ``gloo`` backend on CPU tensors, which
 is how it is tested without GPUs.
 """
+import ctypes as C
+
 import numpy as np
 import torch
 import torch.distributed as dist
 
-from . import spblas
+from . import capi, spblas
 
 
 def row_partition(rows_end, world):
@@ -75,3 +77,61 @@ class IteratedSpmv:
         allgather_rows(self.y_local, self.x_next, self.part, self.group)
         self.x, self.x_next = self.x_next, self.x
         return self.x
+
+
+class FusedExchange:
+    """The product-plus-allgather in one kernel (``alphasparse_?_mv_exchange``): every rank's SpMV
+    stores its finished y rows straight into the next-x buffer of every GPU over NVLink, then the
+    ranks signal each other and the buffers swap.  CUDA only; set-up exchanges 192-byte IPC blobs
+    through ``torch.distributed`` (any backend)."""
+
+    def __init__(self, kind, part, rank, world, group=None):
+        lib = capi.load()
+        self.kind, self.part, self.rank, self.world = kind, np.ascontiguousarray(part, dtype=np.int32), rank, world
+        self.handle = C.c_void_p()
+        dt = capi.FLOAT if kind == "s" else capi.DOUBLE
+        st = lib.alphasparse_cuda_exchange_create(C.byref(self.handle), dt, rank, world, self.part.ctypes.data)
+        assert st == capi.SUCCESS, (capi.STATUS_NAMES[st], spblas.last_error())
+        nbytes = lib.alphasparse_cuda_exchange_blob_bytes()
+        blob = (C.c_ubyte * nbytes)()
+        st = lib.alphasparse_cuda_exchange_export(self.handle, blob)
+        assert st == capi.SUCCESS, (capi.STATUS_NAMES[st], spblas.last_error())
+        if world > 1:
+            blobs = [None] * world
+            dist.all_gather_object(blobs, bytes(blob), group=group)
+        else:
+            blobs = [bytes(blob)]
+        joined = b"".join(blobs)
+        st = lib.alphasparse_cuda_exchange_connect(self.handle, joined)
+        assert st == capi.SUCCESS, (capi.STATUS_NAMES[st], spblas.last_error())
+        if world > 1:
+            dist.barrier(group=group)  # nobody starts pushing before every rank has mapped every buffer
+
+    def x_ptr(self):
+        p = C.c_void_p()
+        st = capi.load().alphasparse_cuda_exchange_x(self.handle, C.byref(p))
+        assert st == capi.SUCCESS
+        return p.value
+
+    def x_tensor(self):
+        """The current x as a torch view of the library's buffer (valid until the next step)."""
+        n = int(self.part[-1])
+        typestr = "<f4" if self.kind == "s" else "<f8"
+
+        class _Raw:
+            __cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (self.x_ptr(), False), "version": 2}
+        return torch.as_tensor(_Raw(), device="cuda")
+
+    def step(self, alpha, A, beta, y_local):
+        fn = getattr(capi.load(), f"alphasparse_{self.kind}_mv_exchange")
+        return fn(alpha, A, spblas.descr(), self.handle, beta, spblas._ptr(y_local))
+
+    def status(self):
+        code = C.c_int()
+        st = capi.load().alphasparse_cuda_exchange_status(self.handle, C.byref(code))
+        return st, code.value
+
+    def destroy(self):
+        if self.handle:
+            capi.load().alphasparse_cuda_exchange_destroy(self.handle)
+            self.handle = C.c_void_p()

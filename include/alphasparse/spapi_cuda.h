@@ -84,6 +84,36 @@ alphasparse_status_t alphasparse_cuda_d_csrmv_noalloc(ALPHA_INT rows, ALPHA_INT 
                                                       const double *d_values, const double *d_x,
                                                       double beta, double *d_y);
 
+/* ---- iterated SpMV over the GPUs of one box (one process per GPU) -----------------------------
+ * No counterpart in the reference (it has no multi-device path).  A square matrix is split into
+ * contiguous row blocks by balanced_partition_row_by_nnz; rank g creates an ordinary handle from its
+ * block (local offsets, global columns).  An exchange object holds two full-length x buffers per GPU.
+ * alphasparse_?_mv_exchange computes y = alpha*A_block*x + beta*y with x = the current buffer and, in
+ * the same kernels, stores every finished y row into the NEXT x buffer of every GPU over NVLink
+ * (peer-mapped pointers); it then signals and awaits all peers (bounded wait) and the buffers swap.
+ * After the call the current x is the gathered y of all ranks.  Every rank must make the same sequence
+ * of calls.  Set-up: create on every rank, export the 192-byte blob, exchange the blobs by any means
+ * (e.g. an allgather of bytes), connect with all blobs in rank order. */
+typedef struct alphasparse_cuda_exchange *alphasparse_cuda_exchange_t;
+
+alphasparse_status_t alphasparse_cuda_exchange_create(alphasparse_cuda_exchange_t *ex,
+                                                      alphasparse_datatype_t datatype, int rank, int world,
+                                                      const ALPHA_INT *part /* world + 1 row boundaries */);
+size_t alphasparse_cuda_exchange_blob_bytes(void);
+alphasparse_status_t alphasparse_cuda_exchange_export(alphasparse_cuda_exchange_t ex, void *blob);
+alphasparse_status_t alphasparse_cuda_exchange_connect(alphasparse_cuda_exchange_t ex, const void *blobs);
+/* Device pointer of the current x (part[world] elements): fill it before the first step, read it after. */
+alphasparse_status_t alphasparse_cuda_exchange_x(alphasparse_cuda_exchange_t ex, void **x);
+/* Waits for the stream and reports whether any bounded wait ran out (status 3) since creation. */
+alphasparse_status_t alphasparse_cuda_exchange_status(alphasparse_cuda_exchange_t ex, int *status);
+alphasparse_status_t alphasparse_cuda_exchange_destroy(alphasparse_cuda_exchange_t ex);
+alphasparse_status_t alphasparse_s_mv_exchange(const float alpha, const alphasparse_matrix_t A,
+                                               const struct alpha_matrix_descr descr,
+                                               alphasparse_cuda_exchange_t ex, const float beta, float *y);
+alphasparse_status_t alphasparse_d_mv_exchange(const double alpha, const alphasparse_matrix_t A,
+                                               const struct alpha_matrix_descr descr,
+                                               alphasparse_cuda_exchange_t ex, const double beta, double *y);
+
 /* Kernel timing for benchmarks.  With profiling enabled on a handle, every mv / mm call on it
  * brackets its dominant kernel (the SpMV or SpMM kernel itself, not the small fix-up or any
  * copies) with CUDA events on the library stream; alphasparse_cuda_kernel_ms waits for the
