@@ -220,6 +220,9 @@ def main():
     ap.add_argument("--rows-log2", type=int, default=None, help="shrink the matrix (development only)")
     ap.add_argument("--grid", type=int, default=None, help="shrink the stencil grid (development only)")
     ap.add_argument("--alg", default="auto", choices=["auto", "vector", "merge", "rowtile"])
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+                    help="iterated workload with several GPUs: y reaches the next x from inside the SpMV kernels "
+                         "over peer memory (fused) or by a NCCL allgather after them (nccl)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -281,6 +284,11 @@ def main():
     y_d = y0_h.cuda()
     xn_d = torch.empty_like(x_d) if iterate else None
     descr = spblas.descr()
+    fused = None
+    if iterate and args.exchange == "fused":
+        fused = multi.FusedExchange(kind, part, rank, world)
+        fused.x_tensor().copy_(x_d)
+        torch.cuda.synchronize()
 
     def step_device(xd, yd):
         if op == "mv":
@@ -291,6 +299,10 @@ def main():
 
     def step():
         nonlocal x_d, xn_d
+        if fused is not None:
+            s = fused.step(alpha, A, beta, y_d)
+            assert s == capi.SUCCESS, capi.STATUS_NAMES[s]
+            return
         step_device(x_d, y_d)
         if iterate:
             multi.allgather_rows(y_d, xn_d, part)
@@ -391,7 +403,10 @@ def main():
             "config": {"workload": name + (" (REDUCED SIZE: development run)" if reduced else ""), "rows": rows,
                        "cols": cols, "nnz": nnz_total, "alpha": alpha, "beta": beta, "columns": columns,
                        "partition": f"nnz-balanced contiguous row blocks over {world} GPU(s), x replicated",
-                       "collective": "allgather of y into the next x each step" if iterate else "none",
+                       "collective": ("none" if not iterate else
+                                      "allgather of y into the next x each step: " +
+                                      ("peer stores from the SpMV kernels + flag exchange" if fused is not None
+                                       else "NCCL all_gather after the SpMV")),
                        "algorithm": ["auto", "vector", "merge", "rowtile"][info.algorithm], "lanes_per_row": info.lanes_per_row,
                        "l2": f"inputs ({nbytes / 1e6:.0f} MB per step) exceed the 126 MB L2; no flush between steps",
                        "algorithmic_bytes_per_step": nbytes},
@@ -411,6 +426,10 @@ def main():
             line["cpu_baseline"] = dict(value=gbs, unit="GB/s", gflops=gfl, ms_per_step=ms, **desc)
         print(json.dumps(line), flush=True)
 
+    if fused is not None:
+        st_, code = fused.status()
+        assert code == 0, f"a bounded wait of the exchange ran out (status {code})"
+        fused.destroy()
     spblas.destroy(A)
     if world > 1:
         dist.barrier()
