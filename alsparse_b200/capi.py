@@ -93,6 +93,7 @@ def prototypes():
     p["alphasparse_cuda_exchange_blob_bytes"] = (C.c_size_t, [])
     p["alphasparse_cuda_exchange_export"] = (C.c_int, [_H, _P])
     p["alphasparse_cuda_exchange_connect"] = (C.c_int, [_H, _P])
+    p["alphasparse_cuda_exchange_set_mode"] = (C.c_int, [_H, C.c_int])
     p["alphasparse_cuda_exchange_x"] = (C.c_int, [_H, _HP])
     p["alphasparse_cuda_exchange_status"] = (C.c_int, [_H, C.POINTER(C.c_int)])
     p["alphasparse_cuda_exchange_destroy"] = (C.c_int, [_H])

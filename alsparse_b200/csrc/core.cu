@@ -66,6 +66,7 @@ void ctx_destroy(DeviceCtx *c) {
     cudaFree(c->d_tile);
     cudaFree(c->d_carry_row);
     cudaFree(c->d_carry_val);
+    cudaFree(c->d_chunk_done);
     cudaFree(c->d_x_stage);
     cudaFree(c->d_y_stage);
     cudaFree(c->d_status);

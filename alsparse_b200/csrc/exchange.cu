@@ -34,6 +34,7 @@ struct Exchange {
     unsigned long long step = 0;
     int cur = 0;                               // index of the buffer holding the current x
     bool connected = false;
+    int mode = 0;                              // alphasparse_cuda_exchange_set_mode
 };
 
 // One thread per peer: publish our arrival for `step`, then wait for theirs.
@@ -87,6 +88,7 @@ static alphasparse_status_t mv_exchange(T alpha, const alphasparse_matrix_t A, s
     PeerPush push{};
     push.n = e->world;
     push.row_off = e->part[e->rank];
+    push.after = e->mode == 1;
     for (int p = 0; p < e->world; p++) push.dst[p] = e->peer_xbuf[nxt][p];
     alphasparse_status_t s = launch_spmv<T>(c, alpha, static_cast<const T *>(e->xbuf[e->cur]), beta, y, st, &push);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
@@ -184,6 +186,14 @@ alphasparse_status_t alphasparse_cuda_exchange_connect(alphasparse_cuda_exchange
     ASB_CUDA_OR(cudaMemcpy(e->counters + kMaxPeers, table, sizeof(table), cudaMemcpyHostToDevice),
                 ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     e->connected = true;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+alphasparse_status_t alphasparse_cuda_exchange_set_mode(alphasparse_cuda_exchange_t h, int mode) {
+    Exchange *e = ex_of(h);
+    if (!e) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+    if (mode != 0 && mode != 1) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    e->mode = mode;
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 

@@ -58,7 +58,15 @@ struct PeerPush {
     void *dst[kMaxPeers];
     int n;
     long long row_off;
+    int after;  // 1: deliver with a separate bulk copy after the product instead of from inside it
+    // merge kernel only: its delivering blocks and their progress counters
+    int tiles, chunk_tiles, pushers;
+    unsigned *chunk_done;  // tiles finished per chunk, reset by the delivering block
+    int *status;           // set to 4 when a delivering block gives up waiting
+    long long max_polls;
 };
+constexpr int kPushChunkTiles = 128;  // tiles per delivered chunk
+constexpr int kPushBlocks = 32;       // delivering blocks in front of the compute blocks
 
 struct MergeCoord {
     int row;  // rows fully consumed before this point
@@ -91,6 +99,7 @@ struct DeviceCtx {
     MergeCoord *d_tile = nullptr;  // merge_tiles + 1
     int *d_carry_row = nullptr;    // merge_tiles
     void *d_carry_val = nullptr;   // merge_tiles
+    unsigned *d_chunk_done = nullptr;  // per chunk of kPushChunkTiles tiles (exchange calls only)
 
     int *d_status = nullptr;  // error word set by kernels whose bounded waits ran out (0 = fine)
 

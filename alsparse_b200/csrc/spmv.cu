@@ -21,6 +21,8 @@
 #include <limits.h>
 #include <stdio.h>
 
+#include <type_traits>
+
 #include "internal.h"
 
 namespace asb {
@@ -237,7 +239,6 @@ __global__ void __launch_bounds__(kRowTile)
             for (int p = 0; p < push.n; p++) static_cast<T *>(push.dst[p])[push.row_off + r] = out;
         }
     }
-    if (PUSH) __threadfence_system();
 }
 
 // ---- merge kernel ----------------------------------------------------------------------------
@@ -250,25 +251,118 @@ __global__ void __launch_bounds__(kRowTile)
 // one block reduction, nothing staged.  Any other tile stages its products in shared memory
 // in load order and lets every thread walk its IPT consecutive merge items.
 #ifndef ASB_MERGE_MINBLOCKS
-#define ASB_MERGE_MINBLOCKS 1
+#define ASB_MERGE_MINBLOCKS 5
 #endif
 //
-// Finished rows are collected in shared memory and written out together, so y is read (beta) and
-// written with coalesced accesses.  With PUSH the same values also go, in the same coalesced
-// pattern, into the next-x buffer of every peer GPU (plain stores through peer-mapped pointers):
-// the product and its allgather happen in one kernel.  The only row a tile may not push is its
-// first one when that row began in an earlier tile: its value is completed by the fix-up kernel,
-// which pushes it then.
+// With PUSH the same grid also performs the allgather of y.  Its first `push.pushers` blocks
+// compute nothing: block k takes chunks k, k + pushers, ... of `push.chunk_tiles` consecutive
+// tiles, waits (bounded) until the compute blocks have counted all tiles of the chunk as done,
+// adds the carries of rows that lie wholly inside the chunk, and then copies the chunk's finished
+// y rows into the next-x buffer of every GPU with wide coalesced stores through peer-mapped
+// pointers.  So the transfer of chunk c over NVLink runs while later chunks are still being
+// multiplied, and the stores are large and contiguous (pushing each tile's few rows from the
+// compute blocks themselves was measured at ~100 GB/s; a bulk copy reaches several times that).
+// Rows whose carries cross a chunk boundary are finished, and pushed, by the fix-up kernel.
+// Compute blocks never wait on anything, so the waiting blocks cannot starve them.
+struct NoPush {};  // kernels instantiated without PUSH carry no delivery arguments at all
+template <bool PUSH>
+using PushArg = typename std::conditional<PUSH, PeerPush, NoPush>::type;
+
+__device__ __forceinline__ void merge_tile_done(const NoPush &, int) {}
+template <typename T>
+__device__ __forceinline__ void merge_pusher(int, const int *, const MergeCoord *, const T *, T *, T,
+                                             const NoPush &) {}
+__device__ __forceinline__ int pusher_blocks(const NoPush &) { return 0; }
+__device__ __forceinline__ int pusher_blocks(const PeerPush &p) { return p.pushers; }
+
+__device__ __forceinline__ void merge_tile_done(const PeerPush &push, int tile_id) {
+    __threadfence();  // this thread's y / carry writes before the count
+    __syncthreads();
+    if (threadIdx.x == 0) atomicAdd(push.chunk_done + tile_id / push.chunk_tiles, 1u);
+}
+
+template <typename T>
+__device__ __noinline__ void merge_pusher(int rows, const int *__restrict__ row_ptr,
+                                          const MergeCoord *__restrict__ tile,
+                                          const T *__restrict__ carry_val, T *__restrict__ y, T alpha,
+                                          const PeerPush &push) {
+    __shared__ int s_ok;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const int nchunks = (push.tiles + push.chunk_tiles - 1) / push.chunk_tiles;
+    for (int c = blockIdx.x; c < nchunks; c += push.pushers) {
+        const int t0 = c * push.chunk_tiles, t1 = min(t0 + push.chunk_tiles, push.tiles);
+        if (tid == 0) {
+            const unsigned want = (unsigned)(t1 - t0);
+            volatile unsigned *cnt = push.chunk_done + c;
+            long long polls = 0;
+            int ok = 1;
+            while (*cnt < want) {
+                if (++polls > push.max_polls) {
+                    atomicExch(push.status, 4);
+                    ok = 0;
+                    break;
+                }
+                __nanosleep(100);
+            }
+            if (ok) *cnt = 0;  // ready for the next call
+            __threadfence();
+            s_ok = ok;
+        }
+        __syncthreads();
+        if (!s_ok) return;  // uniform: give up, the host will see the status word
+
+        // Carries of rows that begin and end inside this chunk (tile t stops in row tile[t+1].row).
+        const int row_hi = tile[t1].row;  // rows below this one ended in the chunk
+        for (int t = t0 + tid; t < t1; t += nt) {
+            const int r = tile[t + 1].row;
+            if (r >= row_hi || r >= rows) continue;           // ends in a later chunk
+            if (t > 0 && tile[t].row == r) continue;          // not the first tile of its run
+            T acc = __ldcg(carry_val + t);  // written by other blocks of this grid: read at L2
+            for (int u = t + 1; tile[u + 1].row == r; u++) acc += __ldcg(carry_val + u);
+            y[r] = fma(alpha, acc, __ldcg(y + r));
+        }
+        __syncthreads();
+
+        // Finished rows of the chunk: all rows that ended in it, except the first one when it began
+        // in an earlier chunk (the fix-up kernel completes and pushes that one).
+        int ra = tile[t0].row;
+        if (ra < rows && tile[t0].nz > row_ptr[ra]) ra++;
+        const int n = row_hi - ra;
+        if (n > 0) {
+            const T *src = y + ra;
+            for (int p = 0; p < push.n; p++) {
+                T *dst = static_cast<T *>(push.dst[p]) + push.row_off + ra;
+                // 16-byte body where source and destination are equally aligned, scalars around it
+                const int per = 16 / (int)sizeof(T);
+                const uintptr_t sa = (uintptr_t)src, da = (uintptr_t)dst;
+                if ((sa & 15) == (da & 15)) {
+                    int head = (int)(((16 - (sa & 15)) & 15) / sizeof(T));
+                    if (head > n) head = n;
+                    const int body = (n - head) / per;
+                    for (int i = tid; i < head; i += nt) dst[i] = __ldcg(src + i);
+                    const int4 *s4 = reinterpret_cast<const int4 *>(src + head);
+                    int4 *d4 = reinterpret_cast<int4 *>(dst + head);
+                    for (int i = tid; i < body; i += nt) d4[i] = __ldcg(s4 + i);
+                    for (int i = head + body * per + tid; i < n; i += nt) dst[i] = __ldcg(src + i);
+                } else {
+                    for (int i = tid; i < n; i += nt) dst[i] = __ldcg(src + i);
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
 template <typename T, int NT, int IPT, bool HAS_BETA, bool PUSH>
 __global__ void __launch_bounds__(NT, ASB_MERGE_MINBLOCKS)
     spmv_merge_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
                       const T *__restrict__ val, const T *__restrict__ x, T *__restrict__ y,
                       T alpha, T beta, const MergeCoord *__restrict__ tile,
-                      int *__restrict__ carry_row, T *__restrict__ carry_val, PeerPush push) {
+                      int *__restrict__ carry_row, T *__restrict__ carry_val,
+                      const __grid_constant__ PushArg<PUSH> push) {
     constexpr int TILE = NT * IPT;
     constexpr int NW = NT / 32;
     __shared__ T s_prod[TILE];
-    __shared__ T s_out[TILE];
     __shared__ int s_rend[TILE + 1];
     __shared__ int s_ckey[NT];
     __shared__ T s_cval[NT];
@@ -277,7 +371,12 @@ __global__ void __launch_bounds__(NT, ASB_MERGE_MINBLOCKS)
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, wid = tid >> 5;
-    const MergeCoord c0 = tile[blockIdx.x], c1 = tile[blockIdx.x + 1];
+    if (PUSH && (int)blockIdx.x < pusher_blocks(push)) {  // the first blocks of the grid deliver, the rest compute
+        merge_pusher<T>(rows, row_ptr, tile, carry_val, y, alpha, push);
+        return;
+    }
+    const int tile_id = (int)blockIdx.x - pusher_blocks(push);
+    const MergeCoord c0 = tile[tile_id], c1 = tile[tile_id + 1];
     const int r0 = c0.row, j0 = c0.nz;
     const int tile_rows = c1.row - r0, tile_nnz = c1.nz - j0;
 
@@ -308,9 +407,10 @@ __global__ void __launch_bounds__(NT, ASB_MERGE_MINBLOCKS)
             T total = s_wval[0];
 #pragma unroll
             for (int w = 1; w < NW; w++) total += s_wval[w];
-            carry_row[blockIdx.x] = r0;
-            carry_val[blockIdx.x] = total;
+            carry_row[tile_id] = r0;
+            carry_val[tile_id] = total;
         }
+        if (PUSH) merge_tile_done(push, tile_id);
         return;
     }
 
@@ -354,7 +454,10 @@ __global__ void __launch_bounds__(NT, ASB_MERGE_MINBLOCKS)
                     first_row = i;
                     first_val = run;
                 } else {
-                    s_out[i] = run;
+                    const int r = r0 + i;
+                    T out = alpha * run;
+                    if (HAS_BETA) out = fma(beta, y[r], out);
+                    y[r] = out;
                 }
                 run = T(0);
                 i++;
@@ -388,31 +491,22 @@ __global__ void __launch_bounds__(NT, ASB_MERGE_MINBLOCKS)
 
     if (first_row >= 0) {
         if (tid > 0 && s_ckey[tid - 1] == first_row) first_val += s_cval[tid - 1];
-        s_out[first_row] = first_val;
-    }
-    if (tid == NT - 1) {
-        carry_row[blockIdx.x] = r0 + key;
-        carry_val[blockIdx.x] = acc;
-    }
-    __syncthreads();
-
-    // Every row that ended in this tile now has its sum in s_out[0 .. tile_rows).
-    const bool first_began_earlier = PUSH && (j0 > __ldg(row_ptr + r0));
-    for (int o = tid; o < tile_rows; o += NT) {
-        const int r = r0 + o;
-        T out = alpha * s_out[o];
+        const int r = r0 + first_row;
+        T out = alpha * first_val;
         if (HAS_BETA) out = fma(beta, y[r], out);
         y[r] = out;
-        if (PUSH && !(o == 0 && first_began_earlier)) {
-#pragma unroll 1
-            for (int p = 0; p < push.n; p++) static_cast<T *>(push.dst[p])[push.row_off + r] = out;
-        }
     }
-    if (PUSH) __threadfence_system();
+    if (tid == NT - 1) {
+        carry_row[tile_id] = r0 + key;
+        carry_val[tile_id] = acc;
+    }
+    if (PUSH) merge_tile_done(push, tile_id);
 }
 
 // Adds the tile leftovers to the rows they belong to.  Consecutive tiles that stopped in the
 // same row form a run; the first thread of a run adds the whole run, front to back.
+// With PUSH the delivering blocks of the merge kernel have already handled every run that begins
+// and ends in one chunk; this kernel takes the runs that cross a chunk boundary and pushes those rows.
 template <typename T, bool PUSH>
 __global__ void spmv_merge_fixup_kernel(int rows, long long tiles, const int *__restrict__ carry_row,
                                         const T *__restrict__ carry_val, T *__restrict__ y,
@@ -423,12 +517,14 @@ __global__ void spmv_merge_fixup_kernel(int rows, long long tiles, const int *__
     if (r >= rows) return;
     if (t > 0 && carry_row[t - 1] == r) return;
     T acc = carry_val[t];
-    for (long long u = t + 1; u < tiles && carry_row[u] == r; u++) acc += carry_val[u];
+    long long u = t + 1;
+    for (; u < tiles && carry_row[u] == r; u++) acc += carry_val[u];
+    // u is now the tile in which row r ends
+    if (PUSH && t / push.chunk_tiles == u / push.chunk_tiles && u < tiles) return;
     const T out = fma(alpha, acc, y[r]);
     y[r] = out;
     if (PUSH) {
         for (int p = 0; p < push.n; p++) static_cast<T *>(push.dst[p])[push.row_off + r] = out;
-        __threadfence_system();
     }
 }
 
@@ -441,7 +537,6 @@ __global__ void push_rows_kernel(long long rows, const T *__restrict__ y, PeerPu
         const T v = y[i];
         for (int p = 0; p < push.n; p++) static_cast<T *>(push.dst[p])[push.row_off + i] = v;
     }
-    __threadfence_system();
 }
 
 // y = beta * y for a matrix without stored elements (the reference still scales y).
@@ -647,6 +742,10 @@ alphasparse_status_t ctx_analyse(DeviceCtx *ctx) {
                     ALPHA_SPARSE_STATUS_ALLOC_FAILED);
         ASB_CUDA_OR(cudaMalloc(&ctx->d_carry_val, tsz * (size_t)ctx->merge_tiles),
                     ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        const size_t nchunks = (size_t)(ctx->merge_tiles + kPushChunkTiles - 1) / kPushChunkTiles;
+        ASB_CUDA_OR(cudaMalloc(&ctx->d_chunk_done, sizeof(unsigned) * nchunks), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        ASB_CUDA_OR(cudaMemsetAsync(ctx->d_chunk_done, 0, sizeof(unsigned) * nchunks, st),
+                    ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
         ctx->device_bytes += (int64_t)(sizeof(MergeCoord) * (size_t)(ctx->merge_tiles + 1) +
                                        (sizeof(int) + tsz) * (size_t)ctx->merge_tiles);
         const int threads = 256;
@@ -685,11 +784,13 @@ static void launch_merge_as(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, c
                             const PeerPush &push) {
     const T *val = static_cast<const T *>(ctx->d_val);
     T *carry = static_cast<T *>(ctx->d_carry_val);
-    const unsigned blocks = (unsigned)ctx->merge_tiles;
+    const unsigned blocks = (unsigned)ctx->merge_tiles + (PUSH ? (unsigned)push.pushers : 0u);
     if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
+    PushArg<PUSH> arg{};
+    if constexpr (PUSH) arg = push;
     spmv_merge_kernel<T, kMergeThreads, IPT, HAS_BETA, PUSH><<<blocks, kMergeThreads, 0, st>>>(
         (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta, ctx->d_tile, ctx->d_carry_row,
-        carry, push);
+        carry, arg);
     if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
     const unsigned fblocks = (unsigned)((ctx->merge_tiles + 255) / 256);
     spmv_merge_fixup_kernel<T, PUSH><<<fblocks, 256, 0, st>>>((int)ctx->rows, ctx->merge_tiles,
@@ -701,9 +802,23 @@ template <typename T, int IPT>
 static void launch_merge(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st,
                          const PeerPush *push) {
     const PeerPush none{};
+    if (push && push->after) {  // deliver with one bulk copy kernel once the product is complete
+        if (beta == T(0)) launch_merge_as<T, IPT, false, false>(ctx, alpha, x, beta, y, st, none);
+        else launch_merge_as<T, IPT, true, false>(ctx, alpha, x, beta, y, st, none);
+        push_rows_kernel<T><<<148 * 4, 256, 0, st>>>(ctx->rows, y, *push);
+        count_launch();
+        return;
+    }
     if (push) {
-        if (beta == T(0)) launch_merge_as<T, IPT, false, true>(ctx, alpha, x, beta, y, st, *push);
-        else launch_merge_as<T, IPT, true, true>(ctx, alpha, x, beta, y, st, *push);
+        PeerPush p = *push;
+        p.tiles = (int)ctx->merge_tiles;
+        p.chunk_tiles = kPushChunkTiles;
+        p.pushers = kPushBlocks;
+        p.chunk_done = ctx->d_chunk_done;
+        p.status = ctx->d_status;
+        p.max_polls = 8LL << 20;
+        if (beta == T(0)) launch_merge_as<T, IPT, false, true>(ctx, alpha, x, beta, y, st, p);
+        else launch_merge_as<T, IPT, true, true>(ctx, alpha, x, beta, y, st, p);
     } else {
         if (beta == T(0)) launch_merge_as<T, IPT, false, false>(ctx, alpha, x, beta, y, st, none);
         else launch_merge_as<T, IPT, true, false>(ctx, alpha, x, beta, y, st, none);
@@ -717,8 +832,9 @@ static alphasparse_status_t launch_rowtile(DeviceCtx *ctx, T alpha, const T *x, 
     const size_t smem = rowtile_smem_bytes(ctx);
     const T *val = static_cast<const T *>(ctx->d_val);
     const unsigned blocks = (unsigned)((ctx->rows + kRowTile - 1) / kRowTile);
-    const PeerPush push = pushp ? *pushp : PeerPush{};
-    const int which = (beta == T(0) ? 0 : 1) + (pushp ? 2 : 0);
+    const bool in_kernel = pushp && !pushp->after;
+    const PeerPush push = in_kernel ? *pushp : PeerPush{};
+    const int which = (beta == T(0) ? 0 : 1) + (in_kernel ? 2 : 0);
     decltype(&spmv_rowtile_kernel<T, false, false>) variants[4] = {
         spmv_rowtile_kernel<T, false, false>, spmv_rowtile_kernel<T, true, false>,
         spmv_rowtile_kernel<T, false, true>, spmv_rowtile_kernel<T, true, true>};
@@ -755,7 +871,7 @@ alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T 
     } else if (ctx->algorithm == ALPHA_SPARSE_CUDA_ALG_ROWTILE) {
         alphasparse_status_t s = launch_rowtile<T>(ctx, alpha, x, beta, y, st, push);
         if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-        pushed = true;
+        pushed = push && !push->after;
     } else {
         switch (ctx->lanes) {
             case 1: launch_vector<T, 1>(ctx, alpha, x, beta, y, st); break;
@@ -884,14 +1000,15 @@ extern "C" alphasparse_status_t alphasparse_cuda_d_csrmv_noalloc(
     merge_tiles_kernel<<<(unsigned)((tiles + 1 + 255) / 256), 256, 0, st>>>(rows, nnz, d_row_ptr, kNoAllocItems,
                                                                           tiles, tile);
     const PeerPush none{};
+    const NoPush nopush{};
     if (beta == 0.0)
         spmv_merge_kernel<double, kMergeThreads, kMergeItemsD, false, false>
             <<<(unsigned)tiles, kMergeThreads, 0, st>>>(rows, d_row_ptr, d_col_indx, d_values, d_x, d_y, alpha,
-                                                        beta, tile, carry_row, carry_val, none);
+                                                        beta, tile, carry_row, carry_val, nopush);
     else
         spmv_merge_kernel<double, kMergeThreads, kMergeItemsD, true, false>
             <<<(unsigned)tiles, kMergeThreads, 0, st>>>(rows, d_row_ptr, d_col_indx, d_values, d_x, d_y, alpha,
-                                                        beta, tile, carry_row, carry_val, none);
+                                                        beta, tile, carry_row, carry_val, nopush);
     spmv_merge_fixup_kernel<double, false><<<(unsigned)((tiles + 255) / 256), 256, 0, st>>>(
         rows, tiles, carry_row, carry_val, d_y, alpha, none);
     count_launch(3);

@@ -220,9 +220,10 @@ def main():
     ap.add_argument("--rows-log2", type=int, default=None, help="shrink the matrix (development only)")
     ap.add_argument("--grid", type=int, default=None, help="shrink the stencil grid (development only)")
     ap.add_argument("--alg", default="auto", choices=["auto", "vector", "merge", "rowtile"])
-    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+    ap.add_argument("--exchange", default="fused", choices=["fused", "push", "nccl"],
                     help="iterated workload with several GPUs: y reaches the next x from inside the SpMV kernels "
-                         "over peer memory (fused) or by a NCCL allgather after them (nccl)")
+                         "over peer memory (fused), by one peer-copy kernel after them (push) "
+                         "or by a NCCL allgather after them (nccl)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -285,8 +286,8 @@ def main():
     xn_d = torch.empty_like(x_d) if iterate else None
     descr = spblas.descr()
     fused = None
-    if iterate and args.exchange == "fused":
-        fused = multi.FusedExchange(kind, part, rank, world)
+    if iterate and args.exchange in ("fused", "push"):
+        fused = multi.FusedExchange(kind, part, rank, world, deliver_after=args.exchange == "push")
         fused.x_tensor().copy_(x_d)
         torch.cuda.synchronize()
 
@@ -405,7 +406,9 @@ def main():
                        "partition": f"nnz-balanced contiguous row blocks over {world} GPU(s), x replicated",
                        "collective": ("none" if not iterate else
                                       "allgather of y into the next x each step: " +
-                                      ("peer stores from the SpMV kernels + flag exchange" if fused is not None
+                                      ({"fused": "peer stores from inside the SpMV kernel + flag exchange",
+                                        "push": "peer-copy kernel after the SpMV + flag exchange"}[args.exchange]
+                                       if fused is not None
                                        else "NCCL all_gather after the SpMV")),
                        "algorithm": ["auto", "vector", "merge", "rowtile"][info.algorithm], "lanes_per_row": info.lanes_per_row,
                        "l2": f"inputs ({nbytes / 1e6:.0f} MB per step) exceed the 126 MB L2; no flush between steps",

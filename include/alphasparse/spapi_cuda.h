@@ -102,6 +102,9 @@ alphasparse_status_t alphasparse_cuda_exchange_create(alphasparse_cuda_exchange_
 size_t alphasparse_cuda_exchange_blob_bytes(void);
 alphasparse_status_t alphasparse_cuda_exchange_export(alphasparse_cuda_exchange_t ex, void *blob);
 alphasparse_status_t alphasparse_cuda_exchange_connect(alphasparse_cuda_exchange_t ex, const void *blobs);
+/* How y reaches the peers: 0 (default) from inside the product kernels, chunk by chunk while later
+ * chunks are still being multiplied; 1 by one bulk peer-copy kernel after the product. */
+alphasparse_status_t alphasparse_cuda_exchange_set_mode(alphasparse_cuda_exchange_t ex, int mode);
 /* Device pointer of the current x (part[world] elements): fill it before the first step, read it after. */
 alphasparse_status_t alphasparse_cuda_exchange_x(alphasparse_cuda_exchange_t ex, void **x);
 /* Waits for the stream and reports whether any bounded wait ran out (status 3) since creation. */

@@ -30,13 +30,14 @@ def _matrices(kind):
 
 
 @pytest.mark.parametrize("kind", ["s", "d"])
-def test_single_rank_push_matches_oracle(kind):
+@pytest.mark.parametrize("after", [False, True])
+def test_single_rank_push_matches_oracle(kind, after):
     for name, alg, m in _matrices(kind):
         spblas.set_algorithm(alg)
         A = make_handle(kind, m)
         spblas.set_algorithm(capi.ALG_AUTO)
         part = np.array([0, m.nrows], np.int32)
-        ex = multi.FusedExchange(kind, part, 0, 1)
+        ex = multi.FusedExchange(kind, part, 0, 1, deliver_after=after)
         x0 = synth.vector(kind, 3, 1, m.cols)
         ex.x_tensor().copy_(torch.from_numpy(x0))
         y0 = synth.vector(kind, 3, 2, m.nrows)
