@@ -66,7 +66,10 @@ struct PeerPush {
     long long max_polls;
 };
 constexpr int kPushChunkTiles = 128;  // tiles per delivered chunk
-constexpr int kPushBlocks = 32;       // delivering blocks in front of the compute blocks
+#ifndef ASB_X_PUSHERS
+#define ASB_X_PUSHERS 32
+#endif
+constexpr int kPushBlocks = ASB_X_PUSHERS;       // delivering blocks in front of the compute blocks
 
 struct MergeCoord {
     int row;  // rows fully consumed before this point

@@ -254,104 +254,111 @@ __global__ void __launch_bounds__(kRowTile)
 #define ASB_MERGE_MINBLOCKS 5
 #endif
 //
-// With PUSH the same grid also performs the allgather of y.  Its first `push.pushers` blocks
-// compute nothing: block k takes chunks k, k + pushers, ... of `push.chunk_tiles` consecutive
-// tiles, waits (bounded) until the compute blocks have counted all tiles of the chunk as done,
-// adds the carries of rows that lie wholly inside the chunk, and then copies the chunk's finished
-// y rows into the next-x buffer of every GPU with wide coalesced stores through peer-mapped
-// pointers.  So the transfer of chunk c over NVLink runs while later chunks are still being
-// multiplied, and the stores are large and contiguous (pushing each tile's few rows from the
-// compute blocks themselves was measured at ~100 GB/s; a bulk copy reaches several times that).
-// Rows whose carries cross a chunk boundary are finished, and pushed, by the fix-up kernel.
-// Compute blocks never wait on anything, so the waiting blocks cannot starve them.
+// With PUSH the same kernel also performs the allgather of y.  Tiles are grouped into chunks of
+// `push.chunk_tiles` consecutive tiles; every block counts its tile as done, and the block that
+// completes a chunk adds the carries of rows lying wholly inside the chunk and then copies the
+// chunk's finished y rows into the next-x buffer of every GPU with wide coalesced stores through
+// peer-mapped pointers.  So the transfer of chunk c over NVLink runs while later chunks are still
+// being multiplied, the stores are long contiguous runs (pushing each tile's few rows as they
+// finish was measured at ~100 GB/s; bulk copies reach several times that), and no block ever waits
+// for another.  Rows whose carries cross a chunk boundary are finished, and pushed, by the fix-up
+// kernel.
 struct NoPush {};  // kernels instantiated without PUSH carry no delivery arguments at all
 template <bool PUSH>
 using PushArg = typename std::conditional<PUSH, PeerPush, NoPush>::type;
 
-__device__ __forceinline__ void merge_tile_done(const NoPush &, int) {}
-template <typename T>
-__device__ __forceinline__ void merge_pusher(int, const int *, const MergeCoord *, const T *, T *, T,
-                                             const NoPush &) {}
-__device__ __forceinline__ int pusher_blocks(const NoPush &) { return 0; }
-__device__ __forceinline__ int pusher_blocks(const PeerPush &p) { return p.pushers; }
 
-__device__ __forceinline__ void merge_tile_done(const PeerPush &push, int tile_id) {
-    __threadfence();  // this thread's y / carry writes before the count
-    __syncthreads();
-    if (threadIdx.x == 0) atomicAdd(push.chunk_done + tile_id / push.chunk_tiles, 1u);
-}
-
-template <typename T>
-__device__ __noinline__ void merge_pusher(int rows, const int *__restrict__ row_ptr,
-                                          const MergeCoord *__restrict__ tile,
-                                          const T *__restrict__ carry_val, T *__restrict__ y, T alpha,
-                                          const PeerPush &push) {
-    __shared__ int s_ok;
+// Copies n elements starting at src (read at L2: other blocks may just have written them) to element
+// `at` of every destination buffer.  Each element is read once and stored push.n times; four
+// independent loads per thread are in flight, and 16-byte accesses are used when source and
+// destinations share their alignment.
+template <typename V>
+__device__ __forceinline__ void push_units(const V *__restrict__ src, int n, const PeerPush &push, size_t byte_at) {
     const int tid = threadIdx.x, nt = blockDim.x;
-    const int nchunks = (push.tiles + push.chunk_tiles - 1) / push.chunk_tiles;
-    for (int c = blockIdx.x; c < nchunks; c += push.pushers) {
-        const int t0 = c * push.chunk_tiles, t1 = min(t0 + push.chunk_tiles, push.tiles);
-        if (tid == 0) {
-            const unsigned want = (unsigned)(t1 - t0);
-            volatile unsigned *cnt = push.chunk_done + c;
-            long long polls = 0;
-            int ok = 1;
-            while (*cnt < want) {
-                if (++polls > push.max_polls) {
-                    atomicExch(push.status, 4);
-                    ok = 0;
-                    break;
-                }
-                __nanosleep(100);
-            }
-            if (ok) *cnt = 0;  // ready for the next call
-            __threadfence();
-            s_ok = ok;
+    for (int i = tid; i < n; i += 4 * nt) {
+        V v[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+            if (i + u * nt < n) v[u] = __ldcg(src + i + u * nt);
+        for (int p = 0; p < push.n; p++) {
+            V *dst = reinterpret_cast<V *>(static_cast<char *>(push.dst[p]) + byte_at);
+#pragma unroll
+            for (int u = 0; u < 4; u++)
+                if (i + u * nt < n) dst[i + u * nt] = v[u];
         }
-        __syncthreads();
-        if (!s_ok) return;  // uniform: give up, the host will see the status word
-
-        // Carries of rows that begin and end inside this chunk (tile t stops in row tile[t+1].row).
-        const int row_hi = tile[t1].row;  // rows below this one ended in the chunk
-        for (int t = t0 + tid; t < t1; t += nt) {
-            const int r = tile[t + 1].row;
-            if (r >= row_hi || r >= rows) continue;           // ends in a later chunk
-            if (t > 0 && tile[t].row == r) continue;          // not the first tile of its run
-            T acc = __ldcg(carry_val + t);  // written by other blocks of this grid: read at L2
-            for (int u = t + 1; tile[u + 1].row == r; u++) acc += __ldcg(carry_val + u);
-            y[r] = fma(alpha, acc, __ldcg(y + r));
-        }
-        __syncthreads();
-
-        // Finished rows of the chunk: all rows that ended in it, except the first one when it began
-        // in an earlier chunk (the fix-up kernel completes and pushes that one).
-        int ra = tile[t0].row;
-        if (ra < rows && tile[t0].nz > row_ptr[ra]) ra++;
-        const int n = row_hi - ra;
-        if (n > 0) {
-            const T *src = y + ra;
-            for (int p = 0; p < push.n; p++) {
-                T *dst = static_cast<T *>(push.dst[p]) + push.row_off + ra;
-                // 16-byte body where source and destination are equally aligned, scalars around it
-                const int per = 16 / (int)sizeof(T);
-                const uintptr_t sa = (uintptr_t)src, da = (uintptr_t)dst;
-                if ((sa & 15) == (da & 15)) {
-                    int head = (int)(((16 - (sa & 15)) & 15) / sizeof(T));
-                    if (head > n) head = n;
-                    const int body = (n - head) / per;
-                    for (int i = tid; i < head; i += nt) dst[i] = __ldcg(src + i);
-                    const int4 *s4 = reinterpret_cast<const int4 *>(src + head);
-                    int4 *d4 = reinterpret_cast<int4 *>(dst + head);
-                    for (int i = tid; i < body; i += nt) d4[i] = __ldcg(s4 + i);
-                    for (int i = head + body * per + tid; i < n; i += nt) dst[i] = __ldcg(src + i);
-                } else {
-                    for (int i = tid; i < n; i += nt) dst[i] = __ldcg(src + i);
-                }
-            }
-        }
-        __syncthreads();
     }
 }
+
+template <typename T>
+__device__ __forceinline__ void push_span(const T *__restrict__ src, int n, const PeerPush &push, long long at) {
+    const size_t byte_at = (size_t)at * sizeof(T);
+    const uintptr_t sa = (uintptr_t)src, da = (uintptr_t)push.dst[0] + byte_at;
+    constexpr int per = 16 / (int)sizeof(T);
+    if ((sa & 15) == (da & 15) && n >= 4 * per) {
+        int head = (int)(((16 - (sa & 15)) & 15) / sizeof(T));
+        const int body = (n - head) / per;
+        push_units<T>(src, head, push, byte_at);
+        push_units<int4>(reinterpret_cast<const int4 *>(src + head), body, push, byte_at + (size_t)head * sizeof(T));
+        const int done = head + body * per;
+        push_units<T>(src + done, n - done, push, byte_at + (size_t)done * sizeof(T));
+    } else {
+        push_units<T>(src, n, push, byte_at);
+    }
+}
+
+// Called by every thread of a compute block when its tile is finished.  The block that completes a
+// chunk of push.chunk_tiles consecutive tiles (whichever arrives last) finishes the chunk: it adds
+// the carries of rows that lie wholly inside the chunk and copies the chunk's rows to every GPU.
+template <typename T>
+__device__ __noinline__ void merge_chunk_deliver(int rows, const int *__restrict__ row_ptr,
+                                                 const MergeCoord *__restrict__ tile,
+                                                 const T *__restrict__ carry_val, T *__restrict__ y, T alpha,
+                                                 const PeerPush &push, int c) {
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const int t0 = c * push.chunk_tiles, t1 = min(t0 + push.chunk_tiles, push.tiles);
+    // Carries of rows that begin and end inside this chunk (tile t stops in row tile[t+1].row).
+    const int row_hi = tile[t1].row;  // rows below this one ended in the chunk
+    for (int t = t0 + tid; t < t1; t += nt) {
+        const int r = tile[t + 1].row;
+        if (r >= row_hi || r >= rows) continue;   // ends in a later chunk
+        if (t > 0 && tile[t].row == r) continue;  // not the first tile of its run
+        T acc = __ldcg(carry_val + t);            // written by other blocks of this grid: read at L2
+        for (int u = t + 1; tile[u + 1].row == r; u++) acc += __ldcg(carry_val + u);
+        y[r] = fma(alpha, acc, __ldcg(y + r));
+    }
+    __syncthreads();
+    // Finished rows of the chunk: all rows that ended in it, except the first one when it began in
+    // an earlier chunk (the fix-up kernel completes and pushes that one).
+    int ra = tile[t0].row;
+    if (ra < rows && tile[t0].nz > row_ptr[ra]) ra++;
+    const int n = row_hi - ra;
+    if (n > 0) push_span<T>(y + ra, n, push, push.row_off + ra);
+}
+
+template <typename T>
+__device__ __forceinline__ void merge_tile_done(int rows, const int *__restrict__ row_ptr,
+                                                const MergeCoord *__restrict__ tile,
+                                                const T *__restrict__ carry_val, T *__restrict__ y, T alpha,
+                                                const PeerPush &push, int tile_id) {
+    __shared__ int s_last;
+    __syncthreads();  // all of this block's y and carry writes are issued
+    const int c = tile_id / push.chunk_tiles;
+    if (threadIdx.x == 0) {
+        const int in_chunk = min(push.chunk_tiles, push.tiles - c * push.chunk_tiles);
+        __threadfence();  // ... and ordered before the count (cumulative over the barrier above)
+        const unsigned old = atomicAdd(push.chunk_done + c, 1u);
+        s_last = (old + 1u == (unsigned)in_chunk);
+        if (s_last) {
+            push.chunk_done[c] = 0;  // ready for the next call
+            __threadfence();         // the other blocks' writes are visible from here on
+        }
+    }
+    __syncthreads();
+    if (s_last) merge_chunk_deliver<T>(rows, row_ptr, tile, carry_val, y, alpha, push, c);
+}
+template <typename T>
+__device__ __forceinline__ void merge_tile_done(int, const int *, const MergeCoord *, const T *, T *, T,
+                                                const NoPush &, int) {}
 
 template <typename T, int NT, int IPT, bool HAS_BETA, bool PUSH>
 __global__ void __launch_bounds__(NT, ASB_MERGE_MINBLOCKS)
@@ -371,11 +378,7 @@ __global__ void __launch_bounds__(NT, ASB_MERGE_MINBLOCKS)
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, wid = tid >> 5;
-    if (PUSH && (int)blockIdx.x < pusher_blocks(push)) {  // the first blocks of the grid deliver, the rest compute
-        merge_pusher<T>(rows, row_ptr, tile, carry_val, y, alpha, push);
-        return;
-    }
-    const int tile_id = (int)blockIdx.x - pusher_blocks(push);
+    const int tile_id = (int)blockIdx.x;
     const MergeCoord c0 = tile[tile_id], c1 = tile[tile_id + 1];
     const int r0 = c0.row, j0 = c0.nz;
     const int tile_rows = c1.row - r0, tile_nnz = c1.nz - j0;
@@ -410,7 +413,7 @@ __global__ void __launch_bounds__(NT, ASB_MERGE_MINBLOCKS)
             carry_row[tile_id] = r0;
             carry_val[tile_id] = total;
         }
-        if (PUSH) merge_tile_done(push, tile_id);
+        if (PUSH) merge_tile_done<T>(rows, row_ptr, tile, carry_val, y, alpha, push, tile_id);
         return;
     }
 
@@ -500,7 +503,7 @@ __global__ void __launch_bounds__(NT, ASB_MERGE_MINBLOCKS)
         carry_row[tile_id] = r0 + key;
         carry_val[tile_id] = acc;
     }
-    if (PUSH) merge_tile_done(push, tile_id);
+    if (PUSH) merge_tile_done<T>(rows, row_ptr, tile, carry_val, y, alpha, push, tile_id);
 }
 
 // Adds the tile leftovers to the rows they belong to.  Consecutive tiles that stopped in the
@@ -531,12 +534,12 @@ __global__ void spmv_merge_fixup_kernel(int rows, long long tiles, const int *__
 // Copies this GPU's finished y block into the next-x buffer of every peer: the exchange step for
 // the kernels that do not push from their own epilogue.
 template <typename T>
-__global__ void push_rows_kernel(long long rows, const T *__restrict__ y, PeerPush push) {
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < rows;
-         i += (long long)gridDim.x * blockDim.x) {
-        const T v = y[i];
-        for (int p = 0; p < push.n; p++) static_cast<T *>(push.dst[p])[push.row_off + i] = v;
-    }
+__global__ void push_rows_kernel(long long rows, const T *__restrict__ y, const __grid_constant__ PeerPush push) {
+    // each block takes a contiguous slice, so that its stores to a peer are long runs
+    const long long per_block = ((rows + gridDim.x - 1) / gridDim.x + 63) & ~63ll;
+    const long long lo = (long long)blockIdx.x * per_block;
+    const long long n = lo < rows ? (rows - lo < per_block ? rows - lo : per_block) : 0;
+    if (n > 0) push_span<T>(y + lo, (int)n, push, push.row_off + lo);
 }
 
 // y = beta * y for a matrix without stored elements (the reference still scales y).
@@ -784,7 +787,7 @@ static void launch_merge_as(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, c
                             const PeerPush &push) {
     const T *val = static_cast<const T *>(ctx->d_val);
     T *carry = static_cast<T *>(ctx->d_carry_val);
-    const unsigned blocks = (unsigned)ctx->merge_tiles + (PUSH ? (unsigned)push.pushers : 0u);
+    const unsigned blocks = (unsigned)ctx->merge_tiles;
     if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
     PushArg<PUSH> arg{};
     if constexpr (PUSH) arg = push;
@@ -813,10 +816,7 @@ static void launch_merge(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cuda
         PeerPush p = *push;
         p.tiles = (int)ctx->merge_tiles;
         p.chunk_tiles = kPushChunkTiles;
-        p.pushers = kPushBlocks;
         p.chunk_done = ctx->d_chunk_done;
-        p.status = ctx->d_status;
-        p.max_polls = 8LL << 20;
         if (beta == T(0)) launch_merge_as<T, IPT, false, true>(ctx, alpha, x, beta, y, st, p);
         else launch_merge_as<T, IPT, true, true>(ctx, alpha, x, beta, y, st, p);
     } else {

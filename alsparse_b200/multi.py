@@ -85,7 +85,7 @@ class FusedExchange:
     ranks signal each other and the buffers swap.  CUDA only; set-up exchanges 192-byte IPC blobs
     through ``torch.distributed`` (any backend)."""
 
-    def __init__(self, kind, part, rank, world, group=None, deliver_after=False):
+    def __init__(self, kind, part, rank, world, group=None, deliver_after=None):
         lib = capi.load()
         self.kind, self.part, self.rank, self.world = kind, np.ascontiguousarray(part, dtype=np.int32), rank, world
         self.handle = C.c_void_p()
@@ -104,8 +104,8 @@ class FusedExchange:
         joined = b"".join(blobs)
         st = lib.alphasparse_cuda_exchange_connect(self.handle, joined)
         assert st == capi.SUCCESS, (capi.STATUS_NAMES[st], spblas.last_error())
-        if deliver_after:
-            lib.alphasparse_cuda_exchange_set_mode(self.handle, 1)
+        if deliver_after is not None:  # None keeps the library's choice for this number of GPUs
+            lib.alphasparse_cuda_exchange_set_mode(self.handle, 1 if deliver_after else 0)
         if world > 1:
             dist.barrier(group=group)  # nobody starts pushing before every rank has mapped every buffer
 

@@ -220,10 +220,10 @@ def main():
     ap.add_argument("--rows-log2", type=int, default=None, help="shrink the matrix (development only)")
     ap.add_argument("--grid", type=int, default=None, help="shrink the stencil grid (development only)")
     ap.add_argument("--alg", default="auto", choices=["auto", "vector", "merge", "rowtile"])
-    ap.add_argument("--exchange", default="fused", choices=["fused", "push", "nccl"],
+    ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "push", "nccl"],
                     help="iterated workload with several GPUs: y reaches the next x from inside the SpMV kernels "
-                         "over peer memory (fused), by one peer-copy kernel after them (push) "
-                         "or by a NCCL allgather after them (nccl)")
+                         "over peer memory (fused), by one peer-copy kernel after them (push), "
+                         "whichever of the two the library prefers for this many GPUs (auto) or by a NCCL allgather (nccl)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -286,7 +286,9 @@ def main():
     xn_d = torch.empty_like(x_d) if iterate else None
     descr = spblas.descr()
     fused = None
-    if iterate and args.exchange in ("fused", "push"):
+    if iterate and args.exchange != "nccl":
+        if args.exchange == "auto":
+            args.exchange = "fused" if world >= 4 else "push"   # the library's own default
         fused = multi.FusedExchange(kind, part, rank, world, deliver_after=args.exchange == "push")
         fused.x_tensor().copy_(x_d)
         torch.cuda.synchronize()

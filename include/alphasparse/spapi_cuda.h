@@ -102,8 +102,9 @@ alphasparse_status_t alphasparse_cuda_exchange_create(alphasparse_cuda_exchange_
 size_t alphasparse_cuda_exchange_blob_bytes(void);
 alphasparse_status_t alphasparse_cuda_exchange_export(alphasparse_cuda_exchange_t ex, void *blob);
 alphasparse_status_t alphasparse_cuda_exchange_connect(alphasparse_cuda_exchange_t ex, const void *blobs);
-/* How y reaches the peers: 0 (default) from inside the product kernels, chunk by chunk while later
- * chunks are still being multiplied; 1 by one bulk peer-copy kernel after the product. */
+/* How y reaches the peers: 0 from inside the product kernels, chunk by chunk while later chunks are
+ * still being multiplied (default from 4 GPUs up); 1 by one bulk peer-copy kernel after the product
+ * (default below 4 GPUs, where there is too little traffic to hide). */
 alphasparse_status_t alphasparse_cuda_exchange_set_mode(alphasparse_cuda_exchange_t ex, int mode);
 /* Device pointer of the current x (part[world] elements): fill it before the first step, read it after. */
 alphasparse_status_t alphasparse_cuda_exchange_x(alphasparse_cuda_exchange_t ex, void **x);
