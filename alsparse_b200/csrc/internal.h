@@ -59,17 +59,11 @@ struct PeerPush {
     int n;
     long long row_off;
     int after;  // 1: deliver with a separate bulk copy after the product instead of from inside it
-    // merge kernel only: its delivering blocks and their progress counters
-    int tiles, chunk_tiles, pushers;
-    unsigned *chunk_done;  // tiles finished per chunk, reset by the delivering block
-    int *status;           // set to 4 when a delivering block gives up waiting
-    long long max_polls;
+    // merge kernel only: progress counters of its chunks of consecutive tiles
+    int tiles, chunk_tiles;
+    unsigned *chunk_done;  // tiles finished per chunk; reset by the block that completes the chunk
 };
-constexpr int kPushChunkTiles = 128;  // tiles per delivered chunk
-#ifndef ASB_X_PUSHERS
-#define ASB_X_PUSHERS 32
-#endif
-constexpr int kPushBlocks = ASB_X_PUSHERS;       // delivering blocks in front of the compute blocks
+constexpr int kPushChunkTiles = 128;  // tiles per delivered chunk (64..512 measured alike on B200)
 
 struct MergeCoord {
     int row;  // rows fully consumed before this point
