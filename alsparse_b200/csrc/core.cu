@@ -70,6 +70,10 @@ void ctx_destroy(DeviceCtx *c) {
     cudaFree(c->d_x_stage);
     cudaFree(c->d_y_stage);
     cudaFree(c->d_status);
+    if (c->copy_in) cudaStreamDestroy(c->copy_in);
+    if (c->copy_out) cudaStreamDestroy(c->copy_out);
+    for (cudaEvent_t ev : c->ev_pipe)
+        if (ev) cudaEventDestroy(ev);
     if (c->ev_start) cudaEventDestroy(c->ev_start);
     if (c->ev_stop) cudaEventDestroy(c->ev_stop);
     if (prev >= 0) cudaSetDevice(prev);
@@ -414,6 +418,64 @@ static alphasparse_status_t check_call(const alphasparse_matrix_t A, const void 
     return ALPHA_SPARSE_STATUS_INVALID_VALUE;
 }
 
+// Host x and host y on a large matrix: the product runs in kPipelineChunks row windows so that
+// PCIe and the kernel overlap.  Three streams: x and the y0 pieces go in on one, the windows run
+// on the library stream as their inputs land, every finished piece of y leaves on the third
+// while the next window is being multiplied (PCIe is full duplex).  The call still returns
+// only when all of y is back in host memory.
+constexpr int64_t kPipelineMinRows = 1 << 20;
+constexpr int kPipelineChunks = 4;
+
+template <typename T>
+static alphasparse_status_t mv_host_pipelined(DeviceCtx *c, T alpha, const T *x, T beta, T *y, cudaStream_t st) {
+    alphasparse_status_t s = grow(&c->d_x_stage, &c->x_stage_bytes, sizeof(T) * (size_t)c->cols, c);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    s = grow(&c->d_y_stage, &c->y_stage_bytes, sizeof(T) * (size_t)c->rows, c);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    if (!c->copy_in) {
+        ASB_CUDA_OR(cudaStreamCreateWithFlags(&c->copy_in, cudaStreamNonBlocking), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        ASB_CUDA_OR(cudaStreamCreateWithFlags(&c->copy_out, cudaStreamNonBlocking), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        for (cudaEvent_t &ev : c->ev_pipe)
+            ASB_CUDA_OR(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    }
+    const T *dx = static_cast<const T *>(c->d_x_stage);
+    T *dy = static_cast<T *>(c->d_y_stage);
+    cudaEvent_t ev_x = c->ev_pipe[0];
+    // work already queued on the library stream (it may still use the staging buffers) goes first
+    ASB_CUDA_OR(cudaEventRecord(ev_x, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    ASB_CUDA_OR(cudaStreamWaitEvent(c->copy_in, ev_x, 0), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    ASB_CUDA_OR(cudaMemcpyAsync(c->d_x_stage, x, sizeof(T) * (size_t)c->cols, cudaMemcpyHostToDevice, c->copy_in),
+                ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    ASB_CUDA_OR(cudaEventRecord(ev_x, c->copy_in), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    ASB_CUDA_OR(cudaStreamWaitEvent(st, ev_x, 0), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+
+    const int64_t step = ((c->rows + kPipelineChunks - 1) / kPipelineChunks + 1023) & ~1023ll;
+    for (int k = 0; k < kPipelineChunks; k++) {
+        const int64_t rb = k * step;
+        if (rb >= c->rows) break;
+        const RowWindow w{rb, std::min<int64_t>(step, c->rows - rb)};
+        cudaEvent_t ev_in = c->ev_pipe[1 + 2 * k], ev_done = c->ev_pipe[2 + 2 * k];
+        if (beta != T(0)) {
+            ASB_CUDA_OR(cudaMemcpyAsync(dy + rb, y + rb, sizeof(T) * (size_t)w.count, cudaMemcpyHostToDevice, c->copy_in),
+                        ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+            ASB_CUDA_OR(cudaEventRecord(ev_in, c->copy_in), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+            ASB_CUDA_OR(cudaStreamWaitEvent(st, ev_in, 0), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        }
+        s = launch_spmv<T>(c, alpha, dx, beta, dy, st, nullptr, &w);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        ASB_CUDA_OR(cudaEventRecord(ev_done, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        ASB_CUDA_OR(cudaStreamWaitEvent(c->copy_out, ev_done, 0), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        ASB_CUDA_OR(cudaMemcpyAsync(y + rb, dy + rb, sizeof(T) * (size_t)w.count, cudaMemcpyDeviceToHost, c->copy_out),
+                    ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    }
+    int kernel_status = 0;
+    ASB_CUDA_OR(cudaMemcpyAsync(&kernel_status, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, c->copy_out),
+                ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    ASB_CUDA_OR(cudaStreamSynchronize(c->copy_out), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    ASB_CUDA_OR(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    return kernel_status == 0 ? ALPHA_SPARSE_STATUS_SUCCESS : ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+}
+
 template <typename T>
 static alphasparse_status_t mv(alphasparse_operation_t op, T alpha, const alphasparse_matrix_t A,
                                struct alpha_matrix_descr descr, const T *x, T beta, T *y) {
@@ -429,6 +491,9 @@ static alphasparse_status_t mv(alphasparse_operation_t op, T alpha, const alphas
     cudaStream_t st = current_stream();
     const bool x_dev = is_device_pointer(x, c->device), y_dev = is_device_pointer(y, c->device);
     std::lock_guard<std::mutex> lock(c->mu);
+
+    if (!x_dev && !y_dev && c->rows >= kPipelineMinRows && spmv_supports_windows(c) && !c->profile)
+        return mv_host_pipelined<T>(c, alpha, x, beta, y, st);
 
     const T *dx = x;
     T *dy = y;

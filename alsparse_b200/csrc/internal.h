@@ -110,6 +110,10 @@ struct DeviceCtx {
     bool profile = false;
     cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
 
+    // second and third stream + events of the pipelined host-vector path (created on first use)
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    cudaEvent_t ev_pipe[1 + 2 * 8] = {};
+
     int64_t device_bytes = 0;
     std::mutex mu;  // serialises calls that share the carry and staging buffers
 };
@@ -124,9 +128,18 @@ void ctx_destroy(DeviceCtx *ctx);
 alphasparse_status_t ctx_analyse(DeviceCtx *ctx);
 
 // ---- kernel launchers (device pointers, enqueue only) ---------------------------------------
+// A contiguous range of rows of the handle: lets a caller run the product in pieces (the
+// host-vector path overlaps the pieces with the PCIe copies of y).  begin must be a multiple of
+// kRowTile.  Only the vector and row-tile kernels can run on a window.
+struct RowWindow {
+    int64_t begin, count;
+};
+bool spmv_supports_windows(const DeviceCtx *ctx);
+
 template <typename T>
 alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y,
-                                 cudaStream_t stream, const PeerPush *push = nullptr);
+                                 cudaStream_t stream, const PeerPush *push = nullptr,
+                                 const RowWindow *window = nullptr);
 
 template <typename T>
 alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx,

@@ -27,6 +27,8 @@
 
 namespace asb {
 
+bool spmv_supports_windows(const DeviceCtx *ctx);
+
 // ---- streaming loads / stores ------------------------------------------------------------
 // ld.global.cs / st.global.cs: data touched once, first in line for eviction from L1 and L2.
 
@@ -766,18 +768,20 @@ alphasparse_status_t ctx_analyse(DeviceCtx *ctx) {
 // ---- launchers -----------------------------------------------------------------------------------
 
 template <typename T, int LANES>
-static void launch_vector(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st) {
+static void launch_vector(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st,
+                          const RowWindow &w) {
     constexpr int RPG = VectorShape<LANES>::RPG;
     constexpr int rows_per_block = (256 / LANES) * RPG;
-    const unsigned blocks = (unsigned)((ctx->rows + rows_per_block - 1) / rows_per_block);
+    const unsigned blocks = (unsigned)((w.count + rows_per_block - 1) / rows_per_block);
     const T *val = static_cast<const T *>(ctx->d_val);
     if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
+    // a window is just an offset view: offsets stay absolute, so col / val need no shift
     if (beta == T(0))
         spmv_vector_kernel<T, LANES, RPG, false><<<blocks, 256, 0, st>>>(
-            (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta);
+            (int)w.count, ctx->d_row_ptr + w.begin, ctx->d_col, val, x, y + w.begin, alpha, beta);
     else
         spmv_vector_kernel<T, LANES, RPG, true><<<blocks, 256, 0, st>>>(
-            (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta);
+            (int)w.count, ctx->d_row_ptr + w.begin, ctx->d_col, val, x, y + w.begin, alpha, beta);
     if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
     count_launch();
 }
@@ -827,11 +831,11 @@ static void launch_merge(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cuda
 
 template <typename T>
 static alphasparse_status_t launch_rowtile(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y,
-                                           cudaStream_t st, const PeerPush *pushp) {
+                                           cudaStream_t st, const PeerPush *pushp, const RowWindow &w) {
     const int cap = (int)((ctx->max_tile_span + 3) & ~3ll);
     const size_t smem = rowtile_smem_bytes(ctx);
     const T *val = static_cast<const T *>(ctx->d_val);
-    const unsigned blocks = (unsigned)((ctx->rows + kRowTile - 1) / kRowTile);
+    const unsigned blocks = (unsigned)((w.count + kRowTile - 1) / kRowTile);
     const bool in_kernel = pushp && !pushp->after;
     const PeerPush push = in_kernel ? *pushp : PeerPush{};
     const int which = (beta == T(0) ? 0 : 1) + (in_kernel ? 2 : 0);
@@ -848,8 +852,10 @@ static alphasparse_status_t launch_rowtile(DeviceCtx *ctx, T alpha, const T *x, 
         granted[which].store(kRowTileMaxSmem);
     }
     if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
-    kernel<<<blocks, kRowTile, smem, st>>>((int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha,
-                                           beta, cap, ctx->d_status, push);
+    // w.begin is a multiple of kRowTile (the caller's duty): tiles, and the 16-byte alignment of the
+    // offset copies, are the same as in a full launch
+    kernel<<<blocks, kRowTile, smem, st>>>((int)w.count, ctx->d_row_ptr + w.begin, ctx->d_col, val, x,
+                                           y + w.begin, alpha, beta, cap, ctx->d_status, push);
     if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
     count_launch();
     return ALPHA_SPARSE_STATUS_SUCCESS;
@@ -857,8 +863,10 @@ static alphasparse_status_t launch_rowtile(DeviceCtx *ctx, T alpha, const T *x, 
 
 template <typename T>
 alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y,
-                                 cudaStream_t st, const PeerPush *push) {
+                                 cudaStream_t st, const PeerPush *push, const RowWindow *window) {
     if (ctx->rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+    const RowWindow w = window ? *window : RowWindow{0, ctx->rows};
+    if (window && (push || !spmv_supports_windows(ctx))) return ALPHA_SPARSE_STATUS_INTERNAL_ERROR;
     bool pushed = false;  // whether the kernel's own epilogue delivered y to the peers
     if (ctx->nnz == 0) {
         const unsigned blocks = (unsigned)((ctx->rows + 255) / 256);
@@ -869,17 +877,17 @@ alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T 
         launch_merge<T, IPT>(ctx, alpha, x, beta, y, st, push);
         pushed = true;
     } else if (ctx->algorithm == ALPHA_SPARSE_CUDA_ALG_ROWTILE) {
-        alphasparse_status_t s = launch_rowtile<T>(ctx, alpha, x, beta, y, st, push);
+        alphasparse_status_t s = launch_rowtile<T>(ctx, alpha, x, beta, y, st, push, w);
         if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
         pushed = push && !push->after;
     } else {
         switch (ctx->lanes) {
-            case 1: launch_vector<T, 1>(ctx, alpha, x, beta, y, st); break;
-            case 2: launch_vector<T, 2>(ctx, alpha, x, beta, y, st); break;
-            case 4: launch_vector<T, 4>(ctx, alpha, x, beta, y, st); break;
-            case 8: launch_vector<T, 8>(ctx, alpha, x, beta, y, st); break;
-            case 16: launch_vector<T, 16>(ctx, alpha, x, beta, y, st); break;
-            default: launch_vector<T, 32>(ctx, alpha, x, beta, y, st); break;
+            case 1: launch_vector<T, 1>(ctx, alpha, x, beta, y, st, w); break;
+            case 2: launch_vector<T, 2>(ctx, alpha, x, beta, y, st, w); break;
+            case 4: launch_vector<T, 4>(ctx, alpha, x, beta, y, st, w); break;
+            case 8: launch_vector<T, 8>(ctx, alpha, x, beta, y, st, w); break;
+            case 16: launch_vector<T, 16>(ctx, alpha, x, beta, y, st, w); break;
+            default: launch_vector<T, 32>(ctx, alpha, x, beta, y, st, w); break;
         }
     }
     if (push && !pushed) {
@@ -891,9 +899,14 @@ alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T 
 }
 
 template alphasparse_status_t launch_spmv<float>(DeviceCtx *, float, const float *, float, float *,
-                                                 cudaStream_t, const PeerPush *);
+                                                 cudaStream_t, const PeerPush *, const RowWindow *);
 template alphasparse_status_t launch_spmv<double>(DeviceCtx *, double, const double *, double,
-                                                  double *, cudaStream_t, const PeerPush *);
+                                                  double *, cudaStream_t, const PeerPush *, const RowWindow *);
+
+bool spmv_supports_windows(const DeviceCtx *ctx) {
+    return ctx->nnz > 0 && (ctx->algorithm == ALPHA_SPARSE_CUDA_ALG_VECTOR ||
+                            ctx->algorithm == ALPHA_SPARSE_CUDA_ALG_ROWTILE);
+}
 
 }  // namespace asb
 

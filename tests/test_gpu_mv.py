@@ -240,3 +240,16 @@ def test_linearity_and_repeatability():
     err = (ys[2] - (2.0 * ys[0] - 3.0 * ys[1])).abs().cpu().numpy()
     assert (err <= 4e-12 * scale + 1e-300).all()
     spblas.destroy(A)
+
+
+@pytest.mark.parametrize("kind,make", [("s", lambda: synth.uniform_fixed("s", 31, (1 << 20) + 12345, 1 << 20, 8)),
+                                       ("d", lambda: synth.stencil27("d", 104))])
+def test_large_host_vectors_take_the_pipelined_path(kind, make):
+    """Host x and y on more than 2^20 rows: the product runs in row windows overlapped with the PCIe
+    copies; the result must not depend on that."""
+    m = make()
+    assert m.nrows >= 1 << 20
+    for alpha, beta in ((1.5, 0.5), (1.0, 0.0)):
+        y_host = check_mv(kind, m, alpha, beta, seed=31, pointers="host")
+        y_dev = check_mv(kind, m, alpha, beta, seed=31, pointers="device")
+        assert np.array_equal(y_host, y_dev)  # same kernels on the same rows: identical bits
