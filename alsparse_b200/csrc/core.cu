@@ -6,6 +6,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <omp.h>
+
 #include <algorithm>
 #include <new>
 #include <numeric>
@@ -57,6 +59,8 @@ DeviceCtx *ctx_of(const alphasparse_matrix_t A) {
 
 void ctx_destroy(DeviceCtx *c) {
     if (!c) return;
+    ctx_destroy(c->transposed);
+    c->transposed = nullptr;
     int prev = -1;
     cudaGetDevice(&prev);
     cudaSetDevice(c->device);
@@ -238,9 +242,13 @@ static alphasparse_status_t create_csr(alphasparse_matrix_t *A, alphasparse_inde
         free(ptr), free(col), free(val);
         return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
     }
-    ptr[0] = rows > 0 ? rows_start[0] - shift : 0;
+    // Offsets are stored relative to the first stored element, which is element 0 of the copied
+    // arrays.  (The reference keeps rows_start[0] as is while copying from element 0, which only
+    // works when rows_start[0] equals the index base; for that case the two agree bit for bit.)
+    const int first = rows > 0 ? rows_start[0] : 0;
+    ptr[0] = 0;
 #pragma omp parallel for schedule(static) if (rows > (1 << 16))
-    for (int64_t i = 0; i < rows; i++) ptr[i + 1] = rows_end[i] - shift;
+    for (int64_t i = 0; i < rows; i++) ptr[i + 1] = rows_end[i] - first;
 #pragma omp parallel for schedule(static) if (nnz > (1 << 16))
     for (int64_t i = 0; i < nnz; i++) {
         col[i] = col_indx[i] - shift;
@@ -335,6 +343,56 @@ static alphasparse_status_t coo_to_csr(const typename CsrOf<T>::coo *src, bool t
         }
     }
     return finish_csr_handle<T>(dest, rows, cols, ptr, col, val);
+}
+
+// ---- transpose ---------------------------------------------------------------------------------
+
+// Device CSR of A^T, built once from the handle's host copy and kept with the handle.  The
+// reference materialises the transpose on every transposed mm call
+// (src/kernel/x86_64/level3/mm/gemm/gemm_x_csr_row_trans.c:5-12 -> src/core/format/transpose_x_csr.c:7-62)
+// and scatters with a serial loop in the transposed mv (src/plain/kernel/level2/mv/gemv/gemv_x_csr_trans_plain.c:14-25).
+// Here a counting sort by column builds it: every thread owns a range of columns and sweeps the
+// rows in order, so the elements of a column come out by ascending row -- the order in which the
+// reference's loop adds them -- and the result is the same for any thread count.
+template <typename T>
+static alphasparse_status_t ensure_transposed(DeviceCtx *c, const typename CsrOf<T>::csr *m) {
+    if (c->transposed) return ALPHA_SPARSE_STATUS_SUCCESS;
+    const int64_t rows = c->rows, cols = c->cols, nnz = c->nnz;
+    const int *ptr = m->rows_start, *col = m->col_indx;
+    const T *val = m->values;
+    int *tptr = static_cast<int *>(host_alloc(sizeof(int) * (size_t)(cols + 1)));
+    int *tcol = static_cast<int *>(host_alloc(sizeof(int) * (size_t)nnz));
+    T *tval = static_cast<T *>(host_alloc(sizeof(T) * (size_t)nnz));
+    if (!tptr || !tcol || !tval) {
+        free(tptr), free(tcol), free(tval);
+        return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+    memset(tptr, 0, sizeof(int) * (size_t)(cols + 1));
+    for (int64_t k = 0; k < nnz; k++) tptr[col[k] + 1]++;
+    for (int64_t j = 0; j < cols; j++) tptr[j + 1] += tptr[j];
+    std::vector<int> fill(tptr, tptr + cols);
+    const int threads = std::max(1, std::min(alpha_get_thread_num(), 64));
+#pragma omp parallel num_threads(threads)
+    {
+        const int t = omp_get_thread_num(), nt = omp_get_num_threads();
+        const int64_t c0 = cols * t / nt, c1 = cols * (t + 1) / nt;
+        for (int64_t r = 0; r < rows; r++)
+            for (int k = ptr[r]; k < ptr[r + 1]; k++) {
+                const int j = col[k];
+                if (j >= c0 && j < c1) {
+                    const int pos = fill[j]++;
+                    tcol[pos] = (int)r;
+                    tval[pos] = val[k];
+                }
+            }
+    }
+    DeviceCtx *t = nullptr;
+    alphasparse_status_t s = ctx_create(c->datatype, cols, rows, tptr, tcol, tval, &t);
+    free(tptr), free(tcol), free(tval);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    c->transposed = t;
+    c->device_bytes += t->device_bytes;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
 // ---- pointer kinds and staging ------------------------------------------------------------------
@@ -481,13 +539,20 @@ static alphasparse_status_t mv(alphasparse_operation_t op, T alpha, const alphas
                                struct alpha_matrix_descr descr, const T *x, T beta, T *y) {
     alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-    if (op != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
     DeviceCtx *c = ctx_of(A);
     if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
-    if (c->rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
 
     DeviceGuard guard(c->device);
     if (!guard.ok) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+    if (op == ALPHA_SPARSE_OPERATION_TRANSPOSE) {  // y (cols entries) = alpha * A^T * x (rows entries) + beta * y
+        {
+            std::lock_guard<std::mutex> build(c->mu);
+            s = ensure_transposed<T>(c, static_cast<const typename CsrOf<T>::csr *>(A->mat));
+            if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        }
+        c = c->transposed;
+    }
+    if (c->rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
     cudaStream_t st = current_stream();
     const bool x_dev = is_device_pointer(x, c->device), y_dev = is_device_pointer(y, c->device);
     std::lock_guard<std::mutex> lock(c->mu);
@@ -539,22 +604,38 @@ static alphasparse_status_t mm(alphasparse_operation_t op, T alpha, const alphas
                                ALPHA_INT ldy) {
     alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-    if (op != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
-    if (layout != ALPHA_SPARSE_LAYOUT_ROW_MAJOR) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    if (layout != ALPHA_SPARSE_LAYOUT_ROW_MAJOR && layout != ALPHA_SPARSE_LAYOUT_COLUMN_MAJOR)
+        return ALPHA_SPARSE_STATUS_INVALID_VALUE;
     DeviceCtx *c = ctx_of(A);
     if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
-    if (columns < 0 || ldx < columns || ldy < columns) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
-    if (c->rows == 0 || columns == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
-
     DeviceGuard guard(c->device);
     if (!guard.ok) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+    if (op == ALPHA_SPARSE_OPERATION_TRANSPOSE) {  // the reference also multiplies by a materialised A^T
+        {
+            std::lock_guard<std::mutex> build(c->mu);
+            s = ensure_transposed<T>(c, static_cast<const typename CsrOf<T>::csr *>(A->mat));
+            if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        }
+        c = c->transposed;
+    }
+    const bool row_major = layout == ALPHA_SPARSE_LAYOUT_ROW_MAJOR;
+    // X is (c->cols x columns), Y is (c->rows x columns); ld = distance between rows (row-major) or
+    // between columns (column-major)
+    if (columns < 0) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    if (row_major ? (ldx < columns || ldy < columns) : (ldx < c->cols || ldy < c->rows))
+        return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    if (c->rows == 0 || columns == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+
     cudaStream_t st = current_stream();
     const bool x_dev = is_device_pointer(x, c->device), y_dev = is_device_pointer(y, c->device);
     std::lock_guard<std::mutex> lock(c->mu);
 
-    // Dense operands: X is cols x columns (leading dimension ldx), Y is rows x columns (ldy).
-    const size_t xbytes = sizeof(T) * ((size_t)(c->cols > 0 ? c->cols - 1 : 0) * ldx + (c->cols > 0 ? columns : 0));
-    const size_t ybytes = sizeof(T) * ((size_t)(c->rows - 1) * ldy + columns);
+    auto extent = [&](int64_t outer, int64_t inner, int64_t ld) -> size_t {  // elements spanned by a dense operand
+        return outer > 0 && inner > 0 ? (size_t)((outer - 1) * ld + inner) : 0;
+    };
+    const size_t xbytes = sizeof(T) * (row_major ? extent(c->cols, columns, ldx) : extent(columns, c->cols, ldx));
+    const size_t ybytes = sizeof(T) * (row_major ? extent(c->rows, columns, ldy) : extent(columns, c->rows, ldy));
+    const bool y_tight = row_major ? ldy == columns : ldy == c->rows;
     const T *dx = x;
     T *dy = y;
     if (!x_dev) {
@@ -568,14 +649,15 @@ static alphasparse_status_t mm(alphasparse_operation_t op, T alpha, const alphas
     if (!y_dev) {
         s = grow(&c->d_y_stage, &c->y_stage_bytes, ybytes, c);
         if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-        // With ldy > columns the gaps between rows belong to the caller and must survive the
-        // round trip, so the whole block is brought over even when beta == 0.
-        if (beta != T(0) || ldy != columns)
+        // Gaps left by a padded leading dimension belong to the caller and must survive the round
+        // trip, so the whole block is brought over even when beta == 0.
+        if (beta != T(0) || !y_tight)
             ASB_CUDA_OR(cudaMemcpyAsync(c->d_y_stage, y, ybytes, cudaMemcpyHostToDevice, st),
                         ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
         dy = static_cast<T *>(c->d_y_stage);
     }
-    s = launch_spmm_row<T>(c, alpha, dx, columns, ldx, beta, dy, ldy, st);
+    s = row_major ? launch_spmm_row<T>(c, alpha, dx, columns, ldx, beta, dy, ldy, st)
+                  : launch_spmm_col<T>(c, alpha, dx, columns, ldx, beta, dy, ldy, st);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     if (!y_dev)
         ASB_CUDA_OR(cudaMemcpyAsync(y, dy, ybytes, cudaMemcpyDeviceToHost, st),

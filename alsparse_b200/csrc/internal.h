@@ -114,6 +114,9 @@ struct DeviceCtx {
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
     cudaEvent_t ev_pipe[1 + 2 * 8] = {};
 
+    // A^T as a second device CSR, built on the first transposed mv / mm call and kept
+    DeviceCtx *transposed = nullptr;
+
     int64_t device_bytes = 0;
     std::mutex mu;  // serialises calls that share the carry and staging buffers
 };
@@ -143,6 +146,10 @@ alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T 
 
 template <typename T>
 alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx,
+                                     T beta, T *Y, int ldy, cudaStream_t stream);
+
+template <typename T>
+alphasparse_status_t launch_spmm_col(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx,
                                      T beta, T *Y, int ldy, cudaStream_t stream);
 
 }  // namespace asb

@@ -177,6 +177,92 @@ alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int co
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
+// ---- column-major dense operands ------------------------------------------------------------------
+//
+// Y[:, c] = beta * Y[:, c] + alpha * (A * X[:, c]) for every dense column c, element (r, c) of a dense
+// operand at [c * ld + r]: the operation of the reference's gemm_{s,d}_csr_col (arithmetic defined by
+// src/plain/kernel/level3/mm/gemm/gemm_x_csr_col_plain.c:4-21: a dot product from zero per (row, column),
+// then y = y*beta + alpha*dot).  Each dense column is an independent SpMV on the same A, so the kernel
+// is the vector SpMV with KC columns carried side by side: a group of LANES lanes owns a sparse row,
+// every stored element is loaded once and multiplied into KC accumulators, one gather per column.
+// blockIdx.y selects the block of KC columns; A is re-read once per block.
+template <typename T, int LANES, int KC, bool HAS_BETA>
+__global__ void __launch_bounds__(256)
+    spmm_col_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
+                    const T *__restrict__ val, const T *__restrict__ X, int columns, long long ldx,
+                    T *__restrict__ Y, long long ldy, T alpha, T beta) {
+    constexpr int GROUPS = 256 / LANES;
+    const int lane = threadIdx.x % LANES;
+    const long long row = (long long)blockIdx.x * GROUPS + threadIdx.x / LANES;
+    const int c0 = blockIdx.y * KC;
+    int s = 0, e = 0;
+    if (row < rows) {
+        s = __ldg(row_ptr + row);
+        e = __ldg(row_ptr + row + 1);
+    }
+    T acc[KC];
+#pragma unroll
+    for (int k = 0; k < KC; k++) acc[k] = T(0);
+    for (int j = s + lane; j < e; j += LANES) {
+        const int cj = __ldg(col + j);
+        const T vj = __ldg(val + j);
+#pragma unroll
+        for (int k = 0; k < KC; k++)
+            if (c0 + k < columns) acc[k] = fma(vj, __ldg(X + (long long)(c0 + k) * ldx + cj), acc[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < KC; k++) {
+#pragma unroll
+        for (int o = LANES / 2; o > 0; o >>= 1) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], o);
+    }
+    if (lane == 0 && row < rows) {
+#pragma unroll
+        for (int k = 0; k < KC; k++)
+            if (c0 + k < columns) {
+                T *out = Y + (long long)(c0 + k) * ldy + row;
+                T o = alpha * acc[k];
+                if (HAS_BETA) o = fma(beta, *out, o);
+                *out = o;
+            }
+    }
+}
+
+template <typename T, int LANES>
+static void launch_col(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx, T beta, T *Y, int ldy,
+                       cudaStream_t st) {
+    constexpr int KC = 4;
+    const dim3 grid((unsigned)((ctx->rows + 256 / LANES - 1) / (256 / LANES)), (unsigned)((columns + KC - 1) / KC));
+    const T *val = static_cast<const T *>(ctx->d_val);
+    if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
+    if (beta == T(0))
+        spmm_col_kernel<T, LANES, KC, false><<<grid, 256, 0, st>>>((int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, X,
+                                                                  columns, ldx, Y, ldy, alpha, beta);
+    else
+        spmm_col_kernel<T, LANES, KC, true><<<grid, 256, 0, st>>>((int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, X,
+                                                                 columns, ldx, Y, ldy, alpha, beta);
+    if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
+    count_launch();
+}
+
+template <typename T>
+alphasparse_status_t launch_spmm_col(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx, T beta, T *Y,
+                                     int ldy, cudaStream_t st) {
+    if (ctx->rows == 0 || columns <= 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+    if ((columns + 3) / 4 > 65535) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    const double m = ctx->mean_row_nnz;
+    if (m <= 8) launch_col<T, 4>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+    else if (m <= 16) launch_col<T, 8>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+    else if (m <= 32) launch_col<T, 16>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+    else launch_col<T, 32>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+    ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+template alphasparse_status_t launch_spmm_col<float>(DeviceCtx *, float, const float *, int, int, float, float *,
+                                                     int, cudaStream_t);
+template alphasparse_status_t launch_spmm_col<double>(DeviceCtx *, double, const double *, int, int, double,
+                                                      double *, int, cudaStream_t);
+
 template alphasparse_status_t launch_spmm_row<float>(DeviceCtx *, float, const float *, int, int,
                                                      float, float *, int, cudaStream_t);
 template alphasparse_status_t launch_spmm_row<double>(DeviceCtx *, double, const double *, int, int,

@@ -76,4 +76,71 @@ def test_status_codes():
     assert spblas.mm("s", capi.CONJUGATE_TRANSPOSE, 1.0, A, g, 0, X, 4, 4, 0.0, Y, 4) == capi.INVALID_VALUE
     assert spblas.mm("s", 0, 1.0, A, spblas.descr(capi.SYMMETRIC), 0, X, 4, 4, 0.0, Y, 4) == capi.INVALID_VALUE
     assert spblas.mm("s", 0, 1.0, A, spblas.descr(capi.TRIANGULAR), 0, X, 4, 4, 0.0, Y, 4) == capi.NOT_SUPPORTED
+    assert spblas.mm("s", 0, 1.0, A, g, 0, X, 4, 3, 0.0, Y, 4) == capi.INVALID_VALUE           # ldx < columns
+    assert spblas.mm("s", 0, 1.0, A, g, capi.COLUMN_MAJOR, X, 4, 39, 0.0, Y, 30) == capi.INVALID_VALUE  # ldx < cols
+    spblas.destroy(A)
+
+
+@pytest.mark.parametrize("kind", ["s", "d"])
+@pytest.mark.parametrize("case", ["w64", "w5"])
+def test_column_major_golden(kind, case):
+    """Column-major operands against the reference's plain gemm_csr_col (golden vectors)."""
+    g = golden(f"mm_{kind}.npz")
+    m = synth.Csr(int(g["rows"]), int(g["cols"]), 0, g["ptr"], g["col"], g["val"])
+    columns, _, _, ldxc, ldyc = (int(v) for v in g[f"{case}_par"][:5])
+    alpha, beta = float(g[f"{case}_par"][5]), float(g[f"{case}_par"][6])
+    A = make_handle(kind, m)
+    Xc, Yc0, Yref = g[f"{case}_Xc"], g[f"{case}_Yc0"], g[f"{case}_col"]
+    for dev in (False, True):
+        if dev:
+            dX, dY = torch.from_numpy(Xc).cuda(), torch.from_numpy(Yc0).cuda()
+            st = spblas.mm(kind, 0, alpha, A, spblas.descr(), capi.COLUMN_MAJOR, dX, columns, ldxc, beta, dY, ldyc)
+            Y = dY.cpu().numpy()
+        else:
+            Y = Yc0.copy()
+            st = spblas.mm(kind, 0, alpha, A, spblas.descr(), capi.COLUMN_MAJOR, Xc, columns, ldxc, beta, Y, ldyc)
+        assert st == capi.SUCCESS, capi.STATUS_NAMES[st]
+        # compare through the row-major view of the same numbers
+        rows, cols = m.nrows, m.cols
+        Xr = Xc.reshape(columns, ldxc)[:, :cols].T.copy()
+        Y0r = Yc0.reshape(columns, ldyc)[:, :rows].T.copy()
+        scale = mm_scale(m.ptr, m.col, m.val, Xr.reshape(-1), columns, columns, alpha, beta, Y0r.reshape(-1), columns)
+        assert_rows_close(kind, Y.reshape(columns, ldyc)[:, :rows].T.reshape(-1),
+                          Yref.reshape(columns, ldyc)[:, :rows].T.reshape(-1), scale.reshape(-1), f"col {case} dev={dev}")
+        assert np.array_equal(Y.reshape(columns, ldyc)[:, rows:], Yc0.reshape(columns, ldyc)[:, rows:]), "padding written"
+    spblas.destroy(A)
+
+
+@pytest.mark.parametrize("kind", ["s", "d"])
+def test_transposed_mm_both_layouts(kind):
+    """op = TRANSPOSE: Y (cols x columns) = alpha * A^T * X (rows x columns) + beta * Y, checked against the
+    oracle applied to the explicitly transposed matrix (what the reference's trans kernels do)."""
+    m = synth.poisson(kind, 51, 900, 1300, 12.0)
+    order = np.lexsort((np.repeat(np.arange(m.nrows), np.diff(m.ptr)), m.col))     # by column, then row
+    trow = m.col[order]
+    tptr = np.concatenate([[0], np.cumsum(np.bincount(trow, minlength=m.cols))]).astype(np.int32)
+    tcol = np.repeat(np.arange(m.nrows), np.diff(m.ptr))[order].astype(np.int32)
+    tval = m.val[order]
+    A = make_handle(kind, m)
+    columns, alpha, beta = 24, 0.75, -0.5
+    # row-major
+    X, Y0 = synth.vector(kind, 51, 3, m.nrows * columns), synth.vector(kind, 51, 4, m.cols * columns)
+    Yref = oracle.gemm(kind, "row", tptr[:-1], tptr[1:], tcol, tval, alpha, X, columns, columns, beta, Y0.copy(), columns)
+    Y = Y0.copy()
+    assert spblas.mm(kind, capi.TRANSPOSE, alpha, A, spblas.descr(), capi.ROW_MAJOR, X, columns, columns, beta, Y,
+                     columns) == capi.SUCCESS
+    scale = mm_scale(tptr, tcol, tval, X, columns, columns, alpha, beta, Y0, columns)
+    assert_rows_close(kind, Y, Yref, scale.reshape(-1), "transposed row-major")
+    # column-major
+    Xc, Yc0 = synth.vector(kind, 51, 5, m.nrows * columns), synth.vector(kind, 51, 6, m.cols * columns)
+    Ycref = oracle.gemm(kind, "col", tptr[:-1], tptr[1:], tcol, tval, alpha, Xc, columns, m.nrows, beta, Yc0.copy(),
+                        m.cols)
+    dX, dY = torch.from_numpy(Xc).cuda(), torch.from_numpy(Yc0).cuda()
+    assert spblas.mm(kind, capi.TRANSPOSE, alpha, A, spblas.descr(), capi.COLUMN_MAJOR, dX, columns, m.nrows, beta, dY,
+                     m.cols) == capi.SUCCESS
+    Xr = Xc.reshape(columns, m.nrows).T.copy()
+    Y0r = Yc0.reshape(columns, m.cols).T.copy()
+    sc = mm_scale(tptr, tcol, tval, Xr.reshape(-1), columns, columns, alpha, beta, Y0r.reshape(-1), columns)
+    assert_rows_close(kind, dY.cpu().numpy().reshape(columns, m.cols).T.reshape(-1),
+                      Ycref.reshape(columns, m.cols).T.reshape(-1), sc.reshape(-1), "transposed column-major")
     spblas.destroy(A)

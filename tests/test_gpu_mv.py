@@ -253,3 +253,39 @@ def test_large_host_vectors_take_the_pipelined_path(kind, make):
         y_host = check_mv(kind, m, alpha, beta, seed=31, pointers="host")
         y_dev = check_mv(kind, m, alpha, beta, seed=31, pointers="device")
         assert np.array_equal(y_host, y_dev)  # same kernels on the same rows: identical bits
+
+
+def test_transposed_mv():
+    """y = alpha * A^T * x + beta * y against the reference's plain transposed kernel (golden vector
+    from its own objects, and the oracle on fresh rectangular inputs)."""
+    g = golden("trans_d.npz")
+    m = _csr(g)
+    A = make_handle("d", m)
+    y = g["y0"].copy()
+    assert spblas.mv("d", capi.TRANSPOSE, float(g["alpha"]), A, spblas.descr(), g["x"], float(g["beta"]), y) == capi.SUCCESS
+    prod = np.abs(g["val"] * np.repeat(g["x"], np.diff(g["ptr"])))
+    scale = np.abs(g["beta"] * g["y0"]) + abs(g["alpha"]) * np.bincount(g["col"], weights=prod, minlength=len(y))
+    assert_rows_close("d", y, g["y"], scale, "transposed mv (golden)")
+    spblas.destroy(A)
+    for kind in ("s", "d"):
+        lens = synth.rowlen_zipf(41, 5000, 1.8, 1, 900 if kind == "s" else 4000)
+        lens[::9] = 0
+        m = synth.from_lengths(kind, 41, lens, 7000)      # 5000 x 7000: x has 5000 entries, y 7000
+        x, y0 = synth.vector(kind, 41, 1, m.nrows), synth.vector(kind, 41, 2, m.cols)
+        A = make_handle(kind, m)
+        for alpha, beta in ((1.0, 0.0), (-0.5, 2.0)):
+            y_ref = oracle.gemv_trans(kind, m.cols, m.rows_start, m.rows_end, m.col, m.val, alpha, x, beta, y0.copy())
+            prod = np.abs(m.val.astype(np.float64) * np.repeat(x.astype(np.float64), np.diff(m.ptr)))
+            scale = np.abs(beta * y0.astype(np.float64)) + abs(alpha) * np.bincount(m.col, weights=prod, minlength=m.cols)
+            for dev in (False, True):
+                if dev:
+                    dx, dy = torch.from_numpy(x).cuda(), torch.from_numpy(y0).cuda()
+                    assert spblas.mv(kind, capi.TRANSPOSE, alpha, A, spblas.descr(), dx, beta, dy) == capi.SUCCESS
+                    y = dy.cpu().numpy()
+                else:
+                    y = y0.copy()
+                    assert spblas.mv(kind, capi.TRANSPOSE, alpha, A, spblas.descr(), x, beta, y) == capi.SUCCESS
+                assert_rows_close(kind, y, y_ref, scale, f"transposed mv {kind} dev={dev}")
+        # the non-transposed product of the same handle is unaffected
+        check_mv(kind, m, 1.5, 0.5, A=A)
+        spblas.destroy(A)
