@@ -163,3 +163,12 @@ def csrmv_noalloc(rows, cols, nnz, alpha, d_row_ptr, d_col_indx, d_values, d_x, 
     (scratch lives in a fixed 4 MiB array inside the library; rows + nnz <= 375,802,112)."""
     return capi.load().alphasparse_cuda_d_csrmv_noalloc(rows, cols, nnz, alpha, _ptr(d_row_ptr), _ptr(d_col_indx),
                                                          _ptr(d_values), _ptr(d_x), beta, _ptr(d_y))
+
+
+def probe_gather_rate(kind, table_elems, gathers=1 << 27):
+    """Random single-element gathers per second the current GPU sustains from a table of that size."""
+    rate = C.c_double()
+    st = capi.load().alphasparse_cuda_probe_gather_rate(capi.FLOAT if kind == "s" else capi.DOUBLE, table_elems,
+                                                         gathers, C.byref(rate))
+    assert st == SUCCESS, (capi.STATUS_NAMES[st], last_error())
+    return rate.value

@@ -395,6 +395,14 @@ def main():
     else:
         peak, peak_src = FALLBACK_HBM_GBS, "fallback"
     achieved = launch_bytes / (kernel_ms * 1e-3) / 1e9
+    # Matrices with unstructured columns: one gather of x per stored element.  The measured gather rate
+    # of this GPU gives a floor for the kernel that no SpMV can beat, whatever its HBM traffic.
+    gather = None
+    if op == "mv" and name != "stencil27":
+        rate = spblas.probe_gather_rate(kind, cols)
+        floor_ms = m.nnz / rate * 1e3
+        gather = {"gathers_per_s": rate, "table_elems": cols, "kernel_floor_ms": floor_ms,
+                  "kernel_vs_floor": floor_ms / kernel_ms}
 
     if rank == 0:
         line = {
@@ -418,7 +426,8 @@ def main():
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": NCU_TRAFFIC.get(name) if not reduced and world == 1 else None,
-                         "peak_source": peak_src, "kernel_ms": kernel_ms, "bytes_per_launch": launch_bytes},
+                         "peak_source": peak_src, "kernel_ms": kernel_ms, "bytes_per_launch": launch_bytes,
+                         "gather_bound": gather},
             "clocks": sampler.summary(t_wall0, t_wall1) if sampler else None,
         }
         if e2e:

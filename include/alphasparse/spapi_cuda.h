@@ -125,6 +125,14 @@ alphasparse_status_t alphasparse_d_mv_exchange(const double alpha, const alphasp
 alphasparse_status_t alphasparse_cuda_profile_kernel(const alphasparse_matrix_t A, int enable);
 alphasparse_status_t alphasparse_cuda_kernel_ms(const alphasparse_matrix_t A, float *ms);
 
+/* Benchmark aid: measures on the current device how many independent single-element gathers per
+ * second the GPU sustains from uniformly random positions of a zero-filled table of `table_elems`
+ * elements of the given precision (`gathers` of them, shaped like the SpMV inner loop).  For matrices
+ * with unstructured columns this rate, not HBM bandwidth, is what bounds SpMV.  Allocates and frees
+ * 4*gathers + table bytes on the device. */
+alphasparse_status_t alphasparse_cuda_probe_gather_rate(alphasparse_datatype_t datatype, int64_t table_elems,
+                                                        int64_t gathers, double *per_second);
+
 /* Number of kernels this library has launched in this process so far. */
 int64_t alphasparse_cuda_launch_count(void);
 
