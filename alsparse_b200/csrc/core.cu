@@ -61,6 +61,10 @@ void ctx_destroy(DeviceCtx *c) {
     if (!c) return;
     ctx_destroy(c->transposed);
     c->transposed = nullptr;
+    for (DeviceCtx *&d : c->derived) {
+        ctx_destroy(d);
+        d = nullptr;
+    }
     int prev = -1;
     cudaGetDevice(&prev);
     cudaSetDevice(c->device);
@@ -293,25 +297,12 @@ static alphasparse_status_t create_coo(alphasparse_matrix_t *A, alphasparse_inde
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
-// COO -> CSR with the output the reference produces (src/core/format/convert_csr_x_coo.c:14-81):
-// elements ordered by (row, column), duplicates all kept, offsets by counting.  The reference
-// sorts nnz records with a serial qsort; here a counting pass buckets the elements by row in
-// input order and each row is then sorted by column with a stable sort, in parallel over rows.
-// Equal (row, column) pairs keep their input order (qsort leaves theirs unspecified).
-// With transpose = true rows and columns swap roles (the reference transposes the COO handle
-// first, src/core/op_/alphasparse_convert_csr.c:144-151).
+// (row, column, value) triples -> 3-array CSR with the elements of a row ordered by column and equal
+// (row, column) pairs kept in input order: counting pass by row, then a stable sort of each row, rows
+// in parallel.  Output arrays are host_alloc'ed.
 template <typename T>
-static alphasparse_status_t coo_to_csr(const typename CsrOf<T>::coo *src, bool transpose,
-                                       alphasparse_matrix_t *dest) {
-    const int64_t rows = transpose ? src->cols : src->rows;
-    const int64_t cols = transpose ? src->rows : src->cols;
-    const int64_t nnz = src->nnz;
-    const int *ri = transpose ? src->col_indx : src->row_indx;
-    const int *ci = transpose ? src->row_indx : src->col_indx;
-    for (int64_t i = 0; i < nnz; i++)
-        if (ri[i] < 0 || ri[i] >= rows || ci[i] < 0 || ci[i] >= cols)
-            return ALPHA_SPARSE_STATUS_INVALID_VALUE;
-
+static alphasparse_status_t triples_to_csr(int64_t rows, int64_t nnz, const int *ri, const int *ci, const T *v,
+                                           int **out_ptr, int **out_col, T **out_val) {
     int *ptr = static_cast<int *>(host_alloc(sizeof(int) * (size_t)(rows + 1)));
     int *col = static_cast<int *>(host_alloc(sizeof(int) * (size_t)nnz));
     T *val = static_cast<T *>(host_alloc(sizeof(T) * (size_t)nnz));
@@ -339,9 +330,36 @@ static alphasparse_status_t coo_to_csr(const typename CsrOf<T>::coo *src, bool t
         for (int *it = b; it != e; ++it) {
             const size_t o = (size_t)(it - order.data());
             col[o] = ci[*it];
-            val[o] = src->values[*it];
+            val[o] = v[*it];
         }
     }
+    *out_ptr = ptr, *out_col = col, *out_val = val;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+// COO -> CSR with the output the reference produces (src/core/format/convert_csr_x_coo.c:14-81):
+// elements ordered by (row, column), duplicates all kept, offsets by counting.  The reference
+// sorts nnz records with a serial qsort; here a counting pass buckets the elements by row in
+// input order and each row is then sorted by column with a stable sort, in parallel over rows.
+// Equal (row, column) pairs keep their input order (qsort leaves theirs unspecified).
+// With transpose = true rows and columns swap roles (the reference transposes the COO handle
+// first, src/core/op_/alphasparse_convert_csr.c:144-151).
+template <typename T>
+static alphasparse_status_t coo_to_csr(const typename CsrOf<T>::coo *src, bool transpose,
+                                       alphasparse_matrix_t *dest) {
+    const int64_t rows = transpose ? src->cols : src->rows;
+    const int64_t cols = transpose ? src->rows : src->cols;
+    const int64_t nnz = src->nnz;
+    const int *ri = transpose ? src->col_indx : src->row_indx;
+    const int *ci = transpose ? src->row_indx : src->col_indx;
+    for (int64_t i = 0; i < nnz; i++)
+        if (ri[i] < 0 || ri[i] >= rows || ci[i] < 0 || ci[i] >= cols)
+            return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+
+    int *ptr = nullptr, *col = nullptr;
+    T *val = nullptr;
+    alphasparse_status_t s = triples_to_csr<T>(rows, nnz, ri, ci, src->values, &ptr, &col, &val);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     return finish_csr_handle<T>(dest, rows, cols, ptr, col, val);
 }
 
@@ -392,6 +410,71 @@ static alphasparse_status_t ensure_transposed(DeviceCtx *c, const typename CsrOf
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     c->transposed = t;
     c->device_bytes += t->device_bytes;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+// ---- structured descriptors ---------------------------------------------------------------------
+
+// mv under a SYMMETRIC, TRIANGULAR or DIAGONAL descriptor (the other CSR branches of the reference's
+// alphasparse_?_mv, src/core/op/level2/alphasparse_x_mv.c:1693-1716; kernels under
+// src/plain/kernel/level2/mv/{symv,trmv,diagmv}) is an ordinary SpMV with a matrix DERIVED from the
+// stored one: the kept triangle (plus an explicit unit diagonal), its mirror image for SYMMETRIC, its
+// transpose for op = TRANSPOSE, or just the diagonal (the FIRST stored diagonal entry of a row, as the
+// reference's loop breaks at it).  Each variant is built once from the host copy, uploaded as its own
+// device CSR, analysed like any matrix and kept with the handle.
+static int derived_slot(int type, int upper, int unit, int trans) {
+    const int t = type == ALPHA_SPARSE_MATRIX_TYPE_SYMMETRIC ? 0 : type == ALPHA_SPARSE_MATRIX_TYPE_TRIANGULAR ? 1 : 2;
+    return t * 8 + upper * 4 + unit * 2 + trans;
+}
+
+template <typename T>
+static alphasparse_status_t ensure_derived(DeviceCtx *c, const typename CsrOf<T>::csr *m, int type, int upper,
+                                           int unit, int trans, DeviceCtx **out) {
+    DeviceCtx *&slot = c->derived[derived_slot(type, upper, unit, trans)];
+    if (slot) {
+        *out = slot;
+        return ALPHA_SPARSE_STATUS_SUCCESS;
+    }
+    const int64_t n = c->rows;
+    const int *ptr = m->rows_start, *col = m->col_indx;
+    const T *val = m->values;
+    std::vector<int> ri, ci;
+    std::vector<T> v;
+    try {
+        for (int64_t i = 0; i < n; i++) {
+            if (unit) ri.push_back((int)i), ci.push_back((int)i), v.push_back(T(1));
+            bool diag_seen = false;
+            for (int k = ptr[i]; k < ptr[i + 1]; k++) {
+                const int j = col[k];
+                if (type == ALPHA_SPARSE_MATRIX_TYPE_DIAGONAL) {
+                    if (!unit && j == i && !diag_seen) ri.push_back((int)i), ci.push_back(j), v.push_back(val[k]);
+                    diag_seen |= (j == i);
+                    continue;
+                }
+                const bool off = upper ? j > i : j < i;
+                if (off) {
+                    const bool flip = type == ALPHA_SPARSE_MATRIX_TYPE_TRIANGULAR && trans;
+                    ri.push_back(flip ? j : (int)i), ci.push_back(flip ? (int)i : j), v.push_back(val[k]);
+                    if (type == ALPHA_SPARSE_MATRIX_TYPE_SYMMETRIC) ri.push_back(j), ci.push_back((int)i), v.push_back(val[k]);
+                } else if (j == i && !unit) {
+                    ri.push_back((int)i), ci.push_back(j), v.push_back(val[k]);
+                }
+            }
+        }
+    } catch (...) {
+        return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+    int *dptr = nullptr, *dcol = nullptr;
+    T *dval = nullptr;
+    alphasparse_status_t s = triples_to_csr<T>(n, (int64_t)v.size(), ri.data(), ci.data(), v.data(), &dptr, &dcol, &dval);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    DeviceCtx *d = nullptr;
+    s = ctx_create(c->datatype, n, n, dptr, dcol, dval, &d);
+    free(dptr), free(dcol), free(dval);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    c->device_bytes += d->device_bytes;
+    slot = d;
+    *out = d;
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
@@ -447,7 +530,7 @@ struct DeviceGuard {
 // kernels is NOT_SUPPORTED here.
 static alphasparse_status_t check_call(const alphasparse_matrix_t A, const void *x, const void *y,
                                        alphasparse_datatype_t dt, alphasparse_operation_t op,
-                                       struct alpha_matrix_descr descr) {
+                                       struct alpha_matrix_descr descr, bool structured_ok) {
     if (!A || !A->mat || !x || !y) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
     if (A->datatype != dt) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
     if (op == ALPHA_SPARSE_OPERATION_CONJUGATE_TRANSPOSE) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
@@ -465,9 +548,10 @@ static alphasparse_status_t check_call(const alphasparse_matrix_t A, const void 
     }
     if (A->format == ALPHA_SPARSE_FORMAT_CSR) {
         if (descr.type == ALPHA_SPARSE_MATRIX_TYPE_GENERAL) return ALPHA_SPARSE_STATUS_SUCCESS;
+        if (descr.type == ALPHA_SPARSE_MATRIX_TYPE_HERMITIAN) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;  // complex only
         if (descr.type >= ALPHA_SPARSE_MATRIX_TYPE_SYMMETRIC &&
             descr.type <= ALPHA_SPARSE_MATRIX_TYPE_DIAGONAL)
-            return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+            return structured_ok ? ALPHA_SPARSE_STATUS_SUCCESS : ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
         return ALPHA_SPARSE_STATUS_INVALID_VALUE;
     }
     if (A->format == ALPHA_SPARSE_FORMAT_COO ||
@@ -537,14 +621,29 @@ static alphasparse_status_t mv_host_pipelined(DeviceCtx *c, T alpha, const T *x,
 template <typename T>
 static alphasparse_status_t mv(alphasparse_operation_t op, T alpha, const alphasparse_matrix_t A,
                                struct alpha_matrix_descr descr, const T *x, T beta, T *y) {
-    alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr);
+    alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr, true);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     DeviceCtx *c = ctx_of(A);
     if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
 
     DeviceGuard guard(c->device);
     if (!guard.ok) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
-    if (op == ALPHA_SPARSE_OPERATION_TRANSPOSE) {  // y (cols entries) = alpha * A^T * x (rows entries) + beta * y
+    if (descr.type != ALPHA_SPARSE_MATRIX_TYPE_GENERAL) {
+        // SYMMETRIC has no transposed entry in the reference's table (NOT_SUPPORTED there too); the
+        // diagonal kernels ignore the operation; fill / diag flags outside {0,1} index past its tables
+        if (descr.type == ALPHA_SPARSE_MATRIX_TYPE_SYMMETRIC && op != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE)
+            return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+        if ((unsigned)descr.mode > 1u || (unsigned)descr.diag > 1u) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+        if (c->rows != c->cols) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+        const int trans = descr.type == ALPHA_SPARSE_MATRIX_TYPE_TRIANGULAR && op == ALPHA_SPARSE_OPERATION_TRANSPOSE;
+        const int upper = descr.type == ALPHA_SPARSE_MATRIX_TYPE_DIAGONAL ? 0 : (int)descr.mode;
+        std::lock_guard<std::mutex> build(c->mu);
+        DeviceCtx *d = nullptr;
+        s = ensure_derived<T>(c, static_cast<const typename CsrOf<T>::csr *>(A->mat), (int)descr.type, upper,
+                              (int)descr.diag, trans, &d);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        c = d;
+    } else if (op == ALPHA_SPARSE_OPERATION_TRANSPOSE) {  // y (cols entries) = alpha * A^T * x (rows entries) + beta * y
         {
             std::lock_guard<std::mutex> build(c->mu);
             s = ensure_transposed<T>(c, static_cast<const typename CsrOf<T>::csr *>(A->mat));
@@ -602,7 +701,7 @@ static alphasparse_status_t mm(alphasparse_operation_t op, T alpha, const alphas
                                struct alpha_matrix_descr descr, alphasparse_layout_t layout,
                                const T *x, ALPHA_INT columns, ALPHA_INT ldx, T beta, T *y,
                                ALPHA_INT ldy) {
-    alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr);
+    alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr, false);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     if (layout != ALPHA_SPARSE_LAYOUT_ROW_MAJOR && layout != ALPHA_SPARSE_LAYOUT_COLUMN_MAJOR)
         return ALPHA_SPARSE_STATUS_INVALID_VALUE;

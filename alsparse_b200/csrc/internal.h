@@ -116,6 +116,8 @@ struct DeviceCtx {
 
     // A^T as a second device CSR, built on the first transposed mv / mm call and kept
     DeviceCtx *transposed = nullptr;
+    // matrices derived for SYMMETRIC / TRIANGULAR / DIAGONAL descriptors, built on first use and kept
+    DeviceCtx *derived[24] = {};
 
     int64_t device_bytes = 0;
     std::mutex mu;  // serialises calls that share the carry and staging buffers

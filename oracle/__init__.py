@@ -52,6 +52,9 @@ def lib():
                                                                       _i32]
             getattr(L, f"oracle_gemm_csr_row_omp_{k}").argtypes = [_i32, _p, _p, _p, _p, T, _p, _i32, _i32, T, _p,
                                                                     _i32, _i32]
+            getattr(L, f"oracle_trmv_csr_{k}").argtypes = [C.c_int, C.c_int, C.c_int, _i32, _p, _p, _p, _p, T, _p, T, _p]
+            getattr(L, f"oracle_symv_csr_{k}").argtypes = [C.c_int, C.c_int, _i32, _p, _p, _p, _p, T, _p, T, _p]
+            getattr(L, f"oracle_diagmv_csr_{k}").argtypes = [C.c_int, _i32, _p, _p, _p, _p, T, _p, T, _p]
             getattr(L, f"oracle_create_csr_{k}").argtypes = [_i32, _i32, _p, _p, _p, _p, _p, _p, _p]
             getattr(L, f"oracle_create_csr_{k}").restype = _i32
             getattr(L, f"oracle_coo_to_csr_{k}").argtypes = [_i32, _i32, _i32, _p, _p, _p, _p, _p, _p]
@@ -92,6 +95,21 @@ def gemm(kind, layout, rows_start, rows_end, col, val, alpha, X, columns, ldx, b
     else:
         getattr(lib(), f"oracle_gemm_csr_{layout}_{kind}")(*args)
     return Y
+
+
+def structured_mv(kind, descr_type, upper, unit, trans, rows_start, rows_end, col, val, alpha, x, beta, y):
+    """mv under a TRIANGULAR (3), SYMMETRIC (1) or DIAGONAL (4) descriptor; y modified in place."""
+    rs, re_, ci = _i(rows_start), _i(rows_end), _i(col)
+    tail = [len(rs), _a(rs), _a(re_), _a(ci), _a(val), alpha, _a(x), beta, _a(y)]
+    if descr_type == 3:
+        getattr(lib(), f"oracle_trmv_csr_{kind}")(int(upper), int(unit), int(trans), *tail)
+    elif descr_type == 1:
+        getattr(lib(), f"oracle_symv_csr_{kind}")(int(upper), int(unit), *tail)
+    elif descr_type == 4:
+        getattr(lib(), f"oracle_diagmv_csr_{kind}")(int(unit), *tail)
+    else:
+        raise ValueError(descr_type)
+    return y
 
 
 def create_csr(kind, base, rows_start, rows_end, col, val):
@@ -161,6 +179,10 @@ def ref():
             for name in (f"gemm_{k}_csr_row_plain", f"gemm_{k}_csr_col_plain", f"gemm_{k}_csr_row",
                          f"gemm_{k}_csr_col", f"gemm_{k}_csr_row_trans_plain", f"gemm_{k}_csr_col_trans_plain"):
                 getattr(L, name).argtypes = [T, _p, _p, _i32, _i32, T, _p, _i32]
+            for name in [f"symv_{k}_csr_{d}_{m}_plain" for d in "nu" for m in ("lo", "hi")] + \
+                        [f"trmv_{k}_csr_{d}_{m}{t}_plain" for d in "nu" for m in ("lo", "hi") for t in ("", "_trans")] + \
+                        [f"diagmv_{k}_csr_{d}_plain" for d in "nu"]:
+                getattr(L, name).argtypes = [T, _p, _p, T, _p]
             getattr(L, f"alphasparse_{k}_export_csr").argtypes = [_p] * 8
         L.balanced_partition_row_by_nnz.argtypes = [_p, _i32, _i32, _p]
         L.alpha_set_thread_num.argtypes = [C.c_int]
@@ -231,6 +253,15 @@ class RefCsr:
         else:
             fn = getattr(L, f"gemv_{self.kind}_csr_plain")
         st = fn(alpha, self.mat, _a(x), beta, _a(y))
+        assert st == 0
+        return y
+
+    def structured_mv(self, descr_type, upper, unit, trans, alpha, x, beta, y):
+        """The reference's plain symv / trmv / diagmv kernel for the given descriptor."""
+        d, m = "u" if unit else "n", "hi" if upper else "lo"
+        name = {1: f"symv_{self.kind}_csr_{d}_{m}_plain", 3: f"trmv_{self.kind}_csr_{d}_{m}{'_trans' if trans else ''}_plain",
+                4: f"diagmv_{self.kind}_csr_{d}_plain"}[descr_type]
+        st = getattr(ref(), name)(alpha, self.mat, _a(x), beta, _a(y))
         assert st == 0
         return y
 

@@ -329,3 +329,91 @@ int oracle_mm_status(int has_handle, int has_mat, int has_x, int has_y, int hand
     return oracle_mv_status(has_handle, has_mat, has_x, has_y, handle_datatype, call_datatype,
                             operation, descr_type, format, rows, cols);
 }
+
+/* ---------------------------------------------------------------------------------------
+ * Structured descriptors on a CSR handle (the other branches of alphasparse_?_mv's CSR
+ * block, src/core/op/level2/alphasparse_x_mv.c:1693-1716).  A is square; only the stored
+ * elements on the requested side of the diagonal take part.
+ *
+ * TRIANGULAR, src/plain/kernel/level2/mv/trmv/csr/trmv_x_csr_{n,u}_{lo,hi}[_trans]_plain.c:
+ *   y = beta*y + alpha*op(T)*x, T = lower (col <= row) or upper (col >= row) part; with a
+ *   unit diagonal the stored diagonal is ignored and x[row] is added instead.  Non-transposed:
+ *   a dot product per row from zero (from x[row] when unit), scaled by alpha, added to beta*y.
+ *   Transposed: y scaled row by row while every kept element scatters (alpha*a)*x[row] into
+ *   y[col]; unit adds alpha*x[row] to y[row].
+ * SYMMETRIC, .../symv/csr/symv_x_csr_{n,u}_{lo,hi}_plain.c: every kept off-diagonal element a
+ *   contributes (alpha*a)*x[row] to y[col] and (alpha*a)*x[col] to y[row]; diagonal elements
+ *   once (or alpha*x[row] when unit).  Only operation NON_TRANSPOSE is in the dispatch table
+ *   (alphasparse_x_mv.c:89-107); TRANSPOSE returns NOT_SUPPORTED.
+ * DIAGONAL, .../diagmv/diagmv_x_csr_{n,u}_plain.c: y = beta*y + alpha*d.*x where d[row] is the
+ *   FIRST stored element of the row whose column equals the row (1 when unit, 0 if none).
+ * ------------------------------------------------------------------------------------- */
+#define DEF_STRUCT(T, sfx)                                                                    \
+    void oracle_trmv_csr_##sfx(int upper, int unit, int trans, aint rows, const aint *rs,     \
+                               const aint *re, const aint *col, const T *val, T alpha,        \
+                               const T *x, T beta, T *y) {                                    \
+        if (!trans) {                                                                         \
+            for (aint i = 0; i < rows; i++) {                                                 \
+                T dot = unit ? x[i] : (T)0;                                                   \
+                for (aint k = rs[i]; k < re[i]; k++) {                                        \
+                    const aint c = col[k];                                                    \
+                    const int keep = upper ? (unit ? c > i : c >= i) : (unit ? c < i : c <= i); \
+                    if (keep) dot += val[k] * x[c];                                           \
+                }                                                                             \
+                dot = dot * alpha;                                                            \
+                y[i] = y[i] * beta;                                                           \
+                y[i] += dot;                                                                  \
+            }                                                                                 \
+        } else {                                                                              \
+            for (aint i = 0; i < rows; i++) y[i] = y[i] * beta;                               \
+            for (aint i = 0; i < rows; i++) {                                                 \
+                if (unit) y[i] += alpha * x[i];                                               \
+                for (aint k = rs[i]; k < re[i]; k++) {                                        \
+                    const aint c = col[k];                                                    \
+                    const int keep = upper ? (unit ? c > i : c >= i) : (unit ? c < i : c <= i); \
+                    if (keep) {                                                               \
+                        T av = alpha * val[k];                                                \
+                        y[c] += av * x[i];                                                    \
+                    }                                                                         \
+                }                                                                             \
+            }                                                                                 \
+        }                                                                                     \
+    }                                                                                         \
+    void oracle_symv_csr_##sfx(int upper, int unit, aint rows, const aint *rs, const aint *re, \
+                               const aint *col, const T *val, T alpha, const T *x, T beta,    \
+                               T *y) {                                                        \
+        for (aint i = 0; i < rows; i++) y[i] = y[i] * beta;                                   \
+        for (aint i = 0; i < rows; i++) {                                                     \
+            if (unit) y[i] += alpha * x[i];                                                   \
+            for (aint k = rs[i]; k < re[i]; k++) {                                            \
+                const aint c = col[k];                                                        \
+                const int off = upper ? c > i : c < i;                                        \
+                T av = alpha * val[k];                                                        \
+                if (off) {                                                                    \
+                    y[c] += av * x[i];                                                        \
+                    y[i] += av * x[c];                                                        \
+                } else if (c == i && !unit) {                                                 \
+                    y[i] += av * x[c];                                                        \
+                }                                                                             \
+            }                                                                                 \
+        }                                                                                     \
+    }                                                                                         \
+    void oracle_diagmv_csr_##sfx(int unit, aint rows, const aint *rs, const aint *re,         \
+                                 const aint *col, const T *val, T alpha, const T *x, T beta,  \
+                                 T *y) {                                                      \
+        for (aint i = 0; i < rows; i++) {                                                     \
+            y[i] = y[i] * beta;                                                               \
+            if (unit) {                                                                       \
+                y[i] += alpha * x[i];                                                         \
+                continue;                                                                     \
+            }                                                                                 \
+            for (aint k = rs[i]; k < re[i]; k++)                                              \
+                if (col[k] == i) {                                                            \
+                    T av = alpha * val[k];                                                    \
+                    y[i] += av * x[i];                                                        \
+                    break;                                                                    \
+                }                                                                             \
+        }                                                                                     \
+    }
+DEF_STRUCT(float, s)
+DEF_STRUCT(double, d)

@@ -98,6 +98,28 @@ def main():
             out[f"{name}_par"] = np.array([columns, ldx, ldy, ldxc, ldyc, alpha, beta])
         np.savez_compressed(os.path.join(OUT, f"mm_{kind}.npz"), **out)
 
+    # -- structured descriptors (symmetric / triangular / diagonal) on a square matrix with missing and
+    #    repeated diagonal entries: the reference's plain symv / trmv / diagmv kernels ---------------------
+    q = synth.poisson("d", 9, 160, 160, 7.0)
+    rid = np.repeat(np.arange(160), np.diff(q.ptr))
+    keep = ~((q.col == rid) & (rid % 3 == 0))                     # every third row loses its diagonal
+    qcol, qval, qlens = q.col[keep], q.val[keep], np.bincount(rid[keep], minlength=160)
+    extra_r = np.arange(1, 160, 5)                                # some rows get a second diagonal entry at the end
+    order = np.argsort(np.concatenate([rid[keep], extra_r]), kind="stable")
+    qcol = np.concatenate([qcol, extra_r])[order].astype(np.int32)
+    qval = np.concatenate([qval, np.full(len(extra_r), 0.25)])[order]
+    qlens[extra_r] += 1
+    qptr = np.concatenate([[0], np.cumsum(qlens)]).astype(np.int32)
+    xs, ys = synth.vector("d", 9, 1, 160), synth.vector("d", 9, 2, 160)
+    Q = oracle.RefCsr.from_csr("d", 0, 160, 160, qptr[:-1], qptr[1:], qcol, qval)
+    out = dict(ptr=qptr, col=qcol, val=qval, x=xs, y0=ys, alpha=0.75, beta=-0.5)
+    for t, transes in ((1, (0,)), (3, (0, 1)), (4, (0,))):
+        for upper in (0, 1):
+            for unit in (0, 1):
+                for tr in transes:
+                    out[f"y_t{t}_u{upper}_d{unit}_o{tr}"] = Q.structured_mv(t, upper, unit, tr, 0.75, xs, -0.5, ys.copy())
+    np.savez_compressed(os.path.join(OUT, "struct_d.npz"), **out)
+
     # -- nnz-balanced row partition: known answers incl. the quirks ---------------------------------
     cases = {}
     accs = {"tiny": np.array([2, 3, 4], np.int32), "cfg1": m.ptr[1:], "zipf": z.ptr[1:],

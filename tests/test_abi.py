@@ -94,7 +94,7 @@ def test_argument_checks_need_no_device():
     assert spblas.mv("d", 0, 1.0, C.byref(h), g, x, 0.0, x) == capi.INVALID_VALUE        # datatype mismatch
     assert spblas.mv("s", capi.CONJUGATE_TRANSPOSE, 1.0, C.byref(h), g, x, 0.0, x) == capi.INVALID_VALUE
     assert spblas.mv("s", 0, 1.0, C.byref(h), spblas.descr(6), x, 0.0, x) == capi.INVALID_VALUE
-    assert spblas.mv("s", 0, 1.0, C.byref(h), spblas.descr(capi.TRIANGULAR), x, 0.0, x) == capi.NOT_SUPPORTED
+    assert spblas.mv("s", 0, 1.0, C.byref(h), spblas.descr(capi.TRIANGULAR), x, 0.0, x) == capi.INVALID_HANDLE  # no device context behind it
     h.format = 9
     assert spblas.mv("s", 0, 1.0, C.byref(h), g, x, 0.0, x) == capi.INVALID_VALUE
     h.format = capi.FORMAT_CSR

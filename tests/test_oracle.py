@@ -74,6 +74,26 @@ def test_gemm_golden(kind, case):
                       g[f"{case}_col"].reshape(columns, ldyc)[:, :rows].T.reshape(-1), sc.reshape(-1), f"mm col {case}")
 
 
+def test_structured_descriptors_golden():
+    """symv / trmv / diagmv restatements against the reference's plain kernels (all fill / diag / op variants)."""
+    g = golden("struct_d.npz")
+    ptr, a, b = g["ptr"], float(g["alpha"]), float(g["beta"])
+    full = np.abs(b * g["y0"]) + abs(a) * (np.bincount(np.repeat(np.arange(160), np.diff(ptr)),
+                                                       weights=np.abs(g["val"] * g["x"][g["col"]]), minlength=160) +
+                                           np.bincount(g["col"], weights=np.abs(g["val"] * np.repeat(g["x"], np.diff(ptr))),
+                                                       minlength=160) + np.abs(g["x"]))
+    n = 0
+    for t, transes in ((1, (0,)), (3, (0, 1)), (4, (0,))):
+        for upper in (0, 1):
+            for unit in (0, 1):
+                for tr in transes:
+                    y = oracle.structured_mv("d", t, upper, unit, tr, ptr[:-1], ptr[1:], g["col"], g["val"], a, g["x"],
+                                             b, g["y0"].copy())
+                    assert_rows_close("d", y, g[f"y_t{t}_u{upper}_d{unit}_o{tr}"], full, f"type {t} {upper}{unit}{tr}")
+                    n += 1
+    assert n == 16
+
+
 def test_coo_to_csr_golden():
     g = golden("cfg1_s.npz")
     ptr, col, val = oracle.coo_to_csr("s", 1, 1000, g["coo_ri"] + 1, g["coo_ci"] + 1, g["coo_v"])
