@@ -112,6 +112,8 @@ def prototypes():
     p["alpha_set_thread_num"] = (None, [C.c_int])
     p["alpha_get_thread_num"] = (C.c_int, [])
     p["alpha_timing_wtime"] = (C.c_double, [])
+    p["alpha_read_coo"] = (None, [C.c_char_p, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I), _HP, _HP, _HP])
+    p["alpha_read_coo_d"] = (None, [C.c_char_p, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I), _HP, _HP, _HP])
     p["lower_bound_int"] = (C.c_int, [_P, _I, _I, _I])
     p["balanced_partition_row_by_nnz"] = (None, [_P, _I, _I, _P])
     return p

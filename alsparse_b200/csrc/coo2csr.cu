@@ -1,0 +1,312 @@
+// COO -> CSR on the GPU, for alphasparse_convert_csr on large COO handles.
+//
+// The reference sorts (row, column, value) records with a serial qsort and then counts rows
+// (src/core/format/convert_csr_x_coo.c:14-81); minutes at 2^28 elements.  Here the same output --
+// elements ordered by row then column, duplicates kept, in input order among equals (qsort leaves
+// that unspecified) -- comes from a stable least-significant-digit radix sort of 64-bit keys
+// (row << 32 | column) carrying the element's input position, 4 bits per pass over only the bits the
+// matrix dimensions use, followed by one binary search per row for the offsets and one gather of the
+// values.  Integer work, HBM-bound: every pass reads and writes 12 bytes per element.
+#include <algorithm>
+
+#include "internal.h"
+
+namespace asb {
+
+constexpr int kSortThreads = 256;
+constexpr int kSortItems = 8;  // consecutive elements per thread (blocked), so order = thread order
+constexpr int kSortTile = kSortThreads * kSortItems;
+
+__global__ void coo_keys_kernel(long long nnz, const int *__restrict__ ri, const int *__restrict__ ci, int rows,
+                                int cols, unsigned long long *__restrict__ keys, unsigned *__restrict__ pos,
+                                unsigned long long *__restrict__ bad) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nnz) return;
+    const int r = ri[i], c = ci[i];
+    if (r < 0 || r >= rows || c < 0 || c >= cols) atomicAdd(bad, 1ull);
+    keys[i] = ((unsigned long long)(unsigned)r << 32) | (unsigned)c;
+    pos[i] = (unsigned)i;
+}
+
+// Per block: how many of its elements fall into each of the 16 digit values.  hist is digit-major
+// (hist[d * blocks + b]) so that one exclusive scan over it yields every block's write offsets.
+__global__ void __launch_bounds__(kSortThreads)
+    radix_hist_kernel(long long n, const unsigned long long *__restrict__ keys, int shift, unsigned *__restrict__ hist) {
+    __shared__ unsigned s_cnt[16];
+    if (threadIdx.x < 16) s_cnt[threadIdx.x] = 0;
+    __syncthreads();
+    const long long base = (long long)blockIdx.x * kSortTile + (long long)threadIdx.x * kSortItems;
+    unsigned local[16];
+#pragma unroll
+    for (int d = 0; d < 16; d++) local[d] = 0;
+#pragma unroll
+    for (int k = 0; k < kSortItems; k++)
+        if (base + k < n) {
+            const unsigned d = (unsigned)(keys[base + k] >> shift) & 15u;
+#pragma unroll
+            for (int q = 0; q < 16; q++) local[q] += (q == d);
+        }
+#pragma unroll
+    for (int d = 0; d < 16; d++)
+        if (local[d]) atomicAdd(&s_cnt[d], local[d]);
+    __syncthreads();
+    if (threadIdx.x < 16) hist[(size_t)threadIdx.x * gridDim.x + blockIdx.x] = s_cnt[threadIdx.x];
+}
+
+// Exclusive scan of n unsigned values in three steps (block sums, scan of the sums by one block, add).
+constexpr int kScanThreads = 256, kScanItems = 16, kScanTile = kScanThreads * kScanItems;
+
+__device__ __forceinline__ unsigned block_exclusive_scan(unsigned v, unsigned *total) {
+    __shared__ unsigned s_warp[kScanThreads / 32];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    unsigned inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) s_warp[wid] = inc;
+    __syncthreads();
+    unsigned before = 0, all = 0;
+    for (int w = 0; w < kScanThreads / 32; w++) {
+        if (w < wid) before += s_warp[w];
+        all += s_warp[w];
+    }
+    __syncthreads();
+    if (total) *total = all;
+    return before + inc - v;
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+    scan_sums_kernel(long long n, const unsigned *__restrict__ in, unsigned *__restrict__ sums) {
+    const long long base = (long long)blockIdx.x * kScanTile + (long long)threadIdx.x * kScanItems;
+    unsigned s = 0;
+    for (int k = 0; k < kScanItems; k++)
+        if (base + k < n) s += in[base + k];
+    unsigned total;
+    block_exclusive_scan(s, &total);
+    if (threadIdx.x == 0) sums[blockIdx.x] = total;
+}
+
+__global__ void __launch_bounds__(kScanThreads) scan_top_kernel(int nblocks, unsigned *__restrict__ sums) {
+    unsigned carry = 0;  // one block walks the block sums, kScanThreads at a time
+    for (int base = 0; base < nblocks; base += kScanThreads) {
+        const int i = base + threadIdx.x;
+        const unsigned v = i < nblocks ? sums[i] : 0;
+        unsigned total;
+        const unsigned ex = block_exclusive_scan(v, &total);
+        if (i < nblocks) sums[i] = carry + ex;
+        carry += total;
+        __syncthreads();
+    }
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+    scan_apply_kernel(long long n, unsigned *__restrict__ data, const unsigned *__restrict__ sums) {
+    const long long base = (long long)blockIdx.x * kScanTile + (long long)threadIdx.x * kScanItems;
+    unsigned v[kScanItems], s = 0;
+    for (int k = 0; k < kScanItems; k++) {
+        v[k] = base + k < n ? data[base + k] : 0;
+        s += v[k];
+    }
+    unsigned run = sums[blockIdx.x] + block_exclusive_scan(s, nullptr);
+    for (int k = 0; k < kScanItems; k++)
+        if (base + k < n) {
+            data[base + k] = run;
+            run += v[k];
+        }
+}
+
+// Stable scatter of one pass: element order inside a block is thread order then item order, so the
+// rank of an element among the block's elements with the same digit is (same-digit elements of
+// earlier threads) + (same-digit elements earlier in this thread).
+__global__ void __launch_bounds__(kSortThreads)
+    radix_scatter_kernel(long long n, const unsigned long long *__restrict__ keys_in,
+                         const unsigned *__restrict__ pos_in, int shift, const unsigned *__restrict__ offs,
+                         unsigned long long *__restrict__ keys_out, unsigned *__restrict__ pos_out) {
+    __shared__ unsigned s_cnt[16][kSortThreads + 1];
+    const int t = threadIdx.x;
+    const long long base = (long long)blockIdx.x * kSortTile + (long long)t * kSortItems;
+    unsigned long long key[kSortItems];
+    unsigned local[16];
+#pragma unroll
+    for (int d = 0; d < 16; d++) local[d] = 0;
+#pragma unroll
+    for (int k = 0; k < kSortItems; k++) {
+        key[k] = base + k < n ? keys_in[base + k] : ~0ull;
+        if (base + k < n) {
+            const unsigned d = (unsigned)(key[k] >> shift) & 15u;
+#pragma unroll
+            for (int q = 0; q < 16; q++) local[q] += (q == d);
+        }
+    }
+#pragma unroll
+    for (int d = 0; d < 16; d++) s_cnt[d][t] = local[d];
+    __syncthreads();
+    // warp w turns the counts of digits 2w and 2w+1 into exclusive prefixes over the 256 threads
+    {
+        const int lane = t & 31, w = t >> 5;
+        for (int d = 2 * w; d < 2 * w + 2; d++) {
+            unsigned carry = 0;
+            for (int seg = 0; seg < kSortThreads; seg += 32) {
+                const unsigned v = s_cnt[d][seg + lane];
+                unsigned inc = v;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const unsigned u = __shfl_up_sync(0xffffffffu, inc, o);
+                    if (lane >= o) inc += u;
+                }
+                s_cnt[d][seg + lane] = carry + inc - v;
+                carry += __shfl_sync(0xffffffffu, inc, 31);
+            }
+        }
+    }
+    __syncthreads();
+    unsigned dst[16];
+#pragma unroll
+    for (int d = 0; d < 16; d++) dst[d] = offs[(size_t)d * gridDim.x + blockIdx.x] + s_cnt[d][t];
+#pragma unroll
+    for (int k = 0; k < kSortItems; k++)
+        if (base + k < n) {
+            const unsigned d = (unsigned)(key[k] >> shift) & 15u;
+            unsigned where = 0;
+#pragma unroll
+            for (int q = 0; q < 16; q++)
+                if (q == d) where = dst[q]++;
+            keys_out[where] = key[k];
+            pos_out[where] = pos_in[base + k];
+        }
+}
+
+// ptr[r] = first sorted element whose row is >= r (r = 0 .. rows); columns and values in sorted order.
+template <typename T>
+__global__ void csr_from_sorted_kernel(long long nnz, int rows, const unsigned long long *__restrict__ keys,
+                                       const unsigned *__restrict__ pos, const T *__restrict__ vals_in,
+                                       int *__restrict__ ptr, int *__restrict__ col, T *__restrict__ val) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i <= rows) {
+        long long lo = 0, hi = nnz;
+        while (lo < hi) {
+            const long long mid = (lo + hi) >> 1;
+            if ((long long)(keys[mid] >> 32) < i) lo = mid + 1;
+            else hi = mid;
+        }
+        ptr[i] = (int)lo;
+    }
+    if (i < nnz) {
+        col[i] = (int)(unsigned)keys[i];
+        val[i] = vals_in[pos[i]];
+    }
+}
+
+static int bits_for(int64_t n) {
+    int b = 1;
+    while (b < 31 && (1ll << b) < n) b++;
+    return b;
+}
+
+static alphasparse_status_t device_exclusive_scan(unsigned *d_data, long long n, unsigned *d_sums, cudaStream_t st) {
+    const int nb = (int)((n + kScanTile - 1) / kScanTile);
+    scan_sums_kernel<<<nb, kScanThreads, 0, st>>>(n, d_data, d_sums);
+    scan_top_kernel<<<1, kScanThreads, 0, st>>>(nb, d_sums);
+    scan_apply_kernel<<<nb, kScanThreads, 0, st>>>(n, d_data, d_sums);
+    count_launch(3);
+    ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+// Host COO arrays in, HOST 3-array CSR out (caller-provided buffers of rows+1 / nnz / nnz elements).
+// All device memory is temporary.  Returns INVALID_VALUE when an index is out of range.
+template <typename T>
+alphasparse_status_t coo_to_csr_device(int64_t rows, int64_t cols, int64_t nnz, const int *ri, const int *ci,
+                                       const T *v, int *out_ptr, int *out_col, T *out_val) {
+    cudaStream_t st = current_stream();
+    const long long nblocks = (nnz + kSortTile - 1) / kSortTile;
+    const long long hist_n = 16 * nblocks;
+    const int scan_blocks = (int)((hist_n + kScanTile - 1) / kScanTile);
+    int *d_ri = nullptr, *d_ci = nullptr, *d_ptr = nullptr, *d_col = nullptr;
+    T *d_v = nullptr, *d_val = nullptr;
+    unsigned long long *d_keys[2] = {nullptr, nullptr}, *d_bad = nullptr;
+    unsigned *d_pos[2] = {nullptr, nullptr}, *d_hist = nullptr, *d_sums = nullptr;
+    alphasparse_status_t status = ALPHA_SPARSE_STATUS_SUCCESS;
+    auto release = [&]() {
+        cudaFree(d_ri), cudaFree(d_ci), cudaFree(d_ptr), cudaFree(d_col), cudaFree(d_v), cudaFree(d_val);
+        cudaFree(d_keys[0]), cudaFree(d_keys[1]), cudaFree(d_pos[0]), cudaFree(d_pos[1]);
+        cudaFree(d_hist), cudaFree(d_sums), cudaFree(d_bad);
+    };
+#define TRY(expr, code)                       \
+    do {                                      \
+        cudaError_t _e = (expr);              \
+        if (_e != cudaSuccess) {              \
+            record_cuda_error(_e, #expr);     \
+            release();                        \
+            return (code);                    \
+        }                                     \
+    } while (0)
+    const size_t n = (size_t)nnz;
+    TRY(cudaMalloc(&d_ri, sizeof(int) * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMalloc(&d_ci, sizeof(int) * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMalloc(&d_v, sizeof(T) * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMalloc(&d_keys[0], 8 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMalloc(&d_keys[1], 8 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMalloc(&d_pos[0], 4 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMalloc(&d_pos[1], 4 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMalloc(&d_hist, sizeof(unsigned) * (size_t)hist_n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMalloc(&d_sums, sizeof(unsigned) * (size_t)(scan_blocks + 1)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMalloc(&d_bad, 8), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMemsetAsync(d_bad, 0, 8, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaMemcpyAsync(d_ri, ri, sizeof(int) * n, cudaMemcpyHostToDevice, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaMemcpyAsync(d_ci, ci, sizeof(int) * n, cudaMemcpyHostToDevice, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaMemcpyAsync(d_v, v, sizeof(T) * n, cudaMemcpyHostToDevice, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+
+    coo_keys_kernel<<<(unsigned)((nnz + 255) / 256), 256, 0, st>>>(nnz, d_ri, d_ci, (int)rows, (int)cols, d_keys[0],
+                                                                  d_pos[0], d_bad);
+    count_launch();
+    int cur = 0;
+    const int col_bits = bits_for(cols), row_bits = bits_for(rows);
+    for (int part = 0; part < 2 && status == ALPHA_SPARSE_STATUS_SUCCESS; part++) {
+        const int first = part == 0 ? 0 : 32, nbits = part == 0 ? col_bits : row_bits;
+        for (int shift = first; shift < first + nbits; shift += 4) {
+            radix_hist_kernel<<<(unsigned)nblocks, kSortThreads, 0, st>>>(nnz, d_keys[cur], shift, d_hist);
+            count_launch();
+            status = device_exclusive_scan(d_hist, hist_n, d_sums, st);
+            if (status != ALPHA_SPARSE_STATUS_SUCCESS) break;
+            radix_scatter_kernel<<<(unsigned)nblocks, kSortThreads, 0, st>>>(nnz, d_keys[cur], d_pos[cur], shift,
+                                                                            d_hist, d_keys[cur ^ 1], d_pos[cur ^ 1]);
+            count_launch();
+            cur ^= 1;
+        }
+    }
+    if (status != ALPHA_SPARSE_STATUS_SUCCESS) {
+        release();
+        return status;
+    }
+    // the input index arrays are no longer needed: reuse them for the result
+    d_ptr = nullptr;
+    TRY(cudaMalloc(&d_ptr, sizeof(int) * (size_t)(rows + 1)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMalloc(&d_val, sizeof(T) * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    d_col = d_ri;
+    d_ri = nullptr;
+    const long long work = std::max<long long>(nnz, rows + 1);
+    csr_from_sorted_kernel<T><<<(unsigned)((work + 255) / 256), 256, 0, st>>>(nnz, (int)rows, d_keys[cur], d_pos[cur],
+                                                                            d_v, d_ptr, d_col, d_val);
+    count_launch();
+    TRY(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    unsigned long long bad = 0;
+    TRY(cudaMemcpyAsync(&bad, d_bad, 8, cudaMemcpyDeviceToHost, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaMemcpyAsync(out_ptr, d_ptr, sizeof(int) * (size_t)(rows + 1), cudaMemcpyDeviceToHost, st),
+        ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaMemcpyAsync(out_col, d_col, sizeof(int) * n, cudaMemcpyDeviceToHost, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaMemcpyAsync(out_val, d_val, sizeof(T) * n, cudaMemcpyDeviceToHost, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+#undef TRY
+    release();
+    return bad ? ALPHA_SPARSE_STATUS_INVALID_VALUE : ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+template alphasparse_status_t coo_to_csr_device<float>(int64_t, int64_t, int64_t, const int *, const int *,
+                                                       const float *, int *, int *, float *);
+template alphasparse_status_t coo_to_csr_device<double>(int64_t, int64_t, int64_t, const int *, const int *,
+                                                        const double *, int *, int *, double *);
+
+}  // namespace asb

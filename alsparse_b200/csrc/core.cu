@@ -352,6 +352,26 @@ static alphasparse_status_t coo_to_csr(const typename CsrOf<T>::coo *src, bool t
     const int64_t nnz = src->nnz;
     const int *ri = transpose ? src->col_indx : src->row_indx;
     const int *ci = transpose ? src->row_indx : src->col_indx;
+    // Large inputs are sorted on the GPU (radix sort, coo2csr.cu); ALPHASPARSE_CUDA_COO=host|device forces a path.
+    static const int forced = [] {
+        const char *e = getenv("ALPHASPARSE_CUDA_COO");
+        return !e ? 0 : !strcmp(e, "host") ? 1 : !strcmp(e, "device") ? 2 : 0;
+    }();
+    if (nnz > 0 && forced != 1 && (forced == 2 || nnz >= (1 << 20))) {
+        int *ptr = static_cast<int *>(host_alloc(sizeof(int) * (size_t)(rows + 1)));
+        int *col = static_cast<int *>(host_alloc(sizeof(int) * (size_t)nnz));
+        T *val = static_cast<T *>(host_alloc(sizeof(T) * (size_t)nnz));
+        if (!ptr || !col || !val) {
+            free(ptr), free(col), free(val);
+            return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+        }
+        alphasparse_status_t s = coo_to_csr_device<T>(rows, cols, nnz, ri, ci, src->values, ptr, col, val);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) {
+            free(ptr), free(col), free(val);
+            return s;
+        }
+        return finish_csr_handle<T>(dest, rows, cols, ptr, col, val);
+    }
     for (int64_t i = 0; i < nnz; i++)
         if (ri[i] < 0 || ri[i] >= rows || ci[i] < 0 || ci[i] >= cols)
             return ALPHA_SPARSE_STATUS_INVALID_VALUE;

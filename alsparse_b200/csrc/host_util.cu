@@ -1,7 +1,9 @@
 // Host helpers exported alongside the sparse entry points (include/alphasparse/util.h).
 // Fresh implementations of the small utility surface every reference test program uses.
 #include <cuda_runtime.h>
+#include <stdio.h>
 #include <stdlib.h>
+#include <string.h>
 #include <time.h>
 
 #include <atomic>
@@ -13,6 +15,68 @@ namespace {
 std::atomic<int> g_threads{0};
 constexpr size_t kPinThreshold = 1 << 16;  // smaller blocks are not worth a page-locking call
 }  // namespace
+
+// Coordinate-text matrix reader with the reference's behaviour (src/util/io.c:39-114 single,
+// :116-191 double): comment lines start with '%'; the word "symmetric" on the FIRST line makes every
+// off-diagonal entry appear twice, the mirrored copy directly after the original; the first
+// non-comment line holds rows, columns and the number of entries; entries are one-based "row col
+// [value]", a missing value reads as 1.  Output arrays come from alpha_malloc (release with
+// alpha_free) and hold zero-based indices.  Unlike the reference, a file that cannot be opened or
+// that ends early yields *nnz_p = -1 and null arrays instead of undefined behaviour.
+template <typename T>
+static void read_coo(const char *file, ALPHA_INT *m_p, ALPHA_INT *n_p, ALPHA_INT *nnz_p, ALPHA_INT **row_index,
+                     ALPHA_INT **col_index, T **values) {
+    *nnz_p = -1, *row_index = nullptr, *col_index = nullptr, *values = nullptr;
+    FILE *fp = fopen(file, "r");
+    if (!fp) return;
+    char line[1024];
+    bool symmetric = false, first = true, have_sizes = false;
+    while (fgets(line, sizeof(line), fp)) {
+        if (first && line[0] == '%') {
+            for (char *tok = strtok(line, " \n"); tok; tok = strtok(nullptr, " \n"))
+                if (!strcmp(tok, "symmetric")) {
+                    symmetric = true;
+                    break;
+                }
+            line[0] = '%';
+        }
+        first = false;
+        if (line[0] != '%') {
+            have_sizes = true;
+            break;
+        }
+    }
+    long long m = 0, n = 0, entries = 0;
+    if (!have_sizes || sscanf(line, "%lld %lld %lld", &m, &n, &entries) != 3 || entries < 0) {
+        fclose(fp);
+        return;
+    }
+    const size_t cap = (size_t)entries * (symmetric ? 2 : 1);
+    ALPHA_INT *ri = static_cast<ALPHA_INT *>(alpha_malloc(sizeof(ALPHA_INT) * (cap ? cap : 1)));
+    ALPHA_INT *ci = static_cast<ALPHA_INT *>(alpha_malloc(sizeof(ALPHA_INT) * (cap ? cap : 1)));
+    T *v = static_cast<T *>(alpha_malloc(sizeof(T) * (cap ? cap : 1)));
+    size_t k = 0;
+    bool ok = ri && ci && v;
+    for (long long e = 0; ok && e < entries; e++) {
+        if (!fgets(line, sizeof(line), fp)) {
+            ok = false;
+            break;
+        }
+        char *end = line;
+        const long long r = strtoll(end, &end, 10), c = strtoll(end, &end, 10);
+        while (*end == ' ' || *end == '\t') end++;
+        const T a = (*end && *end != '\n' && *end != '\r') ? (T)strtod(end, nullptr) : T(1);
+        ri[k] = (ALPHA_INT)(r - 1), ci[k] = (ALPHA_INT)(c - 1), v[k] = a, k++;
+        if (symmetric && r != c) ri[k] = (ALPHA_INT)(c - 1), ci[k] = (ALPHA_INT)(r - 1), v[k] = a, k++;
+    }
+    fclose(fp);
+    if (!ok) {
+        alpha_free(ri), alpha_free(ci), alpha_free(v);
+        return;
+    }
+    *m_p = (ALPHA_INT)m, *n_p = (ALPHA_INT)n, *nnz_p = (ALPHA_INT)k;
+    *row_index = ri, *col_index = ci, *values = v;
+}
 
 extern "C" {
 
@@ -61,6 +125,15 @@ double alpha_timing_wtime(void) {
     struct timespec ts;
     clock_gettime(CLOCK_MONOTONIC, &ts);
     return (double)ts.tv_sec + 1e-9 * (double)ts.tv_nsec;
+}
+
+void alpha_read_coo(const char *file, ALPHA_INT *m_p, ALPHA_INT *n_p, ALPHA_INT *nnz_p, ALPHA_INT **row_index,
+                    ALPHA_INT **col_index, float **values) {
+    read_coo<float>(file, m_p, n_p, nnz_p, row_index, col_index, values);
+}
+void alpha_read_coo_d(const char *file, ALPHA_INT *m_p, ALPHA_INT *n_p, ALPHA_INT *nnz_p, ALPHA_INT **row_index,
+                      ALPHA_INT **col_index, double **values) {
+    read_coo<double>(file, m_p, n_p, nnz_p, row_index, col_index, values);
 }
 
 // Reference: src/util/partition.c:46-61.

@@ -154,4 +154,10 @@ template <typename T>
 alphasparse_status_t launch_spmm_col(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx,
                                      T beta, T *Y, int ldy, cudaStream_t stream);
 
+// COO -> CSR on the device (coo2csr.cu): host arrays in, host 3-array CSR out, same output as the host
+// path in core.cu (ordered by row then column, equal pairs in input order).
+template <typename T>
+alphasparse_status_t coo_to_csr_device(int64_t rows, int64_t cols, int64_t nnz, const int *ri, const int *ci,
+                                       const T *v, int *out_ptr, int *out_col, T *out_val);
+
 }  // namespace asb

@@ -172,3 +172,22 @@ def probe_gather_rate(kind, table_elems, gathers=1 << 27):
                                                          gathers, C.byref(rate))
     assert st == SUCCESS, (capi.STATUS_NAMES[st], last_error())
     return rate.value
+
+
+def read_coo(kind, path):
+    """alpha_read_coo / alpha_read_coo_d: (rows, cols, row_indx, col_indx, values) as numpy copies (zero-based)."""
+    lib = capi.load()
+    m, n, nnz = C.c_int32(), C.c_int32(), C.c_int32()
+    ri, ci, v = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    getattr(lib, "alpha_read_coo" if kind == "s" else "alpha_read_coo_d")(path.encode(), C.byref(m), C.byref(n),
+                                                                          C.byref(nnz), C.byref(ri), C.byref(ci),
+                                                                          C.byref(v))
+    if nnz.value < 0:
+        raise OSError(f"cannot read {path}")
+    k = nnz.value
+
+    def take(p, ct):
+        a = np.ctypeslib.as_array(C.cast(p, C.POINTER(ct)), shape=(max(k, 1),))[:k].copy()
+        lib.alpha_free(p)
+        return a
+    return m.value, n.value, take(ri, C.c_int32), take(ci, C.c_int32), take(v, C.c_float if kind == "s" else C.c_double)

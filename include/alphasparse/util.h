@@ -23,6 +23,14 @@ int alpha_get_thread_num(void);
 
 double alpha_timing_wtime(void);
 
+/* Coordinate-text ("%%MatrixMarket ... coordinate"-like) reader: reference include/alphasparse/util/io.h:19-20,
+ * src/util/io.c:39-191.  Zero-based output in arrays from alpha_malloc; a "symmetric" first line mirrors
+ * off-diagonal entries; a missing value reads as 1.  *nnz_p = -1 on an unreadable or truncated file. */
+void alpha_read_coo(const char *file, ALPHA_INT *m_p, ALPHA_INT *n_p, ALPHA_INT *nnz_p, ALPHA_INT **row_index,
+                    ALPHA_INT **col_index, float **values);
+void alpha_read_coo_d(const char *file, ALPHA_INT *m_p, ALPHA_INT *n_p, ALPHA_INT *nnz_p, ALPHA_INT **row_index,
+                      ALPHA_INT **col_index, double **values);
+
 /* first index in [l, r) whose element is >= value: reference src/util/partition.c:46-61 */
 int lower_bound_int(const ALPHA_INT *t, ALPHA_INT l, ALPHA_INT r, ALPHA_INT value);
 

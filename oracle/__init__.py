@@ -185,6 +185,8 @@ def ref():
                 getattr(L, name).argtypes = [T, _p, _p, T, _p]
             getattr(L, f"alphasparse_{k}_export_csr").argtypes = [_p] * 8
         L.balanced_partition_row_by_nnz.argtypes = [_p, _i32, _i32, _p]
+        for name in ("alpha_read_coo", "alpha_read_coo_d"):
+            getattr(L, name).argtypes = [C.c_char_p] + [_p] * 6
         L.alpha_set_thread_num.argtypes = [C.c_int]
         L.alpha_get_core_num.restype = C.c_int
         _ref = L
@@ -288,3 +290,15 @@ def ref_partition_rows_by_nnz(rows_end, parts):
 
 def ref_cores():
     return ref().alpha_get_core_num()
+
+
+def ref_read_coo(kind, path):
+    """The reference's own reader (src/util/io.c): (rows, cols, row_indx, col_indx, values)."""
+    m, n, nnz = C.c_int32(), C.c_int32(), C.c_int32()
+    ri, ci, v = C.c_void_p(), C.c_void_p(), C.c_void_p()
+    getattr(ref(), "alpha_read_coo" if kind == "s" else "alpha_read_coo_d")(path.encode(), C.byref(m), C.byref(n),
+                                                                            C.byref(nnz), C.byref(ri), C.byref(ci),
+                                                                            C.byref(v))
+    k = nnz.value
+    get = lambda p, ct: np.ctypeslib.as_array(C.cast(p, C.POINTER(ct)), shape=(max(k, 1),))[:k].copy()  # noqa: E731
+    return m.value, n.value, get(ri, C.c_int32), get(ci, C.c_int32), get(v, _CT[kind])

@@ -333,3 +333,39 @@ def test_structured_descriptors():
             assert spblas.mv(kind, tr, 1.25, A, spblas.descr(t, upper, unit), dx, 0.5, dy) == capi.SUCCESS
             assert_rows_close(kind, dy.cpu().numpy(), y_ref, sc, f"{kind} type {t}")
         spblas.destroy(A)
+
+
+@pytest.mark.parametrize("kind", ["s", "d"])
+def test_large_coo_is_sorted_on_the_device(kind):
+    """More than 2^20 COO entries take the GPU radix-sort path of alphasparse_convert_csr; the CSR must be
+    the one the reference's conversion produces (bit-exact, duplicates kept in input order)."""
+    m = synth.poisson(kind, 81, 90000, 70000, 14.0)
+    assert m.nnz > 1 << 20
+    rng = np.random.default_rng(81)
+    ri = np.repeat(np.arange(m.nrows, dtype=np.int32), np.diff(m.ptr))
+    # shuffle, then append repeated (row, col) pairs with different values: stable order keeps them as given
+    dup = rng.integers(0, m.nnz, 5000)
+    ri2 = np.concatenate([ri, ri[dup]])
+    ci2 = np.concatenate([m.col, m.col[dup]])
+    v2 = np.concatenate([m.val, rng.uniform(-1, 1, 5000).astype(m.val.dtype)])
+    perm = rng.permutation(len(ri2))
+    ri2, ci2, v2 = ri2[perm], ci2[perm], v2[perm]
+    for op, rows, cols, a, b in ((capi.NON_TRANSPOSE, m.nrows, m.cols, ri2, ci2), (capi.TRANSPOSE, m.cols, m.nrows, ci2, ri2)):
+        st, coo = spblas.create_coo(kind, capi.BASE_ONE, m.nrows, m.cols, len(ri2), ri2 + 1, ci2 + 1, v2)
+        assert st == capi.SUCCESS
+        st, A = spblas.convert_csr(coo, op)
+        assert st == capi.SUCCESS, spblas.last_error()
+        _, _, r, c, rs, re_, col, val = spblas.export_csr(kind, A)
+        optr, ocol, oval = oracle.coo_to_csr(kind, 0, rows, a, b, v2)
+        assert (r, c) == (rows, cols)
+        assert np.array_equal(np.concatenate([rs[:1], re_]), optr) and np.array_equal(col, ocol)
+        assert np.array_equal(val.view(np.uint8), oval.view(np.uint8))
+        spblas.destroy(A)
+        spblas.destroy(coo)
+    # an index outside the matrix is refused
+    bad = ri2.copy()
+    bad[7] = m.nrows
+    st, coo = spblas.create_coo(kind, capi.BASE_ZERO, m.nrows, m.cols, len(bad), bad, ci2, v2)
+    st, A = spblas.convert_csr(coo, capi.NON_TRANSPOSE)
+    assert st == capi.INVALID_VALUE and not A.value
+    spblas.destroy(coo)

@@ -87,3 +87,29 @@ def test_generator_shapes():
     x = synth.vector("d", 0, 1, 100000, 0.0, 1.0)
     assert 0.0 <= x.min() and x.max() < 1.0 and abs(x.mean() - 0.5) < 0.01
     assert np.array_equal(synth.vector("d", 0, 1, 100, 0.0, 1.0, first=50), x[50:150])
+
+
+def test_matrix_file_reader(tmp_path):
+    """alpha_read_coo / alpha_read_coo_d against the reference's reader on the same files."""
+    files = {
+        "general.mtx": "%%MatrixMarket matrix coordinate real general\n% a comment\n3 5 4\n1 1 2.5\n3 5 -1e-3\n2 4 7\n1 2 0.5\n",
+        "symmetric.mtx": "%%MatrixMarket matrix coordinate real symmetric\n4 4 5\n1 1 2.5\n3 1 -1\n4 2 0.125\n2 2\n4 4 7e-1\n",
+        "pattern.mtx": "% no banner at all\n%\n2 2 3\n1 2\n2 1\n2 2\n",
+    }
+    expect = {"general.mtx": (3, 5, [0, 2, 1, 0], [0, 4, 3, 1], [2.5, -1e-3, 7, 0.5]),
+              "symmetric.mtx": (4, 4, [0, 2, 0, 3, 1, 1, 3], [0, 0, 2, 1, 3, 1, 3], [2.5, -1, -1, 0.125, 0.125, 1, 0.7]),
+              "pattern.mtx": (2, 2, [0, 1, 1], [1, 0, 1], [1, 1, 1])}
+    for name, text in files.items():
+        path = str(tmp_path / name)
+        open(path, "w").write(text)
+        for kind in "sd":
+            m, n, ri, ci, v = spblas.read_coo(kind, path)
+            em, en, eri, eci, ev = expect[name]
+            assert (m, n) == (em, en) and ri.tolist() == eri and ci.tolist() == eci
+            assert np.array_equal(v, np.array(ev, dtype=v.dtype))
+            if oracle.ref_available():
+                rm, rn, rri, rci, rv = oracle.ref_read_coo(kind, path)
+                assert (m, n) == (rm, rn) and np.array_equal(ri, rri) and np.array_equal(ci, rci)
+                assert np.array_equal(v.view(np.uint8), rv.view(np.uint8))
+    with pytest.raises(OSError):
+        spblas.read_coo("s", str(tmp_path / "missing.mtx"))
