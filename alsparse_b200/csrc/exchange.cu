@@ -30,7 +30,7 @@ struct Exchange {
     void *peer_xbuf[2][kMaxPeers] = {};        // peer-mapped (own entries point at the local buffers)
     unsigned long long *peer_counters[kMaxPeers] = {};
     bool opened[kMaxPeers] = {};
-    int *d_status = nullptr;                   // 0 fine, 3 = a peer did not arrive within the poll budget
+    int *d_status = nullptr;                   // 0 fine, 3 = a peer did not arrive within the poll limit
     unsigned long long step = 0;
     int cur = 0;                               // index of the buffer holding the current x
     bool connected = false;

@@ -39,7 +39,10 @@ constexpr uint64_t kCtxMagic = 0x4153423230304358ull;  // guards against foreign
 constexpr int kTailPad = 16;
 
 // Merge-path tile shape: kMergeThreads threads, each consuming kMergeItems (rows+nnz) items.
-constexpr int kMergeThreads = 256;
+#ifndef ASB_MERGE_THREADS
+#define ASB_MERGE_THREADS 256
+#endif
+constexpr int kMergeThreads = ASB_MERGE_THREADS;
 constexpr int kMergeItemsS = 9;  // float
 #ifndef ASB_MERGE_IPT_D
 #define ASB_MERGE_IPT_D 7

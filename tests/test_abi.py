@@ -13,7 +13,7 @@ from alsparse_b200 import capi, spblas
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 INC = os.path.join(ROOT, "include")
-REF_INC = "/root/reference/include"
+REF_INC = os.path.join(os.environ.get("ALPHASPARSE_REFERENCE_DIR", "/root/reference"), "include")
 
 
 def declared_functions():
