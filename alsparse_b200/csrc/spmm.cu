@@ -148,9 +148,11 @@ static void launch_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx
 template <typename T, int VEC>
 static void launch_row_lanes(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx, T beta, T *Y,
                              int ldy, cudaStream_t st) {
-    // smallest group (8, 16 or 32 lanes) whose lanes cover the dense columns in one pass, if any
+    // smallest group (2 .. 32 lanes) whose lanes cover the dense columns in one pass, if any
     const int need = (columns + VEC - 1) / VEC;
-    if (need <= 8) launch_row<T, VEC, 8>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+    if (need <= 2) launch_row<T, VEC, 2>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+    else if (need <= 4) launch_row<T, VEC, 4>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+    else if (need <= 8) launch_row<T, VEC, 8>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
     else if (need <= 16) launch_row<T, VEC, 16>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
     else launch_row<T, VEC, 32>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
 }
