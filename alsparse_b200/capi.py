@@ -96,12 +96,15 @@ def prototypes():
     p["alphasparse_cuda_exchange_set_mode"] = (C.c_int, [_H, C.c_int])
     p["alphasparse_cuda_exchange_x"] = (C.c_int, [_H, _HP])
     p["alphasparse_cuda_exchange_status"] = (C.c_int, [_H, C.POINTER(C.c_int)])
+    p["alphasparse_cuda_exchange_debug_wait"] = (C.c_int, [_H, C.c_int64])
+    p["alphasparse_cuda_exchange_clear_status"] = (C.c_int, [_H])
     p["alphasparse_cuda_exchange_destroy"] = (C.c_int, [_H])
     p["alphasparse_s_mv_exchange"] = (C.c_int, [C.c_float, _H, MatrixDescr, _H, C.c_float, _P])
     p["alphasparse_d_mv_exchange"] = (C.c_int, [C.c_double, _H, MatrixDescr, _H, C.c_double, _P])
     p["alphasparse_cuda_profile_kernel"] = (C.c_int, [_H, C.c_int])
     p["alphasparse_cuda_kernel_ms"] = (C.c_int, [_H, C.POINTER(C.c_float)])
     p["alphasparse_cuda_probe_gather_rate"] = (C.c_int, [C.c_int, C.c_int64, C.c_int64, C.POINTER(C.c_double)])
+    p["alphasparse_cuda_debug_fail_alloc"] = (C.c_int, [C.c_int64])
     p["alphasparse_cuda_launch_count"] = (C.c_int64, [])
     p["alphasparse_cuda_last_error"] = (C.c_char_p, [])
     # include/alphasparse/util.h

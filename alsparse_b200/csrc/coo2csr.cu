@@ -244,16 +244,16 @@ alphasparse_status_t coo_to_csr_device(int64_t rows, int64_t cols, int64_t nnz, 
         }                                     \
     } while (0)
     const size_t n = (size_t)nnz;
-    TRY(cudaMalloc(&d_ri, sizeof(int) * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-    TRY(cudaMalloc(&d_ci, sizeof(int) * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-    TRY(cudaMalloc(&d_v, sizeof(T) * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-    TRY(cudaMalloc(&d_keys[0], 8 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-    TRY(cudaMalloc(&d_keys[1], 8 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-    TRY(cudaMalloc(&d_pos[0], 4 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-    TRY(cudaMalloc(&d_pos[1], 4 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-    TRY(cudaMalloc(&d_hist, sizeof(unsigned) * (size_t)hist_n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-    TRY(cudaMalloc(&d_sums, sizeof(unsigned) * (size_t)(scan_blocks + 1)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-    TRY(cudaMalloc(&d_bad, 8), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_ri, sizeof(int) * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_ci, sizeof(int) * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_v, sizeof(T) * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_keys[0], 8 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_keys[1], 8 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_pos[0], 4 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_pos[1], 4 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_hist, sizeof(unsigned) * (size_t)hist_n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_sums, sizeof(unsigned) * (size_t)(scan_blocks + 1)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_bad, 8), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
     TRY(cudaMemsetAsync(d_bad, 0, 8, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     TRY(cudaMemcpyAsync(d_ri, ri, sizeof(int) * n, cudaMemcpyHostToDevice, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     TRY(cudaMemcpyAsync(d_ci, ci, sizeof(int) * n, cudaMemcpyHostToDevice, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
@@ -283,8 +283,8 @@ alphasparse_status_t coo_to_csr_device(int64_t rows, int64_t cols, int64_t nnz, 
     }
     // the input index arrays are no longer needed: reuse them for the result
     d_ptr = nullptr;
-    TRY(cudaMalloc(&d_ptr, sizeof(int) * (size_t)(rows + 1)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-    TRY(cudaMalloc(&d_val, sizeof(T) * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_ptr, sizeof(int) * (size_t)(rows + 1)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_val, sizeof(T) * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
     d_col = d_ri;
     d_ri = nullptr;
     const long long work = std::max<long long>(nnz, rows + 1);

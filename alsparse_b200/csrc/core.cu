@@ -42,6 +42,19 @@ alphasparse_cuda_alg_t forced_algorithm() {
     return (alphasparse_cuda_alg_t)a;
 }
 
+static std::atomic<long long> g_fail_alloc_in{0};  // > 0: that many allocations from now, the last one fails
+
+cudaError_t device_alloc_bytes(void **p, size_t bytes) {
+    long long left = g_fail_alloc_in.load(std::memory_order_relaxed);
+    while (left > 0 && !g_fail_alloc_in.compare_exchange_weak(left, left - 1)) {
+    }
+    if (left == 1) {
+        *p = nullptr;
+        return cudaErrorMemoryAllocation;
+    }
+    return cudaMalloc(p, bytes);
+}
+
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 void record_cuda_error(cudaError_t e, const char *what) {
@@ -118,12 +131,12 @@ alphasparse_status_t ctx_create(int datatype, int64_t rows, int64_t cols, const 
     } while (0)
 
     // four spare offsets: the row-tile kernel copies offsets in 16-byte units
-    TRY(cudaMalloc(&c->d_row_ptr, sizeof(int) * (size_t)(rows + 1 + 4)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-    TRY(cudaMalloc(&c->d_status, sizeof(int)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&c->d_row_ptr, sizeof(int) * (size_t)(rows + 1 + 4)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&c->d_status, sizeof(int)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
     TRY(cudaMemsetAsync(c->d_status, 0, sizeof(int), st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     TRY(cudaMemsetAsync(c->d_row_ptr + rows + 1, 0, sizeof(int) * 4, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
-    TRY(cudaMalloc(&c->d_col, sizeof(int) * padded), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-    TRY(cudaMalloc(&c->d_val, tsz * padded), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&c->d_col, sizeof(int) * padded), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&c->d_val, tsz * padded), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
     c->device_bytes = (int64_t)(sizeof(int) * (size_t)(rows + 1) + (sizeof(int) + tsz) * padded);
 
     if (rows > 0) {
@@ -520,7 +533,7 @@ static alphasparse_status_t grow(void **buf, size_t *have, size_t want, DeviceCt
     *buf = nullptr;
     c->device_bytes -= (int64_t)*have;
     *have = 0;
-    ASB_CUDA_OR(cudaMalloc(buf, want), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    ASB_CUDA_OR(device_alloc(buf, want), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
     *have = want;
     c->device_bytes += (int64_t)want;
     return ALPHA_SPARSE_STATUS_SUCCESS;
@@ -1027,6 +1040,10 @@ alphasparse_status_t alphasparse_cuda_kernel_ms(const alphasparse_matrix_t A, fl
     if (!c->ev_start) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
     ASB_CUDA_OR(cudaEventSynchronize(c->ev_stop), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     ASB_CUDA_OR(cudaEventElapsedTime(ms, c->ev_start, c->ev_stop), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+alphasparse_status_t alphasparse_cuda_debug_fail_alloc(int64_t nth) {
+    g_fail_alloc_in.store(nth > 0 ? nth : 0, std::memory_order_relaxed);
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 int64_t alphasparse_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

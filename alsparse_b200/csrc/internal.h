@@ -21,6 +21,15 @@ alphasparse_cuda_alg_t forced_algorithm();
 void count_launch(int n = 1);
 void record_cuda_error(cudaError_t e, const char *what);
 
+// Every device allocation of the library goes through here: cudaMalloc, except that a test can ask
+// for the n-th allocation from now on to fail (alphasparse_cuda_debug_fail_alloc), which is how the
+// out-of-memory paths are exercised without exhausting a GPU.
+cudaError_t device_alloc_bytes(void **p, size_t bytes);
+template <typename P>
+inline cudaError_t device_alloc(P **p, size_t bytes) {
+    return device_alloc_bytes(reinterpret_cast<void **>(p), bytes);
+}
+
 // Maps a failed CUDA call to a status and records its text for alphasparse_cuda_last_error.
 #define ASB_CUDA_OR(expr, status)                          \
     do {                                                   \

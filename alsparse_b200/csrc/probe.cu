@@ -36,9 +36,9 @@ static alphasparse_status_t probe(int64_t table_elems, int64_t gathers, double *
     cudaStream_t st = current_stream();
     const size_t n = (size_t)gathers & ~(size_t)3, quads = n / 4;
     alphasparse_status_t status = ALPHA_SPARSE_STATUS_SUCCESS;
-    cudaError_t err = cudaMalloc(&idx, n * sizeof(int));
-    if (err == cudaSuccess) err = cudaMalloc(&table, (size_t)table_elems * sizeof(T));
-    if (err == cudaSuccess) err = cudaMalloc(&sink, sizeof(T) * 4);
+    cudaError_t err = device_alloc(&idx, n * sizeof(int));
+    if (err == cudaSuccess) err = device_alloc(&table, (size_t)table_elems * sizeof(T));
+    if (err == cudaSuccess) err = device_alloc(&sink, sizeof(T) * 4);
     if (err == cudaSuccess) err = cudaMemsetAsync(table, 0, (size_t)table_elems * sizeof(T), st);
     if (err == cudaSuccess) err = cudaEventCreate(&e0);
     if (err == cudaSuccess) err = cudaEventCreate(&e1);

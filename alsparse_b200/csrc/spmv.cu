@@ -683,7 +683,7 @@ alphasparse_status_t ctx_analyse(DeviceCtx *ctx) {
     if (ctx->rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
 
     unsigned long long *d_out = nullptr, h_out[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    ASB_CUDA_OR(cudaMalloc(&d_out, sizeof(h_out)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    ASB_CUDA_OR(device_alloc(&d_out, sizeof(h_out)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
     cudaError_t e = cudaMemsetAsync(d_out, 0, sizeof(h_out), st);
     if (e == cudaSuccess) {
         const int threads = 256;
@@ -741,14 +741,14 @@ alphasparse_status_t ctx_analyse(DeviceCtx *ctx) {
         ctx->merge_items = kMergeThreads * ipt;
         const int64_t total = ctx->rows + ctx->nnz;
         ctx->merge_tiles = (total + ctx->merge_items - 1) / ctx->merge_items;
-        ASB_CUDA_OR(cudaMalloc(&ctx->d_tile, sizeof(MergeCoord) * (size_t)(ctx->merge_tiles + 1)),
+        ASB_CUDA_OR(device_alloc(&ctx->d_tile, sizeof(MergeCoord) * (size_t)(ctx->merge_tiles + 1)),
                     ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-        ASB_CUDA_OR(cudaMalloc(&ctx->d_carry_row, sizeof(int) * (size_t)ctx->merge_tiles),
+        ASB_CUDA_OR(device_alloc(&ctx->d_carry_row, sizeof(int) * (size_t)ctx->merge_tiles),
                     ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-        ASB_CUDA_OR(cudaMalloc(&ctx->d_carry_val, tsz * (size_t)ctx->merge_tiles),
+        ASB_CUDA_OR(device_alloc(&ctx->d_carry_val, tsz * (size_t)ctx->merge_tiles),
                     ALPHA_SPARSE_STATUS_ALLOC_FAILED);
         const size_t nchunks = (size_t)(ctx->merge_tiles + kPushChunkTiles - 1) / kPushChunkTiles;
-        ASB_CUDA_OR(cudaMalloc(&ctx->d_chunk_done, sizeof(unsigned) * nchunks), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        ASB_CUDA_OR(device_alloc(&ctx->d_chunk_done, sizeof(unsigned) * nchunks), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
         ASB_CUDA_OR(cudaMemsetAsync(ctx->d_chunk_done, 0, sizeof(unsigned) * nchunks, st),
                     ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
         ctx->device_bytes += (int64_t)(sizeof(MergeCoord) * (size_t)(ctx->merge_tiles + 1) +

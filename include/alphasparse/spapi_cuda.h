@@ -110,6 +110,10 @@ alphasparse_status_t alphasparse_cuda_exchange_set_mode(alphasparse_cuda_exchang
 alphasparse_status_t alphasparse_cuda_exchange_x(alphasparse_cuda_exchange_t ex, void **x);
 /* Waits for the stream and reports whether any bounded wait ran out (status 3) since creation. */
 alphasparse_status_t alphasparse_cuda_exchange_status(alphasparse_cuda_exchange_t ex, int *status);
+/* Test aids for the bounded wait: enqueue a wait on a counter that no rank ever advances, limited to
+ * max_polls polls (it records status 3 and returns, the context stays usable), and reset the status. */
+alphasparse_status_t alphasparse_cuda_exchange_debug_wait(alphasparse_cuda_exchange_t ex, int64_t max_polls);
+alphasparse_status_t alphasparse_cuda_exchange_clear_status(alphasparse_cuda_exchange_t ex);
 alphasparse_status_t alphasparse_cuda_exchange_destroy(alphasparse_cuda_exchange_t ex);
 alphasparse_status_t alphasparse_s_mv_exchange(const float alpha, const alphasparse_matrix_t A,
                                                const struct alpha_matrix_descr descr,
@@ -132,6 +136,11 @@ alphasparse_status_t alphasparse_cuda_kernel_ms(const alphasparse_matrix_t A, fl
  * 4*gathers + table bytes on the device. */
 alphasparse_status_t alphasparse_cuda_probe_gather_rate(alphasparse_datatype_t datatype, int64_t table_elems,
                                                         int64_t gathers, double *per_second);
+
+/* Test aid: makes the nth device allocation the library performs from now on fail as if the device
+ * were out of memory (0 cancels).  The failing call returns ALPHA_SPARSE_STATUS_ALLOC_FAILED and
+ * releases whatever it had already allocated. */
+alphasparse_status_t alphasparse_cuda_debug_fail_alloc(int64_t nth);
 
 /* Number of kernels this library has launched in this process so far. */
 int64_t alphasparse_cuda_launch_count(void);
