@@ -226,6 +226,8 @@ def main():
                          "whichever of the two the library prefers for this many GPUs (auto) or by a NCCL allgather (nccl)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-others", action="store_true",
+                    help="do not append the short device-resident runs of the other three workloads (N=1 only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -438,6 +440,24 @@ def main():
         if world == 1 and not args.no_cpu_baseline:
             gbs, gfl, ms, desc = cpu_reference_run(name, cfg, 3, 1)
             line["cpu_baseline"] = dict(value=gbs, unit="GB/s", gflops=gfl, ms_per_step=ms, **desc)
+        if world == 1 and not args.no_others and not reduced:
+            # The other single-GPU configurations, each in a fresh process, device-resident numbers only:
+            # context for the headline above (they are parity-test cases, not separate bench lines).
+            others = {}
+            for w in sorted(WORKLOADS):
+                if w == name:
+                    continue
+                try:
+                    out = subprocess.run([sys.executable, os.path.abspath(__file__), "--workload", w, "--steps", "10",
+                                          "--warmup", "3", "--no-e2e", "--no-cpu-baseline", "--no-others"],
+                                         capture_output=True, text=True, timeout=600)
+                    d = json.loads(out.stdout.strip().splitlines()[-1])
+                    others[w] = {"value": d["value"], "unit": d["unit"], "ms_per_step": d["ms_per_step"],
+                                 "gflops": d["gflops"], "roofline_frac": d["roofline"]["frac"],
+                                 "algorithm": d["config"]["algorithm"], "nnz": d["config"]["nnz"]}
+                except Exception as exc:  # the headline must not depend on these
+                    others[w] = {"error": repr(exc)[:200]}
+            line["other_workloads"] = others
         print(json.dumps(line), flush=True)
 
     if fused is not None:
