@@ -219,19 +219,31 @@ __global__ void __launch_bounds__(kRowTile)
 
     if (tid < nr) {
         const int a0 = s_ptr[0] & ~3;
-        int k = s_ptr[tid] - a0;
-        const int e = s_ptr[tid + 1] - a0;
+        const int b = s_ptr[tid] - a0, e = s_ptr[tid + 1] - a0;
         if (e > cap) return;  // the oversize case flagged above
+        const int len = e - b;
+        // Neighbouring lanes read rows that start len elements apart: with an even len several lanes hit
+        // the same shared-memory bank on every step (16-way for len = 16).  Starting lane t at element
+        // t mod len of its row and wrapping round spreads them over the banks; the row is still summed
+        // completely, only from a different starting point.
+        int k = b + ((len & 1) == 0 && len > 0 ? tid % len : 0);
         T acc0 = T(0), acc1 = T(0), acc2 = T(0), acc3 = T(0);
-        for (; k + 4 <= e; k += 4) {
-            const int c0 = s_col[k], c1 = s_col[k + 1], c2 = s_col[k + 2], c3 = s_col[k + 3];
+        int left = len;
+        for (; left >= 4; left -= 4) {
+            const int k0 = k, k1 = (k0 + 1 == e) ? b : k0 + 1, k2 = (k1 + 1 == e) ? b : k1 + 1,
+                      k3 = (k2 + 1 == e) ? b : k2 + 1;
+            k = (k3 + 1 == e) ? b : k3 + 1;
+            const int c0 = s_col[k0], c1 = s_col[k1], c2 = s_col[k2], c3 = s_col[k3];
             const T x0 = __ldg(x + c0), x1 = __ldg(x + c1), x2 = __ldg(x + c2), x3 = __ldg(x + c3);
-            acc0 = fma(s_val[k], x0, acc0);
-            acc1 = fma(s_val[k + 1], x1, acc1);
-            acc2 = fma(s_val[k + 2], x2, acc2);
-            acc3 = fma(s_val[k + 3], x3, acc3);
+            acc0 = fma(s_val[k0], x0, acc0);
+            acc1 = fma(s_val[k1], x1, acc1);
+            acc2 = fma(s_val[k2], x2, acc2);
+            acc3 = fma(s_val[k3], x3, acc3);
         }
-        for (; k < e; k++) acc0 = fma(s_val[k], __ldg(x + s_col[k]), acc0);
+        for (; left > 0; left--) {
+            acc0 = fma(s_val[k], __ldg(x + s_col[k]), acc0);
+            k = (k + 1 == e) ? b : k + 1;
+        }
         const int r = r0 + tid;
         T out = alpha * ((acc0 + acc1) + (acc2 + acc3));
         if (HAS_BETA) out = fma(beta, y[r], out);
@@ -729,8 +741,9 @@ alphasparse_status_t ctx_analyse(DeviceCtx *ctx) {
     if (alg == ALPHA_SPARSE_CUDA_ALG_AUTO) {
         const int64_t comfortable = (int64_t)ctx->lanes * 4 * 8;
         if (ctx->max_row_nnz > comfortable) alg = ALPHA_SPARSE_CUDA_ALG_MERGE;
-        else if (rowtile_fits && ctx->shifted_rows >= 0.5)
-            alg = ALPHA_SPARSE_CUDA_ALG_ROWTILE;  // banded: thread-per-row makes the x gathers coalesce
+        else if (rowtile_fits && (ctx->shifted_rows >= 0.5 || ctx->mean_row_nnz <= 4.0))
+            alg = ALPHA_SPARSE_CUDA_ALG_ROWTILE;  // banded: thread-per-row makes the x gathers coalesce;
+                                                  // very short rows: a whole lane group per row is wasteful
         else alg = ALPHA_SPARSE_CUDA_ALG_VECTOR;
     }
     ctx->algorithm = alg;

@@ -95,26 +95,71 @@ def flops(cfg, nnz):
 # clocks
 # ------------------------------------------------------------------------------------------------
 class ClockSampler:
+    """Samples the SM clock and the throttle reasons of one GPU in a background thread: through NVML every
+    2 ms when the bindings are present, else through `nvidia-smi -lms 50`.  Read-only."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index):
-        self.rows, self.proc = [], None
+    def __init__(self, gpu_index, uuid=None):
+        self.samples, self.proc, self.stop_flag, self.max_mhz = [], None, False, None
+        self.thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = None
+            if uuid:
+                for cand in (f"GPU-{uuid}", str(uuid)):
+                    try:
+                        h = pynvml.nvmlDeviceGetHandleByUUID(cand.encode() if isinstance(cand, str) else cand)
+                        break
+                    except Exception:
+                        h = None
+            if h is None:
+                h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            reasons_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+
+            def pump():
+                while not self.stop_flag:
+                    try:
+                        mhz = float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+                        mask = int(reasons_fn(h))
+                        self.samples.append((time.time(), mhz, [n for b, n in self.REASONS.items() if mask & b]))
+                    except Exception:
+                        pass
+                    time.sleep(0.002)
+            self.thread = threading.Thread(target=pump, daemon=True)
+            self.thread.start()
+            self.source = "nvml"
+            return
+        except Exception:
+            pass
+        self.source = "nvidia-smi"
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50", "-i",
                  str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread = threading.Thread(target=self._pump_smi, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
 
-    def _pump(self):
+    def _pump_smi(self):
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.proc.stdout:
-            self.rows.append((time.time(), line.strip()))
+            p = [x.strip() for x in line.split(",")]
+            try:
+                self.max_mhz = float(p[1])
+                self.samples.append((time.time(), float(p[0]),
+                                     [names[i] for i, f in enumerate(p[3:7]) if f.lower().startswith("active")]))
+            except (ValueError, IndexError):
+                pass
 
     def stop(self):
+        self.stop_flag = True
         if self.proc:
             self.proc.terminate()
             try:
@@ -123,25 +168,15 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self, t0, t1):
-        def parse(rows):
-            out = []
-            for _, line in rows:
-                p = [s.strip() for s in line.split(",")]
-                try:
-                    out.append((float(p[0]), float(p[1]), p[3:7]))
-                except (ValueError, IndexError):
-                    pass
-            return out
-        window = parse([r for r in self.rows if t0 <= r[0] <= t1])
+        window = [x for x in self.samples if t0 <= x[0] <= t1]
         scope = "timed region"
         if len(window) < 3:
-            window, scope = parse(self.rows), "whole measurement phase (timed region shorter than the sampling period)"
+            window, scope = list(self.samples), "warm-up + timed region + kernel-timing pass (timed region too short to sample)"
         if not window:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "scope": "nvidia-smi unavailable"}
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({names[i] for _, _, fl in window for i, f in enumerate(fl) if f.lower().startswith("active")})
-        return {"sm_mhz": statistics.median(w[0] for w in window), "sm_max_mhz": window[0][1], "reasons": reasons,
-                "samples": len(window), "scope": scope}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "scope": "no sampler available"}
+        return {"sm_mhz": statistics.median(w[1] for w in window), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted({r for w in window for r in w[2]}), "samples": len(window), "scope": scope,
+                "source": self.source}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -326,7 +361,13 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    sampler = None
+    if rank == 0:
+        try:
+            uuid = torch.cuda.get_device_properties(local_rank).uuid
+        except Exception:
+            uuid = None
+        sampler = ClockSampler(local_rank, uuid)
     with torch.cuda.stream(stream):
         for _ in range(args.warmup):
             step()
