@@ -48,15 +48,10 @@ constexpr uint64_t kCtxMagic = 0x4153423230304358ull;  // guards against foreign
 constexpr int kTailPad = 16;
 
 // Merge-path tile shape: kMergeThreads threads, each consuming kMergeItems (rows+nnz) items.
-#ifndef ASB_MERGE_THREADS
-#define ASB_MERGE_THREADS 256
-#endif
-constexpr int kMergeThreads = ASB_MERGE_THREADS;
+constexpr int kMergeThreads = 256;
+constexpr int kMergeMinBlocks = 5;  // resident blocks per SM the merge kernel is compiled for (48 registers)
 constexpr int kMergeItemsS = 9;  // float
-#ifndef ASB_MERGE_IPT_D
-#define ASB_MERGE_IPT_D 7
-#endif
-constexpr int kMergeItemsD = ASB_MERGE_IPT_D;  // double
+constexpr int kMergeItemsD = 7;  // double
 
 // Row-tile kernel: rows per block (= threads per block) and the most shared memory one block may
 // ask for (four blocks per SM must still fit in the 227 KB an SM offers).

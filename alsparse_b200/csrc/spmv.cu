@@ -217,32 +217,48 @@ __global__ void __launch_bounds__(kRowTile)
         return;
     }
 
+    const int a0 = s_ptr[0] & ~3;
+    const int b = tid < nr ? s_ptr[tid] - a0 : 0, e = tid < nr ? s_ptr[tid + 1] - a0 : 0;
+    const int len = e - b;
+    // Neighbouring lanes read rows that start len elements apart: with an even len several lanes hit
+    // the same shared-memory bank on every step (16-way for len = 16).  Starting lane t at element
+    // t mod len of its row and wrapping round spreads them over the banks; the row is still summed
+    // completely, only from a different starting point.  Odd lengths are conflict-free as they are.
+    // The choice is made per warp so that no warp runs both loops.
+    const bool even = (len & 1) == 0 && len > 0;
+    const bool wrap = __any_sync(0xffffffffu, even);
     if (tid < nr) {
-        const int a0 = s_ptr[0] & ~3;
-        const int b = s_ptr[tid] - a0, e = s_ptr[tid + 1] - a0;
         if (e > cap) return;  // the oversize case flagged above
-        const int len = e - b;
-        // Neighbouring lanes read rows that start len elements apart: with an even len several lanes hit
-        // the same shared-memory bank on every step (16-way for len = 16).  Starting lane t at element
-        // t mod len of its row and wrapping round spreads them over the banks; the row is still summed
-        // completely, only from a different starting point.
-        int k = b + ((len & 1) == 0 && len > 0 ? tid % len : 0);
         T acc0 = T(0), acc1 = T(0), acc2 = T(0), acc3 = T(0);
-        int left = len;
-        for (; left >= 4; left -= 4) {
-            const int k0 = k, k1 = (k0 + 1 == e) ? b : k0 + 1, k2 = (k1 + 1 == e) ? b : k1 + 1,
-                      k3 = (k2 + 1 == e) ? b : k2 + 1;
-            k = (k3 + 1 == e) ? b : k3 + 1;
-            const int c0 = s_col[k0], c1 = s_col[k1], c2 = s_col[k2], c3 = s_col[k3];
-            const T x0 = __ldg(x + c0), x1 = __ldg(x + c1), x2 = __ldg(x + c2), x3 = __ldg(x + c3);
-            acc0 = fma(s_val[k0], x0, acc0);
-            acc1 = fma(s_val[k1], x1, acc1);
-            acc2 = fma(s_val[k2], x2, acc2);
-            acc3 = fma(s_val[k3], x3, acc3);
-        }
-        for (; left > 0; left--) {
-            acc0 = fma(s_val[k], __ldg(x + s_col[k]), acc0);
-            k = (k + 1 == e) ? b : k + 1;
+        if (!wrap) {
+            int k = b;
+            for (; k + 4 <= e; k += 4) {
+                const int c0 = s_col[k], c1 = s_col[k + 1], c2 = s_col[k + 2], c3 = s_col[k + 3];
+                const T x0 = __ldg(x + c0), x1 = __ldg(x + c1), x2 = __ldg(x + c2), x3 = __ldg(x + c3);
+                acc0 = fma(s_val[k], x0, acc0);
+                acc1 = fma(s_val[k + 1], x1, acc1);
+                acc2 = fma(s_val[k + 2], x2, acc2);
+                acc3 = fma(s_val[k + 3], x3, acc3);
+            }
+            for (; k < e; k++) acc0 = fma(s_val[k], __ldg(x + s_col[k]), acc0);
+        } else {
+            int k = b + (even ? tid % len : 0);
+            int left = len;
+            for (; left >= 4; left -= 4) {
+                const int k0 = k, k1 = (k0 + 1 == e) ? b : k0 + 1, k2 = (k1 + 1 == e) ? b : k1 + 1,
+                          k3 = (k2 + 1 == e) ? b : k2 + 1;
+                k = (k3 + 1 == e) ? b : k3 + 1;
+                const int c0 = s_col[k0], c1 = s_col[k1], c2 = s_col[k2], c3 = s_col[k3];
+                const T x0 = __ldg(x + c0), x1 = __ldg(x + c1), x2 = __ldg(x + c2), x3 = __ldg(x + c3);
+                acc0 = fma(s_val[k0], x0, acc0);
+                acc1 = fma(s_val[k1], x1, acc1);
+                acc2 = fma(s_val[k2], x2, acc2);
+                acc3 = fma(s_val[k3], x3, acc3);
+            }
+            for (; left > 0; left--) {
+                acc0 = fma(s_val[k], __ldg(x + s_col[k]), acc0);
+                k = (k + 1 == e) ? b : k + 1;
+            }
         }
         const int r = r0 + tid;
         T out = alpha * ((acc0 + acc1) + (acc2 + acc3));
@@ -264,9 +280,6 @@ __global__ void __launch_bounds__(kRowTile)
 // of the tiles of a power-law matrix) is a plain dot product: strided loads, register sums,
 // one block reduction, nothing staged.  Any other tile stages its products in shared memory
 // in load order and lets every thread walk its IPT consecutive merge items.
-#ifndef ASB_MERGE_MINBLOCKS
-#define ASB_MERGE_MINBLOCKS 5
-#endif
 //
 // With PUSH the same kernel also performs the allgather of y.  Tiles are grouped into chunks of
 // `push.chunk_tiles` consecutive tiles; every block counts its tile as done, and the block that
@@ -375,7 +388,7 @@ __device__ __forceinline__ void merge_tile_done(int, const int *, const MergeCoo
                                                 const NoPush &, int) {}
 
 template <typename T, int NT, int IPT, bool HAS_BETA, bool PUSH>
-__global__ void __launch_bounds__(NT, ASB_MERGE_MINBLOCKS)
+__global__ void __launch_bounds__(NT, kMergeMinBlocks)
     spmv_merge_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
                       const T *__restrict__ val, const T *__restrict__ x, T *__restrict__ y,
                       T alpha, T beta, const MergeCoord *__restrict__ tile,
