@@ -45,18 +45,14 @@ __device__ __forceinline__ void load_vec(const T *__restrict__ p, T (&out)[VEC])
 // float4 = 256 bytes, two rows per warp instruction).
 // VEC > 1 requires: columns % VEC == 0, ldx % VEC == 0, ldy % VEC == 0 and X, Y aligned to
 // VEC * sizeof(T); the launcher checks and otherwise uses VEC == 1.
-#ifndef ASB_SPMM_UNROLL
-#define ASB_SPMM_UNROLL 4
-#endif
-#ifndef ASB_SPMM_MINBLOCKS
-#define ASB_SPMM_MINBLOCKS 8
-#endif
+constexpr int kSpmmUnroll = 4;     // X rows in flight per lane group (8 and 16 were slower on B200)
+constexpr int kSpmmMinBlocks = 8;  // full occupancy (32 registers) measured fastest
 template <typename T, int VEC, int LPR, bool HAS_BETA>
-__global__ void __launch_bounds__(256, ASB_SPMM_MINBLOCKS)
+__global__ void __launch_bounds__(256, kSpmmMinBlocks)
     spmm_row_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
                     const T *__restrict__ val, const T *__restrict__ X, int columns,
                     long long ldx, T *__restrict__ Y, long long ldy, T alpha, T beta) {
-    constexpr int UNROLL = ASB_SPMM_UNROLL;
+    constexpr int UNROLL = kSpmmUnroll;
     constexpr int RPW = 32 / LPR;  // rows per warp
     const int lane = threadIdx.x & 31;
     const int gl = lane % LPR, grp = lane / LPR;
