@@ -119,7 +119,7 @@ struct DeviceCtx {
 
     // second and third stream + events of the pipelined host-vector path (created on first use)
     cudaStream_t copy_in = nullptr, copy_out = nullptr;
-    cudaEvent_t ev_pipe[1 + 2 * 8] = {};
+    cudaEvent_t ev_pipe[1 + 2 * 16] = {};
 
     // A^T as a second device CSR, built on the first transposed mv / mm call and kept
     DeviceCtx *transposed = nullptr;

@@ -369,3 +369,28 @@ def test_large_coo_is_sorted_on_the_device(kind):
     st, A = spblas.convert_csr(coo, capi.NON_TRANSPOSE)
     assert st == capi.INVALID_VALUE and not A.value
     spblas.destroy(coo)
+
+
+def test_merge_kernel_delivers_into_page_locked_host_y():
+    """Large skewed matrix + page-locked host y: finished chunks of y are stored into the host buffer from
+    inside the kernel.  Same bits as the device-pointer call, and as with pageable memory."""
+    kind = "d"
+    m = synth.zipf(kind, 91, (1 << 20) + 777, 1 << 20, 1.8, 1, 100000)
+    A = make_handle(kind, m)
+    _, info = spblas.mat_info(A)
+    assert info.algorithm == capi.ALG_MERGE
+    x = synth.vector(kind, 91, 1, m.cols)
+    y0 = synth.vector(kind, 91, 2, m.nrows)
+    for alpha, beta in ((1.0, 0.0), (0.5, -1.5)):
+        dx, dy = torch.from_numpy(x).cuda(), torch.from_numpy(y0).cuda()
+        assert spblas.mv(kind, 0, alpha, A, spblas.descr(), dx, beta, dy) == capi.SUCCESS
+        want = dy.cpu().numpy()
+        pinned = torch.from_numpy(y0.copy()).pin_memory()
+        assert spblas.mv(kind, 0, alpha, A, spblas.descr(), x, beta, pinned.numpy()) == capi.SUCCESS
+        assert np.array_equal(pinned.numpy(), want)
+        pageable = y0.copy()
+        assert spblas.mv(kind, 0, alpha, A, spblas.descr(), x, beta, pageable) == capi.SUCCESS
+        assert np.array_equal(pageable, want)
+    y_ref = oracle.gemv(kind, m.rows_start, m.rows_end, m.col, m.val, 0.5, x, -1.5, y0.copy())
+    assert_rows_close(kind, want, y_ref, row_scale(m.ptr, m.col, m.val, x, 0.5, -1.5, y0), "merge e2e")
+    spblas.destroy(A)
