@@ -605,16 +605,13 @@ static alphasparse_status_t check_call(const alphasparse_matrix_t A, const void 
 }
 
 // Host x and host y on a large matrix: the product runs in kPipelineChunks row windows (4 -> 8 windows
-// took uniform16 end to end from 3.14 to 2.90 ms on B200) so that
+// took uniform16 end to end from 3.14 to 2.90 ms on B200, 16 changed nothing) so that
 // PCIe and the kernel overlap.  Three streams: x and the y0 pieces go in on one, the windows run
 // on the library stream as their inputs land, every finished piece of y leaves on the third
 // while the next window is being multiplied (PCIe is full duplex).  The call still returns
 // only when all of y is back in host memory.
-#ifndef ASB_PIPE_CHUNKS
-#define ASB_PIPE_CHUNKS 8
-#endif
 constexpr int64_t kPipelineMinRows = 1 << 20;
-constexpr int kPipelineChunks = ASB_PIPE_CHUNKS;
+constexpr int kPipelineChunks = 8;
 
 template <typename T>
 static alphasparse_status_t mv_host_pipelined(DeviceCtx *c, T alpha, const T *x, T beta, T *y, cudaStream_t st) {
