@@ -38,7 +38,7 @@ FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only without
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (bytes; None where no capture exists yet).
-NCU_TRAFFIC = {"uniform16": 3850661888, "stencil27": 1393904640, "powerlaw": None, "spmm64": 17522641408}
+NCU_TRAFFIC = {"uniform16": 3937436144, "stencil27": 1393600664, "powerlaw": None, "spmm64": 17518304000}
 
 WORKLOADS = {
     "uniform16": dict(kind="s", rows_log2=24, alpha=1.5, beta=0.5, op="mv"),
