@@ -452,18 +452,27 @@ static alphasparse_status_t ensure_transposed(DeviceCtx *c, const typename CsrOf
 // alphasparse_?_mv, src/core/op/level2/alphasparse_x_mv.c:1693-1716; kernels under
 // src/plain/kernel/level2/mv/{symv,trmv,diagmv}) is an ordinary SpMV with a matrix DERIVED from the
 // stored one: the kept triangle (plus an explicit unit diagonal), its mirror image for SYMMETRIC, its
-// transpose for op = TRANSPOSE, or just the diagonal (the FIRST stored diagonal entry of a row, as the
-// reference's loop breaks at it).  Each variant is built once from the host copy, uploaded as its own
-// device CSR, analysed like any matrix and kept with the handle.
-static int derived_slot(int type, int upper, int unit, int trans) {
-    const int t = type == ALPHA_SPARSE_MATRIX_TYPE_SYMMETRIC ? 0 : type == ALPHA_SPARSE_MATRIX_TYPE_TRIANGULAR ? 1 : 2;
+// transpose for op = TRANSPOSE, or just the diagonal.  Each variant is built once from the host copy,
+// uploaded as its own device CSR, analysed like any matrix and kept with the handle.
+//
+// The same matrices serve mm (symm / trmm / diagmm, src/core/op/level3/alphasparse_x_mm.c:2345-2368;
+// kernels under src/plain/kernel/level3/mm/{symm,trmm,diagmm}).  Only rows that store their diagonal
+// more than once tell the reference's three diagonal kernels apart: diagmv stops at the FIRST stored
+// diagonal entry (diagmv_x_csr_n_plain.c:12-27), the row-major diagmm adds ALL of them
+// (diagmm_x_csr_n_row_plain.c:14-22) and the column-major diagmm keeps the LAST
+// (diagmm_x_csr_n_col_plain.c:7-15); `diag_rule` selects which.
+enum DiagRule { kDiagFirst = 0, kDiagAll = 1, kDiagLast = 2 };
+
+static int derived_slot(int type, int upper, int unit, int trans, int diag_rule) {
+    if (type == ALPHA_SPARSE_MATRIX_TYPE_DIAGONAL) return 16 + diag_rule * 2 + unit;  // 16..21
+    const int t = type == ALPHA_SPARSE_MATRIX_TYPE_SYMMETRIC ? 0 : 1;
     return t * 8 + upper * 4 + unit * 2 + trans;
 }
 
 template <typename T>
 static alphasparse_status_t ensure_derived(DeviceCtx *c, const typename CsrOf<T>::csr *m, int type, int upper,
-                                           int unit, int trans, DeviceCtx **out) {
-    DeviceCtx *&slot = c->derived[derived_slot(type, upper, unit, trans)];
+                                           int unit, int trans, int diag_rule, DeviceCtx **out) {
+    DeviceCtx *&slot = c->derived[derived_slot(type, upper, unit, trans, diag_rule)];
     if (slot) {
         *out = slot;
         return ALPHA_SPARSE_STATUS_SUCCESS;
@@ -480,8 +489,11 @@ static alphasparse_status_t ensure_derived(DeviceCtx *c, const typename CsrOf<T>
             for (int k = ptr[i]; k < ptr[i + 1]; k++) {
                 const int j = col[k];
                 if (type == ALPHA_SPARSE_MATRIX_TYPE_DIAGONAL) {
-                    if (!unit && j == i && !diag_seen) ri.push_back((int)i), ci.push_back(j), v.push_back(val[k]);
-                    diag_seen |= (j == i);
+                    if (!unit && j == i) {
+                        if (diag_seen && diag_rule == kDiagLast) v.back() = val[k];
+                        else if (!diag_seen || diag_rule == kDiagAll) ri.push_back((int)i), ci.push_back(j), v.push_back(val[k]);
+                        diag_seen = true;
+                    }
                     continue;
                 }
                 const bool off = upper ? j > i : j < i;
@@ -569,12 +581,12 @@ struct DeviceGuard {
 // ---- mv / mm -----------------------------------------------------------------------------------------
 
 // Argument checks in the reference's order (src/core/op/level2/alphasparse_x_mv.c:1670-1716,
-// src/core/op/level3/alphasparse_x_mm.c:2317-2338).  Returns SUCCESS when the call is the
-// CSR + GENERAL case this backend serves; every other case the reference would run on its CPU
-// kernels is NOT_SUPPORTED here.
+// src/core/op/level3/alphasparse_x_mm.c:2317-2338).  Returns SUCCESS when the call is one of the
+// CSR cases this backend serves (GENERAL, SYMMETRIC, TRIANGULAR, DIAGONAL); every other case the
+// reference would run on its CPU kernels is NOT_SUPPORTED here.
 static alphasparse_status_t check_call(const alphasparse_matrix_t A, const void *x, const void *y,
                                        alphasparse_datatype_t dt, alphasparse_operation_t op,
-                                       struct alpha_matrix_descr descr, bool structured_ok) {
+                                       struct alpha_matrix_descr descr) {
     if (!A || !A->mat || !x || !y) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
     if (A->datatype != dt) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
     if (op == ALPHA_SPARSE_OPERATION_CONJUGATE_TRANSPOSE) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
@@ -595,7 +607,7 @@ static alphasparse_status_t check_call(const alphasparse_matrix_t A, const void 
         if (descr.type == ALPHA_SPARSE_MATRIX_TYPE_HERMITIAN) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;  // complex only
         if (descr.type >= ALPHA_SPARSE_MATRIX_TYPE_SYMMETRIC &&
             descr.type <= ALPHA_SPARSE_MATRIX_TYPE_DIAGONAL)
-            return structured_ok ? ALPHA_SPARSE_STATUS_SUCCESS : ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+            return ALPHA_SPARSE_STATUS_SUCCESS;
         return ALPHA_SPARSE_STATUS_INVALID_VALUE;
     }
     if (A->format == ALPHA_SPARSE_FORMAT_COO ||
@@ -663,10 +675,31 @@ static alphasparse_status_t mv_host_pipelined(DeviceCtx *c, T alpha, const T *x,
     return kernel_status == 0 ? ALPHA_SPARSE_STATUS_SUCCESS : ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
 }
 
+// The matrix a structured (SYMMETRIC / TRIANGULAR / DIAGONAL) mv or mm call multiplies by, in *c.
+template <typename T>
+static alphasparse_status_t select_structured(DeviceCtx *&c, const alphasparse_matrix_t A, alphasparse_operation_t op,
+                                              struct alpha_matrix_descr descr, int diag_rule) {
+    // SYMMETRIC has no transposed entry in the reference's tables (NOT_SUPPORTED there too); the
+    // diagonal kernels ignore the operation; fill / diag flags outside {0,1} index past its tables
+    if (descr.type == ALPHA_SPARSE_MATRIX_TYPE_SYMMETRIC && op != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE)
+        return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    if ((unsigned)descr.mode > 1u || (unsigned)descr.diag > 1u) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    if (c->rows != c->cols) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    const int trans = descr.type == ALPHA_SPARSE_MATRIX_TYPE_TRIANGULAR && op == ALPHA_SPARSE_OPERATION_TRANSPOSE;
+    const int upper = descr.type == ALPHA_SPARSE_MATRIX_TYPE_DIAGONAL ? 0 : (int)descr.mode;
+    std::lock_guard<std::mutex> build(c->mu);
+    DeviceCtx *d = nullptr;
+    alphasparse_status_t s = ensure_derived<T>(c, static_cast<const typename CsrOf<T>::csr *>(A->mat), (int)descr.type,
+                                               upper, (int)descr.diag, trans, diag_rule, &d);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    c = d;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
 template <typename T>
 static alphasparse_status_t mv(alphasparse_operation_t op, T alpha, const alphasparse_matrix_t A,
                                struct alpha_matrix_descr descr, const T *x, T beta, T *y) {
-    alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr, true);
+    alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     DeviceCtx *c = ctx_of(A);
     if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
@@ -674,20 +707,8 @@ static alphasparse_status_t mv(alphasparse_operation_t op, T alpha, const alphas
     DeviceGuard guard(c->device);
     if (!guard.ok) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
     if (descr.type != ALPHA_SPARSE_MATRIX_TYPE_GENERAL) {
-        // SYMMETRIC has no transposed entry in the reference's table (NOT_SUPPORTED there too); the
-        // diagonal kernels ignore the operation; fill / diag flags outside {0,1} index past its tables
-        if (descr.type == ALPHA_SPARSE_MATRIX_TYPE_SYMMETRIC && op != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE)
-            return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
-        if ((unsigned)descr.mode > 1u || (unsigned)descr.diag > 1u) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
-        if (c->rows != c->cols) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
-        const int trans = descr.type == ALPHA_SPARSE_MATRIX_TYPE_TRIANGULAR && op == ALPHA_SPARSE_OPERATION_TRANSPOSE;
-        const int upper = descr.type == ALPHA_SPARSE_MATRIX_TYPE_DIAGONAL ? 0 : (int)descr.mode;
-        std::lock_guard<std::mutex> build(c->mu);
-        DeviceCtx *d = nullptr;
-        s = ensure_derived<T>(c, static_cast<const typename CsrOf<T>::csr *>(A->mat), (int)descr.type, upper,
-                              (int)descr.diag, trans, &d);
+        s = select_structured<T>(c, A, op, descr, kDiagFirst);
         if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-        c = d;
     } else if (op == ALPHA_SPARSE_OPERATION_TRANSPOSE) {  // y (cols entries) = alpha * A^T * x (rows entries) + beta * y
         {
             std::lock_guard<std::mutex> build(c->mu);
@@ -759,7 +780,7 @@ static alphasparse_status_t mm(alphasparse_operation_t op, T alpha, const alphas
                                struct alpha_matrix_descr descr, alphasparse_layout_t layout,
                                const T *x, ALPHA_INT columns, ALPHA_INT ldx, T beta, T *y,
                                ALPHA_INT ldy) {
-    alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr, false);
+    alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     if (layout != ALPHA_SPARSE_LAYOUT_ROW_MAJOR && layout != ALPHA_SPARSE_LAYOUT_COLUMN_MAJOR)
         return ALPHA_SPARSE_STATUS_INVALID_VALUE;
@@ -767,7 +788,10 @@ static alphasparse_status_t mm(alphasparse_operation_t op, T alpha, const alphas
     if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
     DeviceGuard guard(c->device);
     if (!guard.ok) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
-    if (op == ALPHA_SPARSE_OPERATION_TRANSPOSE) {  // the reference also multiplies by a materialised A^T
+    if (descr.type != ALPHA_SPARSE_MATRIX_TYPE_GENERAL) {
+        s = select_structured<T>(c, A, op, descr, layout == ALPHA_SPARSE_LAYOUT_ROW_MAJOR ? kDiagAll : kDiagLast);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    } else if (op == ALPHA_SPARSE_OPERATION_TRANSPOSE) {  // the reference also multiplies by a materialised A^T
         {
             std::lock_guard<std::mutex> build(c->mu);
             s = ensure_transposed<T>(c, static_cast<const typename CsrOf<T>::csr *>(A->mat));

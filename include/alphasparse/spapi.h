@@ -10,9 +10,13 @@
  * library stream and the call returns without waiting, like any CUDA library call).
  * Matrix arrays given to the create calls are host pointers and are deep-copied.
  *
- * What is not served.  Complex precisions, formats other than CSR (COO only as the source of
- * alphasparse_convert_csr) and descriptor types other than GENERAL return
- * ALPHA_SPARSE_STATUS_NOT_SUPPORTED after the argument checks: there is no CPU fallback.
+ * Descriptors.  mv and mm serve GENERAL, SYMMETRIC, TRIANGULAR and DIAGONAL on a CSR handle with
+ * every fill / diag / operation combination the reference's dispatch tables hold (SYMMETRIC with
+ * TRANSPOSE has no entry there and is NOT_SUPPORTED here too).
+ *
+ * What is not served.  Complex precisions (and so HERMITIAN) and formats other than CSR (COO only
+ * as the source of alphasparse_convert_csr) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED after the
+ * argument checks: there is no CPU fallback.
  */
 #include "types.h"
 #include "spdef.h"

@@ -55,6 +55,10 @@ def lib():
             getattr(L, f"oracle_trmv_csr_{k}").argtypes = [C.c_int, C.c_int, C.c_int, _i32, _p, _p, _p, _p, T, _p, T, _p]
             getattr(L, f"oracle_symv_csr_{k}").argtypes = [C.c_int, C.c_int, _i32, _p, _p, _p, _p, T, _p, T, _p]
             getattr(L, f"oracle_diagmv_csr_{k}").argtypes = [C.c_int, _i32, _p, _p, _p, _p, T, _p, T, _p]
+            mm_tail = [_i32, _p, _p, _p, _p, T, _p, _i32, _i32, T, _p, _i32]
+            getattr(L, f"oracle_symm_csr_{k}").argtypes = [C.c_int] * 3 + mm_tail
+            getattr(L, f"oracle_trmm_csr_{k}").argtypes = [C.c_int] * 4 + mm_tail
+            getattr(L, f"oracle_diagmm_csr_{k}").argtypes = [C.c_int] * 2 + mm_tail
             getattr(L, f"oracle_create_csr_{k}").argtypes = [_i32, _i32, _p, _p, _p, _p, _p, _p, _p]
             getattr(L, f"oracle_create_csr_{k}").restype = _i32
             getattr(L, f"oracle_coo_to_csr_{k}").argtypes = [_i32, _i32, _i32, _p, _p, _p, _p, _p, _p]
@@ -110,6 +114,23 @@ def structured_mv(kind, descr_type, upper, unit, trans, rows_start, rows_end, co
     else:
         raise ValueError(descr_type)
     return y
+
+
+def structured_mm(kind, descr_type, upper, unit, trans, layout, rows_start, rows_end, col, val, alpha, X, columns,
+                  ldx, beta, Y, ldy):
+    """mm under a TRIANGULAR (3), SYMMETRIC (1) or DIAGONAL (4) descriptor; Y modified in place."""
+    rs, re_, ci = _i(rows_start), _i(rows_end), _i(col)
+    cm = int(layout == "col")
+    tail = [len(rs), _a(rs), _a(re_), _a(ci), _a(val), alpha, _a(X), columns, ldx, beta, _a(Y), ldy]
+    if descr_type == 3:
+        getattr(lib(), f"oracle_trmm_csr_{kind}")(int(upper), int(unit), int(trans), cm, *tail)
+    elif descr_type == 1:
+        getattr(lib(), f"oracle_symm_csr_{kind}")(int(upper), int(unit), cm, *tail)
+    elif descr_type == 4:
+        getattr(lib(), f"oracle_diagmm_csr_{kind}")(int(unit), cm, *tail)
+    else:
+        raise ValueError(descr_type)
+    return Y
 
 
 def create_csr(kind, base, rows_start, rows_end, col, val):
@@ -183,6 +204,11 @@ def ref():
                         [f"trmv_{k}_csr_{d}_{m}{t}_plain" for d in "nu" for m in ("lo", "hi") for t in ("", "_trans")] + \
                         [f"diagmv_{k}_csr_{d}_plain" for d in "nu"]:
                 getattr(L, name).argtypes = [T, _p, _p, T, _p]
+            for name in [f"symm_{k}_csr_{d}_{m}_{lay}_plain" for d in "nu" for m in ("lo", "hi") for lay in ("row", "col")] + \
+                        [f"trmm_{k}_csr_{d}_{m}_{lay}{t}_plain" for d in "nu" for m in ("lo", "hi")
+                         for lay in ("row", "col") for t in ("", "_trans")] + \
+                        [f"diagmm_{k}_csr_{d}_{lay}_plain" for d in "nu" for lay in ("row", "col")]:
+                getattr(L, name).argtypes = [T, _p, _p, _i32, _i32, T, _p, _i32]
             getattr(L, f"alphasparse_{k}_export_csr").argtypes = [_p] * 8
         L.balanced_partition_row_by_nnz.argtypes = [_p, _i32, _i32, _p]
         for name in ("alpha_read_coo", "alpha_read_coo_d"):
@@ -266,6 +292,16 @@ class RefCsr:
         st = getattr(ref(), name)(alpha, self.mat, _a(x), beta, _a(y))
         assert st == 0
         return y
+
+    def structured_mm(self, descr_type, upper, unit, trans, layout, alpha, X, columns, ldx, beta, Y, ldy):
+        """The reference's plain symm / trmm / diagmm kernel for the given descriptor and layout."""
+        d, m = "u" if unit else "n", "hi" if upper else "lo"
+        name = {1: f"symm_{self.kind}_csr_{d}_{m}_{layout}_plain",
+                3: f"trmm_{self.kind}_csr_{d}_{m}_{layout}{'_trans' if trans else ''}_plain",
+                4: f"diagmm_{self.kind}_csr_{d}_{layout}_plain"}[descr_type]
+        st = getattr(ref(), name)(alpha, self.mat, _a(X), columns, ldx, beta, _a(Y), ldy)
+        assert st == 0
+        return Y
 
     def gemm(self, layout, alpha, X, columns, ldx, beta, Y, ldy, omp_threads=0, trans=False):
         L = ref()

@@ -417,3 +417,106 @@ int oracle_mm_status(int has_handle, int has_mat, int has_x, int has_y, int hand
     }
 DEF_STRUCT(float, s)
 DEF_STRUCT(double, d)
+
+/* ---------------------------------------------------------------------------------------
+ * The same descriptors in alphasparse_?_mm (src/core/op/level3/alphasparse_x_mm.c:2345-2368;
+ * tables :116-151, :303-335, :381-393).  X and Y are dense, `columns` wide; element (r, c) sits at
+ * r*ld + c (row-major) or c*ld + r (column-major).
+ *
+ * SYMMETRIC, src/plain/kernel/level3/mm/symm/csr/symm_x_csr_{n,u}_{lo,hi}_{row,col}_plain.c: Y is
+ *   scaled by beta (plus alpha*X when the diagonal is unit), then every kept off-diagonal element a
+ *   adds (alpha*a)*X[col,:] to Y[row,:] and (alpha*a)*X[row,:] to Y[col,:]; stored diagonal elements
+ *   once.  TRANSPOSE has no table entry (NOT_SUPPORTED).
+ * TRIANGULAR, .../trmm/csr/trmm_x_csr_{n,u}_{lo,hi}_{row,col}[_trans]_plain.c: row-major adds
+ *   (alpha*a)*X[col,:] per kept element; column-major forms the dot product first and adds
+ *   alpha*dot.  The transposed kernels materialise A^T (transpose_csr) and run the kernel of the
+ *   opposite triangle on it.
+ * DIAGONAL, .../diagmm/diagmm_x_csr_{n,u}_{row,col}_plain.c: the row-major kernel adds EVERY stored
+ *   diagonal element of a row, the column-major one keeps the LAST (diagmv keeps the first); the
+ *   three agree unless a row stores its diagonal more than once.
+ * ------------------------------------------------------------------------------------- */
+#define AT(r, c, ld) (col_major ? (size_t)(c) * (size_t)(ld) + (size_t)(r) : (size_t)(r) * (size_t)(ld) + (size_t)(c))
+#define DEF_STRUCT_MM(T, sfx)                                                                 \
+    void oracle_symm_csr_##sfx(int upper, int unit, int col_major, aint rows, const aint *rs, \
+                               const aint *re, const aint *col, const T *val, T alpha,        \
+                               const T *x, aint columns, aint ldx, T beta, T *y, aint ldy) {  \
+        for (aint r = 0; r < rows; r++)                                                       \
+            for (aint c = 0; c < columns; c++) {                                              \
+                y[AT(r, c, ldy)] = y[AT(r, c, ldy)] * beta;                                   \
+                if (unit) y[AT(r, c, ldy)] += alpha * x[AT(r, c, ldx)];                       \
+            }                                                                                 \
+        for (aint r = 0; r < rows; r++)                                                       \
+            for (aint k = rs[r]; k < re[r]; k++) {                                            \
+                const aint j = col[k];                                                        \
+                const int off = upper ? j > r : j < r;                                        \
+                if (!off && (j != r || unit)) continue;                                       \
+                const T av = alpha * val[k];                                                  \
+                for (aint c = 0; c < columns; c++) {                                          \
+                    y[AT(r, c, ldy)] += av * x[AT(j, c, ldx)];                                \
+                    if (off) y[AT(j, c, ldy)] += av * x[AT(r, c, ldx)];                       \
+                }                                                                             \
+            }                                                                                 \
+    }                                                                                         \
+    void oracle_trmm_csr_##sfx(int upper, int unit, int trans, int col_major, aint rows,      \
+                               const aint *rs, const aint *re, const aint *col, const T *val, \
+                               T alpha, const T *x, aint columns, aint ldx, T beta, T *y,     \
+                               aint ldy) {                                                    \
+        aint *tptr = NULL, *tcol = NULL;                                                      \
+        T *tval = NULL;                                                                       \
+        if (trans) { /* A^T by a counting sort: rows ascending inside every column */         \
+            const aint nnz = rows ? re[rows - 1] - rs[0] : 0;                                 \
+            tptr = (aint *)calloc((size_t)rows + 1, sizeof(aint));                            \
+            tcol = (aint *)malloc(sizeof(aint) * (size_t)(nnz ? nnz : 1));                    \
+            tval = (T *)malloc(sizeof(T) * (size_t)(nnz ? nnz : 1));                          \
+            for (aint r = 0; r < rows; r++)                                                   \
+                for (aint k = rs[r]; k < re[r]; k++) tptr[col[k] + 1]++;                      \
+            for (aint r = 0; r < rows; r++) tptr[r + 1] += tptr[r];                           \
+            aint *fill = (aint *)malloc(sizeof(aint) * (size_t)(rows ? rows : 1));            \
+            memcpy(fill, tptr, sizeof(aint) * (size_t)rows);                                  \
+            for (aint r = 0; r < rows; r++)                                                   \
+                for (aint k = rs[r]; k < re[r]; k++) {                                        \
+                    const aint p = fill[col[k]]++;                                            \
+                    tcol[p] = r, tval[p] = val[k];                                            \
+                }                                                                             \
+            free(fill);                                                                       \
+            rs = tptr, re = tptr + 1, col = tcol, val = tval, upper = !upper;                 \
+        }                                                                                     \
+        for (aint c = 0; c < columns; c++)                                                    \
+            for (aint r = 0; r < rows; r++) {                                                 \
+                T *out = &y[AT(r, c, ldy)];                                                   \
+                *out = *out * beta;                                                           \
+                if (unit) *out += alpha * x[AT(r, c, ldx)];                                   \
+                T dot = (T)0;                                                                 \
+                for (aint k = rs[r]; k < re[r]; k++) {                                        \
+                    const aint j = col[k];                                                    \
+                    const int keep = upper ? (unit ? j > r : j >= r) : (unit ? j < r : j <= r); \
+                    if (!keep) continue;                                                      \
+                    if (col_major) dot += val[k] * x[AT(j, c, ldx)];                          \
+                    else { const T av = alpha * val[k]; *out += av * x[AT(j, c, ldx)]; }      \
+                }                                                                             \
+                if (col_major) *out += dot * alpha;                                           \
+            }                                                                                 \
+        free(tptr), free(tcol), free(tval);                                                   \
+    }                                                                                         \
+    void oracle_diagmm_csr_##sfx(int unit, int col_major, aint rows, const aint *rs,          \
+                                 const aint *re, const aint *col, const T *val, T alpha,      \
+                                 const T *x, aint columns, aint ldx, T beta, T *y, aint ldy) { \
+        for (aint r = 0; r < rows; r++)                                                       \
+            for (aint c = 0; c < columns; c++) {                                              \
+                T *out = &y[AT(r, c, ldy)];                                                   \
+                *out = *out * beta;                                                           \
+                if (unit) { *out += alpha * x[AT(r, c, ldx)]; continue; }                     \
+                if (col_major) {                                                              \
+                    T d = (T)0;                                                               \
+                    for (aint k = rs[r]; k < re[r]; k++) if (col[k] == r) d = val[k];         \
+                    const T av = alpha * d;                                                   \
+                    *out += av * x[AT(r, c, ldx)];                                            \
+                } else {                                                                      \
+                    for (aint k = rs[r]; k < re[r]; k++)                                      \
+                        if (col[k] == r) { const T av = alpha * val[k]; *out += av * x[AT(r, c, ldx)]; } \
+                }                                                                             \
+            }                                                                                 \
+    }
+DEF_STRUCT_MM(float, s)
+DEF_STRUCT_MM(double, d)
+#undef AT

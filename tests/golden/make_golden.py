@@ -120,6 +120,22 @@ def main():
                     out[f"y_t{t}_u{upper}_d{unit}_o{tr}"] = Q.structured_mv(t, upper, unit, tr, 0.75, xs, -0.5, ys.copy())
     np.savez_compressed(os.path.join(OUT, "struct_d.npz"), **out)
 
+    # -- the same descriptors in mm: the reference's plain symm / trmm / diagmm kernels, both layouts, padded
+    #    leading dimensions (the repeated diagonal entries separate "all" / "last" / "first") --------------
+    columns, ldx, ldy, ldxc, ldyc = 5, 7, 6, 163, 161
+    Xr, Yr = synth.vector("d", 9, 3, 160 * ldx), synth.vector("d", 9, 4, 160 * ldy)
+    Xc, Yc = synth.vector("d", 9, 5, ldxc * columns), synth.vector("d", 9, 6, ldyc * columns)
+    out = dict(ptr=qptr, col=qcol, val=qval, Xr=Xr, Yr=Yr, Xc=Xc, Yc=Yc, alpha=0.75, beta=-0.5,
+               par=np.array([columns, ldx, ldy, ldxc, ldyc]))
+    for t, transes in ((1, (0,)), (3, (0, 1)), (4, (0,))):
+        for upper in ((0,) if t == 4 else (0, 1)):
+            for unit in (0, 1):
+                for tr in transes:
+                    key = f"t{t}_u{upper}_d{unit}_o{tr}"
+                    out[f"row_{key}"] = Q.structured_mm(t, upper, unit, tr, "row", 0.75, Xr, columns, ldx, -0.5, Yr.copy(), ldy)
+                    out[f"col_{key}"] = Q.structured_mm(t, upper, unit, tr, "col", 0.75, Xc, columns, ldxc, -0.5, Yc.copy(), ldyc)
+    np.savez_compressed(os.path.join(OUT, "struct_mm_d.npz"), **out)
+
     # -- nnz-balanced row partition: known answers incl. the quirks ---------------------------------
     cases = {}
     accs = {"tiny": np.array([2, 3, 4], np.int32), "cfg1": m.ptr[1:], "zipf": z.ptr[1:],

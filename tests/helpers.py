@@ -42,3 +42,11 @@ def mm_scale(ptr, col, val, X, columns, ldx, alpha, beta, Y0, ldy):
     np.add.at(out, row_ids(ptr), np.abs(val.astype(np.float64))[:, None] * Xv[col])
     Y0v = np.abs(Y0.astype(np.float64).reshape(-1)[: rows * ldy].reshape(rows, ldy)[:, :columns])
     return abs(beta) * Y0v + abs(alpha) * out
+
+
+def structured_scale(n, ptr, col, val, X, Y0, alpha, beta):
+    """Per (row, column) scale for a product under a SYMMETRIC / TRIANGULAR / DIAGONAL descriptor: the bound
+    of the widest variant, (|A| + |A|^T + I) |X|, on an n x n matrix small enough to hold densely."""
+    dense = np.zeros((n, n))
+    np.add.at(dense, (row_ids(ptr), col), np.abs(val.astype(np.float64)))
+    return np.abs(beta * Y0.astype(np.float64)) + abs(alpha) * ((dense + dense.T + np.eye(n)) @ np.abs(X.astype(np.float64)))

@@ -6,7 +6,7 @@ import torch
 import oracle
 from alsparse_b200 import capi, spblas, synth
 from gpu_util import make_handle
-from helpers import assert_rows_close, golden, mm_scale
+from helpers import assert_rows_close, golden, mm_scale, structured_scale
 
 pytestmark = pytest.mark.gpu
 
@@ -75,7 +75,7 @@ def test_status_codes():
     assert spblas.mm("d", 0, 1.0, A, g, 0, X, 4, 4, 0.0, Y, 4) == capi.INVALID_VALUE
     assert spblas.mm("s", capi.CONJUGATE_TRANSPOSE, 1.0, A, g, 0, X, 4, 4, 0.0, Y, 4) == capi.INVALID_VALUE
     assert spblas.mm("s", 0, 1.0, A, spblas.descr(capi.SYMMETRIC), 0, X, 4, 4, 0.0, Y, 4) == capi.INVALID_VALUE
-    assert spblas.mm("s", 0, 1.0, A, spblas.descr(capi.TRIANGULAR), 0, X, 4, 4, 0.0, Y, 4) == capi.NOT_SUPPORTED
+    assert spblas.mm("s", 0, 1.0, A, spblas.descr(capi.TRIANGULAR), 0, X, 4, 4, 0.0, Y, 4) == capi.NOT_SUPPORTED  # not square
     assert spblas.mm("s", 0, 1.0, A, g, 0, X, 4, 3, 0.0, Y, 4) == capi.INVALID_VALUE           # ldx < columns
     assert spblas.mm("s", 0, 1.0, A, g, capi.COLUMN_MAJOR, X, 4, 39, 0.0, Y, 30) == capi.INVALID_VALUE  # ldx < cols
     spblas.destroy(A)
@@ -144,3 +144,60 @@ def test_transposed_mm_both_layouts(kind):
     assert_rows_close(kind, dY.cpu().numpy().reshape(columns, m.cols).T.reshape(-1),
                       Ycref.reshape(columns, m.cols).T.reshape(-1), sc.reshape(-1), "transposed column-major")
     spblas.destroy(A)
+
+
+def test_structured_descriptors_mm():
+    """SYMMETRIC / TRIANGULAR / DIAGONAL descriptors in mm: every fill / diag / operation variant of the reference's
+    symm / trmm / diagmm tables in both layouts against its plain kernels (golden vectors; the matrix stores some
+    diagonals twice and some not at all), host and device operands; then a larger matrix against the oracle."""
+    g = golden("struct_mm_d.npz")
+    ptr, a, b = g["ptr"], float(g["alpha"]), float(g["beta"])
+    columns, ldx, ldy, ldxc, ldyc = (int(v) for v in g["par"])
+    n = 160
+    m = synth.Csr(n, n, 0, ptr, g["col"], g["val"])
+    A = make_handle("d", m)
+    cases = 0
+    for key in (k[4:] for k in g.files if k.startswith("row_")):
+        t, upper, unit, tr = (int(f[1:]) for f in key.split("_"))
+        for lay, layout, X, Y0, lx, ly in (("row", capi.ROW_MAJOR, g["Xr"], g["Yr"], ldx, ldy),
+                                           ("col", capi.COLUMN_MAJOR, g["Xc"], g["Yc"], ldxc, ldyc)):
+            view = (lambda v: v.reshape(n, ly)[:, :columns]) if lay == "row" else (lambda v: v.reshape(columns, ly)[:, :n].T)
+            pad = (lambda v: v.reshape(n, ly)[:, columns:]) if lay == "row" else (lambda v: v.reshape(columns, ly)[:, n:])
+            xv = X.reshape(n, lx)[:, :columns] if lay == "row" else X.reshape(columns, lx)[:, :n].T
+            sc = structured_scale(n, ptr, g["col"], g["val"], xv, view(Y0), a, b)
+            for dev in (False, True):
+                if dev:
+                    dX, dY = torch.from_numpy(X).cuda(), torch.from_numpy(Y0).cuda()
+                    st = spblas.mm("d", tr, a, A, spblas.descr(t, upper, unit), layout, dX, columns, lx, b, dY, ly)
+                    Y = dY.cpu().numpy()
+                else:
+                    Y = Y0.copy()
+                    st = spblas.mm("d", tr, a, A, spblas.descr(t, upper, unit), layout, X, columns, lx, b, Y, ly)
+                assert st == capi.SUCCESS, (key, lay, capi.STATUS_NAMES[st], spblas.last_error())
+                assert_rows_close("d", view(Y).reshape(-1), view(g[f"{lay}_{key}"]).reshape(-1), sc.reshape(-1),
+                                  f"{lay} {key} dev={dev}")
+                assert np.array_equal(pad(Y), pad(Y0)), "padding written"
+                cases += 1
+    assert cases == 4 * (4 + 8 + 2)
+    # no transposed symmetric kernel for real types in the reference's table; flags outside {0, 1} index past it
+    X, Y = g["Xr"], g["Yr"].copy()
+    assert spblas.mm("d", capi.TRANSPOSE, a, A, spblas.descr(capi.SYMMETRIC), 0, X, columns, ldx, b, Y, ldy) == capi.NOT_SUPPORTED
+    assert spblas.mm("d", 0, a, A, spblas.descr(capi.TRIANGULAR, 2, 0), 0, X, columns, ldx, b, Y, ldy) == capi.INVALID_VALUE
+    assert np.array_equal(Y, g["Yr"])
+    spblas.destroy(A)
+
+    for kind in ("s", "d"):
+        n, columns = 3000, 16
+        m = synth.poisson(kind, 73, n, n, 9.0)
+        X, Y0 = synth.vector(kind, 73, 1, n * columns), synth.vector(kind, 73, 2, n * columns)
+        A = make_handle(kind, m)
+        sc = structured_scale(n, m.ptr, m.col, m.val, X.reshape(n, columns), Y0.reshape(n, columns), 1.25, 0.5)
+        for t, upper, unit, tr in ((capi.SYMMETRIC, 0, 1, 0), (capi.TRIANGULAR, 1, 0, 1), (capi.TRIANGULAR, 0, 0, 0),
+                                   (capi.DIAGONAL, 0, 0, 0)):
+            Yref = oracle.structured_mm(kind, t, upper, unit, tr, "row", m.rows_start, m.rows_end, m.col, m.val, 1.25, X,
+                                        columns, columns, 0.5, Y0.copy(), columns)
+            dX, dY = torch.from_numpy(X).cuda(), torch.from_numpy(Y0).cuda()
+            assert spblas.mm(kind, tr, 1.25, A, spblas.descr(t, upper, unit), capi.ROW_MAJOR, dX, columns, columns, 0.5, dY,
+                             columns) == capi.SUCCESS
+            assert_rows_close(kind, dY.cpu().numpy(), Yref, sc.reshape(-1), f"{kind} mm type {t}")
+        spblas.destroy(A)

@@ -5,7 +5,7 @@ import pytest
 
 import oracle
 from alsparse_b200 import synth
-from helpers import NP, assert_rows_close, golden, mm_scale, row_scale
+from helpers import NP, assert_rows_close, golden, mm_scale, row_scale, structured_scale
 
 # The reference is built with -Ofast (reassociation, FMA contraction); the restatement sums strictly
 # left to right.  Both are one summation order of the same products, so they agree to a few
@@ -92,6 +92,29 @@ def test_structured_descriptors_golden():
                     assert_rows_close("d", y, g[f"y_t{t}_u{upper}_d{unit}_o{tr}"], full, f"type {t} {upper}{unit}{tr}")
                     n += 1
     assert n == 16
+
+
+def test_structured_mm_golden():
+    """symm / trmm / diagmm restatements against the reference's plain kernels: every fill / diag / operation
+    variant in both layouts with padded leading dimensions."""
+    g = golden("struct_mm_d.npz")
+    ptr, a, b = g["ptr"], float(g["alpha"]), float(g["beta"])
+    columns, ldx, ldy, ldxc, ldyc = (int(v) for v in g["par"])
+    n, n_cases = 160, 0
+    for key in (k[4:] for k in g.files if k.startswith("row_")):
+        t, upper, unit, tr = (int(f[1:]) for f in key.split("_"))
+        for lay, X, Y0, lx, ly in (("row", g["Xr"], g["Yr"], ldx, ldy), ("col", g["Xc"], g["Yc"], ldxc, ldyc)):
+            Y = oracle.structured_mm("d", t, upper, unit, tr, lay, ptr[:-1], ptr[1:], g["col"], g["val"], a, X, columns,
+                                     lx, b, Y0.copy(), ly)
+            ref = g[f"{lay}_{key}"]
+            view = (lambda v: v.reshape(n, ly)[:, :columns]) if lay == "row" else (lambda v: v.reshape(columns, ly)[:, :n].T)
+            xv = X.reshape(n, lx)[:, :columns] if lay == "row" else X.reshape(columns, lx)[:, :n].T
+            sc = structured_scale(n, ptr, g["col"], g["val"], xv, view(Y0), a, b)
+            assert_rows_close("d", view(Y).reshape(-1), view(ref).reshape(-1), sc.reshape(-1), f"{lay} {key}")
+            pad = (lambda v: v.reshape(n, ly)[:, columns:]) if lay == "row" else (lambda v: v.reshape(columns, ly)[:, n:])
+            assert np.array_equal(pad(Y), pad(Y0)) and np.array_equal(pad(ref), pad(Y0))
+            n_cases += 1
+    assert n_cases == 2 * (4 + 8 + 2)
 
 
 def test_coo_to_csr_golden():
