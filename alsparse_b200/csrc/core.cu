@@ -625,18 +625,24 @@ static alphasparse_status_t check_call(const alphasparse_matrix_t A, const void 
 constexpr int64_t kPipelineMinRows = 1 << 20;
 constexpr int kPipelineChunks = 8;
 
+// the two copy streams and the events of the host-operand pipelines, created on first use
+static alphasparse_status_t ensure_pipe(DeviceCtx *c) {
+    if (c->copy_in) return ALPHA_SPARSE_STATUS_SUCCESS;
+    ASB_CUDA_OR(cudaStreamCreateWithFlags(&c->copy_in, cudaStreamNonBlocking), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    ASB_CUDA_OR(cudaStreamCreateWithFlags(&c->copy_out, cudaStreamNonBlocking), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    for (cudaEvent_t &ev : c->ev_pipe)
+        ASB_CUDA_OR(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
 template <typename T>
 static alphasparse_status_t mv_host_pipelined(DeviceCtx *c, T alpha, const T *x, T beta, T *y, cudaStream_t st) {
     alphasparse_status_t s = grow(&c->d_x_stage, &c->x_stage_bytes, sizeof(T) * (size_t)c->cols, c);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     s = grow(&c->d_y_stage, &c->y_stage_bytes, sizeof(T) * (size_t)c->rows, c);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-    if (!c->copy_in) {
-        ASB_CUDA_OR(cudaStreamCreateWithFlags(&c->copy_in, cudaStreamNonBlocking), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-        ASB_CUDA_OR(cudaStreamCreateWithFlags(&c->copy_out, cudaStreamNonBlocking), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-        for (cudaEvent_t &ev : c->ev_pipe)
-            ASB_CUDA_OR(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-    }
+    s = ensure_pipe(c);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     const T *dx = static_cast<const T *>(c->d_x_stage);
     T *dy = static_cast<T *>(c->d_y_stage);
     cudaEvent_t ev_x = c->ev_pipe[0];
@@ -775,6 +781,57 @@ static alphasparse_status_t mv(alphasparse_operation_t op, T alpha, const alphas
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
+// Row-major mm with host X and host Y on a large dense block: X goes over first (every row of A may
+// need any row of X), then the product runs in kPipelineChunks row windows and every finished window
+// of Y leaves on its own stream while the next one is multiplied; when Y must come over first
+// (beta != 0, or a padded ldy whose gaps belong to the caller) its windows arrive behind X on the
+// inbound stream.  Same streams and events as the mv pipeline.
+constexpr size_t kMmPipelineMinBytes = (size_t)32 << 20;
+
+template <typename T>
+static alphasparse_status_t mm_host_pipelined(DeviceCtx *c, T alpha, const T *x, int columns, int ldx, size_t xbytes,
+                                              T beta, T *y, int ldy, size_t y_elems, bool y_in, cudaStream_t st) {
+    alphasparse_status_t s = grow(&c->d_x_stage, &c->x_stage_bytes, xbytes, c);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    s = grow(&c->d_y_stage, &c->y_stage_bytes, sizeof(T) * y_elems, c);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    s = ensure_pipe(c);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    const T *dx = static_cast<const T *>(c->d_x_stage);
+    T *dy = static_cast<T *>(c->d_y_stage);
+    cudaEvent_t ev_x = c->ev_pipe[0];
+    ASB_CUDA_OR(cudaEventRecord(ev_x, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    ASB_CUDA_OR(cudaStreamWaitEvent(c->copy_in, ev_x, 0), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    ASB_CUDA_OR(cudaMemcpyAsync(c->d_x_stage, x, xbytes, cudaMemcpyHostToDevice, c->copy_in),
+                ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    ASB_CUDA_OR(cudaEventRecord(ev_x, c->copy_in), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    ASB_CUDA_OR(cudaStreamWaitEvent(st, ev_x, 0), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+
+    const int64_t step = ((c->rows + kPipelineChunks - 1) / kPipelineChunks + 63) & ~63ll;
+    for (int k = 0; k < kPipelineChunks; k++) {
+        const int64_t rb = k * step;
+        if (rb >= c->rows) break;
+        const RowWindow w{rb, std::min<int64_t>(step, c->rows - rb)};
+        const size_t e0 = (size_t)rb * (size_t)ldy, e1 = std::min((size_t)(rb + w.count) * (size_t)ldy, y_elems);
+        cudaEvent_t ev_in = c->ev_pipe[1 + 2 * k], ev_done = c->ev_pipe[2 + 2 * k];
+        if (y_in) {
+            ASB_CUDA_OR(cudaMemcpyAsync(dy + e0, y + e0, sizeof(T) * (e1 - e0), cudaMemcpyHostToDevice, c->copy_in),
+                        ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+            ASB_CUDA_OR(cudaEventRecord(ev_in, c->copy_in), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+            ASB_CUDA_OR(cudaStreamWaitEvent(st, ev_in, 0), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        }
+        s = launch_spmm_row<T>(c, alpha, dx, columns, ldx, beta, dy, ldy, st, &w);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        ASB_CUDA_OR(cudaEventRecord(ev_done, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        ASB_CUDA_OR(cudaStreamWaitEvent(c->copy_out, ev_done, 0), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        ASB_CUDA_OR(cudaMemcpyAsync(y + e0, dy + e0, sizeof(T) * (e1 - e0), cudaMemcpyDeviceToHost, c->copy_out),
+                    ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    }
+    ASB_CUDA_OR(cudaStreamSynchronize(c->copy_out), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    ASB_CUDA_OR(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
 template <typename T>
 static alphasparse_status_t mm(alphasparse_operation_t op, T alpha, const alphasparse_matrix_t A,
                                struct alpha_matrix_descr descr, alphasparse_layout_t layout,
@@ -817,6 +874,10 @@ static alphasparse_status_t mm(alphasparse_operation_t op, T alpha, const alphas
     const size_t xbytes = sizeof(T) * (row_major ? extent(c->cols, columns, ldx) : extent(columns, c->cols, ldx));
     const size_t ybytes = sizeof(T) * (row_major ? extent(c->rows, columns, ldy) : extent(columns, c->rows, ldy));
     const bool y_tight = row_major ? ldy == columns : ldy == c->rows;
+    if (row_major && !x_dev && !y_dev && !c->profile && xbytes > 0 && ybytes >= kMmPipelineMinBytes &&
+        c->rows >= 64 * kPipelineChunks)
+        return mm_host_pipelined<T>(c, alpha, x, columns, ldx, xbytes, beta, y, ldy, ybytes / sizeof(T),
+                                    beta != T(0) || !y_tight, st);
     const T *dx = x;
     T *dy = y;
     if (!x_dev) {

@@ -155,7 +155,8 @@ alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T 
 
 template <typename T>
 alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx,
-                                     T beta, T *Y, int ldy, cudaStream_t stream);
+                                     T beta, T *Y, int ldy, cudaStream_t stream,
+                                     const RowWindow *window = nullptr);
 
 template <typename T>
 alphasparse_status_t launch_spmm_col(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx,

@@ -126,37 +126,42 @@ __global__ void __launch_bounds__(256, kSpmmMinBlocks)
 
 template <typename T, int VEC, int LPR>
 static void launch_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx, T beta, T *Y,
-                       int ldy, cudaStream_t st) {
+                       int ldy, cudaStream_t st, const RowWindow *w) {
     constexpr int rows_per_block = 8 * (32 / LPR);
-    const unsigned blocks = (unsigned)((ctx->rows + rows_per_block - 1) / rows_per_block);
+    // A window is the same kernel on a slice: offsets are absolute, so shifting the offset array and Y
+    // by the first row is all it takes.
+    const int64_t first = w ? w->begin : 0, rows = w ? w->count : ctx->rows;
+    const unsigned blocks = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
     const T *val = static_cast<const T *>(ctx->d_val);
+    const int *row_ptr = ctx->d_row_ptr + first;
+    Y += first * (int64_t)ldy;
     if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
     if (beta == T(0))
         spmm_row_kernel<T, VEC, LPR, false><<<blocks, 256, 0, st>>>(
-            (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, X, columns, ldx, Y, ldy, alpha, beta);
+            (int)rows, row_ptr, ctx->d_col, val, X, columns, ldx, Y, ldy, alpha, beta);
     else
         spmm_row_kernel<T, VEC, LPR, true><<<blocks, 256, 0, st>>>(
-            (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, X, columns, ldx, Y, ldy, alpha, beta);
+            (int)rows, row_ptr, ctx->d_col, val, X, columns, ldx, Y, ldy, alpha, beta);
     if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
     count_launch();
 }
 
 template <typename T, int VEC>
 static void launch_row_lanes(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx, T beta, T *Y,
-                             int ldy, cudaStream_t st) {
+                             int ldy, cudaStream_t st, const RowWindow *w) {
     // smallest group (2 .. 32 lanes) whose lanes cover the dense columns in one pass, if any
     const int need = (columns + VEC - 1) / VEC;
-    if (need <= 2) launch_row<T, VEC, 2>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
-    else if (need <= 4) launch_row<T, VEC, 4>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
-    else if (need <= 8) launch_row<T, VEC, 8>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
-    else if (need <= 16) launch_row<T, VEC, 16>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
-    else launch_row<T, VEC, 32>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+    if (need <= 2) launch_row<T, VEC, 2>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st, w);
+    else if (need <= 4) launch_row<T, VEC, 4>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st, w);
+    else if (need <= 8) launch_row<T, VEC, 8>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st, w);
+    else if (need <= 16) launch_row<T, VEC, 16>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st, w);
+    else launch_row<T, VEC, 32>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st, w);
 }
 
 template <typename T>
 alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx,
-                                     T beta, T *Y, int ldy, cudaStream_t st) {
-    if (ctx->rows == 0 || columns <= 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+                                     T beta, T *Y, int ldy, cudaStream_t st, const RowWindow *w) {
+    if (ctx->rows == 0 || columns <= 0 || (w && w->count <= 0)) return ALPHA_SPARSE_STATUS_SUCCESS;
     auto fits = [&](int vec) {
         const uintptr_t mask = (uintptr_t)(vec * sizeof(T) - 1);
         return columns % vec == 0 && ldx % vec == 0 && ldy % vec == 0 &&
@@ -164,12 +169,12 @@ alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int co
     };
     // Widest 16-byte pack the shapes and alignments allow.
     if constexpr (sizeof(T) == 4) {
-        if (fits(4)) launch_row_lanes<T, 4>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
-        else if (fits(2)) launch_row_lanes<T, 2>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
-        else launch_row_lanes<T, 1>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+        if (fits(4)) launch_row_lanes<T, 4>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st, w);
+        else if (fits(2)) launch_row_lanes<T, 2>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st, w);
+        else launch_row_lanes<T, 1>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st, w);
     } else {
-        if (fits(2)) launch_row_lanes<T, 2>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
-        else launch_row_lanes<T, 1>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+        if (fits(2)) launch_row_lanes<T, 2>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st, w);
+        else launch_row_lanes<T, 1>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st, w);
     }
     ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     return ALPHA_SPARSE_STATUS_SUCCESS;
@@ -262,8 +267,8 @@ template alphasparse_status_t launch_spmm_col<double>(DeviceCtx *, double, const
                                                       double *, int, cudaStream_t);
 
 template alphasparse_status_t launch_spmm_row<float>(DeviceCtx *, float, const float *, int, int,
-                                                     float, float *, int, cudaStream_t);
+                                                     float, float *, int, cudaStream_t, const RowWindow *);
 template alphasparse_status_t launch_spmm_row<double>(DeviceCtx *, double, const double *, int, int,
-                                                      double, double *, int, cudaStream_t);
+                                                      double, double *, int, cudaStream_t, const RowWindow *);
 
 }  // namespace asb

@@ -201,3 +201,19 @@ def test_structured_descriptors_mm():
                              columns) == capi.SUCCESS
             assert_rows_close(kind, dY.cpu().numpy(), Yref, sc.reshape(-1), f"{kind} mm type {t}")
         spblas.destroy(A)
+
+
+@pytest.mark.parametrize("ldy,beta", [(64, 0.0), (72, 0.5)])
+def test_large_host_operands_take_the_windowed_path(ldy, beta):
+    """Host X and Y above 32 MB: the product runs in row windows that overlap the copies of Y; results and the
+    caller's padding must be what the single-launch path gives."""
+    rows, cols, columns, ldx = 140001, 50000, 64, 64
+    m = synth.poisson("s", 77, rows, cols, 6.0)
+    X, Y0 = synth.vector("s", 77, 1, cols * ldx), synth.vector("s", 77, 2, rows * ldy)
+    A = make_handle("s", m)
+    Yref = oracle.gemm("s", "row", m.rows_start, m.rows_end, m.col, m.val, 1.25, X, columns, ldx, beta, Y0.copy(), ldy)
+    Y = run_mm("s", A, m, X, columns, ldx, 1.25, beta, Y0, ldy, device=False)
+    compare("s", m, Y, Yref, X, columns, ldx, 1.25, beta, Y0, ldy, f"windowed ldy={ldy}")
+    Yd = run_mm("s", A, m, X, columns, ldx, 1.25, beta, Y0, ldy, device=True)
+    assert np.array_equal(Y.reshape(rows, ldy)[:, :columns], Yd.reshape(rows, ldy)[:, :columns])  # same kernel, same sums
+    spblas.destroy(A)
