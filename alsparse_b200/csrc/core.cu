@@ -610,10 +610,40 @@ static alphasparse_status_t check_call(const alphasparse_matrix_t A, const void 
             return ALPHA_SPARSE_STATUS_SUCCESS;
         return ALPHA_SPARSE_STATUS_INVALID_VALUE;
     }
-    if (A->format == ALPHA_SPARSE_FORMAT_COO ||
-        (A->format >= ALPHA_SPARSE_FORMAT_CSC && A->format <= ALPHA_SPARSE_FORMAT_DIA))
+    if (A->format == ALPHA_SPARSE_FORMAT_COO) {  // served for GENERAL through a CSR copy (csr_shadow_of)
+        if (descr.type == ALPHA_SPARSE_MATRIX_TYPE_GENERAL) return ALPHA_SPARSE_STATUS_SUCCESS;
+        if (descr.type >= ALPHA_SPARSE_MATRIX_TYPE_SYMMETRIC && descr.type <= ALPHA_SPARSE_MATRIX_TYPE_DIAGONAL)
+            return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+        return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    }
+    if (A->format >= ALPHA_SPARSE_FORMAT_CSC && A->format <= ALPHA_SPARSE_FORMAT_DIA)
         return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
     return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+}
+
+// A COO handle given straight to mv / mm (the COO block of the reference's dispatchers,
+// src/core/op/level2/alphasparse_x_mv.c:1718-1741 and src/core/op/level3/alphasparse_x_mm.c:2370-2376; kernels
+// src/plain/kernel/level2/mv/gemv/gemv_x_coo[_trans]_plain.c and .../level3/mm/gemm/gemm_x_coo_{row,col}[_trans]_plain.c):
+// those kernels add alpha*a*x[col] into y[row] entry by entry, i.e. the general product in another
+// summation order.  Here the product runs on a CSR copy of the matrix, converted on first use (the
+// device radix sort for large inputs) and kept in the handle's otherwise unused `inspector` slot
+// until alphasparse_destroy.
+static std::mutex g_shadow_mu;
+
+static alphasparse_status_t csr_shadow_of(const alphasparse_matrix_t A, alphasparse_matrix_t *out) {
+    std::lock_guard<std::mutex> lock(g_shadow_mu);
+    if (!A->inspector) {
+        alphasparse_matrix_t csr = nullptr;
+        alphasparse_status_t s = ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+        if (A->datatype == ALPHA_SPARSE_DATATYPE_FLOAT)
+            s = coo_to_csr<float>(static_cast<const spmat_coo_s_t *>(A->mat), false, &csr);
+        else if (A->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE)
+            s = coo_to_csr<double>(static_cast<const spmat_coo_d_t *>(A->mat), false, &csr);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        A->inspector = csr;
+    }
+    *out = static_cast<alphasparse_matrix_t>(A->inspector);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
 // Host x and host y on a large matrix: the product runs in kPipelineChunks row windows (4 -> 8 windows
@@ -703,10 +733,14 @@ static alphasparse_status_t select_structured(DeviceCtx *&c, const alphasparse_m
 }
 
 template <typename T>
-static alphasparse_status_t mv(alphasparse_operation_t op, T alpha, const alphasparse_matrix_t A,
+static alphasparse_status_t mv(alphasparse_operation_t op, T alpha, alphasparse_matrix_t A,
                                struct alpha_matrix_descr descr, const T *x, T beta, T *y) {
     alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    if (A->format == ALPHA_SPARSE_FORMAT_COO) {
+        s = csr_shadow_of(A, &A);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    }
     DeviceCtx *c = ctx_of(A);
     if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
 
@@ -833,7 +867,7 @@ static alphasparse_status_t mm_host_pipelined(DeviceCtx *c, T alpha, const T *x,
 }
 
 template <typename T>
-static alphasparse_status_t mm(alphasparse_operation_t op, T alpha, const alphasparse_matrix_t A,
+static alphasparse_status_t mm(alphasparse_operation_t op, T alpha, alphasparse_matrix_t A,
                                struct alpha_matrix_descr descr, alphasparse_layout_t layout,
                                const T *x, ALPHA_INT columns, ALPHA_INT ldx, T beta, T *y,
                                ALPHA_INT ldy) {
@@ -841,6 +875,10 @@ static alphasparse_status_t mm(alphasparse_operation_t op, T alpha, const alphas
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     if (layout != ALPHA_SPARSE_LAYOUT_ROW_MAJOR && layout != ALPHA_SPARSE_LAYOUT_COLUMN_MAJOR)
         return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    if (A->format == ALPHA_SPARSE_FORMAT_COO) {
+        s = csr_shadow_of(A, &A);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    }
     DeviceCtx *c = ctx_of(A);
     if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
     DeviceGuard guard(c->device);
@@ -975,6 +1013,8 @@ alphasparse_status_t alphasparse_destroy(alphasparse_matrix_t A) {
             if (A->datatype == ALPHA_SPARSE_DATATYPE_FLOAT) free_csr_host<float>(static_cast<spmat_csr_s_t *>(A->mat));
             else if (A->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE) free_csr_host<double>(static_cast<spmat_csr_d_t *>(A->mat));
         } else if (A->format == ALPHA_SPARSE_FORMAT_COO) {
+            alphasparse_destroy(static_cast<alphasparse_matrix_t>(A->inspector));  // the CSR copy mv / mm made, if any
+            A->inspector = nullptr;
             spmat_coo_s_t *m = static_cast<spmat_coo_s_t *>(A->mat);  // pointer fields first in both precisions
             free(m->values), free(m->row_indx), free(m->col_indx), free(m);
         }

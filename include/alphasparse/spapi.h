@@ -14,9 +14,12 @@
  * every fill / diag / operation combination the reference's dispatch tables hold (SYMMETRIC with
  * TRANSPOSE has no entry there and is NOT_SUPPORTED here too).
  *
- * What is not served.  Complex precisions (and so HERMITIAN) and formats other than CSR (COO only
- * as the source of alphasparse_convert_csr) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED after the
- * argument checks: there is no CPU fallback.
+ * A COO handle may be given to mv / mm directly with a GENERAL descriptor: the product runs on a CSR
+ * copy converted on first use and kept with the handle.
+ *
+ * What is not served.  Complex precisions (and so HERMITIAN), structured descriptors on a COO handle
+ * and formats other than CSR and COO return ALPHA_SPARSE_STATUS_NOT_SUPPORTED after the argument
+ * checks: there is no CPU fallback.
  */
 #include "types.h"
 #include "spdef.h"

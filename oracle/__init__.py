@@ -59,6 +59,9 @@ def lib():
             getattr(L, f"oracle_symm_csr_{k}").argtypes = [C.c_int] * 3 + mm_tail
             getattr(L, f"oracle_trmm_csr_{k}").argtypes = [C.c_int] * 4 + mm_tail
             getattr(L, f"oracle_diagmm_csr_{k}").argtypes = [C.c_int] * 2 + mm_tail
+            getattr(L, f"oracle_gemv_coo_{k}").argtypes = [C.c_int, _i32, _i32, _i32, _p, _p, _p, T, _p, T, _p]
+            getattr(L, f"oracle_gemm_coo_{k}").argtypes = [C.c_int, C.c_int, _i32, _i32, _i32, _p, _p, _p, T, _p, _i32,
+                                                            _i32, T, _p, _i32]
             getattr(L, f"oracle_create_csr_{k}").argtypes = [_i32, _i32, _p, _p, _p, _p, _p, _p, _p]
             getattr(L, f"oracle_create_csr_{k}").restype = _i32
             getattr(L, f"oracle_coo_to_csr_{k}").argtypes = [_i32, _i32, _i32, _p, _p, _p, _p, _p, _p]
@@ -130,6 +133,21 @@ def structured_mm(kind, descr_type, upper, unit, trans, layout, rows_start, rows
         getattr(lib(), f"oracle_diagmm_csr_{kind}")(int(unit), cm, *tail)
     else:
         raise ValueError(descr_type)
+    return Y
+
+
+def gemv_coo(kind, trans, rows, cols, row_indx, col_indx, val, alpha, x, beta, y):
+    """mv on a COO matrix (zero-based entries in stored order); y modified in place."""
+    ri, ci = _i(row_indx), _i(col_indx)
+    getattr(lib(), f"oracle_gemv_coo_{kind}")(int(trans), rows, cols, len(ri), _a(ri), _a(ci), _a(val), alpha, _a(x),
+                                               beta, _a(y))
+    return y
+
+
+def gemm_coo(kind, trans, layout, rows, cols, row_indx, col_indx, val, alpha, X, columns, ldx, beta, Y, ldy):
+    ri, ci = _i(row_indx), _i(col_indx)
+    getattr(lib(), f"oracle_gemm_coo_{kind}")(int(trans), int(layout == "col"), rows, cols, len(ri), _a(ri), _a(ci),
+                                               _a(val), alpha, _a(X), columns, ldx, beta, _a(Y), ldy)
     return Y
 
 
@@ -208,6 +226,10 @@ def ref():
                         [f"trmm_{k}_csr_{d}_{m}_{lay}{t}_plain" for d in "nu" for m in ("lo", "hi")
                          for lay in ("row", "col") for t in ("", "_trans")] + \
                         [f"diagmm_{k}_csr_{d}_{lay}_plain" for d in "nu" for lay in ("row", "col")]:
+                getattr(L, name).argtypes = [T, _p, _p, _i32, _i32, T, _p, _i32]
+            for name in (f"gemv_{k}_coo_plain", f"gemv_{k}_coo_trans_plain"):
+                getattr(L, name).argtypes = [T, _p, _p, T, _p]
+            for name in [f"gemm_{k}_coo_{lay}{t}_plain" for lay in ("row", "col") for t in ("", "_trans")]:
                 getattr(L, name).argtypes = [T, _p, _p, _i32, _i32, T, _p, _i32]
             getattr(L, f"alphasparse_{k}_export_csr").argtypes = [_p] * 8
         L.balanced_partition_row_by_nnz.argtypes = [_p, _i32, _i32, _p]
@@ -313,6 +335,29 @@ class RefCsr:
         else:
             fn = getattr(L, f"gemm_{self.kind}_csr_{layout}_plain")
         st = fn(alpha, self.mat, _a(X), columns, ldx, beta, _a(Y), ldy)
+        assert st == 0
+        return Y
+
+
+class RefCoo:
+    """A COO handle owned by the reference library (never freed, like RefCsr)."""
+
+    def __init__(self, kind, base, rows, cols, row_indx, col_indx, val):
+        ri, ci = _i(row_indx), _i(col_indx)
+        v = np.ascontiguousarray(val, dtype=_NP[kind])
+        h = C.c_void_p()
+        st = getattr(ref(), f"alphasparse_{kind}_create_coo")(C.byref(h), base, rows, cols, len(ri), _a(ri), _a(ci), _a(v))
+        assert st == 0
+        self.kind, self.mat = kind, C.cast(h, C.POINTER(_RefHandle)).contents.mat
+
+    def gemv(self, trans, alpha, x, beta, y):
+        st = getattr(ref(), f"gemv_{self.kind}_coo{'_trans' if trans else ''}_plain")(alpha, self.mat, _a(x), beta, _a(y))
+        assert st == 0
+        return y
+
+    def gemm(self, trans, layout, alpha, X, columns, ldx, beta, Y, ldy):
+        st = getattr(ref(), f"gemm_{self.kind}_coo_{layout}{'_trans' if trans else ''}_plain")(
+            alpha, self.mat, _a(X), columns, ldx, beta, _a(Y), ldy)
         assert st == 0
         return Y
 

@@ -520,3 +520,52 @@ DEF_STRUCT(double, d)
 DEF_STRUCT_MM(float, s)
 DEF_STRUCT_MM(double, d)
 #undef AT
+
+/* ---------------------------------------------------------------------------------------
+ * A COO handle given straight to mv / mm with a GENERAL descriptor
+ * (src/core/op/level2/alphasparse_x_mv.c:1718-1724, src/core/op/level3/alphasparse_x_mm.c:2370-2376).
+ *   src/plain/kernel/level2/mv/gemv/gemv_x_coo_plain.c, gemv_x_coo_trans_plain.c: y scaled by beta,
+ *   then every entry in stored order adds alpha*(a*x[col]) to y[row] (transposed: alpha*(a*x[row]) to
+ *   y[col], y has `cols` entries).
+ *   src/plain/kernel/level3/mm/gemm/gemm_x_coo_row_plain.c: every entry adds (alpha*a)*X[col,:] to
+ *   Y[row,:]; gemm_x_coo_col_plain.c: alpha*(a*X[col,c]) per dense column c.  The transposed kernels
+ *   swap the index arrays (transpose_coo) and run the same loops.
+ * ------------------------------------------------------------------------------------- */
+#define DEF_COO(T, sfx)                                                                       \
+    void oracle_gemv_coo_##sfx(int trans, aint rows, aint cols, aint nnz, const aint *ri,     \
+                               const aint *ci, const T *val, T alpha, const T *x, T beta,     \
+                               T *y) {                                                        \
+        const aint m = trans ? cols : rows;                                                   \
+        for (aint i = 0; i < m; i++) y[i] = y[i] * beta;                                      \
+        for (aint k = 0; k < nnz; k++) {                                                      \
+            const aint r = trans ? ci[k] : ri[k], c = trans ? ri[k] : ci[k];                  \
+            const T v = val[k] * x[c];                                                        \
+            y[r] += alpha * v;                                                                \
+        }                                                                                     \
+    }                                                                                         \
+    void oracle_gemm_coo_##sfx(int trans, int col_major, aint rows, aint cols, aint nnz,      \
+                               const aint *ri, const aint *ci, const T *val, T alpha,         \
+                               const T *x, aint columns, aint ldx, T beta, T *y, aint ldy) {  \
+        const aint m = trans ? cols : rows;                                                   \
+        for (aint r = 0; r < m; r++)                                                          \
+            for (aint c = 0; c < columns; c++) {                                              \
+                T *out = col_major ? &y[(size_t)c * ldy + r] : &y[(size_t)r * ldy + c];       \
+                *out = *out * beta;                                                           \
+            }                                                                                 \
+        if (col_major) {                                                                      \
+            for (aint c = 0; c < columns; c++)                                                \
+                for (aint k = 0; k < nnz; k++) {                                              \
+                    const aint r = trans ? ci[k] : ri[k], j = trans ? ri[k] : ci[k];          \
+                    const T v = val[k] * x[(size_t)c * ldx + j];                              \
+                    y[(size_t)c * ldy + r] += alpha * v;                                      \
+                }                                                                             \
+        } else {                                                                              \
+            for (aint k = 0; k < nnz; k++) {                                                  \
+                const aint r = trans ? ci[k] : ri[k], j = trans ? ri[k] : ci[k];              \
+                const T av = alpha * val[k];                                                  \
+                for (aint c = 0; c < columns; c++) y[(size_t)r * ldy + c] += av * x[(size_t)j * ldx + c]; \
+            }                                                                                 \
+        }                                                                                     \
+    }
+DEF_COO(float, s)
+DEF_COO(double, d)

@@ -136,6 +136,30 @@ def main():
                     out[f"col_{key}"] = Q.structured_mm(t, upper, unit, tr, "col", 0.75, Xc, columns, ldxc, -0.5, Yc.copy(), ldyc)
     np.savez_compressed(os.path.join(OUT, "struct_mm_d.npz"), **out)
 
+    # -- a COO handle given straight to mv / mm: the reference's plain gemv_coo / gemm_coo kernels on unsorted
+    #    one-based entries with a few repeated (row, col) pairs ---------------------------------------------
+    cm = synth.poisson("d", 13, 150, 210, 5.0)
+    rng = np.random.default_rng(13)
+    cri = np.repeat(np.arange(150, dtype=np.int32), np.diff(cm.ptr))
+    dup = rng.integers(0, cm.nnz, 40)
+    cri, cci = np.concatenate([cri, cri[dup]]), np.concatenate([cm.col, cm.col[dup]])
+    cv = np.concatenate([cm.val, rng.uniform(-1, 1, 40)])
+    perm = rng.permutation(len(cri))
+    cri, cci, cv = cri[perm].astype(np.int32), cci[perm].astype(np.int32), cv[perm]
+    K = oracle.RefCoo("d", 1, 150, 210, cri + 1, cci + 1, cv)
+    columns, ldx, ldy = 6, 8, 7
+    out = dict(ri=cri, ci=cci, val=cv, rows=150, cols=210, alpha=1.25, beta=-0.75, par=np.array([columns, ldx, ldy]))
+    for tr, m_out, m_in in ((0, 150, 210), (1, 210, 150)):
+        xk, yk = synth.vector("d", 13, 1 + tr, m_in), synth.vector("d", 13, 3 + tr, m_out)
+        out[f"x_o{tr}"], out[f"y0_o{tr}"] = xk, yk
+        out[f"y_o{tr}"] = K.gemv(tr, 1.25, xk, -0.75, yk.copy())
+        Xr, Yr = synth.vector("d", 13, 5 + tr, m_in * ldx), synth.vector("d", 13, 7 + tr, m_out * ldy)
+        Xc, Yc = synth.vector("d", 13, 9 + tr, (m_in + 2) * columns), synth.vector("d", 13, 11 + tr, (m_out + 1) * columns)
+        out[f"Xr_o{tr}"], out[f"Yr0_o{tr}"], out[f"Xc_o{tr}"], out[f"Yc0_o{tr}"] = Xr, Yr, Xc, Yc
+        out[f"Yr_o{tr}"] = K.gemm(tr, "row", 1.25, Xr, columns, ldx, -0.75, Yr.copy(), ldy)
+        out[f"Yc_o{tr}"] = K.gemm(tr, "col", 1.25, Xc, columns, m_in + 2, -0.75, Yc.copy(), m_out + 1)
+    np.savez_compressed(os.path.join(OUT, "coo_d.npz"), **out)
+
     # -- nnz-balanced row partition: known answers incl. the quirks ---------------------------------
     cases = {}
     accs = {"tiny": np.array([2, 3, 4], np.int32), "cfg1": m.ptr[1:], "zipf": z.ptr[1:],

@@ -394,3 +394,73 @@ def test_merge_kernel_delivers_into_page_locked_host_y():
     y_ref = oracle.gemv(kind, m.rows_start, m.rows_end, m.col, m.val, 0.5, x, -1.5, y0.copy())
     assert_rows_close(kind, want, y_ref, row_scale(m.ptr, m.col, m.val, x, 0.5, -1.5, y0), "merge e2e")
     spblas.destroy(A)
+
+
+def test_coo_handle_goes_straight_to_mv_and_mm():
+    """A COO handle with a GENERAL descriptor is served by mv / mm directly (a CSR copy is made on first use):
+    both operations and both dense layouts against the reference's plain COO kernels (golden vectors, unsorted
+    one-based entries with repeated pairs), host and device operands."""
+    g = golden("coo_d.npz")
+    ri, ci, val, a, b = g["ri"], g["ci"], g["val"], float(g["alpha"]), float(g["beta"])
+    rows, cols = int(g["rows"]), int(g["cols"])
+    columns, ldx, ldy = (int(v) for v in g["par"])
+    st, A = spblas.create_coo("d", capi.BASE_ONE, rows, cols, len(ri), ri + 1, ci + 1, val)
+    assert st == capi.SUCCESS
+
+    def scale(m_out, r, c, X, Y0):
+        out = np.zeros((m_out, X.shape[1]))
+        np.add.at(out, r, np.abs(val)[:, None] * np.abs(X)[c])
+        return (np.abs(b * Y0) + abs(a) * out).reshape(-1)
+
+    for tr in (0, 1):
+        m_out, m_in = (cols, rows) if tr else (rows, cols)
+        r, c = (ci, ri) if tr else (ri, ci)
+        x, y0 = g[f"x_o{tr}"], g[f"y0_o{tr}"]
+        for dev in (False, True):
+            if dev:
+                dx, dy = torch.from_numpy(x).cuda(), torch.from_numpy(y0).cuda()
+                assert spblas.mv("d", tr, a, A, spblas.descr(), dx, b, dy) == capi.SUCCESS
+                y = dy.cpu().numpy()
+            else:
+                y = y0.copy()
+                assert spblas.mv("d", tr, a, A, spblas.descr(), x, b, y) == capi.SUCCESS, spblas.last_error()
+            assert_rows_close("d", y, g[f"y_o{tr}"], scale(m_out, r, c, x[:, None], y0[:, None]), f"coo mv op {tr}")
+        Xr, Yr0 = g[f"Xr_o{tr}"], g[f"Yr0_o{tr}"]
+        Y = Yr0.copy()
+        assert spblas.mm("d", tr, a, A, spblas.descr(), capi.ROW_MAJOR, Xr, columns, ldx, b, Y, ldy) == capi.SUCCESS
+        view = lambda v: v.reshape(m_out, ldy)[:, :columns]  # noqa: E731
+        assert_rows_close("d", view(Y).reshape(-1), view(g[f"Yr_o{tr}"]).reshape(-1),
+                          scale(m_out, r, c, Xr.reshape(m_in, ldx)[:, :columns], view(Yr0)), f"coo mm row op {tr}")
+        assert np.array_equal(Y.reshape(m_out, ldy)[:, columns:], Yr0.reshape(m_out, ldy)[:, columns:])
+        lx, ly = m_in + 2, m_out + 1
+        Xc, Yc0 = g[f"Xc_o{tr}"], g[f"Yc0_o{tr}"]
+        dX, dY = torch.from_numpy(Xc).cuda(), torch.from_numpy(Yc0).cuda()
+        assert spblas.mm("d", tr, a, A, spblas.descr(), capi.COLUMN_MAJOR, dX, columns, lx, b, dY, ly) == capi.SUCCESS
+        viewc = lambda v: v.reshape(columns, ly)[:, :m_out].T  # noqa: E731
+        assert_rows_close("d", viewc(dY.cpu().numpy()).reshape(-1), viewc(g[f"Yc_o{tr}"]).reshape(-1),
+                          scale(m_out, r, c, Xc.reshape(columns, lx)[:, :m_in].T, viewc(Yc0)), f"coo mm col op {tr}")
+    # checks keep the reference's order; structured descriptors on a COO handle are not served
+    x, y = g["x_o0"], g["y0_o0"].copy()
+    assert spblas.mv("s", 0, 1.0, A, spblas.descr(), x, 0.0, y) == capi.INVALID_VALUE
+    assert spblas.mv("d", 0, a, A, spblas.descr(capi.SYMMETRIC), x, b, y) == capi.INVALID_VALUE      # 150 x 210
+    assert spblas.mv("d", 0, a, A, spblas.descr(capi.TRIANGULAR), x, b, y) == capi.NOT_SUPPORTED
+    assert spblas.mv("d", 0, a, A, spblas.descr(9), x, b, y) == capi.INVALID_VALUE
+    assert np.array_equal(y, g["y0_o0"])
+    # the conversion entry point still works on the same handle, and destroy releases the copy made by mv
+    st, B = spblas.convert_csr(A, capi.NON_TRANSPOSE)
+    assert st == capi.SUCCESS
+    assert spblas.destroy(B) == capi.SUCCESS and spblas.destroy(A) == capi.SUCCESS
+
+    # a larger single-precision matrix against the oracle, entries in random order
+    m = synth.poisson("s", 91, 30000, 20000, 9.0)
+    rng = np.random.default_rng(91)
+    perm = rng.permutation(m.nnz)
+    ri = np.repeat(np.arange(m.nrows, dtype=np.int32), np.diff(m.ptr))[perm]
+    ci, v = m.col[perm], m.val[perm]
+    st, A = spblas.create_coo("s", capi.BASE_ZERO, m.nrows, m.cols, m.nnz, ri, ci, v)
+    x, y0 = synth.vector("s", 91, 1, m.cols), synth.vector("s", 91, 2, m.nrows)
+    y_ref = oracle.gemv_coo("s", 0, m.nrows, m.cols, ri, ci, v, 1.5, x, 0.5, y0.copy())
+    y = y0.copy()
+    assert spblas.mv("s", 0, 1.5, A, spblas.descr(), x, 0.5, y) == capi.SUCCESS
+    assert_rows_close("s", y, y_ref, row_scale(m.ptr, m.col, m.val, x, 1.5, 0.5, y0), "coo mv s")
+    spblas.destroy(A)

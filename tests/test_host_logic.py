@@ -37,8 +37,14 @@ def test_coo_handle_lives_on_the_host():
     assert st == capi.SUCCESS and A.value
     h = C.cast(A, C.POINTER(capi.Matrix)).contents
     assert h.format == capi.FORMAT_COO and h.datatype == capi.DOUBLE and h.dcu_info is None
-    # not a CSR handle: mv refuses without touching a device
-    assert spblas.mv("d", 0, 1.0, A, spblas.descr(), v, 0.0, v) == capi.NOT_SUPPORTED
+    # structured descriptors on a COO handle are refused without touching a device; the general product needs
+    # one (it runs on a device CSR copy) and fails loudly, y untouched, where there is none
+    y = v.copy()
+    assert spblas.mv("d", 0, 1.0, A, spblas.descr(capi.TRIANGULAR), v, 0.0, y) == capi.NOT_SUPPORTED
+    if not torch.cuda.is_available():
+        assert spblas.mv("d", 0, 1.0, A, spblas.descr(), v, 0.0, y) not in (capi.SUCCESS, capi.NOT_SUPPORTED)
+        assert spblas.last_error() != "" and h.inspector is None
+    assert np.array_equal(y, v)
     st, _ = spblas.convert_csr(A, capi.CONJUGATE_TRANSPOSE)
     assert st == capi.NOT_SUPPORTED
     assert spblas.destroy(A) == capi.SUCCESS

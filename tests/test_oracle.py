@@ -117,6 +117,42 @@ def test_structured_mm_golden():
     assert n_cases == 2 * (4 + 8 + 2)
 
 
+def coo_scale(rows_out, r, c, val, X, Y0, alpha, beta):
+    """|beta*Y0| + |alpha| * sum |a * X[c, :]| scattered to row r; X, Y0 two-dimensional (rows, dense columns)."""
+    out = np.zeros((rows_out, X.shape[1]))
+    np.add.at(out, r, np.abs(val.astype(np.float64))[:, None] * np.abs(X.astype(np.float64))[c])
+    return np.abs(beta * Y0.astype(np.float64)) + abs(alpha) * out
+
+
+def test_coo_products_golden():
+    """gemv_coo / gemm_coo restatements (both operations and layouts) against the reference's plain kernels on
+    unsorted entries with repeated pairs."""
+    g = golden("coo_d.npz")
+    ri, ci, val, a, b = g["ri"], g["ci"], g["val"], float(g["alpha"]), float(g["beta"])
+    rows, cols = int(g["rows"]), int(g["cols"])
+    columns, ldx, ldy = (int(v) for v in g["par"])
+    for tr in (0, 1):
+        m_out, m_in = (cols, rows) if tr else (rows, cols)
+        r, c = (ci, ri) if tr else (ri, ci)
+        y = oracle.gemv_coo("d", tr, rows, cols, ri, ci, val, a, g[f"x_o{tr}"], b, g[f"y0_o{tr}"].copy())
+        sc = coo_scale(m_out, r, c, val, g[f"x_o{tr}"][:, None], g[f"y0_o{tr}"][:, None], a, b)
+        assert_rows_close("d", y, g[f"y_o{tr}"], sc.reshape(-1), f"coo mv op {tr}")
+        Y = oracle.gemm_coo("d", tr, "row", rows, cols, ri, ci, val, a, g[f"Xr_o{tr}"], columns, ldx, b,
+                            g[f"Yr0_o{tr}"].copy(), ldy)
+        sc = coo_scale(m_out, r, c, val, g[f"Xr_o{tr}"].reshape(m_in, ldx)[:, :columns],
+                       g[f"Yr0_o{tr}"].reshape(m_out, ldy)[:, :columns], a, b)
+        assert_rows_close("d", Y.reshape(m_out, ldy)[:, :columns].reshape(-1),
+                          g[f"Yr_o{tr}"].reshape(m_out, ldy)[:, :columns].reshape(-1), sc.reshape(-1), f"coo mm row op {tr}")
+        assert np.array_equal(Y.reshape(m_out, ldy)[:, columns:], g[f"Yr0_o{tr}"].reshape(m_out, ldy)[:, columns:])
+        lx, ly = m_in + 2, m_out + 1
+        Y = oracle.gemm_coo("d", tr, "col", rows, cols, ri, ci, val, a, g[f"Xc_o{tr}"], columns, lx, b,
+                            g[f"Yc0_o{tr}"].copy(), ly)
+        sc = coo_scale(m_out, r, c, val, g[f"Xc_o{tr}"].reshape(columns, lx)[:, :m_in].T,
+                       g[f"Yc0_o{tr}"].reshape(columns, ly)[:, :m_out].T, a, b)
+        assert_rows_close("d", Y.reshape(columns, ly)[:, :m_out].T.reshape(-1),
+                          g[f"Yc_o{tr}"].reshape(columns, ly)[:, :m_out].T.reshape(-1), sc.reshape(-1), f"coo mm col op {tr}")
+
+
 def test_coo_to_csr_golden():
     g = golden("cfg1_s.npz")
     ptr, col, val = oracle.coo_to_csr("s", 1, 1000, g["coo_ri"] + 1, g["coo_ci"] + 1, g["coo_v"])
