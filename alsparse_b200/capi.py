@@ -46,7 +46,7 @@ class MatInfo(C.Structure):
     _fields_ = [("rows", C.c_int64), ("cols", C.c_int64), ("nnz", C.c_int64),
                 ("max_row_nnz", C.c_int64), ("empty_rows", C.c_int64), ("mean_row_nnz", C.c_double),
                 ("algorithm", C.c_int32), ("lanes_per_row", C.c_int32), ("merge_tiles", C.c_int64),
-                ("device_bytes", C.c_int64), ("device", C.c_int32), ("reserved", C.c_int32)]
+                ("device_bytes", C.c_int64), ("device", C.c_int32), ("scheduled", C.c_int32)]
 
 
 class Complex8(C.Structure):

@@ -88,6 +88,7 @@ void ctx_destroy(DeviceCtx *c) {
     cudaFree(c->d_carry_row);
     cudaFree(c->d_carry_val);
     cudaFree(c->d_chunk_done);
+    cudaFree(c->d_sched);
     cudaFree(c->d_x_stage);
     cudaFree(c->d_y_stage);
     cudaFree(c->d_status);
@@ -1160,6 +1161,7 @@ alphasparse_status_t alphasparse_cuda_get_mat_info(const alphasparse_matrix_t A,
     info->algorithm = c->algorithm, info->lanes_per_row = c->lanes;
     info->merge_tiles = c->algorithm == ALPHA_SPARSE_CUDA_ALG_MERGE ? c->merge_tiles : 0;
     info->device_bytes = c->device_bytes, info->device = c->device;
+    info->scheduled = c->d_sched != nullptr;
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 alphasparse_status_t alphasparse_cuda_get_device_csr(const alphasparse_matrix_t A, ALPHA_INT **d_row_ptr,

@@ -103,6 +103,7 @@ struct DeviceCtx {
     MergeCoord *d_tile = nullptr;  // merge_tiles + 1
     int *d_carry_row = nullptr;    // merge_tiles
     void *d_carry_val = nullptr;   // merge_tiles
+    int *d_sched = nullptr;            // block -> tile order of the merge kernel, or null (tile_key_kernel)
     unsigned *d_chunk_done = nullptr;  // per chunk of kPushChunkTiles tiles (exchange calls only)
 
     int *d_status = nullptr;  // error word set by kernels whose bounded waits ran out (0 = fine)

@@ -44,7 +44,7 @@ typedef struct {
     int64_t merge_tiles;   /* merge kernel: thread blocks per call */
     int64_t device_bytes;  /* device memory held by the handle */
     int32_t device;        /* CUDA device ordinal that owns the device copy */
-    int32_t reserved;
+    int32_t scheduled;     /* merge kernel: 1 when its blocks take single-row tiles in column order (large x) */
 } alphasparse_cuda_mat_info_t;
 
 alphasparse_status_t alphasparse_cuda_get_mat_info(const alphasparse_matrix_t A,

@@ -464,3 +464,30 @@ def test_coo_handle_goes_straight_to_mv_and_mm():
     assert spblas.mv("s", 0, 1.5, A, spblas.descr(), x, 0.5, y) == capi.SUCCESS
     assert_rows_close("s", y, y_ref, row_scale(m.ptr, m.col, m.val, x, 1.5, 0.5, y0), "coo mv s")
     spblas.destroy(A)
+
+
+def test_merge_blocks_follow_the_column_schedule_when_x_is_large():
+    """With an x too large to sit in L2 beside the matrix stream the merge kernel's blocks take the single-row
+    tiles in the order of their first column; the product must be what the natural order gives (the order only
+    changes which block computes which tile), and small matrices keep the natural order."""
+    cols = 1 << 22                                             # 32 MB of fp64 x
+    lens = np.concatenate([np.full(30, 70000), synth.rowlen_zipf(5, 20000, 1.8, 1, 3000), np.full(10, 120001)])
+    m = synth.from_lengths("d", 5, lens, cols)
+    A = make_handle("d", m)
+    st, info = spblas.mat_info(A)
+    assert st == capi.SUCCESS and info.algorithm == capi.ALG_MERGE and info.scheduled == 1
+    x, y0 = synth.vector("d", 5, 1, cols), synth.vector("d", 5, 2, m.nrows)
+    y_ref = oracle.gemv("d", m.rows_start, m.rows_end, m.col, m.val, 1.5, x, -0.25, y0.copy())
+    dx, dy = torch.from_numpy(x).cuda(), torch.from_numpy(y0).cuda()
+    assert spblas.mv("d", 0, 1.5, A, spblas.descr(), dx, -0.25, dy) == capi.SUCCESS
+    first = dy.cpu().numpy()
+    assert_rows_close("d", first, y_ref, row_scale(m.ptr, m.col, m.val, x, 1.5, -0.25, y0), "scheduled merge")
+    dy = torch.from_numpy(y0).cuda()
+    assert spblas.mv("d", 0, 1.5, A, spblas.descr(), dx, -0.25, dy) == capi.SUCCESS
+    assert np.array_equal(first, dy.cpu().numpy())             # same schedule, same sums: bit-identical repeats
+    spblas.destroy(A)
+    small = synth.from_lengths("d", 6, np.concatenate([np.full(4, 30000), np.full(500, 3)]), 1 << 16)
+    B = make_handle("d", small)
+    st, info = spblas.mat_info(B)
+    assert info.algorithm == capi.ALG_MERGE and info.scheduled == 0
+    spblas.destroy(B)
