@@ -30,7 +30,9 @@ typedef enum {
 } alphasparse_cuda_alg_t;
 
 /* Forces the SpMV kernel family for handles analysed after the call (A/B measurements);
- * the environment variable ALPHASPARSE_CUDA_ALG=auto|vector|merge|rowtile sets the initial value. */
+ * the environment variable ALPHASPARSE_CUDA_ALG=auto|vector|merge|rowtile sets the initial value.
+ * ALPHASPARSE_CUDA_NO_SCHEDULE=1 keeps the merge kernel's blocks in natural tile order (see
+ * alphasparse_cuda_mat_info_t.scheduled). */
 alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg);
 
 /* What the analysis at handle creation found and chose. */
