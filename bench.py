@@ -295,7 +295,9 @@ def main():
     kind, alpha, beta, op = cfg["kind"], cfg["alpha"], cfg["beta"], cfg["op"]
     tdt = torch.float32 if kind == "s" else torch.float64
     columns = cfg.get("columns", 1)
-    iterate = name == "powerlaw" and world > 1   # y becomes the next x through an allgather
+    # y becomes the next x through an allgather; on one GPU only when the in-library exchange is asked for
+    # by name (its kernels then deliver into this GPU's own next-x buffer: the form an ncu capture can take)
+    iterate = name == "powerlaw" and (world > 1 or args.exchange in ("fused", "push"))
 
     # ---- build this rank's row block ---------------------------------------------------------------
     lens = global_row_lengths(name, cfg)
