@@ -1068,6 +1068,10 @@ alphasparse_status_t alphasparse_set_mv_hint(const alphasparse_matrix_t A, const
 
 alphasparse_status_t alphasparse_optimize(alphasparse_matrix_t A) {
     if (!A || !A->mat) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    if (A->format == ALPHA_SPARSE_FORMAT_COO) {  // builds (or re-analyses) the CSR copy that mv / mm will use
+        alphasparse_status_t s = csr_shadow_of(A, &A);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    }
     DeviceCtx *c = ctx_of(A);
     if (!c) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
     DeviceGuard guard(c->device);

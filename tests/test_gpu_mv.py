@@ -458,6 +458,8 @@ def test_coo_handle_goes_straight_to_mv_and_mm():
     ri = np.repeat(np.arange(m.nrows, dtype=np.int32), np.diff(m.ptr))[perm]
     ci, v = m.col[perm], m.val[perm]
     st, A = spblas.create_coo("s", capi.BASE_ZERO, m.nrows, m.cols, m.nnz, ri, ci, v)
+    assert capi.load().alphasparse_optimize(A) == capi.SUCCESS      # converts ahead of the first product
+    assert C.cast(A, C.POINTER(capi.Matrix)).contents.inspector is not None
     x, y0 = synth.vector("s", 91, 1, m.cols), synth.vector("s", 91, 2, m.nrows)
     y_ref = oracle.gemv_coo("s", 0, m.nrows, m.cols, ri, ci, v, 1.5, x, 0.5, y0.copy())
     y = y0.copy()
