@@ -493,3 +493,38 @@ def test_merge_blocks_follow_the_column_schedule_when_x_is_large():
     st, info = spblas.mat_info(B)
     assert info.algorithm == capi.ALG_MERGE and info.scheduled == 0
     spblas.destroy(B)
+
+
+@pytest.mark.parametrize("kind", ["s", "d"])
+def test_large_transpose_keeps_the_reference_order(kind):
+    """A^T of a matrix with more than a million stored elements, some pairs stored twice: the transposed product
+    must agree with the oracle's transposed kernel, and bit for bit with the plain product of a handle created
+    from the explicitly transposed arrays (a column's elements by ascending row, repeated pairs in stored order)."""
+    m = synth.poisson(kind, 83, 90000, 70000, 14.0)
+    assert m.nnz > 1 << 20
+    # repeat some stored pairs with other values, in place: create_csr keeps them as they come
+    rid = np.repeat(np.arange(m.nrows), np.diff(m.ptr))
+    rng = np.random.default_rng(83)
+    dup = np.sort(rng.choice(m.nnz, 3000, replace=False))       # each copy lands right after its original
+    col = np.insert(m.col, dup + 1, m.col[dup])
+    val = np.insert(m.val, dup + 1, rng.uniform(-1, 1, len(dup)).astype(m.val.dtype))
+    rid2 = np.insert(rid, dup + 1, rid[dup])
+    ptr = np.concatenate([[0], np.cumsum(np.bincount(rid2, minlength=m.nrows))]).astype(np.int32)
+    st, A = spblas.create_csr(kind, 0, m.nrows, m.cols, ptr[:-1], ptr[1:], col, val)
+    assert st == capi.SUCCESS
+    x, y0 = synth.vector(kind, 83, 1, m.nrows), synth.vector(kind, 83, 2, m.cols)
+    y_ref = oracle.gemv_trans(kind, m.cols, ptr[:-1], ptr[1:], col, val, 1.5, x, 0.5, y0.copy())
+    dx, dy = torch.from_numpy(x).cuda(), torch.from_numpy(y0).cuda()
+    assert spblas.mv(kind, capi.TRANSPOSE, 1.5, A, spblas.descr(), dx, 0.5, dy) == capi.SUCCESS, spblas.last_error()
+    order = np.lexsort((np.arange(len(col)), rid2, col))       # by column, then row, then stored position
+    tptr = np.concatenate([[0], np.cumsum(np.bincount(col, minlength=m.cols))]).astype(np.int32)
+    tcol, tval = rid2[order].astype(np.int32), val[order]
+    scale = row_scale(tptr, tcol, tval, x, 1.5, 0.5, y0)
+    assert_rows_close(kind, dy.cpu().numpy(), y_ref, scale, "transposed, large")
+    st, B = spblas.create_csr(kind, 0, m.cols, m.nrows, tptr[:-1], tptr[1:], tcol, tval)
+    assert st == capi.SUCCESS
+    dy2 = torch.from_numpy(y0).cuda()
+    assert spblas.mv(kind, 0, 1.5, B, spblas.descr(), dx, 0.5, dy2) == capi.SUCCESS
+    assert torch.equal(dy, dy2)
+    spblas.destroy(A)
+    spblas.destroy(B)
