@@ -204,3 +204,48 @@ def test_live_against_reference_objects(kind):
     Yr = A.gemm("row", 1.25, X, 8, 8, 0.5, Y0.copy(), 8)
     Yo = oracle.gemm(kind, "row", m.rows_start, m.rows_end, m.col, m.val, 1.25, X, 8, 8, 0.5, Y0.copy(), 8)
     assert_rows_close(kind, Yo, Yr, mm_scale(m.ptr, m.col, m.val, X, 8, 8, 1.25, 0.5, Y0, 8).reshape(-1), "mm")
+
+
+@pytest.mark.skipif(not oracle.ref_available(), reason="reference objects not built on this machine")
+@pytest.mark.parametrize("kind", ["s", "d"])
+def test_live_structured_and_coo_against_reference_objects(kind):
+    """Fresh seeded square matrix through the restatements of symm / trmm / diagmm and of the COO kernels and
+    through the reference's compiled sources: every variant, both precisions."""
+    n, columns = 300, 4
+    m = synth.poisson(kind, 17, n, n, 6.0)
+    A = oracle.RefCsr.from_csr(kind, 0, n, n, m.rows_start, m.rows_end, m.col, m.val)
+    X, Y0 = synth.vector(kind, 17, 1, n * columns), synth.vector(kind, 17, 2, n * columns)
+    checked = 0
+    for t, transes in ((1, (0,)), (3, (0, 1)), (4, (0,))):
+        for upper in ((0,) if t == 4 else (0, 1)):
+            for unit in (0, 1):
+                for tr in transes:
+                    for lay in ("row", "col"):
+                        ld = columns if lay == "row" else n
+                        want = A.structured_mm(t, upper, unit, tr, lay, 1.5, X, columns, ld, -0.5, Y0.copy(), ld)
+                        got = oracle.structured_mm(kind, t, upper, unit, tr, lay, m.rows_start, m.rows_end, m.col, m.val,
+                                                   1.5, X, columns, ld, -0.5, Y0.copy(), ld)
+                        as2d = (lambda v: v.reshape(n, columns)) if lay == "row" else (lambda v: v.reshape(columns, n).T)
+                        sc = structured_scale(n, m.ptr, m.col, m.val, as2d(X), as2d(Y0), 1.5, -0.5)
+                        assert_rows_close(kind, as2d(got).reshape(-1), as2d(want).reshape(-1), sc.reshape(-1),
+                                          f"type {t} {upper}{unit}{tr} {lay}")
+                        checked += 1
+    assert checked == 28
+    rng = np.random.default_rng(17)
+    perm = rng.permutation(m.nnz)
+    ri = np.repeat(np.arange(n, dtype=np.int32), np.diff(m.ptr))[perm]
+    ci, v = m.col[perm], m.val[perm]
+    K = oracle.RefCoo(kind, 0, n, n, ri, ci, v)
+    x, y0 = synth.vector(kind, 17, 3, n), synth.vector(kind, 17, 4, n)
+    for tr in (0, 1):
+        r, c = (ci, ri) if tr else (ri, ci)
+        sc = coo_scale(n, r, c, v, x[:, None], y0[:, None], 0.75, 1.25).reshape(-1)
+        assert_rows_close(kind, oracle.gemv_coo(kind, tr, n, n, ri, ci, v, 0.75, x, 1.25, y0.copy()),
+                          K.gemv(tr, 0.75, x, 1.25, y0.copy()), sc, f"coo mv {tr}")
+        for lay in ("row", "col"):
+            ld = columns if lay == "row" else n
+            as2d = (lambda w: w.reshape(n, columns)) if lay == "row" else (lambda w: w.reshape(columns, n).T)
+            sc = coo_scale(n, r, c, v, as2d(X), as2d(Y0), 0.75, 1.25)
+            got = oracle.gemm_coo(kind, tr, lay, n, n, ri, ci, v, 0.75, X, columns, ld, 1.25, Y0.copy(), ld)
+            want = K.gemm(tr, lay, 0.75, X, columns, ld, 1.25, Y0.copy(), ld)
+            assert_rows_close(kind, as2d(got).reshape(-1), as2d(want).reshape(-1), sc.reshape(-1), f"coo mm {tr} {lay}")
