@@ -24,7 +24,7 @@ BASE_ZERO, BASE_ONE = 0, 1
 # alphasparse_layout_t
 ROW_MAJOR, COLUMN_MAJOR = 0, 1
 # alphasparse_format_t / alphasparse_datatype_t
-FORMAT_COO, FORMAT_CSR = 0, 1
+FORMAT_COO, FORMAT_CSR, FORMAT_CSC = 0, 1, 2
 FLOAT, DOUBLE, FLOAT_COMPLEX, DOUBLE_COMPLEX = 0, 1, 2, 3
 # alphasparse_cuda_alg_t
 ALG_AUTO, ALG_VECTOR, ALG_MERGE, ALG_ROWTILE = 0, 1, 2, 3
@@ -72,13 +72,17 @@ def prototypes():
     for k, T in list(_REAL.items()) + list(_CPLX.items()):
         p[f"alphasparse_{k}_create_coo"] = (C.c_int, [_HP, C.c_int, _I, _I, _I, _P, _P, _P])
         p[f"alphasparse_{k}_create_csr"] = (C.c_int, [_HP, C.c_int, _I, _I, _P, _P, _P, _P])
+        p[f"alphasparse_{k}_create_csc"] = (C.c_int, [_HP, C.c_int, _I, _I, _P, _P, _P, _P])
         p[f"alphasparse_{k}_mv"] = (C.c_int, [C.c_int, T, _H, MatrixDescr, _P, T, _P])
         p[f"alphasparse_{k}_mm"] = (C.c_int, [C.c_int, T, _H, MatrixDescr, C.c_int, _P, _I, _I, T, _P, _I])
     for k in _REAL:
         p[f"alphasparse_{k}_export_csr"] = (C.c_int, [_H, C.POINTER(C.c_int), C.POINTER(_I), C.POINTER(_I),
                                                        _HP, _HP, _HP, _HP])
+        p[f"alphasparse_{k}_export_csc"] = (C.c_int, [_H, C.POINTER(C.c_int), C.POINTER(_I), C.POINTER(_I),
+                                                       _HP, _HP, _HP, _HP])
     p["alphasparse_destroy"] = (C.c_int, [_H])
     p["alphasparse_convert_csr"] = (C.c_int, [_H, C.c_int, _HP])
+    p["alphasparse_convert_csc"] = (C.c_int, [_H, C.c_int, _HP])
     p["alphasparse_set_mv_hint"] = (C.c_int, [_H, C.c_int, MatrixDescr, _I])
     p["alphasparse_optimize"] = (C.c_int, [_H])
     # include/alphasparse/spapi_cuda.h

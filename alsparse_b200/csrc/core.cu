@@ -174,12 +174,14 @@ template <>
 struct CsrOf<float> {
     using csr = spmat_csr_s_t;
     using coo = spmat_coo_s_t;
+    using csc = spmat_csc_s_t;
     static constexpr alphasparse_datatype_t dt = ALPHA_SPARSE_DATATYPE_FLOAT;
 };
 template <>
 struct CsrOf<double> {
     using csr = spmat_csr_d_t;
     using coo = spmat_coo_d_t;
+    using csc = spmat_csc_d_t;
     static constexpr alphasparse_datatype_t dt = ALPHA_SPARSE_DATATYPE_DOUBLE;
 };
 
@@ -273,6 +275,48 @@ static alphasparse_status_t create_csr(alphasparse_matrix_t *A, alphasparse_inde
         val[i] = values[i];
     }
     return finish_csr_handle<T>(A, rows, cols, ptr, col, val);
+}
+
+// A CSC handle around `t`, the CSR handle of the transposed matrix (which it takes over): the CSC
+// record borrows t's host arrays -- cols_start / cols_end / row_indx / values of A are
+// rows_start / rows_end / col_indx / values of A^T -- and t itself sits in `inspector`.
+template <typename T>
+static alphasparse_status_t wrap_as_csc(alphasparse_matrix_t t, alphasparse_matrix_t *A) {
+    using M = typename CsrOf<T>::csc;
+    const typename CsrOf<T>::csr *tm = static_cast<const typename CsrOf<T>::csr *>(t->mat);
+    alphasparse_matrix *h = static_cast<alphasparse_matrix *>(calloc(1, sizeof(alphasparse_matrix)));
+    M *m = static_cast<M *>(calloc(1, sizeof(M)));
+    if (!h || !m) {
+        free(h), free(m);
+        alphasparse_destroy(t);
+        return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+    m->values = tm->values;
+    m->cols_start = tm->rows_start, m->cols_end = tm->rows_end;
+    m->row_indx = tm->col_indx;
+    m->rows = tm->cols, m->cols = tm->rows;
+    m->ordered = false;
+    h->mat = m;
+    h->format = ALPHA_SPARSE_FORMAT_CSC;
+    h->datatype = CsrOf<T>::dt;
+    h->inspector = t;
+    *A = h;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+// Reference semantics: src/core/format/alphasparse_x_create_csc.c:7-57 (deep copy; element count
+// cols_end[cols-1]; one-based input rebased).  That file copies cols_end over `rows` entries
+// (:35,46), which leaves offsets unset when cols > rows; here all `cols` entries are copied.
+template <typename T>
+static alphasparse_status_t create_csc(alphasparse_matrix_t *A, alphasparse_index_base_t indexing,
+                                       ALPHA_INT rows, ALPHA_INT cols, const ALPHA_INT *cols_start,
+                                       const ALPHA_INT *cols_end, const ALPHA_INT *row_indx, const T *values) {
+    if (!A) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    *A = nullptr;
+    alphasparse_matrix_t t = nullptr;
+    alphasparse_status_t s = create_csr<T>(&t, indexing, cols, rows, cols_start, cols_end, row_indx, values);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    return wrap_as_csc<T>(t, A);
 }
 
 // Reference semantics: src/core/format/alphasparse_x_create_coo.c:16-45 (deep copy, one-based
@@ -600,6 +644,9 @@ static alphasparse_status_t check_call(const alphasparse_matrix_t A, const void 
         } else if (A->format == ALPHA_SPARSE_FORMAT_COO) {
             const spmat_coo_s_t *m = static_cast<const spmat_coo_s_t *>(A->mat);
             r = m->rows, c = m->cols;
+        } else if (A->format == ALPHA_SPARSE_FORMAT_CSC) {
+            const spmat_csc_s_t *m = static_cast<const spmat_csc_s_t *>(A->mat);
+            r = m->rows, c = m->cols;
         }
         if (r != c) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
     }
@@ -611,7 +658,8 @@ static alphasparse_status_t check_call(const alphasparse_matrix_t A, const void 
             return ALPHA_SPARSE_STATUS_SUCCESS;
         return ALPHA_SPARSE_STATUS_INVALID_VALUE;
     }
-    if (A->format == ALPHA_SPARSE_FORMAT_COO) {  // served for GENERAL through a CSR copy (csr_shadow_of)
+    if (A->format == ALPHA_SPARSE_FORMAT_COO ||   // served for GENERAL through a CSR copy (csr_shadow_of)
+        (A->format == ALPHA_SPARSE_FORMAT_CSC && A->inspector)) {  // ... through the CSR handle of A^T
         if (descr.type == ALPHA_SPARSE_MATRIX_TYPE_GENERAL) return ALPHA_SPARSE_STATUS_SUCCESS;
         if (descr.type >= ALPHA_SPARSE_MATRIX_TYPE_SYMMETRIC && descr.type <= ALPHA_SPARSE_MATRIX_TYPE_DIAGONAL)
             return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
@@ -632,6 +680,10 @@ static alphasparse_status_t check_call(const alphasparse_matrix_t A, const void 
 static std::mutex g_shadow_mu;
 
 static alphasparse_status_t csr_shadow_of(const alphasparse_matrix_t A, alphasparse_matrix_t *out) {
+    if (A->format == ALPHA_SPARSE_FORMAT_CSC) {  // made at creation; the caller flips the operation
+        *out = static_cast<alphasparse_matrix_t>(A->inspector);
+        return ALPHA_SPARSE_STATUS_SUCCESS;
+    }
     std::lock_guard<std::mutex> lock(g_shadow_mu);
     if (!A->inspector) {
         alphasparse_matrix_t csr = nullptr;
@@ -738,7 +790,12 @@ static alphasparse_status_t mv(alphasparse_operation_t op, T alpha, alphasparse_
                                struct alpha_matrix_descr descr, const T *x, T beta, T *y) {
     alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-    if (A->format == ALPHA_SPARSE_FORMAT_COO) {
+    if (A->format != ALPHA_SPARSE_FORMAT_CSR) {
+        // A CSC matrix is held as the CSR of its transpose (src/core/op/level2/alphasparse_x_mv.c's CSC block
+        // runs gemv_csc / gemv_csc_trans, src/plain/kernel/level2/mv/gemv/gemv_x_csc[_trans]_plain.c: the
+        // same products in another summation order)
+        if (A->format == ALPHA_SPARSE_FORMAT_CSC)
+            op = op == ALPHA_SPARSE_OPERATION_NON_TRANSPOSE ? ALPHA_SPARSE_OPERATION_TRANSPOSE : ALPHA_SPARSE_OPERATION_NON_TRANSPOSE;
         s = csr_shadow_of(A, &A);
         if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     }
@@ -876,7 +933,9 @@ static alphasparse_status_t mm(alphasparse_operation_t op, T alpha, alphasparse_
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     if (layout != ALPHA_SPARSE_LAYOUT_ROW_MAJOR && layout != ALPHA_SPARSE_LAYOUT_COLUMN_MAJOR)
         return ALPHA_SPARSE_STATUS_INVALID_VALUE;
-    if (A->format == ALPHA_SPARSE_FORMAT_COO) {
+    if (A->format != ALPHA_SPARSE_FORMAT_CSR) {
+        if (A->format == ALPHA_SPARSE_FORMAT_CSC)  // held as the CSR of A^T (gemm_x_csc_{row,col}[_trans]_plain.c)
+            op = op == ALPHA_SPARSE_OPERATION_NON_TRANSPOSE ? ALPHA_SPARSE_OPERATION_TRANSPOSE : ALPHA_SPARSE_OPERATION_NON_TRANSPOSE;
         s = csr_shadow_of(A, &A);
         if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     }
@@ -980,6 +1039,29 @@ alphasparse_status_t alphasparse_z_create_csr(alphasparse_matrix_t *A, const alp
     return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
 }
 
+alphasparse_status_t alphasparse_s_create_csc(alphasparse_matrix_t *A, const alphasparse_index_base_t indexing,
+                                              const ALPHA_INT rows, const ALPHA_INT cols, ALPHA_INT *cols_start,
+                                              ALPHA_INT *cols_end, ALPHA_INT *row_indx, float *values) {
+    return create_csc<float>(A, indexing, rows, cols, cols_start, cols_end, row_indx, values);
+}
+alphasparse_status_t alphasparse_d_create_csc(alphasparse_matrix_t *A, const alphasparse_index_base_t indexing,
+                                              const ALPHA_INT rows, const ALPHA_INT cols, ALPHA_INT *cols_start,
+                                              ALPHA_INT *cols_end, ALPHA_INT *row_indx, double *values) {
+    return create_csc<double>(A, indexing, rows, cols, cols_start, cols_end, row_indx, values);
+}
+alphasparse_status_t alphasparse_c_create_csc(alphasparse_matrix_t *A, const alphasparse_index_base_t,
+                                              const ALPHA_INT, const ALPHA_INT, ALPHA_INT *, ALPHA_INT *,
+                                              ALPHA_INT *, ALPHA_Complex8 *) {
+    if (A) *A = nullptr;
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+}
+alphasparse_status_t alphasparse_z_create_csc(alphasparse_matrix_t *A, const alphasparse_index_base_t,
+                                              const ALPHA_INT, const ALPHA_INT, ALPHA_INT *, ALPHA_INT *,
+                                              ALPHA_INT *, ALPHA_Complex16 *) {
+    if (A) *A = nullptr;
+    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+}
+
 alphasparse_status_t alphasparse_s_create_coo(alphasparse_matrix_t *A, const alphasparse_index_base_t indexing,
                                               const ALPHA_INT rows, const ALPHA_INT cols, const ALPHA_INT nnz,
                                               ALPHA_INT *row_indx, ALPHA_INT *col_indx, float *values) {
@@ -1013,6 +1095,10 @@ alphasparse_status_t alphasparse_destroy(alphasparse_matrix_t A) {
         if (A->format == ALPHA_SPARSE_FORMAT_CSR) {
             if (A->datatype == ALPHA_SPARSE_DATATYPE_FLOAT) free_csr_host<float>(static_cast<spmat_csr_s_t *>(A->mat));
             else if (A->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE) free_csr_host<double>(static_cast<spmat_csr_d_t *>(A->mat));
+        } else if (A->format == ALPHA_SPARSE_FORMAT_CSC) {
+            alphasparse_destroy(static_cast<alphasparse_matrix_t>(A->inspector));  // owns the arrays the record borrows
+            A->inspector = nullptr;
+            free(A->mat);
         } else if (A->format == ALPHA_SPARSE_FORMAT_COO) {
             alphasparse_destroy(static_cast<alphasparse_matrix_t>(A->inspector));  // the CSR copy mv / mm made, if any
             A->inspector = nullptr;
@@ -1061,6 +1147,48 @@ alphasparse_status_t alphasparse_convert_csr(const alphasparse_matrix_t source, 
 ASB_EXPORT(float, s, ALPHA_SPARSE_DATATYPE_FLOAT)
 ASB_EXPORT(double, d, ALPHA_SPARSE_DATATYPE_DOUBLE)
 
+// Reference: src/core/format/alphasparse_x_export_csc.c:5-25.
+#define ASB_EXPORT_CSC(T, sfx, DT)                                                                          \
+    alphasparse_status_t alphasparse_##sfx##_export_csc(                                                    \
+        const alphasparse_matrix_t source, alphasparse_index_base_t *indexing, ALPHA_INT *rows,             \
+        ALPHA_INT *cols, ALPHA_INT **cols_start, ALPHA_INT **cols_end, ALPHA_INT **row_indx, T **values) {  \
+        if (!source) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;                                            \
+        if (!source->mat) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;                                         \
+        if (source->datatype != DT) return ALPHA_SPARSE_STATUS_INVALID_VALUE;                               \
+        if (source->format != ALPHA_SPARSE_FORMAT_CSC) return ALPHA_SPARSE_STATUS_INVALID_VALUE;            \
+        spmat_csc_##sfx##_t *m = static_cast<spmat_csc_##sfx##_t *>(source->mat);                           \
+        *indexing = ALPHA_SPARSE_INDEX_BASE_ZERO;                                                           \
+        *rows = m->rows, *cols = m->cols;                                                                   \
+        *cols_start = m->cols_start, *cols_end = m->cols_end;                                               \
+        *row_indx = m->row_indx, *values = m->values;                                                       \
+        return ALPHA_SPARSE_STATUS_SUCCESS;                                                                 \
+    }
+ASB_EXPORT_CSC(float, s, ALPHA_SPARSE_DATATYPE_FLOAT)
+ASB_EXPORT_CSC(double, d, ALPHA_SPARSE_DATATYPE_DOUBLE)
+
+// Reference: src/core/op_/alphasparse_convert_csc.c:101-150 (only a COO source) ->
+// src/core/format/convert_csc_x_coo.c.  CSC of op(A) = CSR arrays of op(A)^T: the COO->CSR conversion
+// with the opposite transposition, wrapped.
+alphasparse_status_t alphasparse_convert_csc(const alphasparse_matrix_t source, const alphasparse_operation_t operation,
+                                             alphasparse_matrix_t *dest) {
+    if (!source || !source->mat) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    if (!dest) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    *dest = nullptr;
+    if (operation == ALPHA_SPARSE_OPERATION_CONJUGATE_TRANSPOSE) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    if (operation != ALPHA_SPARSE_OPERATION_NON_TRANSPOSE && operation != ALPHA_SPARSE_OPERATION_TRANSPOSE)
+        return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    if (source->format != ALPHA_SPARSE_FORMAT_COO) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    const bool tr = operation == ALPHA_SPARSE_OPERATION_TRANSPOSE;
+    alphasparse_matrix_t t = nullptr;
+    alphasparse_status_t s = ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    if (source->datatype == ALPHA_SPARSE_DATATYPE_FLOAT)
+        s = coo_to_csr<float>(static_cast<const spmat_coo_s_t *>(source->mat), !tr, &t);
+    else if (source->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE)
+        s = coo_to_csr<double>(static_cast<const spmat_coo_d_t *>(source->mat), !tr, &t);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    return source->datatype == ALPHA_SPARSE_DATATYPE_FLOAT ? wrap_as_csc<float>(t, dest) : wrap_as_csc<double>(t, dest);
+}
+
 alphasparse_status_t alphasparse_set_mv_hint(const alphasparse_matrix_t A, const alphasparse_operation_t,
                                              const struct alpha_matrix_descr, const ALPHA_INT) {
     return A ? ALPHA_SPARSE_STATUS_SUCCESS : ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
@@ -1068,7 +1196,8 @@ alphasparse_status_t alphasparse_set_mv_hint(const alphasparse_matrix_t A, const
 
 alphasparse_status_t alphasparse_optimize(alphasparse_matrix_t A) {
     if (!A || !A->mat) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
-    if (A->format == ALPHA_SPARSE_FORMAT_COO) {  // builds (or re-analyses) the CSR copy that mv / mm will use
+    if (A->format == ALPHA_SPARSE_FORMAT_COO || (A->format == ALPHA_SPARSE_FORMAT_CSC && A->inspector)) {
+        // builds (or re-analyses) the CSR handle that mv / mm use for this matrix
         alphasparse_status_t s = csr_shadow_of(A, &A);
         if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     }

@@ -94,6 +94,48 @@ def export_csr(kind, source):
             view(v, nnz, ct))
 
 
+def create_csc(kind, indexing, rows, cols, cols_start, cols_end, row_indx, values):
+    """alphasparse_{s,d}_create_csc.  Returns (status, handle)."""
+    lib = capi.load()
+    cs, ce, ri = _i32(cols_start), _i32(cols_end), _i32(row_indx)
+    v = None if values is None else np.ascontiguousarray(values, dtype=_NP.get(kind, np.float32))
+    h = C.c_void_p()
+    st = getattr(lib, f"alphasparse_{kind}_create_csc")(C.byref(h), indexing, rows, cols, _ptr(cs), _ptr(ce),
+                                                         _ptr(ri), _ptr(v))
+    return st, h
+
+
+def convert_csc(source, operation=capi.NON_TRANSPOSE):
+    """alphasparse_convert_csc (COO source).  Returns (status, handle)."""
+    h = C.c_void_p()
+    st = capi.load().alphasparse_convert_csc(source, operation, C.byref(h))
+    return st, h
+
+
+def export_csc(kind, source):
+    """alphasparse_{s,d}_export_csc.  Returns (status, base, rows, cols, cols_start, cols_end, row_indx, values)
+    as borrowed numpy views, like export_csr."""
+    lib = capi.load()
+    base, rows, cols = C.c_int(), C.c_int32(), C.c_int32()
+    cs, ce, ri, v = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_void_p()
+    st = getattr(lib, f"alphasparse_{kind}_export_csc")(source, C.byref(base), C.byref(rows), C.byref(cols),
+                                                         C.byref(cs), C.byref(ce), C.byref(ri), C.byref(v))
+    if st != SUCCESS:
+        return (st,) + (None,) * 7
+    n = cols.value
+
+    def view(p, k, ct):
+        if k == 0 or not p.value:
+            return np.zeros(0, dtype=np.dtype(ct))
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(ct)), shape=(k,))
+
+    ptr = view(cs, n + 1, C.c_int32)
+    nnz = int(ptr[n] - ptr[0]) if n > 0 else 0
+    ct = C.c_float if kind == "s" else C.c_double
+    return (st, base.value, rows.value, n, ptr[:n], ptr[1:n + 1] if n > 0 else ptr[:0], view(ri, nnz, C.c_int32),
+            view(v, nnz, ct))
+
+
 def destroy(handle):
     return capi.load().alphasparse_destroy(handle)
 

@@ -15,10 +15,10 @@
  * TRANSPOSE has no entry there and is NOT_SUPPORTED here too).
  *
  * A COO handle may be given to mv / mm directly with a GENERAL descriptor: the product runs on a CSR
- * copy converted on first use and kept with the handle.
+ * copy converted on first use and kept with the handle.  CSC handles: see the CSC group below.
  *
- * What is not served.  Complex precisions (and so HERMITIAN), structured descriptors on a COO handle
- * and formats other than CSR and COO return ALPHA_SPARSE_STATUS_NOT_SUPPORTED after the argument
+ * What is not served.  Complex precisions (and so HERMITIAN), structured descriptors on a COO or CSC
+ * handle and formats other than CSR, COO and CSC return ALPHA_SPARSE_STATUS_NOT_SUPPORTED after the argument
  * checks: there is no CPU fallback.
  */
 #include "types.h"
@@ -96,6 +96,45 @@ alphasparse_status_t alphasparse_d_export_csr(const alphasparse_matrix_t source,
                                               ALPHA_INT *rows, ALPHA_INT *cols,
                                               ALPHA_INT **rows_start, ALPHA_INT **rows_end,
                                               ALPHA_INT **col_indx, double **values);
+
+/* ---- CSC handles: reference spapi.h:186-220 (create), :388-422 (export), :17-19 (convert; COO source
+ * only, as in src/core/op_/alphasparse_convert_csc.c:101-123).  The arrays of a CSC matrix are the
+ * CSR arrays of its transpose: the handle keeps a CSR handle of A^T (host copy, device copy,
+ * analysis) in its `inspector` slot, mv / mm run on it with the operation flipped, and export_csc
+ * returns that handle's host arrays.  GENERAL descriptor only. ------------------------------------ */
+alphasparse_status_t alphasparse_s_create_csc(alphasparse_matrix_t *A,
+                                              const alphasparse_index_base_t indexing,
+                                              const ALPHA_INT rows, const ALPHA_INT cols,
+                                              ALPHA_INT *cols_start, ALPHA_INT *cols_end,
+                                              ALPHA_INT *row_indx, float *values);
+alphasparse_status_t alphasparse_d_create_csc(alphasparse_matrix_t *A,
+                                              const alphasparse_index_base_t indexing,
+                                              const ALPHA_INT rows, const ALPHA_INT cols,
+                                              ALPHA_INT *cols_start, ALPHA_INT *cols_end,
+                                              ALPHA_INT *row_indx, double *values);
+alphasparse_status_t alphasparse_c_create_csc(alphasparse_matrix_t *A,
+                                              const alphasparse_index_base_t indexing,
+                                              const ALPHA_INT rows, const ALPHA_INT cols,
+                                              ALPHA_INT *cols_start, ALPHA_INT *cols_end,
+                                              ALPHA_INT *row_indx, ALPHA_Complex8 *values);
+alphasparse_status_t alphasparse_z_create_csc(alphasparse_matrix_t *A,
+                                              const alphasparse_index_base_t indexing,
+                                              const ALPHA_INT rows, const ALPHA_INT cols,
+                                              ALPHA_INT *cols_start, ALPHA_INT *cols_end,
+                                              ALPHA_INT *row_indx, ALPHA_Complex16 *values);
+alphasparse_status_t alphasparse_s_export_csc(const alphasparse_matrix_t source,
+                                              alphasparse_index_base_t *indexing,
+                                              ALPHA_INT *rows, ALPHA_INT *cols,
+                                              ALPHA_INT **cols_start, ALPHA_INT **cols_end,
+                                              ALPHA_INT **row_indx, float **values);
+alphasparse_status_t alphasparse_d_export_csc(const alphasparse_matrix_t source,
+                                              alphasparse_index_base_t *indexing,
+                                              ALPHA_INT *rows, ALPHA_INT *cols,
+                                              ALPHA_INT **cols_start, ALPHA_INT **cols_end,
+                                              ALPHA_INT **row_indx, double **values);
+alphasparse_status_t alphasparse_convert_csc(const alphasparse_matrix_t source,
+                                             const alphasparse_operation_t operation,
+                                             alphasparse_matrix_t *dest);
 
 /* ---- hints: reference spapi.h:615-671 (declared there, defined nowhere).  Here
  * alphasparse_optimize re-runs the analysis; the hints are accepted and ignored. ----------- */

@@ -81,7 +81,8 @@ typedef void *alpha_internal_spmat;
 /*
  * The handle.  `mat` points at an spmat_csr_?_t or spmat_coo_?_t (alphasparse/spmat.h).
  * `inspector` of a COO handle holds the CSR copy that mv / mm build on first use (NULL until
- * then, and always NULL on a CSR handle).  `dcu_info` is the slot the reference reserves for
+ * then); of a CSC handle, the CSR handle of the transposed matrix made at creation; it is always
+ * NULL on a CSR handle.  `dcu_info` is the slot the reference reserves for
  * per-matrix device analysis; this backend stores its own device context there (device CSR
  * arrays, row statistics, load-balancing tables, staging buffers).  Both are NULL-initialised
  * by every create call; callers only ever hold the pointer.

@@ -62,6 +62,9 @@ def lib():
             getattr(L, f"oracle_gemv_coo_{k}").argtypes = [C.c_int, _i32, _i32, _i32, _p, _p, _p, T, _p, T, _p]
             getattr(L, f"oracle_gemm_coo_{k}").argtypes = [C.c_int, C.c_int, _i32, _i32, _i32, _p, _p, _p, T, _p, _i32,
                                                             _i32, T, _p, _i32]
+            getattr(L, f"oracle_gemv_csc_{k}").argtypes = [C.c_int, _i32, _i32, _p, _p, _p, _p, T, _p, T, _p]
+            getattr(L, f"oracle_gemm_csc_{k}").argtypes = [C.c_int, C.c_int, _i32, _i32, _p, _p, _p, _p, T, _p, _i32,
+                                                            _i32, T, _p, _i32]
             getattr(L, f"oracle_create_csr_{k}").argtypes = [_i32, _i32, _p, _p, _p, _p, _p, _p, _p]
             getattr(L, f"oracle_create_csr_{k}").restype = _i32
             getattr(L, f"oracle_coo_to_csr_{k}").argtypes = [_i32, _i32, _i32, _p, _p, _p, _p, _p, _p]
@@ -151,6 +154,21 @@ def gemm_coo(kind, trans, layout, rows, cols, row_indx, col_indx, val, alpha, X,
     return Y
 
 
+def gemv_csc(kind, trans, rows, cols, cols_start, cols_end, row_indx, val, alpha, x, beta, y):
+    """mv on a CSC matrix (zero-based); y modified in place."""
+    cs, ce, ri = _i(cols_start), _i(cols_end), _i(row_indx)
+    getattr(lib(), f"oracle_gemv_csc_{kind}")(int(trans), rows, cols, _a(cs), _a(ce), _a(ri), _a(val), alpha, _a(x),
+                                               beta, _a(y))
+    return y
+
+
+def gemm_csc(kind, trans, layout, rows, cols, cols_start, cols_end, row_indx, val, alpha, X, columns, ldx, beta, Y, ldy):
+    cs, ce, ri = _i(cols_start), _i(cols_end), _i(row_indx)
+    getattr(lib(), f"oracle_gemm_csc_{kind}")(int(trans), int(layout == "col"), rows, cols, _a(cs), _a(ce), _a(ri),
+                                               _a(val), alpha, _a(X), columns, ldx, beta, _a(Y), ldy)
+    return Y
+
+
 def create_csr(kind, base, rows_start, rows_end, col, val):
     """(offsets[rows+1], col[nnz], val[nnz]) as the reference's create_csr would store them."""
     rs, re_, ci = _i(rows_start), _i(rows_end), _i(col)
@@ -230,6 +248,10 @@ def ref():
             for name in (f"gemv_{k}_coo_plain", f"gemv_{k}_coo_trans_plain"):
                 getattr(L, name).argtypes = [T, _p, _p, T, _p]
             for name in [f"gemm_{k}_coo_{lay}{t}_plain" for lay in ("row", "col") for t in ("", "_trans")]:
+                getattr(L, name).argtypes = [T, _p, _p, _i32, _i32, T, _p, _i32]
+            for name in (f"gemv_{k}_csc_plain", f"gemv_{k}_csc_trans_plain"):
+                getattr(L, name).argtypes = [T, _p, _p, T, _p]
+            for name in [f"gemm_{k}_csc_{lay}{t}_plain" for lay in ("row", "col") for t in ("", "_trans")]:
                 getattr(L, name).argtypes = [T, _p, _p, _i32, _i32, T, _p, _i32]
             getattr(L, f"alphasparse_{k}_export_csr").argtypes = [_p] * 8
         L.balanced_partition_row_by_nnz.argtypes = [_p, _i32, _i32, _p]
@@ -358,6 +380,35 @@ class RefCoo:
     def gemm(self, trans, layout, alpha, X, columns, ldx, beta, Y, ldy):
         st = getattr(ref(), f"gemm_{self.kind}_coo_{layout}{'_trans' if trans else ''}_plain")(
             alpha, self.mat, _a(X), columns, ldx, beta, _a(Y), ldy)
+        assert st == 0
+        return Y
+
+
+class _CscRecord(C.Structure):
+    """spmat_csc_?_t of the reference (include/alphasparse/spmat.h:288-297, :311-320)."""
+    _fields_ = [("values", C.c_void_p), ("cols_start", C.c_void_p), ("cols_end", C.c_void_p), ("row_indx", C.c_void_p),
+                ("rows", C.c_int32), ("cols", C.c_int32), ("ordered", C.c_bool)]
+
+
+class RefCsc:
+    """A CSC record laid out for the reference's kernels.  Built here rather than by the reference's create_csc,
+    which copies only `rows` of the `cols` column offsets (src/core/format/alphasparse_x_create_csc.c:35)."""
+
+    def __init__(self, kind, rows, cols, cols_start, cols_end, row_indx, val):
+        self.kind = kind
+        self._keep = (_i(cols_start), _i(cols_end), _i(row_indx), np.ascontiguousarray(val, dtype=_NP[kind]))
+        cs, ce, ri, v = self._keep
+        self.rec = _CscRecord(_a(v), _a(cs), _a(ce), _a(ri), rows, cols, False)
+
+    def gemv(self, trans, alpha, x, beta, y):
+        st = getattr(ref(), f"gemv_{self.kind}_csc{'_trans' if trans else ''}_plain")(alpha, C.addressof(self.rec), _a(x),
+                                                                                    beta, _a(y))
+        assert st == 0
+        return y
+
+    def gemm(self, trans, layout, alpha, X, columns, ldx, beta, Y, ldy):
+        st = getattr(ref(), f"gemm_{self.kind}_csc_{layout}{'_trans' if trans else ''}_plain")(
+            alpha, C.addressof(self.rec), _a(X), columns, ldx, beta, _a(Y), ldy)
         assert st == 0
         return Y
 

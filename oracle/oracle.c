@@ -569,3 +569,59 @@ DEF_STRUCT_MM(double, d)
     }
 DEF_COO(float, s)
 DEF_COO(double, d)
+
+/* ---------------------------------------------------------------------------------------
+ * A CSC handle in mv / mm with a GENERAL descriptor (the CSC blocks of alphasparse_x_mv.c and
+ * alphasparse_x_mm.c).  Arrays: cs/ce column offsets, ri row indices.
+ *   src/plain/kernel/level2/mv/gemv/gemv_x_csc_plain.c: y scaled by beta, then column by column every
+ *   element adds alpha*(a*x[col]) to y[row]; gemv_x_csc_trans_plain.c: per column a dot product with
+ *   x[row], times alpha, added to beta*y[col].
+ *   src/plain/kernel/level3/mm/gemm/gemm_x_csc_row_plain.c / _col_plain.c: Y scaled by beta, then every
+ *   element adds (alpha*a)*X[col,:] to Y[row,:] in column order; the transposed kernels materialise
+ *   the CSC of A^T (transpose_csc) and run the same loops on it.
+ * ------------------------------------------------------------------------------------- */
+#define DEF_CSC(T, sfx)                                                                       \
+    void oracle_gemv_csc_##sfx(int trans, aint rows, aint cols, const aint *cs, const aint *ce, \
+                               const aint *ri, const T *val, T alpha, const T *x, T beta,     \
+                               T *y) {                                                        \
+        if (!trans) {                                                                         \
+            for (aint j = 0; j < rows; j++) y[j] = y[j] * beta;                               \
+            for (aint c = 0; c < cols; c++)                                                   \
+                for (aint k = cs[c]; k < ce[c]; k++) {                                        \
+                    T t = val[k] * x[c];                                                      \
+                    t = alpha * t;                                                            \
+                    y[ri[k]] = y[ri[k]] + t;                                                  \
+                }                                                                             \
+        } else {                                                                              \
+            for (aint c = 0; c < cols; c++) {                                                 \
+                T t = (T)0;                                                                   \
+                y[c] = y[c] * beta;                                                           \
+                for (aint k = cs[c]; k < ce[c]; k++) t = t + val[k] * x[ri[k]];               \
+                t = alpha * t;                                                                \
+                y[c] = y[c] + t;                                                              \
+            }                                                                                 \
+        }                                                                                     \
+    }                                                                                         \
+    void oracle_gemm_csc_##sfx(int trans, int col_major, aint rows, aint cols, const aint *cs, \
+                               const aint *ce, const aint *ri, const T *val, T alpha,         \
+                               const T *x, aint columns, aint ldx, T beta, T *y, aint ldy) {  \
+        /* op(A) is m x n; with trans the roles of stored column and row index swap, and the   \
+           reference walks A^T's columns (A's rows) in order: same sums, another order */      \
+        const aint m = trans ? cols : rows;                                                   \
+        for (aint r = 0; r < m; r++)                                                          \
+            for (aint c = 0; c < columns; c++) {                                              \
+                T *out = col_major ? &y[(size_t)c * ldy + r] : &y[(size_t)r * ldy + c];       \
+                *out = *out * beta;                                                           \
+            }                                                                                 \
+        for (aint c = 0; c < cols; c++)                                                       \
+            for (aint k = cs[c]; k < ce[c]; k++) {                                            \
+                const aint out_r = trans ? c : ri[k], in_r = trans ? ri[k] : c;               \
+                const T av = alpha * val[k];                                                  \
+                for (aint d = 0; d < columns; d++) {                                          \
+                    if (col_major) y[(size_t)d * ldy + out_r] += av * x[(size_t)d * ldx + in_r]; \
+                    else y[(size_t)out_r * ldy + d] += av * x[(size_t)in_r * ldx + d];        \
+                }                                                                             \
+            }                                                                                 \
+    }
+DEF_CSC(float, s)
+DEF_CSC(double, d)

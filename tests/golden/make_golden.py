@@ -160,6 +160,25 @@ def main():
         out[f"Yc_o{tr}"] = K.gemm(tr, "col", 1.25, Xc, columns, m_in + 2, -0.75, Yc.copy(), m_out + 1)
     np.savez_compressed(os.path.join(OUT, "coo_d.npz"), **out)
 
+    # -- a CSC handle in mv / mm: the reference's plain gemv_csc / gemm_csc kernels on a matrix with more columns
+    #    than rows (one-based input to the product library) ------------------------------------------------
+    rows_c, cols_c = 130, 170
+    t = synth.poisson("d", 19, cols_c, rows_c, 5.0)            # the CSR of A^T holds the CSC arrays of A
+    Kc = oracle.RefCsc("d", rows_c, cols_c, t.ptr[:-1], t.ptr[1:], t.col, t.val)
+    columns, ldx, ldy = 6, 8, 7
+    out = dict(ptr=t.ptr, ri=t.col, val=t.val, rows=rows_c, cols=cols_c, alpha=1.25, beta=-0.75,
+               par=np.array([columns, ldx, ldy]))
+    for tr, m_out, m_in in ((0, rows_c, cols_c), (1, cols_c, rows_c)):
+        xk, yk = synth.vector("d", 19, 1 + tr, m_in), synth.vector("d", 19, 3 + tr, m_out)
+        out[f"x_o{tr}"], out[f"y0_o{tr}"] = xk, yk
+        out[f"y_o{tr}"] = Kc.gemv(tr, 1.25, xk, -0.75, yk.copy())
+        Xr, Yr = synth.vector("d", 19, 5 + tr, m_in * ldx), synth.vector("d", 19, 7 + tr, m_out * ldy)
+        Xc, Yc = synth.vector("d", 19, 9 + tr, (m_in + 2) * columns), synth.vector("d", 19, 11 + tr, (m_out + 1) * columns)
+        out[f"Xr_o{tr}"], out[f"Yr0_o{tr}"], out[f"Xc_o{tr}"], out[f"Yc0_o{tr}"] = Xr, Yr, Xc, Yc
+        out[f"Yr_o{tr}"] = Kc.gemm(tr, "row", 1.25, Xr, columns, ldx, -0.75, Yr.copy(), ldy)
+        out[f"Yc_o{tr}"] = Kc.gemm(tr, "col", 1.25, Xc, columns, m_in + 2, -0.75, Yc.copy(), m_out + 1)
+    np.savez_compressed(os.path.join(OUT, "csc_d.npz"), **out)
+
     # -- nnz-balanced row partition: known answers incl. the quirks ---------------------------------
     cases = {}
     accs = {"tiny": np.array([2, 3, 4], np.int32), "cfg1": m.ptr[1:], "zipf": z.ptr[1:],

@@ -528,3 +528,81 @@ def test_large_transpose_keeps_the_reference_order(kind):
     assert torch.equal(dy, dy2)
     spblas.destroy(A)
     spblas.destroy(B)
+
+
+def test_csc_handle_in_mv_and_mm():
+    """A CSC handle (created from one-based arrays, more columns than rows) in mv / mm: both operations and both
+    dense layouts against the reference's plain CSC kernels (golden vectors); export_csc; convert_csc from COO."""
+    g = golden("csc_d.npz")
+    ptr, ri, val, a, b = g["ptr"], g["ri"], g["val"], float(g["alpha"]), float(g["beta"])
+    rows, cols = int(g["rows"]), int(g["cols"])
+    columns, ldx, ldy = (int(v) for v in g["par"])
+    st, A = spblas.create_csc("d", capi.BASE_ONE, rows, cols, ptr[:-1] + 1, ptr[1:] + 1, ri + 1, val)
+    assert st == capi.SUCCESS, spblas.last_error()
+    st, base, er, ec, cs, ce, eri, ev = spblas.export_csc("d", A)
+    assert (st, base, er, ec) == (capi.SUCCESS, 0, rows, cols)
+    assert np.array_equal(cs, ptr[:-1]) and np.array_equal(ce, ptr[1:]) and np.array_equal(eri, ri) and np.array_equal(ev, val)
+    cid = np.repeat(np.arange(cols), np.diff(ptr))
+
+    def scale(m_out, r, c, X, Y0):
+        out = np.zeros((m_out, X.shape[1]))
+        np.add.at(out, r, np.abs(val)[:, None] * np.abs(X)[c])
+        return (np.abs(b * Y0) + abs(a) * out).reshape(-1)
+
+    for tr in (0, 1):
+        m_out, m_in = (cols, rows) if tr else (rows, cols)
+        r, c = (cid, ri) if tr else (ri, cid)
+        x, y0 = g[f"x_o{tr}"], g[f"y0_o{tr}"]
+        for dev in (False, True):
+            if dev:
+                dx, dy = torch.from_numpy(x).cuda(), torch.from_numpy(y0).cuda()
+                assert spblas.mv("d", tr, a, A, spblas.descr(), dx, b, dy) == capi.SUCCESS
+                y = dy.cpu().numpy()
+            else:
+                y = y0.copy()
+                assert spblas.mv("d", tr, a, A, spblas.descr(), x, b, y) == capi.SUCCESS, spblas.last_error()
+            assert_rows_close("d", y, g[f"y_o{tr}"], scale(m_out, r, c, x[:, None], y0[:, None]), f"csc mv op {tr}")
+        Xr, Yr0 = g[f"Xr_o{tr}"], g[f"Yr0_o{tr}"]
+        Y = Yr0.copy()
+        assert spblas.mm("d", tr, a, A, spblas.descr(), capi.ROW_MAJOR, Xr, columns, ldx, b, Y, ldy) == capi.SUCCESS
+        view = lambda v: v.reshape(m_out, ldy)[:, :columns]  # noqa: E731
+        assert_rows_close("d", view(Y).reshape(-1), view(g[f"Yr_o{tr}"]).reshape(-1),
+                          scale(m_out, r, c, Xr.reshape(m_in, ldx)[:, :columns], view(Yr0)), f"csc mm row op {tr}")
+        assert np.array_equal(Y.reshape(m_out, ldy)[:, columns:], Yr0.reshape(m_out, ldy)[:, columns:])
+        lx, ly = m_in + 2, m_out + 1
+        Xc, Yc0 = g[f"Xc_o{tr}"], g[f"Yc0_o{tr}"]
+        dX, dY = torch.from_numpy(Xc).cuda(), torch.from_numpy(Yc0).cuda()
+        assert spblas.mm("d", tr, a, A, spblas.descr(), capi.COLUMN_MAJOR, dX, columns, lx, b, dY, ly) == capi.SUCCESS
+        viewc = lambda v: v.reshape(columns, ly)[:, :m_out].T  # noqa: E731
+        assert_rows_close("d", viewc(dY.cpu().numpy()).reshape(-1), viewc(g[f"Yc_o{tr}"]).reshape(-1),
+                          scale(m_out, r, c, Xc.reshape(columns, lx)[:, :m_in].T, viewc(Yc0)), f"csc mm col op {tr}")
+    x, y = g["x_o0"], g["y0_o0"].copy()
+    assert spblas.mv("s", 0, 1.0, A, spblas.descr(), x, 0.0, y) == capi.INVALID_VALUE
+    assert spblas.mv("d", 0, a, A, spblas.descr(capi.SYMMETRIC), x, b, y) == capi.INVALID_VALUE      # 130 x 170
+    assert spblas.mv("d", 0, a, A, spblas.descr(capi.DIAGONAL), x, b, y) == capi.NOT_SUPPORTED
+    assert np.array_equal(y, g["y0_o0"])
+    assert spblas.destroy(A) == capi.SUCCESS
+
+    # COO -> CSC, as is and transposed: column-major sorted arrays of op(A), and products that agree with the COO handle's
+    m = synth.poisson("s", 93, 700, 900, 7.0)
+    rng = np.random.default_rng(93)
+    perm = rng.permutation(m.nnz)
+    cri = np.repeat(np.arange(m.nrows, dtype=np.int32), np.diff(m.ptr))[perm]
+    cci, cv = m.col[perm], m.val[perm]
+    st, coo = spblas.create_coo("s", capi.BASE_ZERO, m.nrows, m.cols, m.nnz, cri, cci, cv)
+    for op, orows, ocols, oi, oj in ((capi.NON_TRANSPOSE, m.nrows, m.cols, cri, cci), (capi.TRANSPOSE, m.cols, m.nrows, cci, cri)):
+        st, B = spblas.convert_csc(coo, op)
+        assert st == capi.SUCCESS, spblas.last_error()
+        st, base, er, ec, cs, ce, eri, ev = spblas.export_csc("s", B)
+        assert (st, er, ec) == (capi.SUCCESS, orows, ocols)
+        order = np.lexsort((np.arange(m.nnz), oi, oj))           # by column, then row, then stored position
+        assert np.array_equal(eri, oi[order]) and np.array_equal(ev, cv[order])
+        assert np.array_equal(np.concatenate([cs[:1], ce]), np.concatenate([[0], np.cumsum(np.bincount(oj, minlength=ocols))]))
+        x, y0 = synth.vector("s", 93, 1, ocols), synth.vector("s", 93, 2, orows)
+        y_ref = oracle.gemv_coo("s", 0, orows, ocols, oi, oj, cv, 1.5, x, 0.5, y0.copy())
+        y = y0.copy()
+        assert spblas.mv("s", 0, 1.5, B, spblas.descr(), x, 0.5, y) == capi.SUCCESS
+        sc = np.abs(0.5 * y0.astype(np.float64)) + 1.5 * np.bincount(oi, weights=np.abs(cv.astype(np.float64) * x[oj]), minlength=orows)
+        assert_rows_close("s", y, y_ref, sc, f"converted csc op {op}")
+        spblas.destroy(B)
+    spblas.destroy(coo)

@@ -153,6 +153,36 @@ def test_coo_products_golden():
                           g[f"Yc_o{tr}"].reshape(columns, ly)[:, :m_out].T.reshape(-1), sc.reshape(-1), f"coo mm col op {tr}")
 
 
+def test_csc_products_golden():
+    """gemv_csc / gemm_csc restatements (both operations and layouts) against the reference's plain kernels on a
+    matrix with more columns than rows."""
+    g = golden("csc_d.npz")
+    ptr, ri, val, a, b = g["ptr"], g["ri"], g["val"], float(g["alpha"]), float(g["beta"])
+    rows, cols = int(g["rows"]), int(g["cols"])
+    columns, ldx, ldy = (int(v) for v in g["par"])
+    cid = np.repeat(np.arange(cols), np.diff(ptr))
+    for tr in (0, 1):
+        m_out, m_in = (cols, rows) if tr else (rows, cols)
+        r, c = (cid, ri) if tr else (ri, cid)
+        y = oracle.gemv_csc("d", tr, rows, cols, ptr[:-1], ptr[1:], ri, val, a, g[f"x_o{tr}"], b, g[f"y0_o{tr}"].copy())
+        sc = coo_scale(m_out, r, c, val, g[f"x_o{tr}"][:, None], g[f"y0_o{tr}"][:, None], a, b)
+        assert_rows_close("d", y, g[f"y_o{tr}"], sc.reshape(-1), f"csc mv op {tr}")
+        Y = oracle.gemm_csc("d", tr, "row", rows, cols, ptr[:-1], ptr[1:], ri, val, a, g[f"Xr_o{tr}"], columns, ldx, b,
+                            g[f"Yr0_o{tr}"].copy(), ldy)
+        sc = coo_scale(m_out, r, c, val, g[f"Xr_o{tr}"].reshape(m_in, ldx)[:, :columns],
+                       g[f"Yr0_o{tr}"].reshape(m_out, ldy)[:, :columns], a, b)
+        assert_rows_close("d", Y.reshape(m_out, ldy)[:, :columns].reshape(-1),
+                          g[f"Yr_o{tr}"].reshape(m_out, ldy)[:, :columns].reshape(-1), sc.reshape(-1), f"csc mm row op {tr}")
+        assert np.array_equal(Y.reshape(m_out, ldy)[:, columns:], g[f"Yr0_o{tr}"].reshape(m_out, ldy)[:, columns:])
+        lx, ly = m_in + 2, m_out + 1
+        Y = oracle.gemm_csc("d", tr, "col", rows, cols, ptr[:-1], ptr[1:], ri, val, a, g[f"Xc_o{tr}"], columns, lx, b,
+                            g[f"Yc0_o{tr}"].copy(), ly)
+        sc = coo_scale(m_out, r, c, val, g[f"Xc_o{tr}"].reshape(columns, lx)[:, :m_in].T,
+                       g[f"Yc0_o{tr}"].reshape(columns, ly)[:, :m_out].T, a, b)
+        assert_rows_close("d", Y.reshape(columns, ly)[:, :m_out].T.reshape(-1),
+                          g[f"Yc_o{tr}"].reshape(columns, ly)[:, :m_out].T.reshape(-1), sc.reshape(-1), f"csc mm col op {tr}")
+
+
 def test_coo_to_csr_golden():
     g = golden("cfg1_s.npz")
     ptr, col, val = oracle.coo_to_csr("s", 1, 1000, g["coo_ri"] + 1, g["coo_ci"] + 1, g["coo_v"])
