@@ -99,6 +99,7 @@ def prototypes():
     p["alphasparse_cuda_exchange_connect"] = (C.c_int, [_H, _P])
     p["alphasparse_cuda_exchange_set_mode"] = (C.c_int, [_H, C.c_int])
     p["alphasparse_cuda_exchange_x"] = (C.c_int, [_H, _HP])
+    p["alphasparse_cuda_exchange_load_x"] = (C.c_int, [_H, _P])
     p["alphasparse_cuda_exchange_status"] = (C.c_int, [_H, C.POINTER(C.c_int)])
     p["alphasparse_cuda_exchange_debug_wait"] = (C.c_int, [_H, C.c_int64])
     p["alphasparse_cuda_exchange_clear_status"] = (C.c_int, [_H])

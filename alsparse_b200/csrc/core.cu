@@ -699,7 +699,7 @@ static alphasparse_status_t csr_shadow_of(const alphasparse_matrix_t A, alphaspa
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
-// Host x and host y on a large matrix: the product runs in kPipelineChunks row windows (4 -> 8 windows
+// Host y (and host or device x) on a large matrix: the product runs in kPipelineChunks row windows (4 -> 8 windows
 // took uniform16 end to end from 3.14 to 2.90 ms on B200, 16 changed nothing) so that
 // PCIe and the kernel overlap.  Three streams: x and the y0 pieces go in on one, the windows run
 // on the library stream as their inputs land, every finished piece of y leaves on the third
@@ -719,23 +719,27 @@ static alphasparse_status_t ensure_pipe(DeviceCtx *c) {
 }
 
 template <typename T>
-static alphasparse_status_t mv_host_pipelined(DeviceCtx *c, T alpha, const T *x, T beta, T *y, cudaStream_t st) {
-    alphasparse_status_t s = grow(&c->d_x_stage, &c->x_stage_bytes, sizeof(T) * (size_t)c->cols, c);
+static alphasparse_status_t mv_host_pipelined(DeviceCtx *c, T alpha, const T *x, bool x_dev, T beta, T *y,
+                                              cudaStream_t st) {
+    alphasparse_status_t s = ALPHA_SPARSE_STATUS_SUCCESS;
+    if (!x_dev) s = grow(&c->d_x_stage, &c->x_stage_bytes, sizeof(T) * (size_t)c->cols, c);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     s = grow(&c->d_y_stage, &c->y_stage_bytes, sizeof(T) * (size_t)c->rows, c);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     s = ensure_pipe(c);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-    const T *dx = static_cast<const T *>(c->d_x_stage);
+    const T *dx = x_dev ? x : static_cast<const T *>(c->d_x_stage);
     T *dy = static_cast<T *>(c->d_y_stage);
     cudaEvent_t ev_x = c->ev_pipe[0];
     // work already queued on the library stream (it may still use the staging buffers) goes first
     ASB_CUDA_OR(cudaEventRecord(ev_x, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     ASB_CUDA_OR(cudaStreamWaitEvent(c->copy_in, ev_x, 0), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
-    ASB_CUDA_OR(cudaMemcpyAsync(c->d_x_stage, x, sizeof(T) * (size_t)c->cols, cudaMemcpyHostToDevice, c->copy_in),
-                ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
-    ASB_CUDA_OR(cudaEventRecord(ev_x, c->copy_in), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
-    ASB_CUDA_OR(cudaStreamWaitEvent(st, ev_x, 0), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    if (!x_dev) {  // a device x is already where the kernels read it (and ordered on the library stream)
+        ASB_CUDA_OR(cudaMemcpyAsync(c->d_x_stage, x, sizeof(T) * (size_t)c->cols, cudaMemcpyHostToDevice, c->copy_in),
+                    ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        ASB_CUDA_OR(cudaEventRecord(ev_x, c->copy_in), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        ASB_CUDA_OR(cudaStreamWaitEvent(st, ev_x, 0), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    }
 
     const int64_t step = ((c->rows + kPipelineChunks - 1) / kPipelineChunks + 1023) & ~1023ll;
     for (int k = 0; k < kPipelineChunks; k++) {
@@ -820,8 +824,8 @@ static alphasparse_status_t mv(alphasparse_operation_t op, T alpha, alphasparse_
     const bool x_dev = is_device_pointer(x, c->device), y_dev = is_device_pointer(y, c->device);
     std::lock_guard<std::mutex> lock(c->mu);
 
-    if (!x_dev && !y_dev && c->rows >= kPipelineMinRows && spmv_supports_windows(c) && !c->profile)
-        return mv_host_pipelined<T>(c, alpha, x, beta, y, st);
+    if (!y_dev && c->rows >= kPipelineMinRows && spmv_supports_windows(c) && !c->profile)
+        return mv_host_pipelined<T>(c, alpha, x, x_dev, beta, y, st);
 
     const T *dx = x;
     T *dy = y;

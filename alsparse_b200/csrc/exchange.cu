@@ -119,6 +119,36 @@ static alphasparse_status_t mv_exchange(T alpha, const alphasparse_matrix_t A, s
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
+// x from host memory, each GPU uploading only its own rows: the block goes over PCIe into this GPU's
+// *next* buffer and from there over NVLink into the next buffer of every peer; the same arrive / wait
+// and buffer swap as after a product follow, so afterwards every GPU holds all of x in its current
+// buffer.  world GPUs move 1/world of x each over their PCIe links instead of all of it each.
+template <typename T>
+static alphasparse_status_t load_x(Exchange *e, const void *block) {
+    const int64_t off = e->part[e->rank], rows = e->part[e->rank + 1] - off;
+    if (rows > 0 && !block) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+    cudaStream_t st = current_stream();
+    const int nxt = e->cur ^ 1;
+    T *mine = static_cast<T *>(e->xbuf[nxt]) + off;
+    if (rows > 0) {
+        ASB_CUDA_OR(cudaMemcpyAsync(mine, block, sizeof(T) * (size_t)rows, cudaMemcpyDefault, st),
+                    ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        PeerPush push{};
+        for (int p = 0; p < e->world; p++)
+            if (p != e->rank) push.dst[push.n++] = e->peer_xbuf[nxt][p];
+        push.row_off = off;
+        launch_push_rows<T>(rows, mine, push, st);
+    }
+    e->step++;
+    unsigned long long *const *table = reinterpret_cast<unsigned long long *const *>(e->counters + kMaxPeers);
+    exchange_arrive_wait_kernel<<<1, 32, 0, st>>>(e->step, e->rank, e->world, table, e->counters, e->d_status,
+                                                  4LL << 20);
+    count_launch();
+    ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    e->cur = nxt;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
 }  // namespace asb
 
 using namespace asb;
@@ -221,6 +251,13 @@ alphasparse_status_t alphasparse_cuda_exchange_x(alphasparse_cuda_exchange_t h, 
     if (!e || !x) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
     *x = e->xbuf[e->cur];
     return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+alphasparse_status_t alphasparse_cuda_exchange_load_x(alphasparse_cuda_exchange_t h, const void *x_block) {
+    Exchange *e = ex_of(h);
+    if (!e) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+    if (!e->connected) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    return e->datatype == ALPHA_SPARSE_DATATYPE_FLOAT ? load_x<float>(e, x_block) : load_x<double>(e, x_block);
 }
 
 alphasparse_status_t alphasparse_cuda_exchange_status(alphasparse_cuda_exchange_t h, int *status) {

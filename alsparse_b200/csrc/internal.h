@@ -154,6 +154,10 @@ alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T 
                                  cudaStream_t stream, const PeerPush *push = nullptr,
                                  const RowWindow *window = nullptr);
 
+// Copies src[0 .. rows) to element push.row_off of every buffer in push.dst (peer-mapped or local).
+template <typename T>
+void launch_push_rows(int64_t rows, const T *src, const PeerPush &push, cudaStream_t stream);
+
 template <typename T>
 alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx,
                                      T beta, T *Y, int ldy, cudaStream_t stream,

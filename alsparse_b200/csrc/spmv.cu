@@ -572,6 +572,15 @@ __global__ void push_rows_kernel(long long rows, const T *__restrict__ y, const 
     if (n > 0) push_span<T>(y + lo, (int)n, push, push.row_off + lo);
 }
 
+template <typename T>
+void launch_push_rows(int64_t rows, const T *src, const PeerPush &push, cudaStream_t st) {
+    if (rows <= 0 || push.n <= 0) return;
+    push_rows_kernel<T><<<148 * 4, 256, 0, st>>>(rows, src, push);
+    count_launch();
+}
+template void launch_push_rows<float>(int64_t, const float *, const PeerPush &, cudaStream_t);
+template void launch_push_rows<double>(int64_t, const double *, const PeerPush &, cudaStream_t);
+
 // y = beta * y for a matrix without stored elements (the reference still scales y).
 template <typename T>
 __global__ void scale_kernel(long long n, T *__restrict__ y, T beta) {

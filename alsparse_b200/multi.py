@@ -124,6 +124,11 @@ class FusedExchange:
             __cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (self.x_ptr(), False), "version": 2}
         return torch.as_tensor(_Raw(), device="cuda")
 
+    def load_x(self, x_block):
+        """Sets x on every GPU from the ranks' own rows of it (numpy / pinned host tensor or CUDA tensor of
+        part[rank+1] - part[rank] elements): each GPU uploads 1/world of x and the pieces cross NVLink."""
+        return capi.load().alphasparse_cuda_exchange_load_x(self.handle, spblas._ptr(x_block))
+
     def step(self, alpha, A, beta, y_local):
         fn = getattr(capi.load(), f"alphasparse_{self.kind}_mv_exchange")
         return fn(alpha, A, spblas.descr(), self.handle, beta, spblas._ptr(y_local))

@@ -356,6 +356,13 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def sum_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([float(v)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
     def max_over_ranks(v):
         if world == 1:
             return v
@@ -409,8 +416,24 @@ def main():
 
             yh[:] = y0h
 
+            # Several GPUs, square matrix: every rank uploads only its own rows of x and the pieces are exchanged
+            # over NVLink (alphasparse_cuda_exchange_load_x) instead of every rank pulling all of x over PCIe.
+            loader, x_upload = None, "every rank uploads all of x"
+            if world > 1 and op == "mv" and rows == cols:
+                try:
+                    loader = multi.FusedExchange(kind, part, rank, world)
+                    x_block_h = x_h[r0:r1].clone().pin_memory()
+                    x_upload = "each rank uploads its own rows of x; the pieces cross NVLink to every GPU"
+                except Exception as exc:  # e.g. no peer access between these GPUs: keep the plain path
+                    print(f"[bench] sharded upload of x unavailable: {exc}", file=sys.stderr)
+                    loader = None
+
             def step_host():  # y is updated in place; with beta = 0.5 it converges, no reset needed
-                if op == "mv":
+                if loader is not None:
+                    s = loader.load_x(x_block_h)
+                    assert s == capi.SUCCESS, capi.STATUS_NAMES[s]
+                    s = spblas.mv(kind, 0, alpha, A, descr, loader.x_ptr(), beta, yh)
+                elif op == "mv":
                     s = spblas.mv(kind, 0, alpha, A, descr, xh, beta, yh)
                 else:
                     s = spblas.mm(kind, 0, alpha, A, descr, capi.ROW_MAJOR, xh, columns, columns, beta, yh, columns)
@@ -428,9 +451,15 @@ def main():
             wall = (time.perf_counter() - t0) / n_e2e * 1e3
             barrier()
             ms_e2e = max_over_ranks(max(e0.elapsed_time(e1) / n_e2e, wall))
-            h2d = x_h.numel() * x_h.element_size() + (y0_h.numel() * y0_h.element_size() if beta != 0.0 else 0)
+            x_bytes = (x_block_h if loader is not None else x_h)
+            h2d = x_bytes.numel() * x_bytes.element_size() + (y0_h.numel() * y0_h.element_size() if beta != 0.0 else 0)
             d2h = y_h.numel() * y_h.element_size()
-            e2e = (ms_e2e, h2d, d2h)
+            if loader is not None:
+                st_code, code = loader.status()
+                assert st_code == capi.SUCCESS and code == 0, f"a bounded wait of the exchange ran out (status {code})"
+                loader.destroy()
+            # bytes of the whole job: every rank's copies added up
+            e2e = (ms_e2e, sum_over_ranks(h2d), sum_over_ranks(d2h), x_upload)
     if sampler:
         sampler.stop()
 
@@ -482,7 +511,7 @@ def main():
         }
         if e2e:
             line["e2e"] = {"value": nbytes / (e2e[0] * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e[0],
-                           "h2d_bytes_per_step": int(e2e[1]), "d2h_bytes_per_step": int(e2e[2])}
+                           "h2d_bytes_per_step": int(e2e[1]), "d2h_bytes_per_step": int(e2e[2]), "x_upload": e2e[3]}
         else:
             line["e2e"] = None
         if world == 1 and not args.no_cpu_baseline:

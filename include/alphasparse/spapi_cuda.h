@@ -110,6 +110,12 @@ alphasparse_status_t alphasparse_cuda_exchange_connect(alphasparse_cuda_exchange
 alphasparse_status_t alphasparse_cuda_exchange_set_mode(alphasparse_cuda_exchange_t ex, int mode);
 /* Device pointer of the current x (part[world] elements): fill it before the first step, read it after. */
 alphasparse_status_t alphasparse_cuda_exchange_x(alphasparse_cuda_exchange_t ex, void **x);
+/* Sets x from the ranks' own pieces: every rank passes ITS rows of x (part[rank+1] - part[rank] elements,
+ * host or device memory); the piece is copied into this GPU's buffer and stored into every peer's over
+ * NVLink, the ranks signal each other as after a product, and the buffers swap: afterwards
+ * alphasparse_cuda_exchange_x is the complete vector on every GPU.  With x in host memory each GPU
+ * moves 1/world of it over PCIe.  Collective: all ranks call it, in the same order as their products. */
+alphasparse_status_t alphasparse_cuda_exchange_load_x(alphasparse_cuda_exchange_t ex, const void *x_block);
 /* Waits for the stream and reports whether any bounded wait ran out (status 3) since creation. */
 alphasparse_status_t alphasparse_cuda_exchange_status(alphasparse_cuda_exchange_t ex, int *status);
 /* Test aids for the bounded wait: enqueue a wait on a counter that no rank ever advances, limited to

@@ -50,6 +50,9 @@ def check_mv(kind, m, alpha, beta, seed=1, pointers="host", alg=None, A=None):
     if pointers == "host":
         y = y0.copy()
         st = spblas.mv(kind, capi.NON_TRANSPOSE, alpha, A, spblas.descr(), x, beta, y)
+    elif pointers == "device_x_host_y":
+        dx, y = torch.from_numpy(x).cuda(), y0.copy()
+        st = spblas.mv(kind, capi.NON_TRANSPOSE, alpha, A, spblas.descr(), dx, beta, y)
     else:
         dx, dy = torch.from_numpy(x).cuda(), torch.from_numpy(y0).cuda()
         st = spblas.mv(kind, capi.NON_TRANSPOSE, alpha, A, spblas.descr(), dx, beta, dy)

@@ -59,6 +59,27 @@ def test_single_rank_push_matches_oracle(kind, after):
         spblas.destroy(A)
 
 
+def test_single_rank_load_x():
+    """alphasparse_cuda_exchange_load_x with one rank: the piece is the whole vector; buffers swap as after a product."""
+    m = synth.uniform_fixed("s", 4, 5000, 5000, 8)
+    A = make_handle("s", m)
+    ex = multi.FusedExchange("s", np.array([0, m.nrows], np.int32), 0, 1)
+    xa, xb = synth.vector("s", 5, 1, m.cols), synth.vector("s", 5, 2, m.cols)
+    before = ex.x_ptr()
+    assert ex.load_x(xa) == capi.SUCCESS
+    assert ex.x_ptr() != before and np.array_equal(ex.x_tensor().cpu().numpy(), xa)
+    y = torch.zeros(m.nrows, device="cuda")
+    assert ex.step(1.0, A, 0.0, y) == capi.SUCCESS
+    ref = oracle.gemv("s", m.rows_start, m.rows_end, m.col, m.val, 1.0, xa, 0.0, np.zeros(m.nrows, np.float32))
+    assert (np.abs(y.cpu().numpy() - ref) <= TOL["s"] * row_scale(m.ptr, m.col, m.val, xa, 1.0, 0.0, ref * 0) + 1e-30).all()
+    assert ex.load_x(torch.from_numpy(xb).cuda()) == capi.SUCCESS
+    assert np.array_equal(ex.x_tensor().cpu().numpy(), xb)
+    assert ex.load_x(None) == capi.INVALID_POINTER
+    assert ex.status() == (capi.SUCCESS, 0)
+    ex.destroy()
+    spblas.destroy(A)
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -96,6 +117,17 @@ def _rank_main(rank, world, port, out_dir):
             assert (err <= TOL[kind] * scale + 1e-300).all(), (rank, it, float(np.max(err / np.maximum(scale, 1e-300))))
             assert np.array_equal(x_new[r0:r1], y.cpu().numpy())
             x_ref = x_new
+        # x set from the ranks' own rows of a host vector: every GPU ends up with all of it, and the
+        # products carry on from there
+        x1 = synth.vector(kind, 8, 5, m.cols)
+        assert ex.load_x(x1[r0:r1].copy()) == capi.SUCCESS
+        assert np.array_equal(ex.x_tensor().cpu().numpy(), x1)
+        assert ex.step(0.2, A, 0.0, y) == capi.SUCCESS
+        ref = oracle.gemv(kind, m.rows_start, m.rows_end, m.col, m.val, 0.2, x1, 0.0, np.zeros(m.nrows))
+        scale = row_scale(m.ptr, m.col, m.val, x1, 0.2, 0.0, np.zeros(m.nrows))
+        assert (np.abs(ex.x_tensor().cpu().numpy() - ref) <= TOL[kind] * scale + 1e-300).all()
+        assert ex.load_x(torch.from_numpy(x0[r0:r1].copy()).cuda()) == capi.SUCCESS      # a device piece works too
+        assert np.array_equal(ex.x_tensor().cpu().numpy(), x0)
         assert ex.status() == (capi.SUCCESS, 0)
         dist.barrier()
         ex.destroy()

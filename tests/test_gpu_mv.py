@@ -253,6 +253,8 @@ def test_large_host_vectors_take_the_pipelined_path(kind, make):
         y_host = check_mv(kind, m, alpha, beta, seed=31, pointers="host")
         y_dev = check_mv(kind, m, alpha, beta, seed=31, pointers="device")
         assert np.array_equal(y_host, y_dev)  # same kernels on the same rows: identical bits
+        y_mixed = check_mv(kind, m, alpha, beta, seed=31, pointers="device_x_host_y")   # windows, x already on the GPU
+        assert np.array_equal(y_mixed, y_dev)
 
 
 def test_transposed_mv():
