@@ -19,7 +19,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libalphasparse_b200.so")
 SYNTH_SRC = os.path.join(HERE, "synth", "synth.c")
 SYNTH_LIB = os.path.join(HERE, "synth", "libsynth.so")
-CUDA_SOURCES = ["core.cu", "spmv.cu", "spmm.cu", "exchange.cu", "coo2csr.cu", "probe.cu", "host_util.cu"]
+CUDA_SOURCES = ["core.cu", "spmv.cu", "spmv_band.cu", "spmm.cu", "exchange.cu", "coo2csr.cu", "probe.cu", "host_util.cu", "host_args.cu"]
 
 
 def _newer(target, deps):

@@ -46,7 +46,14 @@ class MatInfo(C.Structure):
     _fields_ = [("rows", C.c_int64), ("cols", C.c_int64), ("nnz", C.c_int64),
                 ("max_row_nnz", C.c_int64), ("empty_rows", C.c_int64), ("mean_row_nnz", C.c_double),
                 ("algorithm", C.c_int32), ("lanes_per_row", C.c_int32), ("merge_tiles", C.c_int64),
-                ("device_bytes", C.c_int64), ("device", C.c_int32), ("scheduled", C.c_int32)]
+                ("device_bytes", C.c_int64), ("device", C.c_int32), ("scheduled", C.c_int32),
+                ("band_rows", C.c_int32), ("band_count", C.c_int32), ("band_width", C.c_int32),
+                ("band_elements", C.c_int64)]
+
+
+class AlphaTimer(C.Structure):
+    """alpha_timer_t"""
+    _fields_ = [("start", C.c_double), ("end", C.c_double)]
 
 
 class Complex8(C.Structure):
@@ -90,6 +97,8 @@ def prototypes():
     p["alphasparse_cuda_get_stream"] = (C.c_int, [_HP])
     p["alphasparse_cuda_synchronize"] = (C.c_int, [])
     p["alphasparse_cuda_set_algorithm"] = (C.c_int, [C.c_int])
+    p["alphasparse_cuda_set_option"] = (C.c_int, [C.c_char_p, C.c_int64])
+    p["alphasparse_cuda_get_option"] = (C.c_int, [C.c_char_p, C.POINTER(C.c_int64)])
     p["alphasparse_cuda_get_mat_info"] = (C.c_int, [_H, C.POINTER(MatInfo)])
     p["alphasparse_cuda_get_device_csr"] = (C.c_int, [_H, _HP, _HP, _HP])
     p["alphasparse_cuda_d_csrmv_noalloc"] = (C.c_int, [_I, _I, _I, C.c_double, _P, _P, _P, _P, C.c_double, _P])
@@ -112,6 +121,13 @@ def prototypes():
     p["alphasparse_cuda_debug_fail_alloc"] = (C.c_int, [C.c_int64])
     p["alphasparse_cuda_launch_count"] = (C.c_int64, [])
     p["alphasparse_cuda_last_error"] = (C.c_char_p, [])
+    # include/alphasparse/kernel_cuda.h
+    for k, T in _REAL.items():
+        for name in (f"gemv_{k}_csr", f"gemv_{k}_csr_trans"):
+            p[name] = (C.c_int, [T, _P, _P, T, _P])
+        for name in (f"gemm_{k}_csr_row", f"gemm_{k}_csr_col", f"gemm_{k}_csr_row_trans", f"gemm_{k}_csr_col_trans"):
+            p[name] = (C.c_int, [T, _P, _P, _I, _I, T, _P, _I])
+    p["alphasparse_cuda_release_csr"] = (C.c_int, [_P])
     # include/alphasparse/util.h
     p["alpha_malloc"] = (C.c_void_p, [C.c_size_t])
     p["alpha_memalign"] = (C.c_void_p, [C.c_size_t, C.c_size_t])
@@ -120,6 +136,41 @@ def prototypes():
     p["alpha_set_thread_num"] = (None, [C.c_int])
     p["alpha_get_thread_num"] = (C.c_int, [])
     p["alpha_timing_wtime"] = (C.c_double, [])
+    _T = C.POINTER(AlphaTimer)
+    p["alpha_timing_start"] = (None, [_T])
+    p["alpha_timing_end"] = (None, [_T])
+    p["alpha_timing_elapsed_time"] = (C.c_double, [_T])
+    p["alpha_timing_gflops"] = (C.c_double, [_T, C.c_int64])
+    p["alpha_timing_elaped_time_print"] = (None, [_T, C.c_char_p])
+    p["alpha_timing_gflops_print"] = (None, [_T, C.c_int64, C.c_char_p])
+    p["alpha_fill_s"] = (None, [_P, C.c_float, C.c_size_t])
+    p["alpha_fill_d"] = (None, [_P, C.c_double, C.c_size_t])
+    p["alpha_fill_random_s"] = (None, [_P, C.c_uint, C.c_size_t])
+    p["alpha_fill_random_d"] = (None, [_P, C.c_uint, C.c_size_t])
+    p["alpha_clear_cache"] = (None, [])
+    _ARGV = [C.c_int, C.POINTER(C.c_char_p)]
+    for name, res in (("alphasparse_layout_parse", C.c_int), ("alphasparse_operation_parse", C.c_int),
+                      ("alphasparse_matrix_type_parse", C.c_int), ("alphasparse_fill_mode_parse", C.c_int),
+                      ("alphasparse_diag_type_parse", C.c_int)):
+        p[name] = (res, [C.c_char_p])
+    p["args_help"] = (None, _ARGV)
+    p["args_get_if_check"] = (C.c_bool, _ARGV)
+    p["args_get_thread_num"] = (C.c_int, _ARGV)
+    p["args_get_columns"] = (C.c_int, _ARGV + [C.c_int])
+    p["args_get_iter"] = (C.c_int, _ARGV)
+    for name in ("args_get_data_file", "args_get_data_fileA", "args_get_data_fileB"):
+        p[name] = (C.c_char_p, _ARGV)
+    p["alpha_args_get_layout_helper"] = (C.c_int, _ARGV + [C.c_int])
+    p["alpha_args_get_matrix_descr_helper"] = (MatrixDescr, _ARGV + [C.c_int, C.c_int, C.c_int])
+    p["alpha_args_get_trans_helper"] = (C.c_int, _ARGV + [C.c_int])
+    for name in ("alpha_args_get_layout", "alpha_args_get_layoutB", "alpha_args_get_layoutC", "alpha_args_get_transA",
+                 "alpha_args_get_transB"):
+        p[name] = (C.c_int, _ARGV)
+    p["alpha_args_get_matrix_descrA"] = (MatrixDescr, _ARGV)
+    p["alpha_args_get_matrix_descrB"] = (MatrixDescr, _ARGV)
+    p["alphasparse_nnz_counter_coo"] = (None, [_P, _P, _I, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I)])
+    p["alphasparse_operations_mm"] = (C.c_int64, [_I, _I, _I, _I, _I, C.c_int, MatrixDescr, _I, C.c_int])
+    p["alphasparse_operations_mv"] = (C.c_int64, [_I, _I, _I, _I, _I, C.c_int, MatrixDescr, C.c_int])
     p["alpha_read_coo"] = (None, [C.c_char_p, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I), _HP, _HP, _HP])
     p["alpha_read_coo_d"] = (None, [C.c_char_p, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I), _HP, _HP, _HP])
     p["lower_bound_int"] = (C.c_int, [_P, _I, _I, _I])

@@ -11,8 +11,10 @@
 #include <algorithm>
 #include <new>
 #include <numeric>
+#include <unordered_map>
 #include <vector>
 
+#include "alphasparse/kernel_cuda.h"
 #include "alphasparse/spapi.h"
 #include "alphasparse/util.h"
 #include "internal.h"
@@ -57,6 +59,47 @@ cudaError_t device_alloc_bytes(void **p, size_t bytes) {
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+// ---- tuning options ------------------------------------------------------------------------------
+struct OptionDef {
+    const char *name;
+    int64_t def;
+};
+static const OptionDef kOptionDefs[kOptCount] = {
+    {"band_enable", 1},       {"band_bytes", 64 * 1024}, {"band_min_seg", 8},      {"band_min_rows", 128},
+    {"band_min_share_pct", 10}, {"band_splits", 0},      {"band_overlap", 1},      {"band_variant", 1},     {"spmm_col_blocks", 0},
+    {"spmm_block_bytes", (int64_t)48 << 20},
+};
+static std::atomic<int64_t> g_options[kOptCount];
+static std::once_flag g_options_once;
+
+static int option_index(const char *name, size_t len) {
+    for (int i = 0; i < kOptCount; i++)
+        if (strlen(kOptionDefs[i].name) == len && !strncmp(kOptionDefs[i].name, name, len)) return i;
+    return -1;
+}
+
+static void options_init() {
+    std::call_once(g_options_once, [] {
+        for (int i = 0; i < kOptCount; i++) g_options[i].store(kOptionDefs[i].def);
+        // ALPHASPARSE_CUDA_OPTIONS="name=value,name=value": initial values
+        const char *env = getenv("ALPHASPARSE_CUDA_OPTIONS");
+        while (env && *env) {
+            const char *eq = strchr(env, '='), *end = strchr(env, ',');
+            if (!end) end = env + strlen(env);
+            if (eq && eq < end) {
+                const int i = option_index(env, (size_t)(eq - env));
+                if (i >= 0) g_options[i].store(strtoll(eq + 1, nullptr, 10));
+            }
+            env = *end ? end + 1 : end;
+        }
+    });
+}
+
+int64_t option(Option o) {
+    options_init();
+    return g_options[o].load(std::memory_order_relaxed);
+}
+
 void record_cuda_error(cudaError_t e, const char *what) {
     snprintf(t_error, sizeof(t_error), "%s: %s", what, cudaGetErrorString(e));
     (void)cudaGetLastError();  // clear the sticky-free error so later calls start clean
@@ -89,6 +132,7 @@ void ctx_destroy(DeviceCtx *c) {
     cudaFree(c->d_carry_val);
     cudaFree(c->d_chunk_done);
     cudaFree(c->d_sched);
+    band_destroy(c->band);
     cudaFree(c->d_x_stage);
     cudaFree(c->d_y_stage);
     cudaFree(c->d_status);
@@ -200,6 +244,32 @@ static void free_csr_host(typename CsrOf<T>::csr *m) {
     free(m);
 }
 
+// Host CSR record -> device context.  The kernel-level entry points (gemv_?_csr, gemm_?_csr_row, ... at the
+// end of this file) receive only the record, as the reference's dispatch tables pass it; records of handles
+// made by this library are entered at creation and removed by alphasparse_destroy, records the library has
+// never seen are uploaded on first use (`adopted`) and stay until alphasparse_cuda_release_csr.
+struct RegistryEntry {
+    DeviceCtx *ctx;
+    bool adopted;
+};
+static std::mutex g_registry_mu;
+static std::unordered_map<const void *, RegistryEntry> &registry() {
+    static std::unordered_map<const void *, RegistryEntry> r;
+    return r;
+}
+static void registry_add(const void *record, DeviceCtx *c, bool adopted) {
+    std::lock_guard<std::mutex> lock(g_registry_mu);
+    registry()[record] = RegistryEntry{c, adopted};
+}
+static RegistryEntry registry_take(const void *record) {
+    std::lock_guard<std::mutex> lock(g_registry_mu);
+    auto it = registry().find(record);
+    if (it == registry().end()) return RegistryEntry{nullptr, false};
+    RegistryEntry e = it->second;
+    registry().erase(it);
+    return e;
+}
+
 // Takes ownership of ptr / col / val (host_alloc'ed, zero-based 3-array CSR) and builds the
 // handle around them: host record for export_csr, device copy and analysis for mv / mm.
 template <typename T>
@@ -234,6 +304,7 @@ static alphasparse_status_t finish_csr_handle(alphasparse_matrix_t *A, int64_t r
     m->d_row_ptr = c->d_row_ptr;
     m->d_col_indx = c->d_col;
     h->dcu_info = c;
+    registry_add(m, c, false);
     *A = h;
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
@@ -789,36 +860,12 @@ static alphasparse_status_t select_structured(DeviceCtx *&c, const alphasparse_m
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
+// y = alpha * (matrix of c) * x + beta * y with x, y in host or device memory: the part of mv that no longer
+// looks at the handle.  Host vectors are staged (pipelined in row windows when large) and the call returns when
+// y is complete; device vectors are only enqueued.
 template <typename T>
-static alphasparse_status_t mv(alphasparse_operation_t op, T alpha, alphasparse_matrix_t A,
-                               struct alpha_matrix_descr descr, const T *x, T beta, T *y) {
-    alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr);
-    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-    if (A->format != ALPHA_SPARSE_FORMAT_CSR) {
-        // A CSC matrix is held as the CSR of its transpose (src/core/op/level2/alphasparse_x_mv.c's CSC block
-        // runs gemv_csc / gemv_csc_trans, src/plain/kernel/level2/mv/gemv/gemv_x_csc[_trans]_plain.c: the
-        // same products in another summation order)
-        if (A->format == ALPHA_SPARSE_FORMAT_CSC)
-            op = op == ALPHA_SPARSE_OPERATION_NON_TRANSPOSE ? ALPHA_SPARSE_OPERATION_TRANSPOSE : ALPHA_SPARSE_OPERATION_NON_TRANSPOSE;
-        s = csr_shadow_of(A, &A);
-        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-    }
-    DeviceCtx *c = ctx_of(A);
-    if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
-
-    DeviceGuard guard(c->device);
-    if (!guard.ok) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
-    if (descr.type != ALPHA_SPARSE_MATRIX_TYPE_GENERAL) {
-        s = select_structured<T>(c, A, op, descr, kDiagFirst);
-        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-    } else if (op == ALPHA_SPARSE_OPERATION_TRANSPOSE) {  // y (cols entries) = alpha * A^T * x (rows entries) + beta * y
-        {
-            std::lock_guard<std::mutex> build(c->mu);
-            s = ensure_transposed<T>(c, static_cast<const typename CsrOf<T>::csr *>(A->mat));
-            if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-        }
-        c = c->transposed;
-    }
+static alphasparse_status_t mv_on_ctx(DeviceCtx *c, T alpha, const T *x, T beta, T *y) {
+    alphasparse_status_t s = ALPHA_SPARSE_STATUS_SUCCESS;
     if (c->rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
     cudaStream_t st = current_stream();
     const bool x_dev = is_device_pointer(x, c->device), y_dev = is_device_pointer(y, c->device);
@@ -877,6 +924,39 @@ static alphasparse_status_t mv(alphasparse_operation_t op, T alpha, alphasparse_
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
+template <typename T>
+static alphasparse_status_t mv(alphasparse_operation_t op, T alpha, alphasparse_matrix_t A,
+                               struct alpha_matrix_descr descr, const T *x, T beta, T *y) {
+    alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    if (A->format != ALPHA_SPARSE_FORMAT_CSR) {
+        // A CSC matrix is held as the CSR of its transpose (src/core/op/level2/alphasparse_x_mv.c's CSC block
+        // runs gemv_csc / gemv_csc_trans, src/plain/kernel/level2/mv/gemv/gemv_x_csc[_trans]_plain.c: the
+        // same products in another summation order)
+        if (A->format == ALPHA_SPARSE_FORMAT_CSC)
+            op = op == ALPHA_SPARSE_OPERATION_NON_TRANSPOSE ? ALPHA_SPARSE_OPERATION_TRANSPOSE : ALPHA_SPARSE_OPERATION_NON_TRANSPOSE;
+        s = csr_shadow_of(A, &A);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    }
+    DeviceCtx *c = ctx_of(A);
+    if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+
+    DeviceGuard guard(c->device);
+    if (!guard.ok) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+    if (descr.type != ALPHA_SPARSE_MATRIX_TYPE_GENERAL) {
+        s = select_structured<T>(c, A, op, descr, kDiagFirst);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    } else if (op == ALPHA_SPARSE_OPERATION_TRANSPOSE) {  // y (cols entries) = alpha * A^T * x (rows entries) + beta * y
+        {
+            std::lock_guard<std::mutex> build(c->mu);
+            s = ensure_transposed<T>(c, static_cast<const typename CsrOf<T>::csr *>(A->mat));
+            if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        }
+        c = c->transposed;
+    }
+    return mv_on_ctx<T>(c, alpha, x, beta, y);
+}
+
 // Row-major mm with host X and host Y on a large dense block: X goes over first (every row of A may
 // need any row of X), then the product runs in kPipelineChunks row windows and every finished window
 // of Y leaves on its own stream while the next one is multiplied; when Y must come over first
@@ -928,36 +1008,12 @@ static alphasparse_status_t mm_host_pipelined(DeviceCtx *c, T alpha, const T *x,
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
+// Y = alpha * (matrix of c) * X + beta * Y for dense operands in host or device memory: the part of mm that no
+// longer looks at the handle.
 template <typename T>
-static alphasparse_status_t mm(alphasparse_operation_t op, T alpha, alphasparse_matrix_t A,
-                               struct alpha_matrix_descr descr, alphasparse_layout_t layout,
-                               const T *x, ALPHA_INT columns, ALPHA_INT ldx, T beta, T *y,
-                               ALPHA_INT ldy) {
-    alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr);
-    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-    if (layout != ALPHA_SPARSE_LAYOUT_ROW_MAJOR && layout != ALPHA_SPARSE_LAYOUT_COLUMN_MAJOR)
-        return ALPHA_SPARSE_STATUS_INVALID_VALUE;
-    if (A->format != ALPHA_SPARSE_FORMAT_CSR) {
-        if (A->format == ALPHA_SPARSE_FORMAT_CSC)  // held as the CSR of A^T (gemm_x_csc_{row,col}[_trans]_plain.c)
-            op = op == ALPHA_SPARSE_OPERATION_NON_TRANSPOSE ? ALPHA_SPARSE_OPERATION_TRANSPOSE : ALPHA_SPARSE_OPERATION_NON_TRANSPOSE;
-        s = csr_shadow_of(A, &A);
-        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-    }
-    DeviceCtx *c = ctx_of(A);
-    if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
-    DeviceGuard guard(c->device);
-    if (!guard.ok) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
-    if (descr.type != ALPHA_SPARSE_MATRIX_TYPE_GENERAL) {
-        s = select_structured<T>(c, A, op, descr, layout == ALPHA_SPARSE_LAYOUT_ROW_MAJOR ? kDiagAll : kDiagLast);
-        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-    } else if (op == ALPHA_SPARSE_OPERATION_TRANSPOSE) {  // the reference also multiplies by a materialised A^T
-        {
-            std::lock_guard<std::mutex> build(c->mu);
-            s = ensure_transposed<T>(c, static_cast<const typename CsrOf<T>::csr *>(A->mat));
-            if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-        }
-        c = c->transposed;
-    }
+static alphasparse_status_t mm_on_ctx(DeviceCtx *c, alphasparse_layout_t layout, T alpha, const T *x, ALPHA_INT columns,
+                                      ALPHA_INT ldx, T beta, T *y, ALPHA_INT ldy) {
+    alphasparse_status_t s = ALPHA_SPARSE_STATUS_SUCCESS;
     const bool row_major = layout == ALPHA_SPARSE_LAYOUT_ROW_MAJOR;
     // X is (c->cols x columns), Y is (c->rows x columns); ld = distance between rows (row-major) or
     // between columns (column-major)
@@ -1009,6 +1065,125 @@ static alphasparse_status_t mm(alphasparse_operation_t op, T alpha, alphasparse_
     if (!y_dev || !x_dev)
         ASB_CUDA_OR(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+template <typename T>
+static alphasparse_status_t mm(alphasparse_operation_t op, T alpha, alphasparse_matrix_t A,
+                               struct alpha_matrix_descr descr, alphasparse_layout_t layout,
+                               const T *x, ALPHA_INT columns, ALPHA_INT ldx, T beta, T *y,
+                               ALPHA_INT ldy) {
+    alphasparse_status_t s = check_call(A, x, y, CsrOf<T>::dt, op, descr);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    if (layout != ALPHA_SPARSE_LAYOUT_ROW_MAJOR && layout != ALPHA_SPARSE_LAYOUT_COLUMN_MAJOR)
+        return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    if (A->format != ALPHA_SPARSE_FORMAT_CSR) {
+        if (A->format == ALPHA_SPARSE_FORMAT_CSC)  // held as the CSR of A^T (gemm_x_csc_{row,col}[_trans]_plain.c)
+            op = op == ALPHA_SPARSE_OPERATION_NON_TRANSPOSE ? ALPHA_SPARSE_OPERATION_TRANSPOSE : ALPHA_SPARSE_OPERATION_NON_TRANSPOSE;
+        s = csr_shadow_of(A, &A);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    }
+    DeviceCtx *c = ctx_of(A);
+    if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+    DeviceGuard guard(c->device);
+    if (!guard.ok) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+    if (descr.type != ALPHA_SPARSE_MATRIX_TYPE_GENERAL) {
+        s = select_structured<T>(c, A, op, descr, layout == ALPHA_SPARSE_LAYOUT_ROW_MAJOR ? kDiagAll : kDiagLast);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    } else if (op == ALPHA_SPARSE_OPERATION_TRANSPOSE) {  // the reference also multiplies by a materialised A^T
+        {
+            std::lock_guard<std::mutex> build(c->mu);
+            s = ensure_transposed<T>(c, static_cast<const typename CsrOf<T>::csr *>(A->mat));
+            if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        }
+        c = c->transposed;
+    }
+    return mm_on_ctx<T>(c, layout, alpha, x, columns, ldx, beta, y, ldy);
+}
+
+
+// ---- kernel-level entry points ----------------------------------------------------------------------
+// The symbols the reference's dispatch tables call for CSR + GENERAL (include/alphasparse/kernel/kernel_csr_s.h:13-17,
+// 65-72 and kernel_csr_d.h of the reference; chosen per architecture by src/kernel/Makefile:2-11).  A `cuda` kernel
+// tree beside plain / arm / hygon / dcu consists of these: they take the bare CSR record, find (or make) its device
+// copy and run the same kernels as alphasparse_?_mv / _mm.
+
+template <typename T>
+static alphasparse_status_t ctx_for_record(const typename CsrOf<T>::csr *m, DeviceCtx **out) {
+    {
+        std::lock_guard<std::mutex> lock(g_registry_mu);
+        auto it = registry().find(m);
+        if (it != registry().end()) {
+            *out = it->second.ctx;
+            return ALPHA_SPARSE_STATUS_SUCCESS;
+        }
+    }
+    // A record made elsewhere (the reference's own create_csr, src/core/format/alphasparse_x_create_csr.c:16-55,
+    // in a build that links this library as its kernel tree): zero-based host arrays.  Upload and analyse it now.
+    const int64_t rows = m->rows;
+    if (rows < 0 || m->cols < 0 || (rows > 0 && (!m->rows_start || !m->rows_end))) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    std::vector<int> ptr;
+    const int *offsets = m->rows_start;
+    if (rows > 0 && m->rows_end != m->rows_start + 1) {  // four-array form: rows must still be contiguous
+        ptr.resize((size_t)rows + 1);
+        ptr[0] = m->rows_start[0];
+        for (int64_t i = 0; i < rows; i++) {
+            if (i + 1 < rows && m->rows_end[i] != m->rows_start[i + 1]) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+            ptr[(size_t)i + 1] = m->rows_end[i];
+        }
+        offsets = ptr.data();
+    }
+    if (rows > 0 && offsets[0] != 0) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    static const int zero = 0;
+    DeviceCtx *c = nullptr;
+    alphasparse_status_t s = ctx_create(CsrOf<T>::dt, rows, m->cols, rows > 0 ? offsets : &zero, m->col_indx, m->values, &c);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    {
+        std::lock_guard<std::mutex> lock(g_registry_mu);
+        auto it = registry().find(m);
+        if (it != registry().end()) {  // another thread was faster
+            ctx_destroy(c);
+            c = it->second.ctx;
+        } else {
+            registry()[m] = RegistryEntry{c, true};
+        }
+    }
+    *out = c;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+template <typename T>
+static alphasparse_status_t kernel_mv(const typename CsrOf<T>::csr *A, bool trans, T alpha, const T *x, T beta, T *y) {
+    if (!A || !x || !y) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    DeviceCtx *c = nullptr;
+    alphasparse_status_t s = ctx_for_record<T>(A, &c);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    DeviceGuard guard(c->device);
+    if (!guard.ok) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+    if (trans) {
+        std::lock_guard<std::mutex> build(c->mu);
+        s = ensure_transposed<T>(c, A);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        c = c->transposed;
+    }
+    return mv_on_ctx<T>(c, alpha, x, beta, y);
+}
+
+template <typename T>
+static alphasparse_status_t kernel_mm(const typename CsrOf<T>::csr *A, bool trans, alphasparse_layout_t layout, T alpha,
+                                      const T *x, ALPHA_INT columns, ALPHA_INT ldx, T beta, T *y, ALPHA_INT ldy) {
+    if (!A || !x || !y) return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
+    DeviceCtx *c = nullptr;
+    alphasparse_status_t s = ctx_for_record<T>(A, &c);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    DeviceGuard guard(c->device);
+    if (!guard.ok) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+    if (trans) {
+        std::lock_guard<std::mutex> build(c->mu);
+        s = ensure_transposed<T>(c, A);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        c = c->transposed;
+    }
+    return mm_on_ctx<T>(c, layout, alpha, x, columns, ldx, beta, y, ldy);
 }
 
 }  // namespace asb
@@ -1093,6 +1268,7 @@ alphasparse_status_t alphasparse_z_create_coo(alphasparse_matrix_t *A, const alp
 // reference, whose alpha_free releases nothing, host and device storage is really returned.
 alphasparse_status_t alphasparse_destroy(alphasparse_matrix_t A) {
     if (!A) return ALPHA_SPARSE_STATUS_SUCCESS;
+    if (A->mat && A->format == ALPHA_SPARSE_FORMAT_CSR) registry_take(A->mat);
     ctx_destroy(ctx_of(A));
     A->dcu_info = nullptr;
     if (A->mat) {
@@ -1267,6 +1443,53 @@ alphasparse_status_t alphasparse_z_mm(const alphasparse_operation_t, const ALPHA
     return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
 }
 
+
+// ---- kernel-level symbols (include/alphasparse/kernel_cuda.h) -------------------------------------------
+
+#define ASB_KERNEL_SYMBOLS(T, sfx)                                                                                  \
+    alphasparse_status_t gemv_##sfx##_csr(const T alpha, const spmat_csr_##sfx##_t *A, const T *x, const T beta,   \
+                                          T *y) {                                                                   \
+        return kernel_mv<T>(A, false, alpha, x, beta, y);                                                           \
+    }                                                                                                               \
+    alphasparse_status_t gemv_##sfx##_csr_trans(const T alpha, const spmat_csr_##sfx##_t *A, const T *x,           \
+                                                const T beta, T *y) {                                               \
+        return kernel_mv<T>(A, true, alpha, x, beta, y);                                                            \
+    }                                                                                                               \
+    alphasparse_status_t gemm_##sfx##_csr_row(const T alpha, const spmat_csr_##sfx##_t *mat, const T *x,           \
+                                              const ALPHA_INT columns, const ALPHA_INT ldx, const T beta, T *y,     \
+                                              const ALPHA_INT ldy) {                                                \
+        return kernel_mm<T>(mat, false, ALPHA_SPARSE_LAYOUT_ROW_MAJOR, alpha, x, columns, ldx, beta, y, ldy);       \
+    }                                                                                                               \
+    alphasparse_status_t gemm_##sfx##_csr_col(const T alpha, const spmat_csr_##sfx##_t *mat, const T *x,           \
+                                              const ALPHA_INT columns, const ALPHA_INT ldx, const T beta, T *y,     \
+                                              const ALPHA_INT ldy) {                                                \
+        return kernel_mm<T>(mat, false, ALPHA_SPARSE_LAYOUT_COLUMN_MAJOR, alpha, x, columns, ldx, beta, y, ldy);    \
+    }                                                                                                               \
+    alphasparse_status_t gemm_##sfx##_csr_row_trans(const T alpha, const spmat_csr_##sfx##_t *mat, const T *x,     \
+                                                    const ALPHA_INT columns, const ALPHA_INT ldx, const T beta,     \
+                                                    T *y, const ALPHA_INT ldy) {                                    \
+        return kernel_mm<T>(mat, true, ALPHA_SPARSE_LAYOUT_ROW_MAJOR, alpha, x, columns, ldx, beta, y, ldy);        \
+    }                                                                                                               \
+    alphasparse_status_t gemm_##sfx##_csr_col_trans(const T alpha, const spmat_csr_##sfx##_t *mat, const T *x,     \
+                                                    const ALPHA_INT columns, const ALPHA_INT ldx, const T beta,     \
+                                                    T *y, const ALPHA_INT ldy) {                                    \
+        return kernel_mm<T>(mat, true, ALPHA_SPARSE_LAYOUT_COLUMN_MAJOR, alpha, x, columns, ldx, beta, y, ldy);     \
+    }
+ASB_KERNEL_SYMBOLS(float, s)
+ASB_KERNEL_SYMBOLS(double, d)
+
+alphasparse_status_t alphasparse_cuda_release_csr(const void *record) {
+    if (!record) return ALPHA_SPARSE_STATUS_SUCCESS;
+    RegistryEntry e = registry_take(record);
+    if (!e.ctx) return ALPHA_SPARSE_STATUS_SUCCESS;
+    if (!e.adopted) {  // belongs to a live handle of this library: alphasparse_destroy releases it
+        registry_add(record, e.ctx, false);
+        return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    }
+    ctx_destroy(e.ctx);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
 // ---- additions (include/alphasparse/spapi_cuda.h) ---------------------------------------------
 
 alphasparse_status_t alphasparse_cuda_set_stream(void *stream) {
@@ -1287,6 +1510,22 @@ alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg) 
     g_alg.store((int)alg, std::memory_order_relaxed);
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
+alphasparse_status_t alphasparse_cuda_set_option(const char *name, int64_t value) {
+    if (!name) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+    options_init();
+    const int i = option_index(name, strlen(name));
+    if (i < 0) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    g_options[i].store(value < 0 ? kOptionDefs[i].def : value, std::memory_order_relaxed);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+alphasparse_status_t alphasparse_cuda_get_option(const char *name, int64_t *value) {
+    if (!name || !value) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+    options_init();
+    const int i = option_index(name, strlen(name));
+    if (i < 0) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    *value = g_options[i].load(std::memory_order_relaxed);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
 alphasparse_status_t alphasparse_cuda_get_mat_info(const alphasparse_matrix_t A, alphasparse_cuda_mat_info_t *info) {
     if (!info) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
     DeviceCtx *c = ctx_of(A);
@@ -1299,6 +1538,8 @@ alphasparse_status_t alphasparse_cuda_get_mat_info(const alphasparse_matrix_t A,
     info->merge_tiles = c->algorithm == ALPHA_SPARSE_CUDA_ALG_MERGE ? c->merge_tiles : 0;
     info->device_bytes = c->device_bytes, info->device = c->device;
     info->scheduled = c->d_sched != nullptr;
+    info->band_rows = c->band.rows, info->band_count = c->band.bands, info->band_width = c->band.width;
+    info->band_elements = c->band.elements;
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 alphasparse_status_t alphasparse_cuda_get_device_csr(const alphasparse_matrix_t A, ALPHA_INT **d_row_ptr,

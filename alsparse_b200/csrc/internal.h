@@ -7,6 +7,7 @@
 
 #include <atomic>
 #include <mutex>
+#include <vector>
 
 #include "alphasparse/spapi_cuda.h"
 #include "alphasparse/spdef.h"
@@ -20,6 +21,23 @@ cudaStream_t current_stream();
 alphasparse_cuda_alg_t forced_algorithm();
 void count_launch(int n = 1);
 void record_cuda_error(cudaError_t e, const char *what);
+
+// Tuning values of the analysis (alphasparse_cuda_set_option / ALPHASPARSE_CUDA_OPTIONS); each has a
+// default that measurements on B200 chose, tests shrink them to reach every branch on small matrices.
+enum Option {
+    kOptBandEnable = 0,   // 1: long rows of a skewed matrix go through the column-band kernel
+    kOptBandBytes,        // bytes of x one column band stages in shared memory
+    kOptBandMinSeg,       // a row is long when its elements average at least this many per band
+    kOptBandMinRows,      // fewer long rows than this: not worth a second kernel
+    kOptBandMinSharePct,  // long rows must hold at least this share of the stored elements
+    kOptBandSplits,       // thread blocks per band (0: chosen from the band count)
+    kOptBandOverlap,      // 1: the band kernel runs on a second stream beside the merge kernel
+    kOptBandVariant,      // shape of the band kernel (measurement aid)
+    kOptSpmmColBlocks,    // column blocks of the row-major dense-block product (0: chosen from the size of X)
+    kOptSpmmBlockBytes,   // bytes of X one column block may span when the count is chosen automatically
+    kOptCount
+};
+int64_t option(Option o);
 
 // Every device allocation of the library goes through here: cudaMalloc, except that a test can ask
 // for the n-th allocation from now on to fail (alphasparse_cuda_debug_fail_alloc), which is how the
@@ -77,6 +95,24 @@ struct MergeCoord {
     int nz;   // stored elements consumed before this point
 };
 
+// Long rows of a skewed matrix, handled by the column-band kernel (spmv_band.cu).  Position p of the
+// list is row `row[p]`, of which the elements [seg[0*rows+p], seg[bands*rows+p]) -- the part covered by
+// merge tiles lying wholly inside the row -- are multiplied band by band; seg[b*rows+p] is the first of
+// them whose column is >= b*width.
+struct BandTables {
+    int rows = 0;       // long rows
+    int bands = 0;      // column bands of `width` columns
+    int width = 0;
+    int splits = 1;     // thread blocks per band; block (b, s) takes positions [s*chunk, (s+1)*chunk)
+    int chunk = 0;
+    int64_t elements = 0;  // stored elements handled here
+    int *d_row = nullptr;      // rows
+    int *d_seg = nullptr;      // (bands + 1) * rows
+    void *d_partial = nullptr; // rows * bands sums, written by every call
+    cudaStream_t side = nullptr;  // second stream + fork / join events when the kernels overlap
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+};
+
 struct DeviceCtx {
     uint64_t magic = kCtxMagic;
     int device = 0;
@@ -104,6 +140,9 @@ struct DeviceCtx {
     int *d_carry_row = nullptr;    // merge_tiles
     void *d_carry_val = nullptr;   // merge_tiles
     int *d_sched = nullptr;            // block -> tile order of the merge kernel, or null (tile_key_kernel)
+    int64_t sched_tiles = 0;           // tiles the merge kernel runs (= merge_tiles unless long rows are banded)
+    bool carry_stale = false;          // a run over ALL tiles wrote carries for tiles the schedule leaves out
+    BandTables band;                   // long rows taken out of the merge tiles (spmv_band.cu); rows == 0: none
     unsigned *d_chunk_done = nullptr;  // per chunk of kPushChunkTiles tiles (exchange calls only)
 
     int *d_status = nullptr;  // error word set by kernels whose bounded waits ran out (0 = fine)
@@ -155,6 +194,17 @@ alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T 
                                  const RowWindow *window = nullptr);
 
 // Copies src[0 .. rows) to element push.row_off of every buffer in push.dst (peer-mapped or local).
+// Column-band path for long rows (spmv_band.cu).  build: called by the analysis once the merge tiles exist,
+// with the tile table copied to the host; marks in `skip` the tiles it takes over.  launch_band: partial sums
+// per (long row, band); launch_band_reduce: y[row] += alpha * (sum of the row's partials), after the merge
+// kernel and its fix-up have written y.
+alphasparse_status_t band_build(DeviceCtx *ctx, const MergeCoord *h_tile, std::vector<char> &skip, cudaStream_t st);
+void band_destroy(BandTables &b);
+template <typename T>
+void launch_band(DeviceCtx *ctx, const T *x, cudaStream_t st);
+template <typename T>
+void launch_band_reduce(DeviceCtx *ctx, T alpha, T *y, cudaStream_t st);
+
 template <typename T>
 void launch_push_rows(int64_t rows, const T *src, const PeerPush &push, cudaStream_t stream);
 

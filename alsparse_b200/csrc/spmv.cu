@@ -742,33 +742,55 @@ static bool schedule_disabled() {
     return off;
 }
 
+// Decides which tiles the merge kernel runs and in which order.  Tiles covered by the column-band path
+// (band_build) drop out; the remaining single-row tiles are taken in the order of their first column when
+// x is large (tile_key_kernel).  Leaves d_sched null when the natural order over all tiles is what is wanted.
 static alphasparse_status_t build_tile_schedule(DeviceCtx *ctx, cudaStream_t st) {
     const size_t tsz = ctx->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE ? 8 : 4;
     const long long tiles = ctx->merge_tiles;
-    if (schedule_disabled() || tiles < 2 || (size_t)ctx->cols * tsz < kScheduleMinXBytes) return ALPHA_SPARSE_STATUS_SUCCESS;
-    int *d_key = nullptr;
-    ASB_CUDA_OR(device_alloc(&d_key, sizeof(int) * (size_t)tiles), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-    tile_key_kernel<<<(unsigned)((tiles + 255) / 256), 256, 0, st>>>(tiles, ctx->d_tile, ctx->d_col, d_key);
-    count_launch();
-    std::vector<int> key((size_t)tiles), order((size_t)tiles);
-    cudaError_t e = cudaMemcpyAsync(key.data(), d_key, sizeof(int) * (size_t)tiles, cudaMemcpyDeviceToHost, st);
+    ctx->sched_tiles = tiles;
+    if (tiles < 2) return ALPHA_SPARSE_STATUS_SUCCESS;
+    std::vector<MergeCoord> h_tile((size_t)tiles + 1);
+    cudaError_t e = cudaMemcpyAsync(h_tile.data(), ctx->d_tile, sizeof(MergeCoord) * ((size_t)tiles + 1),
+                                    cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) {
-        cudaFree(d_key);
         record_cuda_error(e, "tile schedule");
         return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
     }
+    std::vector<char> skip((size_t)tiles, 0);
+    alphasparse_status_t s = band_build(ctx, h_tile.data(), skip, st);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    const bool banded = ctx->band.rows > 0;
+    const bool by_column = !schedule_disabled() && (size_t)ctx->cols * tsz >= kScheduleMinXBytes;
+    if (!banded && !by_column) return ALPHA_SPARSE_STATUS_SUCCESS;
+
+    std::vector<int> order;
+    order.reserve((size_t)tiles);
     long long single = 0;
     for (long long t = 0; t < tiles; t++) {
-        order[(size_t)t] = (int)t;
-        single += key[(size_t)t] >= 0;
+        if (skip[(size_t)t]) continue;
+        order.push_back((int)t);
+        single += h_tile[(size_t)t].row == h_tile[(size_t)t + 1].row;
     }
-    if (single * 8 < tiles) {  // fewer than one tile in eight: not worth a level of indirection
-        cudaFree(d_key);
-        return ALPHA_SPARSE_STATUS_SUCCESS;
+    const bool sort_it = by_column && single * 8 >= (long long)order.size();  // fewer than one tile in eight: leave it
+    if (!banded && !sort_it) return ALPHA_SPARSE_STATUS_SUCCESS;
+    int *d_key = nullptr;
+    ASB_CUDA_OR(device_alloc(&d_key, sizeof(int) * (size_t)tiles), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    if (sort_it) {
+        tile_key_kernel<<<(unsigned)((tiles + 255) / 256), 256, 0, st>>>(tiles, ctx->d_tile, ctx->d_col, d_key);
+        count_launch();
+        std::vector<int> key((size_t)tiles);
+        e = cudaMemcpyAsync(key.data(), d_key, sizeof(int) * (size_t)tiles, cudaMemcpyDeviceToHost, st);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+        if (e != cudaSuccess) {
+            cudaFree(d_key);
+            record_cuda_error(e, "tile schedule");
+            return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+        }
+        std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return key[(size_t)a] < key[(size_t)b]; });
     }
-    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return key[(size_t)a] < key[(size_t)b]; });
-    e = cudaMemcpyAsync(d_key, order.data(), sizeof(int) * (size_t)tiles, cudaMemcpyHostToDevice, st);
+    e = cudaMemcpyAsync(d_key, order.data(), sizeof(int) * order.size(), cudaMemcpyHostToDevice, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) {
         cudaFree(d_key);
@@ -776,7 +798,66 @@ static alphasparse_status_t build_tile_schedule(DeviceCtx *ctx, cudaStream_t st)
         return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
     }
     ctx->d_sched = d_key;
+    ctx->sched_tiles = (long long)order.size();
     ctx->device_bytes += (int64_t)(sizeof(int) * (size_t)tiles);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+// Merge-path tables of a handle: tile coordinates, carry arrays, chunk counters, block schedule and the
+// column-band tables.  Everything is built into `tmp` and handed to the handle only when all of it exists,
+// so a failure half-way (alphasparse_optimize on a live handle) leaves the handle as it was.
+static alphasparse_status_t build_merge_tables(DeviceCtx *ctx, cudaStream_t st) {
+    const int ipt = (ctx->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE) ? kMergeItemsD : kMergeItemsS;
+    const size_t tsz = (ctx->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE) ? 8 : 4;
+    const int items = kMergeThreads * ipt;
+    const int64_t total = ctx->rows + ctx->nnz;
+    const int64_t tiles = (total + items - 1) / items;
+    const size_t nchunks = (size_t)(tiles + kPushChunkTiles - 1) / kPushChunkTiles;
+    MergeCoord *d_tile = nullptr;
+    int *d_carry_row = nullptr;
+    void *d_carry_val = nullptr;
+    unsigned *d_chunk_done = nullptr;
+    auto undo = [&] {
+        cudaFree(d_tile), cudaFree(d_carry_row), cudaFree(d_carry_val), cudaFree(d_chunk_done);
+        cudaFree(ctx->d_sched);
+        ctx->d_sched = nullptr;
+        band_destroy(ctx->band);
+        ctx->d_tile = nullptr, ctx->d_carry_row = nullptr, ctx->d_carry_val = nullptr, ctx->d_chunk_done = nullptr;
+        ctx->merge_tiles = 0, ctx->sched_tiles = 0;
+    };
+#define TRY(expr, status)                 \
+    do {                                  \
+        cudaError_t _e = (expr);          \
+        if (_e != cudaSuccess) {          \
+            record_cuda_error(_e, #expr); \
+            undo();                       \
+            return (status);              \
+        }                                 \
+    } while (0)
+    TRY(device_alloc(&d_tile, sizeof(MergeCoord) * (size_t)(tiles + 1)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_carry_row, sizeof(int) * (size_t)tiles), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_carry_val, tsz * (size_t)tiles), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_chunk_done, sizeof(unsigned) * nchunks), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMemsetAsync(d_chunk_done, 0, sizeof(unsigned) * nchunks, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    // 0x7f7f7f7f lies beyond any row: the fix-up kernel ignores tiles that never ran
+    TRY(cudaMemsetAsync(d_carry_row, 0x7f, sizeof(int) * (size_t)tiles, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    const int threads = 256;
+    const int blocks = (int)((tiles + 1 + threads - 1) / threads);
+    merge_tiles_kernel<<<blocks, threads, 0, st>>>((int)ctx->rows, (int)ctx->nnz, ctx->d_row_ptr, items, tiles, d_tile);
+    count_launch();
+    TRY(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+#undef TRY
+    // the schedule and the band tables read these through the handle
+    ctx->merge_items = items, ctx->merge_tiles = tiles;
+    ctx->d_tile = d_tile, ctx->d_carry_row = d_carry_row, ctx->d_carry_val = d_carry_val, ctx->d_chunk_done = d_chunk_done;
+    ctx->carry_stale = false;
+    alphasparse_status_t s = build_tile_schedule(ctx, st);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) {
+        undo();
+        return s;
+    }
+    ctx->device_bytes += (int64_t)(sizeof(MergeCoord) * (size_t)(tiles + 1) + (sizeof(int) + tsz) * (size_t)tiles);
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
@@ -839,37 +920,12 @@ alphasparse_status_t ctx_analyse(DeviceCtx *ctx) {
                                                   // very short rows: a whole lane group per row is wasteful
         else alg = ALPHA_SPARSE_CUDA_ALG_VECTOR;
     }
-    ctx->algorithm = alg;
-
     if (alg == ALPHA_SPARSE_CUDA_ALG_MERGE && ctx->d_tile == nullptr) {
-        const int ipt = (ctx->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE) ? kMergeItemsD : kMergeItemsS;
-        const size_t tsz = (ctx->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE) ? 8 : 4;
-        ctx->merge_items = kMergeThreads * ipt;
-        const int64_t total = ctx->rows + ctx->nnz;
-        ctx->merge_tiles = (total + ctx->merge_items - 1) / ctx->merge_items;
-        ASB_CUDA_OR(device_alloc(&ctx->d_tile, sizeof(MergeCoord) * (size_t)(ctx->merge_tiles + 1)),
-                    ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-        ASB_CUDA_OR(device_alloc(&ctx->d_carry_row, sizeof(int) * (size_t)ctx->merge_tiles),
-                    ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-        ASB_CUDA_OR(device_alloc(&ctx->d_carry_val, tsz * (size_t)ctx->merge_tiles),
-                    ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-        const size_t nchunks = (size_t)(ctx->merge_tiles + kPushChunkTiles - 1) / kPushChunkTiles;
-        ASB_CUDA_OR(device_alloc(&ctx->d_chunk_done, sizeof(unsigned) * nchunks), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-        ASB_CUDA_OR(cudaMemsetAsync(ctx->d_chunk_done, 0, sizeof(unsigned) * nchunks, st),
-                    ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
-        ctx->device_bytes += (int64_t)(sizeof(MergeCoord) * (size_t)(ctx->merge_tiles + 1) +
-                                       (sizeof(int) + tsz) * (size_t)ctx->merge_tiles);
-        const int threads = 256;
-        const int blocks = (int)((ctx->merge_tiles + 1 + threads - 1) / threads);
-        merge_tiles_kernel<<<blocks, threads, 0, st>>>((int)ctx->rows, (int)ctx->nnz, ctx->d_row_ptr,
-                                                       ctx->merge_items, ctx->merge_tiles,
-                                                       ctx->d_tile);
-        count_launch();
-        ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
-        ASB_CUDA_OR(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
-        alphasparse_status_t s = build_tile_schedule(ctx, st);
+        // on failure the handle keeps the algorithm it had (or the vector kernel, which needs no tables)
+        alphasparse_status_t s = build_merge_tables(ctx, st);
         if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     }
+    ctx->algorithm = alg;
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
@@ -899,20 +955,49 @@ static void launch_merge_as(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, c
                             const PeerPush &push) {
     const T *val = static_cast<const T *>(ctx->d_val);
     T *carry = static_cast<T *>(ctx->d_carry_val);
-    // In-kernel delivery wants chunks of neighbouring tiles to finish together: no schedule there.
+    // In-kernel delivery wants chunks of neighbouring tiles to finish together: every tile, natural order,
+    // and therefore no column-band path either.
+    const bool banded = !PUSH && ctx->band.rows > 0;
     const int *sched = PUSH ? nullptr : ctx->d_sched;
-    const unsigned blocks = (unsigned)ctx->merge_tiles;
+    const unsigned blocks = (unsigned)(PUSH ? ctx->merge_tiles : ctx->sched_tiles);
+    if (PUSH && ctx->band.rows > 0) ctx->carry_stale = true;  // tiles the schedule leaves out write carries now
+    if (banded && ctx->carry_stale) {
+        cudaMemsetAsync(ctx->d_carry_row, 0x7f, sizeof(int) * (size_t)ctx->merge_tiles, st);
+        ctx->carry_stale = false;
+    }
     if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
+    BandTables &bt = ctx->band;
+    cudaStream_t band_st = st;
+    if (banded) {
+        // The band kernel only reads the matrix and x and writes its own partial sums: with a second stream
+        // it runs beside the merge kernel (one is bound by HBM, the other by L2 requests).
+        if (bt.side) {
+            cudaEventRecord(bt.ev_fork, st);
+            cudaStreamWaitEvent(bt.side, bt.ev_fork, 0);
+            band_st = bt.side;
+        }
+        launch_band<T>(ctx, x, band_st);
+    }
     PushArg<PUSH> arg{};
     if constexpr (PUSH) arg = push;
-    spmv_merge_kernel<T, kMergeThreads, IPT, HAS_BETA, PUSH><<<blocks, kMergeThreads, 0, st>>>(
-        (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta, ctx->d_tile, sched,
-        ctx->d_carry_row, carry, arg);
-    if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
+    if (blocks > 0)
+        spmv_merge_kernel<T, kMergeThreads, IPT, HAS_BETA, PUSH><<<blocks, kMergeThreads, 0, st>>>(
+            (int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta, ctx->d_tile, sched,
+            ctx->d_carry_row, carry, arg);
+    if (ctx->profile && !banded) cudaEventRecord(ctx->ev_stop, st);
     const unsigned fblocks = (unsigned)((ctx->merge_tiles + 255) / 256);
     spmv_merge_fixup_kernel<T, PUSH><<<fblocks, 256, 0, st>>>((int)ctx->rows, ctx->merge_tiles,
                                                              ctx->d_carry_row, carry, y, alpha, push);
     count_launch(2);
+    if (banded) {
+        if (bt.side) {
+            cudaEventRecord(bt.ev_join, bt.side);
+            cudaStreamWaitEvent(st, bt.ev_join, 0);
+        }
+        launch_band_reduce<T>(ctx, alpha, y, st);
+        // with two large kernels the timed span is the whole product
+        if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
+    }
 }
 
 template <typename T, int IPT>

@@ -1,0 +1,456 @@
+// Column-band SpMV for the long rows of a skewed matrix (sm_100a).
+//
+// Every stored element of a row with unstructured columns gathers one x element from a different
+// cache line, and a B200 SM gets roughly one such line per clock out of L2: for a matrix whose
+// elements sit mostly in rows of tens of thousands of entries that rate, not HBM, sets the time.
+// A long row with ascending columns can do better.  Cut the columns into bands of `width`; the part
+// of the row that falls into one band is a contiguous run of its elements (a "segment"), and all of
+// its gathers land in the `width` x elements of that band.  So a thread block stages one band of x
+// in shared memory with coalesced loads (64 KB), and then runs through the segments that ALL long
+// rows have in this band, gathering from shared memory at many elements per clock instead of one.
+// The col / val streams are still read exactly once, coalesced, which leaves HBM as the limit.
+//
+// Each (row, band) segment yields one partial sum; a second kernel adds a row's partials in band
+// order and accumulates alpha times the total into y.  No atomics: the result does not depend on
+// scheduling.  The analysis decides which rows qualify (band_build) and removes the merge tiles they
+// cover from the merge kernel's schedule; what is left of such a row at its two ends (less than a
+// tile each) stays with the merge kernel, which also applies beta.
+//
+// Arithmetic defined by the reference's gemv kernel, src/plain/kernel/level2/mv/gemv/gemv_x_csr_plain.c:4-24
+// (same products, another summation order, inside the parity tolerance).  The reference's device
+// build has one kernel shape for all rows (src/kernel/dcu/level2/mv/csrmv/dcu_gemv_vector.h:59-182
+// picks a sub-wavefront width from nnz/m); it has no counterpart of this path.
+#include <algorithm>
+#include <numeric>
+#include <vector>
+
+#include "internal.h"
+
+namespace asb {
+
+constexpr int kBandThreads = 512;
+constexpr int kBandLanes = 8;  // lanes per segment (sizing of the splits)
+
+// Block (b, s): band b, list positions [s*chunk, (s+1)*chunk).  A group of G lanes takes R segments
+// at a time and keeps U (col, val) pairs per segment in flight in every lane.
+template <typename T, int G, int U, int R, int NT>
+__global__ void __launch_bounds__(NT)
+    spmv_band_kernel(int cols, int width, int bands, int nl, int chunk, const int *__restrict__ seg,
+                     const int *__restrict__ col, const T *__restrict__ val, const T *__restrict__ x,
+                     T *__restrict__ partial) {
+    extern __shared__ __align__(16) unsigned char band_smem[];
+    T *sx = reinterpret_cast<T *>(band_smem);
+    const int b = blockIdx.x, s = blockIdx.y, tid = threadIdx.x;
+    const long long c0l = (long long)b * width;
+    const int c0 = (int)c0l;
+    const int n = (int)(cols - c0l < width ? cols - c0l : width);
+    const T *xb = x + c0l;
+
+    if ((reinterpret_cast<uintptr_t>(xb) & 15) == 0) {
+        constexpr int per = 16 / (int)sizeof(T);
+        const int nv = n / per;
+        const int4 *src = reinterpret_cast<const int4 *>(xb);
+        int4 *dst = reinterpret_cast<int4 *>(sx);
+        for (int i = tid; i < nv; i += NT) dst[i] = __ldg(src + i);
+        for (int i = nv * per + tid; i < n; i += NT) sx[i] = __ldg(xb + i);
+    } else {
+        for (int i = tid; i < n; i += NT) sx[i] = __ldg(xb + i);
+    }
+    __syncthreads();
+
+    constexpr int NG = NT / G;
+    const int g = tid / G, gl = tid % G;
+    const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (((tid & 31) / G) * G));
+    const int p1 = min(nl, (s + 1) * chunk);
+    const int *seg_lo = seg + (size_t)b * nl, *seg_hi = seg_lo + nl;
+
+    for (int p = s * chunk + g; p < p1; p += NG * R) {
+        int k[R], e[R];
+        T acc[R];
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const int pp = p + r * NG;
+            k[r] = 0, e[r] = 0, acc[r] = T(0);
+            if (pp < p1) {
+                k[r] = __ldg(seg_lo + pp) + gl;
+                e[r] = __ldg(seg_hi + pp);
+            }
+        }
+        bool more = true;
+        while (more) {
+            int cc[R][U];
+            T vv[R][U];
+#pragma unroll
+            for (int r = 0; r < R; r++)
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int kk = k[r] + u * G;
+                    if (kk < e[r]) {
+                        cc[r][u] = __ldcs(col + kk);
+                        vv[r][u] = __ldcs(val + kk);
+                    }
+                }
+            more = false;
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+#pragma unroll
+                for (int u = 0; u < U; u++)
+                    if (k[r] + u * G < e[r]) acc[r] = fma(vv[r][u], sx[cc[r][u] - c0], acc[r]);
+                k[r] += G * U;
+                more |= k[r] < e[r];
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+#pragma unroll
+            for (int o = G / 2; o > 0; o >>= 1) acc[r] += __shfl_xor_sync(gmask, acc[r], o, G);
+            const int pp = p + r * NG;
+            if (gl == 0 && pp < p1) partial[(size_t)pp * bands + b] = acc[r];
+        }
+    }
+}
+
+// The same work with 16-byte loads: a lane takes whole aligned quads (four consecutive stored elements: one
+// int4 of columns, one or two 16-byte loads of values) and masks the elements that fall outside the
+// segment, as the vector SpMV kernel does for rows.  Four times the bytes in flight per load instruction,
+// which is what a kernel that streams the matrix once needs to cover the latency of HBM.
+template <typename T>
+struct BandQuad {
+    T v[4];
+};
+__device__ __forceinline__ BandQuad<float> band_load_val(const float *__restrict__ val, int q) {
+    const float4 t = __ldcs(reinterpret_cast<const float4 *>(val) + q);
+    return {{t.x, t.y, t.z, t.w}};
+}
+__device__ __forceinline__ BandQuad<double> band_load_val(const double *__restrict__ val, int q) {
+    const double2 a = __ldcs(reinterpret_cast<const double2 *>(val) + 2 * (size_t)q);
+    const double2 b = __ldcs(reinterpret_cast<const double2 *>(val) + 2 * (size_t)q + 1);
+    return {{a.x, a.y, b.x, b.y}};
+}
+
+template <typename T, int G, int U, int R, int NT>
+__global__ void __launch_bounds__(NT)
+    spmv_band_quad_kernel(int cols, int width, int bands, int nl, int chunk, const int *__restrict__ seg,
+                          const int *__restrict__ col, const T *__restrict__ val, const T *__restrict__ x,
+                          T *__restrict__ partial) {
+    extern __shared__ __align__(16) unsigned char band_smem[];
+    T *sx = reinterpret_cast<T *>(band_smem);
+    const int b = blockIdx.x, s = blockIdx.y, tid = threadIdx.x;
+    const long long c0l = (long long)b * width;
+    const int c0 = (int)c0l;
+    const int n = (int)(cols - c0l < width ? cols - c0l : width);
+    const T *xb = x + c0l;
+    if ((reinterpret_cast<uintptr_t>(xb) & 15) == 0) {
+        constexpr int per = 16 / (int)sizeof(T);
+        const int nv = n / per;
+        const int4 *src = reinterpret_cast<const int4 *>(xb);
+        int4 *dst = reinterpret_cast<int4 *>(sx);
+        for (int i = tid; i < nv; i += NT) dst[i] = __ldg(src + i);
+        for (int i = nv * per + tid; i < n; i += NT) sx[i] = __ldg(xb + i);
+    } else {
+        for (int i = tid; i < n; i += NT) sx[i] = __ldg(xb + i);
+    }
+    __syncthreads();
+
+    constexpr int NG = NT / G;
+    const int g = tid / G, gl = tid % G;
+    const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (((tid & 31) / G) * G));
+    const int p1 = min(nl, (s + 1) * chunk);
+    const int *seg_lo = seg + (size_t)b * nl, *seg_hi = seg_lo + nl;
+
+    for (int p = s * chunk + g; p < p1; p += NG * R) {
+        int a[R], e[R], q[R];
+        T acc[R];
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            const int pp = p + r * NG;
+            a[r] = 0, e[r] = 0, acc[r] = T(0);
+            if (pp < p1) {
+                a[r] = __ldg(seg_lo + pp);
+                e[r] = __ldg(seg_hi + pp);
+            }
+            q[r] = (a[r] >> 2) + gl;
+        }
+        bool more = true;
+        while (more) {
+            int4 cc[R][U];
+            BandQuad<T> vv[R][U];
+#pragma unroll
+            for (int r = 0; r < R; r++)
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int qq = q[r] + u * G;
+                    if ((qq << 2) < e[r]) {
+                        cc[r][u] = __ldcs(reinterpret_cast<const int4 *>(col) + qq);
+                        vv[r][u] = band_load_val(val, qq);
+                    }
+                }
+            more = false;
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int base = (q[r] + u * G) << 2;
+                    if (base < e[r]) {
+                        if (base + 0 >= a[r]) acc[r] = fma(vv[r][u].v[0], sx[cc[r][u].x - c0], acc[r]);
+                        if (base + 1 >= a[r] && base + 1 < e[r]) acc[r] = fma(vv[r][u].v[1], sx[cc[r][u].y - c0], acc[r]);
+                        if (base + 2 >= a[r] && base + 2 < e[r]) acc[r] = fma(vv[r][u].v[2], sx[cc[r][u].z - c0], acc[r]);
+                        if (base + 3 >= a[r] && base + 3 < e[r]) acc[r] = fma(vv[r][u].v[3], sx[cc[r][u].w - c0], acc[r]);
+                    }
+                }
+                q[r] += G * U;
+                more |= (q[r] << 2) < e[r];
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+#pragma unroll
+            for (int o = G / 2; o > 0; o >>= 1) acc[r] += __shfl_xor_sync(gmask, acc[r], o, G);
+            const int pp = p + r * NG;
+            if (gl == 0 && pp < p1) partial[(size_t)pp * bands + b] = acc[r];
+        }
+    }
+}
+
+// One warp per long row: its partial sums in band order (lane j takes bands j, j+32, ..., then a fixed
+// tree over the lanes), alpha times the total added to what the merge kernel and its fix-up left in y.
+template <typename T>
+__global__ void spmv_band_reduce_kernel(int nl, int bands, const int *__restrict__ row,
+                                        const T *__restrict__ partial, T *__restrict__ y, T alpha) {
+    const int p = (int)(((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+    const int lane = threadIdx.x & 31;
+    if (p >= nl) return;
+    const T *src = partial + (size_t)p * bands;
+    T acc = T(0);
+    for (int b = lane; b < bands; b += 32) acc += src[b];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+        const int r = row[p];
+        y[r] = fma(alpha, acc, y[r]);
+    }
+}
+
+// flag[p] = 1 when the elements [a[p], e[p]) are not in ascending column order (such a row cannot be cut
+// into segments by searching its columns).
+__global__ void band_sorted_kernel(const int *__restrict__ a, const int *__restrict__ e, const int *__restrict__ col,
+                                   int *__restrict__ flag) {
+    const int p = blockIdx.x;
+    int bad = 0;
+    for (long long k = (long long)a[p] + threadIdx.x; k + 1 < e[p]; k += blockDim.x) bad |= col[k] > col[k + 1];
+    if (__syncthreads_or(bad) && threadIdx.x == 0) flag[p] = 1;
+}
+
+// seg[b * nl + p] = first element of [a[p], e[p]) whose column is >= b * width (b = 0 .. bands).
+__global__ void band_seg_kernel(int nl, int bands, int width, const int *__restrict__ a, const int *__restrict__ e,
+                                const int *__restrict__ col, int *__restrict__ seg) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)nl * (bands + 1)) return;
+    const int b = (int)(i / nl), p = (int)(i % nl);
+    const long long want = (long long)b * width;
+    int lo = a[p], hi = e[p];
+    if (b == 0) hi = lo;
+    else if (b == bands) lo = hi;
+    while (lo < hi) {
+        const int mid = lo + ((hi - lo) >> 1);
+        if ((long long)col[mid] < want) lo = mid + 1;
+        else hi = mid;
+    }
+    seg[i] = lo;
+}
+
+void band_destroy(BandTables &b) {
+    cudaFree(b.d_row);
+    cudaFree(b.d_seg);
+    cudaFree(b.d_partial);
+    if (b.side) cudaStreamDestroy(b.side);
+    if (b.ev_fork) cudaEventDestroy(b.ev_fork);
+    if (b.ev_join) cudaEventDestroy(b.ev_join);
+    b = BandTables{};
+}
+
+alphasparse_status_t band_build(DeviceCtx *ctx, const MergeCoord *h_tile, std::vector<char> &skip, cudaStream_t st) {
+    if (!option(kOptBandEnable)) return ALPHA_SPARSE_STATUS_SUCCESS;
+    const size_t tsz = ctx->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE ? 8 : 4;
+    const int64_t tiles = ctx->merge_tiles;
+    int64_t width = option(kOptBandBytes) / (int64_t)tsz & ~31ll;
+    if (width < 32) width = 32;
+    if (width * (int64_t)tsz > 200 * 1024) width = (200 * 1024 / (int64_t)tsz) & ~31ll;
+    const int64_t bands = (ctx->cols + width - 1) / width;
+    if (bands < 1 || bands > (1 << 20)) return ALPHA_SPARSE_STATUS_SUCCESS;
+    const int64_t min_len = std::max<int64_t>(1, option(kOptBandMinSeg) * bands);
+
+    // Candidates: maximal runs of tiles that lie wholly inside one row.
+    struct Cand {
+        int row, a, e;
+        int64_t t0, t1;
+    };
+    std::vector<Cand> cand;
+    int64_t covered = 0;
+    for (int64_t t = 0; t < tiles;) {
+        if (h_tile[t].row != h_tile[t + 1].row || h_tile[t].row >= ctx->rows) {
+            t++;
+            continue;
+        }
+        int64_t u = t + 1;
+        while (u < tiles && h_tile[u + 1].row == h_tile[t].row) u++;
+        const int a = h_tile[t].nz, e = h_tile[u].nz;
+        if ((int64_t)e - a >= min_len) {
+            cand.push_back({h_tile[t].row, a, e, t, u});
+            covered += e - a;
+        }
+        t = u;
+    }
+    auto worth = [&] {
+        return (int64_t)cand.size() >= std::max<int64_t>(1, option(kOptBandMinRows)) &&
+               covered * 100 >= ctx->nnz * option(kOptBandMinSharePct);
+    };
+    if (cand.empty() || !worth()) return ALPHA_SPARSE_STATUS_SUCCESS;
+
+    // Longest first, dealt round-robin to the `splits` blocks of a band: equal work per block, and the
+    // lane groups of a warp meet segments of similar length.
+    std::stable_sort(cand.begin(), cand.end(), [](const Cand &p, const Cand &q) { return p.e - p.a > q.e - q.a; });
+    int nl = (int)cand.size();
+    std::vector<int> h_a((size_t)nl), h_e((size_t)nl), h_flag((size_t)nl, 0);
+    for (int i = 0; i < nl; i++) h_a[(size_t)i] = cand[(size_t)i].a, h_e[(size_t)i] = cand[(size_t)i].e;
+
+    int *d_a = nullptr, *d_e = nullptr, *d_flag = nullptr;
+    BandTables bt;
+    auto fail = [&](alphasparse_status_t s) {
+        cudaFree(d_a), cudaFree(d_e), cudaFree(d_flag);
+        band_destroy(bt);
+        return s;
+    };
+#define TRY(expr, status)                 \
+    do {                                  \
+        cudaError_t _e = (expr);          \
+        if (_e != cudaSuccess) {          \
+            record_cuda_error(_e, #expr); \
+            return fail(status);          \
+        }                                 \
+    } while (0)
+    TRY(device_alloc(&d_a, sizeof(int) * (size_t)nl), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_e, sizeof(int) * (size_t)nl), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&d_flag, sizeof(int) * (size_t)nl), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMemcpyAsync(d_a, h_a.data(), sizeof(int) * (size_t)nl, cudaMemcpyHostToDevice, st),
+        ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaMemcpyAsync(d_e, h_e.data(), sizeof(int) * (size_t)nl, cudaMemcpyHostToDevice, st),
+        ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaMemsetAsync(d_flag, 0, sizeof(int) * (size_t)nl, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    band_sorted_kernel<<<(unsigned)nl, 256, 0, st>>>(d_a, d_e, ctx->d_col, d_flag);
+    count_launch();
+    TRY(cudaMemcpyAsync(h_flag.data(), d_flag, sizeof(int) * (size_t)nl, cudaMemcpyDeviceToHost, st),
+        ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    {
+        size_t keep = 0;
+        for (int i = 0; i < nl; i++) {
+            if (h_flag[(size_t)i]) {
+                covered -= cand[(size_t)i].e - cand[(size_t)i].a;
+                continue;
+            }
+            cand[keep++] = cand[(size_t)i];
+        }
+        cand.resize(keep);
+        nl = (int)keep;
+    }
+    if (cand.empty() || !worth()) return fail(ALPHA_SPARSE_STATUS_SUCCESS);
+
+    int64_t splits = option(kOptBandSplits);
+    if (splits <= 0) splits = (148 * 3 * 8 + bands - 1) / bands;  // about eight waves of blocks
+    splits = std::max<int64_t>(1, std::min<int64_t>(splits, std::max(1, nl / (kBandThreads / kBandLanes))));
+    splits = std::min<int64_t>(splits, 65535);
+    const int chunk = (int)((nl + splits - 1) / splits);
+    std::vector<int> h_row((size_t)nl);
+    {
+        // sorted index i sits in split i % splits at place i / splits
+        std::vector<int> pos_of((size_t)nl);
+        std::vector<int> filled((size_t)splits, 0);
+        for (int i = 0; i < nl; i++) {
+            const int s = (int)(i % splits);
+            pos_of[(size_t)i] = s * chunk + filled[(size_t)s]++;
+        }
+        // the last splits may hold fewer rows than `chunk`: positions must stay dense, so renumber
+        std::vector<int> order((size_t)nl);
+        std::iota(order.begin(), order.end(), 0);
+        std::stable_sort(order.begin(), order.end(), [&](int p, int q) { return pos_of[(size_t)p] < pos_of[(size_t)q]; });
+        for (int p = 0; p < nl; p++) {
+            const Cand &c = cand[(size_t)order[(size_t)p]];
+            h_row[(size_t)p] = c.row, h_a[(size_t)p] = c.a, h_e[(size_t)p] = c.e;
+        }
+    }
+
+    bt.rows = nl, bt.bands = (int)bands, bt.width = (int)width, bt.splits = (int)splits, bt.chunk = chunk;
+    bt.elements = covered;
+    TRY(device_alloc(&bt.d_row, sizeof(int) * (size_t)nl), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&bt.d_seg, sizeof(int) * (size_t)nl * (size_t)(bands + 1)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&bt.d_partial, tsz * (size_t)nl * (size_t)bands), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMemcpyAsync(bt.d_row, h_row.data(), sizeof(int) * (size_t)nl, cudaMemcpyHostToDevice, st),
+        ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaMemcpyAsync(d_a, h_a.data(), sizeof(int) * (size_t)nl, cudaMemcpyHostToDevice, st),
+        ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaMemcpyAsync(d_e, h_e.data(), sizeof(int) * (size_t)nl, cudaMemcpyHostToDevice, st),
+        ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    const long long cells = (long long)nl * (bands + 1);
+    band_seg_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, st>>>(nl, (int)bands, (int)width, d_a, d_e, ctx->d_col,
+                                                                   bt.d_seg);
+    count_launch();
+    TRY(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    if (option(kOptBandOverlap)) {
+        TRY(cudaStreamCreateWithFlags(&bt.side, cudaStreamNonBlocking), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        TRY(cudaEventCreateWithFlags(&bt.ev_fork, cudaEventDisableTiming), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        TRY(cudaEventCreateWithFlags(&bt.ev_join, cudaEventDisableTiming), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    }
+    TRY(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+#undef TRY
+    cudaFree(d_a), cudaFree(d_e), cudaFree(d_flag);
+    for (const Cand &c : cand)
+        for (int64_t t = c.t0; t < c.t1; t++) skip[(size_t)t] = 1;
+    ctx->band = bt;
+    ctx->device_bytes += (int64_t)(sizeof(int) * (size_t)nl * (size_t)(bands + 2) + tsz * (size_t)nl * (size_t)bands);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+template <typename K, typename T>
+static void launch_band_as(K kernel, int threads, std::atomic<size_t> &granted, DeviceCtx *ctx, const T *x,
+                           cudaStream_t st) {
+    const BandTables &b = ctx->band;
+    const size_t smem = sizeof(T) * (size_t)b.width;
+    if (smem > 48 * 1024 && granted.load() < smem) {  // the opt-in limit belongs to the kernel: only ever raise it
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess)
+            granted.store(200 * 1024);
+    }
+    const dim3 grid((unsigned)b.bands, (unsigned)b.splits);
+    kernel<<<grid, threads, smem, st>>>((int)ctx->cols, b.width, b.bands, b.rows, b.chunk, b.d_seg, ctx->d_col,
+                                        static_cast<const T *>(ctx->d_val), x, static_cast<T *>(b.d_partial));
+    count_launch();
+}
+
+template <typename T>
+void launch_band(DeviceCtx *ctx, const T *x, cudaStream_t st) {
+    static std::atomic<size_t> granted[6] = {{0}, {0}, {0}, {0}, {0}, {0}};
+    switch (option(kOptBandVariant)) {
+        case 1: launch_band_as(spmv_band_quad_kernel<T, 4, 2, 2, 256>, 256, granted[1], ctx, x, st); break;
+        case 2: launch_band_as(spmv_band_quad_kernel<T, 4, 2, 1, 512>, 512, granted[2], ctx, x, st); break;
+        case 3: launch_band_as(spmv_band_quad_kernel<T, 8, 1, 2, 512>, 512, granted[3], ctx, x, st); break;
+        case 4: launch_band_as(spmv_band_quad_kernel<T, 4, 1, 2, 512>, 512, granted[4], ctx, x, st); break;
+        case 5: launch_band_as(spmv_band_quad_kernel<T, 2, 2, 2, 256>, 256, granted[5], ctx, x, st); break;
+        default: launch_band_as(spmv_band_kernel<T, 8, sizeof(T) == 8 ? 2 : 4, 2, 512>, 512, granted[0], ctx, x, st); break;
+    }
+}
+
+template <typename T>
+void launch_band_reduce(DeviceCtx *ctx, T alpha, T *y, cudaStream_t st) {
+    const BandTables &b = ctx->band;
+    const unsigned blocks = (unsigned)(((long long)b.rows * 32 + 255) / 256);
+    spmv_band_reduce_kernel<T><<<blocks, 256, 0, st>>>(b.rows, b.bands, b.d_row, static_cast<const T *>(b.d_partial), y,
+                                                       alpha);
+    count_launch();
+}
+
+template void launch_band<float>(DeviceCtx *, const float *, cudaStream_t);
+template void launch_band<double>(DeviceCtx *, const double *, cudaStream_t);
+template void launch_band_reduce<float>(DeviceCtx *, float, float *, cudaStream_t);
+template void launch_band_reduce<double>(DeviceCtx *, double, double *, cudaStream_t);
+
+}  // namespace asb

@@ -172,6 +172,18 @@ def set_algorithm(alg):
     return capi.load().alphasparse_cuda_set_algorithm(alg)
 
 
+def set_option(name, value):
+    """alphasparse_cuda_set_option: a tuning value of the analysis (negative restores the default)."""
+    return capi.load().alphasparse_cuda_set_option(name.encode(), int(value))
+
+
+def get_option(name):
+    v = C.c_int64()
+    st = capi.load().alphasparse_cuda_get_option(name.encode(), C.byref(v))
+    assert st == SUCCESS, capi.STATUS_NAMES[st]
+    return v.value
+
+
 def launch_count():
     return capi.load().alphasparse_cuda_launch_count()
 

@@ -35,6 +35,21 @@ typedef enum {
  * alphasparse_cuda_mat_info_t.scheduled). */
 alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg);
 
+/* Tuning values read by the analysis of handles created (or re-analysed by alphasparse_optimize) after the
+ * call; a negative value restores the default.  ALPHASPARSE_CUDA_OPTIONS="name=value,..." sets initial values.
+ *   band_enable (1)         long rows of a skewed matrix go through the column-band kernel
+ *   band_bytes (65536)      bytes of x one column band stages in shared memory
+ *   band_min_seg (8)        a row is long when it averages at least this many elements per band
+ *   band_min_rows (128)     fewer long rows than this are left to the merge kernel
+ *   band_min_share_pct (10) ... and so are long rows holding less than this share of the elements
+ *   band_splits (0)         thread blocks per band, 0 = about eight waves of blocks
+ *   band_overlap (1)        the column-band kernel runs on a second stream beside the merge kernel
+ *   spmm_col_blocks (0)     column blocks of the row-major dense-block product, 0 = from the size of X
+ *   spmm_block_bytes (48Mi) bytes of X per column block when the count is chosen automatically
+ * Unknown names return ALPHA_SPARSE_STATUS_INVALID_VALUE. */
+alphasparse_status_t alphasparse_cuda_set_option(const char *name, int64_t value);
+alphasparse_status_t alphasparse_cuda_get_option(const char *name, int64_t *value);
+
 /* What the analysis at handle creation found and chose. */
 typedef struct {
     int64_t rows, cols, nnz;
@@ -46,7 +61,12 @@ typedef struct {
     int64_t merge_tiles;   /* merge kernel: thread blocks per call */
     int64_t device_bytes;  /* device memory held by the handle */
     int32_t device;        /* CUDA device ordinal that owns the device copy */
-    int32_t scheduled;     /* merge kernel: 1 when its blocks take single-row tiles in column order (large x) */
+    int32_t scheduled;     /* merge kernel: 1 when its blocks follow a schedule (column order for large x, and / or
+                              without the tiles the column-band kernel covers) */
+    int32_t band_rows;     /* long rows handled by the column-band kernel (0: none) */
+    int32_t band_count;    /* column bands of band_width columns each */
+    int32_t band_width;
+    int64_t band_elements; /* stored elements the column-band kernel multiplies */
 } alphasparse_cuda_mat_info_t;
 
 alphasparse_status_t alphasparse_cuda_get_mat_info(const alphasparse_matrix_t A,

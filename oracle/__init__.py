@@ -89,6 +89,20 @@ def gemv(kind, rows_start, rows_end, col, val, alpha, x, beta, y, threads=0):
     return y
 
 
+def gemv_exact(rows_start, rows_end, col, val, alpha, x, beta, y0):
+    """The product of the reference's gemv kernel (src/plain/kernel/level2/mv/gemv/gemv_x_csr_plain.c:4-24:
+    y[r] = beta*y[r] + alpha * sum a_rj * x[col_rj]) with every product and sum carried in double precision,
+    returned as float64.  The comparand for single-precision rows so long that the reference's own serial
+    float sum leaves the parity tolerance (1e-5 of the row's sum of |a*x|): against this one the tolerance
+    is spent on the tested kernel alone.  Requires rows_end[r] == rows_start[r+1] (3-array CSR)."""
+    rs, re_ = np.asarray(rows_start, dtype=np.int64), np.asarray(rows_end, dtype=np.int64)
+    prod = np.asarray(val, dtype=np.float64) * np.asarray(x, dtype=np.float64)[np.asarray(col)]
+    # each row summed on its own (differences of one running sum would cancel badly on large matrices)
+    out = np.add.reduceat(np.concatenate([prod, [0.0]]), np.minimum(rs - rs[0], len(prod))) if len(rs) else prod[:0]
+    out = np.where(re_ > rs, out, 0.0)
+    return beta * np.asarray(y0, dtype=np.float64) + alpha * out
+
+
 def gemv_trans(kind, cols, rows_start, rows_end, col, val, alpha, x, beta, y):
     rs, re_, ci = _i(rows_start), _i(rows_end), _i(col)
     getattr(lib(), f"oracle_gemv_csr_trans_{kind}")(len(rs), cols, _a(rs), _a(re_), _a(ci), _a(val), alpha, _a(x),

@@ -3,11 +3,21 @@ import os
 
 import numpy as np
 
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 NP = {"s": np.float32, "d": np.float64}
 # Tolerance of the parity gate: |y - y_ref| <= TOL * (|beta*y0| + |alpha| * sum_j |a_ij * x_j|) per row
 # (1e-5 in single, 1e-12 in double precision).
 TOL = {"s": 1e-5, "d": 1e-12}
+
+
+def reference_dir():
+    """The reference's source tree, when this machine has it: ALPHASPARSE_REFERENCE_DIR, else a checkout
+    named ``reference`` next to this repository.  None when neither exists."""
+    for cand in (os.environ.get("ALPHASPARSE_REFERENCE_DIR"), os.path.join(os.path.dirname(ROOT), "reference")):
+        if cand and os.path.isfile(os.path.join(cand, "include", "alphasparse.h")):
+            return cand
+    return None
 
 
 def golden(name):

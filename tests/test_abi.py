@@ -10,18 +10,20 @@ import numpy as np
 import pytest
 
 from alsparse_b200 import capi, spblas
+from helpers import reference_dir
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 INC = os.path.join(ROOT, "include")
-REF_INC = os.path.join(os.environ.get("ALPHASPARSE_REFERENCE_DIR", "/root/reference"), "include")
+REF_INC = os.path.join(reference_dir() or "", "include")
 
 
 def declared_functions():
     names = set()
-    for h in ("spapi.h", "spapi_cuda.h", "util.h"):
+    for h in ("spapi.h", "spapi_cuda.h", "util.h", "kernel_cuda.h"):
         text = open(os.path.join(INC, "alphasparse", h)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-        names |= set(re.findall(r"\b(alpha\w+|lower_bound_int|balanced_partition_row_by_nnz)\s*\(", text))
+        text = re.sub(r"#define(?:.*\\\n)*.*\n", "", text)   # macros (with their continuation lines) are not exports
+        names |= set(re.findall(r"\b(alpha\w+|args_\w+|gem[vm]_\w+|lower_bound_int|balanced_partition_row_by_nnz)\s*\(", text))
     return {n for n in names if not n.startswith(("alphasparse_status_t", "alphasparse_cuda_alg_t"))}
 
 

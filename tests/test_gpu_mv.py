@@ -497,6 +497,84 @@ def test_merge_blocks_follow_the_column_schedule_when_x_is_large():
     spblas.destroy(B)
 
 
+class _Options:
+    """Sets analysis options for the handles created inside the block and restores the defaults after it."""
+
+    def __init__(self, **kw):
+        self.kw = kw
+
+    def __enter__(self):
+        for k, v in self.kw.items():
+            assert spblas.set_option(k, v) == capi.SUCCESS
+        return self
+
+    def __exit__(self, *exc):
+        for k in self.kw:
+            spblas.set_option(k, -1)
+
+
+@pytest.mark.parametrize("kind", ["s", "d"])
+@pytest.mark.parametrize("overlap", [0, 1])
+def test_long_rows_take_the_column_band_path(kind, overlap):
+    """Row binning of the analysis: rows long enough to average several elements per column band leave the merge
+    tiles and go through the column-band kernel (x bands staged in shared memory).  Tiny limits make a small
+    matrix take every branch: several splits per band, a ragged last band, long rows first / last / adjacent,
+    an unsorted long row (must stay with the merge kernel), all scalar combinations, bit-identical repeats, and
+    a run over all tiles (the delivering form of the merge kernel) in between two banded runs."""
+    cols = 70001
+    body = np.concatenate([[40000], synth.rowlen_zipf(9, 6000, 1.8, 1, 900), [9000, 25000, 3],
+                           synth.rowlen_zipf(10, 3000, 1.8, 1, 50), [12000, 1, 1]])
+    # square (the exchange below wants that): empty rows fill up, the last row is long
+    lens = np.concatenate([body, np.zeros(cols - len(body) - 1), [30000]]).astype(np.int32)
+    m = synth.from_lengths(kind, 9, lens, cols)
+    ptr = m.ptr
+    unsorted_row = 6002                                        # the 25000-element row: swap two of its columns
+    assert ptr[unsorted_row + 1] - ptr[unsorted_row] == 25000
+    a = int(ptr[unsorted_row]) + 7000
+    m.col[a], m.col[a + 1] = m.col[a + 1], m.col[a]
+    m.val[a], m.val[a + 1] = m.val[a + 1], m.val[a]
+    with _Options(band_bytes=4096, band_min_seg=1, band_min_rows=1, band_min_share_pct=0, band_splits=3,
+                  band_overlap=overlap):
+        spblas.set_algorithm(capi.ALG_MERGE)
+        try:
+            A = make_handle(kind, m)
+        finally:
+            spblas.set_algorithm(capi.ALG_AUTO)
+    st, info = spblas.mat_info(A)
+    assert st == capi.SUCCESS and info.algorithm == capi.ALG_MERGE
+    assert info.band_rows == 4 and info.band_width == 4096 // m.val.itemsize, (info.band_rows, info.band_width)
+    assert info.band_count == -(-cols // info.band_width) and info.scheduled == 1
+    tile = 256 * (7 if kind == "d" else 9)
+    assert 40000 + 9000 + 12000 + 30000 - 8 * tile <= info.band_elements <= 40000 + 9000 + 12000 + 30000
+    x, y0 = synth.vector(kind, 9, 1, cols), synth.vector(kind, 9, 2, m.nrows)
+    dx = torch.from_numpy(x).cuda()
+    results = {}
+    for alpha, beta in ((1.0, 0.0), (1.5, 0.5), (-2.0, 1.0), (0.0, 3.0)):
+        y_ref = oracle.gemv_exact(m.rows_start, m.rows_end, m.col, m.val, alpha, x, beta, y0)
+        dy = torch.from_numpy(y0).cuda()
+        assert spblas.mv(kind, 0, alpha, A, spblas.descr(), dx, beta, dy) == capi.SUCCESS
+        y = dy.cpu().numpy()
+        assert_rows_close(kind, y, y_ref, row_scale(m.ptr, m.col, m.val, x, alpha, beta, y0), f"band {kind} {alpha} {beta}")
+        results[(alpha, beta)] = y
+        yh = y0.copy()                                           # host vectors through the same handle
+        assert spblas.mv(kind, 0, alpha, A, spblas.descr(), x, beta, yh) == capi.SUCCESS
+        assert np.array_equal(yh, y)
+    # the delivering merge kernel runs every tile and leaves carries behind for the tiles the schedule skips
+    from alsparse_b200 import multi
+    ex = multi.FusedExchange(kind, np.array([0, m.nrows], np.int32), 0, 1, deliver_after=False)
+    ex.x_tensor().copy_(dx)
+    dy = torch.from_numpy(y0).cuda()
+    assert ex.step(1.5, A, 0.5, dy) == capi.SUCCESS
+    y_ref = oracle.gemv_exact(m.rows_start, m.rows_end, m.col, m.val, 1.5, x, 0.5, y0)
+    assert_rows_close(kind, dy.cpu().numpy(), y_ref, row_scale(m.ptr, m.col, m.val, x, 1.5, 0.5, y0), "all tiles")
+    assert np.array_equal(ex.x_tensor().cpu().numpy(), dy.cpu().numpy())
+    ex.destroy()
+    dy = torch.from_numpy(y0).cuda()
+    assert spblas.mv(kind, 0, 1.5, A, spblas.descr(), dx, 0.5, dy) == capi.SUCCESS
+    assert np.array_equal(dy.cpu().numpy(), results[(1.5, 0.5)])
+    spblas.destroy(A)
+
+
 @pytest.mark.parametrize("kind", ["s", "d"])
 def test_large_transpose_keeps_the_reference_order(kind):
     """A^T of a matrix with more than a million stored elements, some pairs stored twice: the transposed product
