@@ -5,6 +5,7 @@
 * ``alsparse_b200/libalphasparse_b200.so`` -- the product: CUDA kernels and the C ABI,
   compiled by nvcc for sm_100a only (cross-compiles without a GPU).
 * ``alsparse_b200/synth/libsynth.so`` -- seeded input generators (host C).
+* ``libbench_gather_probe.so`` (repository root) -- the gather-rate probe of ``bench.py``.
 * ``oracle/liboracle.so`` and, when the reference tree is present, ``oracle/_ref/libalpha_ref.so``
   -- the CPU checkers used by tests and by the CPU legs of the benchmark (``make -C oracle``).
 """
@@ -19,7 +20,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libalphasparse_b200.so")
 SYNTH_SRC = os.path.join(HERE, "synth", "synth.c")
 SYNTH_LIB = os.path.join(HERE, "synth", "libsynth.so")
-CUDA_SOURCES = ["core.cu", "spmv.cu", "spmv_band.cu", "spmm.cu", "exchange.cu", "coo2csr.cu", "probe.cu", "host_util.cu", "host_args.cu"]
+CUDA_SOURCES = ["core.cu", "spmv.cu", "spmv_band.cu", "spmv_bins.cu", "spmm.cu", "exchange.cu", "coo2csr.cu", "host_util.cu", "host_args.cu"]
 
 
 def _newer(target, deps):
@@ -65,6 +66,18 @@ def build_synth(force=False):
     return SYNTH_LIB
 
 
+PROBE_SRC = os.path.join(ROOT, "bench_gather_probe.cu")
+PROBE_LIB = os.path.join(ROOT, "libbench_gather_probe.so")
+
+
+def build_bench_probe(force=False):
+    """The gather-rate probe bench.py reports beside its kernel times (a helper of the benchmark, not of the library)."""
+    if os.path.exists(PROBE_SRC) and (force or _newer(PROBE_LIB, [PROBE_SRC])):
+        _run([nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
+              "-Xcompiler", "-fPIC", "-ccbin", "/usr/bin/g++", "-cudart", "static", "-o", PROBE_LIB, PROBE_SRC])
+    return PROBE_LIB
+
+
 def build_oracle():
     """C restatement always; the reference's own objects only where its tree is mounted."""
     _run(["make", "-s", "-C", os.path.join(ROOT, "oracle"), "all"])
@@ -73,6 +86,7 @@ def build_oracle():
 def build_all(force=False):
     build_library(force)
     build_synth(force)
+    build_bench_probe(force)
     build_oracle()
 
 

@@ -48,7 +48,7 @@ class MatInfo(C.Structure):
                 ("algorithm", C.c_int32), ("lanes_per_row", C.c_int32), ("merge_tiles", C.c_int64),
                 ("device_bytes", C.c_int64), ("device", C.c_int32), ("scheduled", C.c_int32),
                 ("band_rows", C.c_int32), ("band_count", C.c_int32), ("band_width", C.c_int32),
-                ("band_elements", C.c_int64)]
+                ("band_elements", C.c_int64), ("spmm_col_blocks", C.c_int32), ("binned", C.c_int32)]
 
 
 class AlphaTimer(C.Structure):
@@ -115,9 +115,9 @@ def prototypes():
     p["alphasparse_cuda_exchange_destroy"] = (C.c_int, [_H])
     p["alphasparse_s_mv_exchange"] = (C.c_int, [C.c_float, _H, MatrixDescr, _H, C.c_float, _P])
     p["alphasparse_d_mv_exchange"] = (C.c_int, [C.c_double, _H, MatrixDescr, _H, C.c_double, _P])
+    p["alphasparse_cuda_kernel_status"] = (C.c_int, [_H, C.POINTER(C.c_int), C.c_int])
     p["alphasparse_cuda_profile_kernel"] = (C.c_int, [_H, C.c_int])
     p["alphasparse_cuda_kernel_ms"] = (C.c_int, [_H, C.POINTER(C.c_float)])
-    p["alphasparse_cuda_probe_gather_rate"] = (C.c_int, [C.c_int, C.c_int64, C.c_int64, C.POINTER(C.c_double)])
     p["alphasparse_cuda_debug_fail_alloc"] = (C.c_int, [C.c_int64])
     p["alphasparse_cuda_launch_count"] = (C.c_int64, [])
     p["alphasparse_cuda_last_error"] = (C.c_char_p, [])

@@ -304,6 +304,125 @@ alphasparse_status_t coo_to_csr_device(int64_t rows, int64_t cols, int64_t nnz, 
     return bad ? ALPHA_SPARSE_STATUS_INVALID_VALUE : ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
+// ---- A^T from the device copy of A ------------------------------------------------------------------
+//
+// The reference materialises the transpose on the host with a counting sort (src/core/format/transpose_x_csr.c:7-62)
+// and its transposed gemv adds the elements of a column of A in ascending row order
+// (src/plain/kernel/level2/mv/gemv/gemv_x_csr_trans_plain.c:14-25).  Here the same arrays come from the device copy
+// without touching the host: the stored elements, taken in storage order (rows ascending), are sorted by column
+// with the stable radix sort above (keys = column, over the bits the column count uses; the payload is the
+// element's position), so the elements of a column come out by ascending row; the row of each is found again by a
+// binary search in the row offsets, the new offsets by a binary search in the sorted columns.
+__global__ void transpose_keys_kernel(long long nnz, const int *__restrict__ col, unsigned long long *__restrict__ keys,
+                                      unsigned *__restrict__ pos) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nnz) return;
+    keys[i] = (unsigned)col[i];
+    pos[i] = (unsigned)i;
+}
+
+template <typename T>
+__global__ void transpose_fill_kernel(long long nnz, int rows, int cols, const unsigned long long *__restrict__ keys,
+                                      const unsigned *__restrict__ pos, const int *__restrict__ row_ptr,
+                                      const T *__restrict__ val, int *__restrict__ tptr, int *__restrict__ tcol,
+                                      T *__restrict__ tval) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i <= cols) {  // first sorted element whose column is >= i
+        long long lo = 0, hi = nnz;
+        while (lo < hi) {
+            const long long mid = (lo + hi) >> 1;
+            if ((long long)(unsigned)keys[mid] < i) lo = mid + 1;
+            else hi = mid;
+        }
+        tptr[i] = (int)lo;
+    }
+    if (i < nnz) {
+        const int k = (int)pos[i];
+        int lo = 0, hi = rows;  // last row whose first element is <= k (empty rows share an offset: take the last)
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (row_ptr[mid] <= k) lo = mid;
+            else hi = mid;
+        }
+        tcol[i] = lo;
+        tval[i] = val[k];
+    }
+}
+
+// Device arrays of A^T in the layout ctx_adopt expects (cols + 1 + 4 offsets, nnz + kTailPad columns and values,
+// tails zeroed), allocated here and handed to the caller.
+template <typename T>
+alphasparse_status_t transpose_csr_device(const DeviceCtx *c, int **out_ptr, int **out_col, T **out_val) {
+    cudaStream_t st = current_stream();
+    const int64_t nnz = c->nnz, rows = c->rows, cols = c->cols;
+    const long long nblocks = std::max<long long>(1, (nnz + kSortTile - 1) / kSortTile);
+    const long long hist_n = 16 * nblocks;
+    const int scan_blocks = (int)((hist_n + kScanTile - 1) / kScanTile);
+    unsigned long long *d_keys[2] = {nullptr, nullptr};
+    unsigned *d_pos[2] = {nullptr, nullptr}, *d_hist = nullptr, *d_sums = nullptr;
+    int *tptr = nullptr, *tcol = nullptr;
+    T *tval = nullptr;
+    auto release = [&](bool all) {
+        cudaFree(d_keys[0]), cudaFree(d_keys[1]), cudaFree(d_pos[0]), cudaFree(d_pos[1]), cudaFree(d_hist), cudaFree(d_sums);
+        if (all) cudaFree(tptr), cudaFree(tcol), cudaFree(tval);
+    };
+#define TRY(expr, code)                   \
+    do {                                  \
+        cudaError_t _e = (expr);          \
+        if (_e != cudaSuccess) {          \
+            record_cuda_error(_e, #expr); \
+            release(true);                \
+            return (code);                \
+        }                                 \
+    } while (0)
+    const size_t n = (size_t)nnz, padded = n + kTailPad;
+    TRY(device_alloc(&tptr, sizeof(int) * (size_t)(cols + 1 + 4)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&tcol, sizeof(int) * padded), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&tval, sizeof(T) * padded), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMemsetAsync(tptr, 0, sizeof(int) * (size_t)(cols + 1 + 4), st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaMemsetAsync(tcol + n, 0, sizeof(int) * kTailPad, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaMemsetAsync(tval + n, 0, sizeof(T) * kTailPad, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    if (nnz > 0) {
+        TRY(device_alloc(&d_keys[0], 8 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        TRY(device_alloc(&d_keys[1], 8 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        TRY(device_alloc(&d_pos[0], 4 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        TRY(device_alloc(&d_pos[1], 4 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        TRY(device_alloc(&d_hist, sizeof(unsigned) * (size_t)hist_n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        TRY(device_alloc(&d_sums, sizeof(unsigned) * (size_t)(scan_blocks + 1)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        transpose_keys_kernel<<<(unsigned)((nnz + 255) / 256), 256, 0, st>>>(nnz, c->d_col, d_keys[0], d_pos[0]);
+        count_launch();
+        int cur = 0;
+        const int col_bits = bits_for(cols);
+        for (int shift = 0; shift < col_bits; shift += 4) {
+            radix_hist_kernel<<<(unsigned)nblocks, kSortThreads, 0, st>>>(nnz, d_keys[cur], shift, d_hist);
+            count_launch();
+            alphasparse_status_t s = device_exclusive_scan(d_hist, hist_n, d_sums, st);
+            if (s != ALPHA_SPARSE_STATUS_SUCCESS) {
+                release(true);
+                return s;
+            }
+            radix_scatter_kernel<<<(unsigned)nblocks, kSortThreads, 0, st>>>(nnz, d_keys[cur], d_pos[cur], shift, d_hist,
+                                                                            d_keys[cur ^ 1], d_pos[cur ^ 1]);
+            count_launch();
+            cur ^= 1;
+        }
+        const long long work = std::max<long long>(nnz, cols + 1);
+        transpose_fill_kernel<T><<<(unsigned)((work + 255) / 256), 256, 0, st>>>(
+            nnz, (int)rows, (int)cols, d_keys[cur], d_pos[cur], c->d_row_ptr, static_cast<const T *>(c->d_val), tptr, tcol,
+            tval);
+        count_launch();
+        TRY(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    }
+    TRY(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+#undef TRY
+    release(false);
+    *out_ptr = tptr, *out_col = tcol, *out_val = tval;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+template alphasparse_status_t transpose_csr_device<float>(const DeviceCtx *, int **, int **, float **);
+template alphasparse_status_t transpose_csr_device<double>(const DeviceCtx *, int **, int **, double **);
+
 template alphasparse_status_t coo_to_csr_device<float>(int64_t, int64_t, int64_t, const int *, const int *,
                                                        const float *, int *, int *, float *);
 template alphasparse_status_t coo_to_csr_device<double>(int64_t, int64_t, int64_t, const int *, const int *,

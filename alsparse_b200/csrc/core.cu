@@ -66,8 +66,7 @@ struct OptionDef {
 };
 static const OptionDef kOptionDefs[kOptCount] = {
     {"band_enable", 1},       {"band_bytes", 64 * 1024}, {"band_min_seg", 8},      {"band_min_rows", 128},
-    {"band_min_share_pct", 10}, {"band_splits", 0},      {"band_overlap", 1},      {"band_variant", 1},     {"spmm_col_blocks", 0},
-    {"spmm_block_bytes", (int64_t)48 << 20},
+    {"band_min_share_pct", 10}, {"band_splits", 0},      {"band_overlap", 0},      {"band_variant", 0},     {"bin_enable", 1},        {"bin_short", 8},         {"bin_overlap", 1},      {"bin_mid_max", 16384},   {"spmm_col_blocks", 0},
 };
 static std::atomic<int64_t> g_options[kOptCount];
 static std::once_flag g_options_once;
@@ -133,6 +132,8 @@ void ctx_destroy(DeviceCtx *c) {
     cudaFree(c->d_chunk_done);
     cudaFree(c->d_sched);
     band_destroy(c->band);
+    bins_destroy(c->bins);
+    spmm_blocks_destroy(c->spmm);
     cudaFree(c->d_x_stage);
     cudaFree(c->d_y_stage);
     cudaFree(c->d_status);
@@ -204,8 +205,40 @@ alphasparse_status_t ctx_create(int datatype, int64_t rows, int64_t cols, const 
     TRY(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
 #undef TRY
 
+    c->h_row_ptr = rows > 0 ? ptr : nullptr;  // the analysis may bin the rows on the host
     alphasparse_status_t s = ctx_analyse(c);
+    c->h_row_ptr = nullptr;
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return fail(s);
+    *out = c;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+alphasparse_status_t ctx_adopt(int datatype, int64_t rows, int64_t cols, int64_t nnz, int *d_ptr, int *d_col,
+                               void *d_val, DeviceCtx **out) {
+    *out = nullptr;
+    DeviceCtx *c = new (std::nothrow) DeviceCtx();
+    int dev = 0;
+    if (!c || cudaGetDevice(&dev) != cudaSuccess) {
+        delete c;
+        cudaFree(d_ptr), cudaFree(d_col), cudaFree(d_val);
+        return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+    const size_t tsz = datatype == ALPHA_SPARSE_DATATYPE_DOUBLE ? 8 : 4;
+    c->device = dev, c->datatype = datatype, c->rows = rows, c->cols = cols, c->nnz = nnz;
+    c->d_row_ptr = d_ptr, c->d_col = d_col, c->d_val = d_val;
+    c->device_bytes = (int64_t)(sizeof(int) * (size_t)(rows + 1) + (sizeof(int) + tsz) * ((size_t)nnz + kTailPad));
+    cudaError_t e = device_alloc(&c->d_status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemsetAsync(c->d_status, 0, sizeof(int), current_stream());
+    if (e != cudaSuccess) {
+        record_cuda_error(e, "ctx_adopt");
+        ctx_destroy(c);
+        return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+    alphasparse_status_t s = ctx_analyse(c);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) {
+        ctx_destroy(c);
+        return s;
+    }
     *out = c;
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
@@ -514,48 +547,20 @@ static alphasparse_status_t coo_to_csr(const typename CsrOf<T>::coo *src, bool t
 
 // ---- transpose ---------------------------------------------------------------------------------
 
-// Device CSR of A^T, built once from the handle's host copy and kept with the handle.  The
-// reference materialises the transpose on every transposed mm call
+// Device CSR of A^T, built once from the handle's DEVICE copy (transpose_csr_device: a stable radix sort by
+// column) and kept with the handle.  The reference materialises the transpose on every transposed mm call
 // (src/kernel/x86_64/level3/mm/gemm/gemm_x_csr_row_trans.c:5-12 -> src/core/format/transpose_x_csr.c:7-62)
 // and scatters with a serial loop in the transposed mv (src/plain/kernel/level2/mv/gemv/gemv_x_csr_trans_plain.c:14-25).
-// Here a counting sort by column builds it: every thread owns a range of columns and sweeps the
-// rows in order, so the elements of a column come out by ascending row -- the order in which the
-// reference's loop adds them -- and the result is the same for any thread count.
+// The elements of a column come out by ascending row -- the order in which the reference's loop adds them.
 template <typename T>
-static alphasparse_status_t ensure_transposed(DeviceCtx *c, const typename CsrOf<T>::csr *m) {
+static alphasparse_status_t ensure_transposed(DeviceCtx *c, const typename CsrOf<T>::csr *) {
     if (c->transposed) return ALPHA_SPARSE_STATUS_SUCCESS;
-    const int64_t rows = c->rows, cols = c->cols, nnz = c->nnz;
-    const int *ptr = m->rows_start, *col = m->col_indx;
-    const T *val = m->values;
-    int *tptr = static_cast<int *>(host_alloc(sizeof(int) * (size_t)(cols + 1)));
-    int *tcol = static_cast<int *>(host_alloc(sizeof(int) * (size_t)nnz));
-    T *tval = static_cast<T *>(host_alloc(sizeof(T) * (size_t)nnz));
-    if (!tptr || !tcol || !tval) {
-        free(tptr), free(tcol), free(tval);
-        return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
-    }
-    memset(tptr, 0, sizeof(int) * (size_t)(cols + 1));
-    for (int64_t k = 0; k < nnz; k++) tptr[col[k] + 1]++;
-    for (int64_t j = 0; j < cols; j++) tptr[j + 1] += tptr[j];
-    std::vector<int> fill(tptr, tptr + cols);
-    const int threads = std::max(1, std::min(alpha_get_thread_num(), 64));
-#pragma omp parallel num_threads(threads)
-    {
-        const int t = omp_get_thread_num(), nt = omp_get_num_threads();
-        const int64_t c0 = cols * t / nt, c1 = cols * (t + 1) / nt;
-        for (int64_t r = 0; r < rows; r++)
-            for (int k = ptr[r]; k < ptr[r + 1]; k++) {
-                const int j = col[k];
-                if (j >= c0 && j < c1) {
-                    const int pos = fill[j]++;
-                    tcol[pos] = (int)r;
-                    tval[pos] = val[k];
-                }
-            }
-    }
+    int *tptr = nullptr, *tcol = nullptr;
+    T *tval = nullptr;
+    alphasparse_status_t s = transpose_csr_device<T>(c, &tptr, &tcol, &tval);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     DeviceCtx *t = nullptr;
-    alphasparse_status_t s = ctx_create(c->datatype, cols, rows, tptr, tcol, tval, &t);
-    free(tptr), free(tcol), free(tval);
+    s = ctx_adopt(c->datatype, c->cols, c->rows, c->nnz, tptr, tcol, tval, &t);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     c->transposed = t;
     c->device_bytes += t->device_bytes;
@@ -770,14 +775,22 @@ static alphasparse_status_t csr_shadow_of(const alphasparse_matrix_t A, alphaspa
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
-// Host y (and host or device x) on a large matrix: the product runs in kPipelineChunks row windows (4 -> 8 windows
-// took uniform16 end to end from 3.14 to 2.90 ms on B200, 16 changed nothing) so that
-// PCIe and the kernel overlap.  Three streams: x and the y0 pieces go in on one, the windows run
-// on the library stream as their inputs land, every finished piece of y leaves on the third
-// while the next window is being multiplied (PCIe is full duplex).  The call still returns
-// only when all of y is back in host memory.
+// Host y (and host or device x) on a large matrix: the product runs in row windows so that PCIe and the kernel
+// overlap.  Three streams: x and the y0 pieces go in on one, the windows run on the library stream as their inputs
+// land, every finished piece of y leaves on the third while the next window is being multiplied (PCIe is full
+// duplex).  The call still returns only when all of y is back in host memory.
+// The number of windows follows the size of y: pieces of at least kPipelineMinPiece bytes, at most kPipelineChunks of
+// them (on B200 4 -> 8 windows took a 64 MB y from 3.14 to 2.90 ms end to end, 16 changed nothing; an 8 MB y --
+// one GPU's share of the same vector on eight GPUs -- is quicker in two pieces than in eight, where the seventeen
+// events and copies of 1 MB cost more than they hide).
 constexpr int64_t kPipelineMinRows = 1 << 20;
 constexpr int kPipelineChunks = 8;
+constexpr size_t kPipelineMinPiece = (size_t)4 << 20;
+
+static int pipeline_windows(size_t y_bytes) {
+    const size_t n = y_bytes / kPipelineMinPiece;
+    return (int)std::max<size_t>(1, std::min<size_t>(n, kPipelineChunks));
+}
 
 // the two copy streams and the events of the host-operand pipelines, created on first use
 static alphasparse_status_t ensure_pipe(DeviceCtx *c) {
@@ -802,9 +815,9 @@ static alphasparse_status_t mv_host_pipelined(DeviceCtx *c, T alpha, const T *x,
     const T *dx = x_dev ? x : static_cast<const T *>(c->d_x_stage);
     T *dy = static_cast<T *>(c->d_y_stage);
     cudaEvent_t ev_x = c->ev_pipe[0];
-    // work already queued on the library stream (it may still use the staging buffers) goes first
-    ASB_CUDA_OR(cudaEventRecord(ev_x, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
-    ASB_CUDA_OR(cudaStreamWaitEvent(c->copy_in, ev_x, 0), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    // The staging buffers are free: every call that uses them waits for its copies before it returns.  So the
+    // inbound copies start at once, beside whatever is still queued on the library stream (for instance the
+    // exchange that is bringing a device x together).
     if (!x_dev) {  // a device x is already where the kernels read it (and ordered on the library stream)
         ASB_CUDA_OR(cudaMemcpyAsync(c->d_x_stage, x, sizeof(T) * (size_t)c->cols, cudaMemcpyHostToDevice, c->copy_in),
                     ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
@@ -812,8 +825,9 @@ static alphasparse_status_t mv_host_pipelined(DeviceCtx *c, T alpha, const T *x,
         ASB_CUDA_OR(cudaStreamWaitEvent(st, ev_x, 0), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     }
 
-    const int64_t step = ((c->rows + kPipelineChunks - 1) / kPipelineChunks + 1023) & ~1023ll;
-    for (int k = 0; k < kPipelineChunks; k++) {
+    const int windows = pipeline_windows(sizeof(T) * (size_t)c->rows);
+    const int64_t step = ((c->rows + windows - 1) / windows + 1023) & ~1023ll;
+    for (int k = 0; k < windows; k++) {
         const int64_t rb = k * step;
         if (rb >= c->rows) break;
         const RowWindow w{rb, std::min<int64_t>(step, c->rows - rb)};
@@ -836,6 +850,7 @@ static alphasparse_status_t mv_host_pipelined(DeviceCtx *c, T alpha, const T *x,
                 ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     ASB_CUDA_OR(cudaStreamSynchronize(c->copy_out), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     ASB_CUDA_OR(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    if (kernel_status != 0) (void)cudaMemsetAsync(c->d_status, 0, sizeof(int), st);  // reported once
     return kernel_status == 0 ? ALPHA_SPARSE_STATUS_SUCCESS : ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
 }
 
@@ -919,7 +934,10 @@ static alphasparse_status_t mv_on_ctx(DeviceCtx *c, T alpha, const T *x, T beta,
         ASB_CUDA_OR(cudaMemcpyAsync(&kernel_status, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, st),
                     ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
         ASB_CUDA_OR(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
-        if (kernel_status != 0) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+        if (kernel_status != 0) {  // reported once: later calls start clean
+            (void)cudaMemsetAsync(c->d_status, 0, sizeof(int), st);
+            return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+        }
     }
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
@@ -1540,6 +1558,8 @@ alphasparse_status_t alphasparse_cuda_get_mat_info(const alphasparse_matrix_t A,
     info->scheduled = c->d_sched != nullptr;
     info->band_rows = c->band.rows, info->band_count = c->band.bands, info->band_width = c->band.width;
     info->band_elements = c->band.elements;
+    info->spmm_col_blocks = c->spmm.d_split ? c->spmm.blocks : (c->spmm.blocks ? 1 : 0);
+    info->binned = c->bins.active ? 1 : 0;
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 alphasparse_status_t alphasparse_cuda_get_device_csr(const alphasparse_matrix_t A, ALPHA_INT **d_row_ptr,
@@ -1549,6 +1569,31 @@ alphasparse_status_t alphasparse_cuda_get_device_csr(const alphasparse_matrix_t 
     if (d_row_ptr) *d_row_ptr = c->d_row_ptr;
     if (d_col_indx) *d_col_indx = c->d_col;
     if (d_values) *d_values = c->d_val;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+alphasparse_status_t alphasparse_cuda_kernel_status(const alphasparse_matrix_t A, int *status, int clear) {
+    if (!status) return ALPHA_SPARSE_STATUS_INVALID_POINTER;
+    DeviceCtx *c = ctx_of(A);
+    if (!c) return ALPHA_SPARSE_STATUS_INVALID_HANDLE;
+    DeviceGuard guard(c->device);
+    if (!guard.ok) return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+    std::lock_guard<std::mutex> lock(c->mu);
+    cudaStream_t st = current_stream();
+    int worst = 0;
+    // the handle's own word and those of the matrices derived from it (A^T, structured variants)
+    DeviceCtx *all[2 + 24] = {c, c->transposed};
+    for (int i = 0; i < 24; i++) all[2 + i] = c->derived[i];
+    for (DeviceCtx *d : all) {
+        if (!d) continue;
+        int code = 0;
+        ASB_CUDA_OR(cudaMemcpyAsync(&code, d->d_status, sizeof(int), cudaMemcpyDeviceToHost, st),
+                    ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        ASB_CUDA_OR(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        if (code != 0 && worst == 0) worst = code;
+        if (clear && code != 0)
+            ASB_CUDA_OR(cudaMemsetAsync(d->d_status, 0, sizeof(int), st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    }
+    *status = worst;
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 alphasparse_status_t alphasparse_cuda_profile_kernel(const alphasparse_matrix_t A, int enable) {

@@ -41,8 +41,10 @@ struct Exchange {
 __global__ void exchange_arrive_wait_kernel(unsigned long long step, int rank, int world,
                                             unsigned long long *const *peer_counters,
                                             volatile unsigned long long *my_counters, int *status,
-                                            long long max_polls) {
+                                            long long max_polls, const int *matrix_status) {
     const int p = threadIdx.x;
+    // an error word left by the product's own kernels (a bounded wait that ran out) becomes the exchange's
+    if (p == 0 && matrix_status && *matrix_status != 0) atomicCAS(status, 0, *matrix_status);
     if (p >= world) return;
     __threadfence_system();  // everything this GPU wrote before (same stream) is ordered before the flag
     unsigned long long *dst = peer_counters[p] + rank;
@@ -112,7 +114,7 @@ static alphasparse_status_t mv_exchange(T alpha, const alphasparse_matrix_t A, s
     // peer_counters table lives in device memory right behind our own counters
     unsigned long long *const *table = reinterpret_cast<unsigned long long *const *>(e->counters + kMaxPeers);
     exchange_arrive_wait_kernel<<<1, 32, 0, st>>>(e->step, e->rank, e->world, table, e->counters, e->d_status,
-                                                  4LL << 20);
+                                                  4LL << 20, c->d_status);
     count_launch();
     ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     e->cur = nxt;
@@ -142,7 +144,7 @@ static alphasparse_status_t load_x(Exchange *e, const void *block) {
     e->step++;
     unsigned long long *const *table = reinterpret_cast<unsigned long long *const *>(e->counters + kMaxPeers);
     exchange_arrive_wait_kernel<<<1, 32, 0, st>>>(e->step, e->rank, e->world, table, e->counters, e->d_status,
-                                                  4LL << 20);
+                                                  4LL << 20, nullptr);
     count_launch();
     ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     e->cur = nxt;

@@ -32,9 +32,12 @@ enum Option {
     kOptBandMinSharePct,  // long rows must hold at least this share of the stored elements
     kOptBandSplits,       // thread blocks per band (0: chosen from the band count)
     kOptBandOverlap,      // 1: the band kernel runs on a second stream beside the merge kernel
-    kOptBandVariant,      // shape of the band kernel (measurement aid)
-    kOptSpmmColBlocks,    // column blocks of the row-major dense-block product (0: chosen from the size of X)
-    kOptSpmmBlockBytes,   // bytes of X one column block may span when the count is chosen automatically
+    kOptBandVariant,      // shape of the band kernel: 0 = 8 lanes x 1 quad x 2 segments, 1 = 4 lanes x 2 quads x 1 segment
+    kOptBinEnable,        // 1: skewed matrices are multiplied bin by bin (short / mid / long rows) instead of merge tiles
+    kOptBinShort,         // rows of at most this many elements take the thread-per-row kernel
+    kOptBinOverlap,       // 1: the kernels of the bins run on streams of their own, side by side
+    kOptBinMidMax,        // longest row the lane-group kernels may be given; longer non-band rows: merge tiles instead
+    kOptSpmmColBlocks,    // column blocks of the row-major dense-block product (0 or 1: one pass)
     kOptCount
 };
 int64_t option(Option o);
@@ -106,12 +109,40 @@ struct BandTables {
     int splits = 1;     // thread blocks per band; block (b, s) takes positions [s*chunk, (s+1)*chunk)
     int chunk = 0;
     int64_t elements = 0;  // stored elements handled here
+    bool whole_rows = false;  // the listed rows are handled from first to last element (row bins) instead of
+                              // only where whole merge tiles lie inside them
     int *d_row = nullptr;      // rows
     int *d_seg = nullptr;      // (bands + 1) * rows
     void *d_partial = nullptr; // rows * bands sums, written by every call
     cudaStream_t side = nullptr;  // second stream + fork / join events when the kernels overlap
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 };
+
+// Row bins of a skewed matrix (spmv_bins.cu): rows of at most short_limit elements are found by the thread-per-row
+// kernel itself; d_list holds the row numbers of the three mid bins back to back (lengths up to 32, up to 256,
+// longer); the long rows are in BandTables.
+constexpr int kMidBins = 3;
+struct RowBins {
+    bool active = false;
+    int short_limit = 0;
+    int64_t short_rows = 0;
+    int64_t offset[kMidBins] = {}, count[kMidBins] = {};
+    int *d_list = nullptr;
+    // one extra stream per mid list (+ fork / join events) when the bin kernels are to run side by side
+    cudaStream_t side[kMidBins] = {};
+    cudaEvent_t ev_fork = nullptr, ev_join[kMidBins] = {};
+};
+void bins_destroy(RowBins &b);
+
+// Column blocks of the row-major dense-block product (spmm.cu): split[p * rows + r] is the first element of
+// row r whose column lies in block p or beyond; blocks == 1: the product runs in one pass.
+struct SpmmBlocks {
+    int blocks = 0;   // 0: nothing decided yet
+    int width = 0;    // columns per block
+    bool unsorted = false;  // some row is not in ascending column order: no blocking for this matrix
+    int *d_split = nullptr;
+};
+void spmm_blocks_destroy(SpmmBlocks &b);
 
 struct DeviceCtx {
     uint64_t magic = kCtxMagic;
@@ -141,6 +172,9 @@ struct DeviceCtx {
     void *d_carry_val = nullptr;   // merge_tiles
     int *d_sched = nullptr;            // block -> tile order of the merge kernel, or null (tile_key_kernel)
     int64_t sched_tiles = 0;           // tiles the merge kernel runs (= merge_tiles unless long rows are banded)
+    RowBins bins;                      // row bins of a skewed matrix; active: products run bin by bin
+    const int *h_row_ptr = nullptr;    // host copy of the offsets, valid only while the handle is being created
+    SpmmBlocks spmm;                   // column blocks of the row-major dense-block product
     bool carry_stale = false;          // a run over ALL tiles wrote carries for tiles the schedule leaves out
     BandTables band;                   // long rows taken out of the merge tiles (spmv_band.cu); rows == 0: none
     unsigned *d_chunk_done = nullptr;  // per chunk of kPushChunkTiles tiles (exchange calls only)
@@ -176,6 +210,10 @@ DeviceCtx *ctx_of(const alphasparse_matrix_t A);
 // so far is released and *out stays null.
 alphasparse_status_t ctx_create(int datatype, int64_t rows, int64_t cols, const int *ptr,
                                 const int *col, const void *val, DeviceCtx **out);
+// Wraps device arrays that already have the layout ctx_create produces (rows + 1 + 4 offsets, nnz + kTailPad columns
+// and values with zeroed tails) and analyses them.  Takes the arrays over: on failure they are freed.
+alphasparse_status_t ctx_adopt(int datatype, int64_t rows, int64_t cols, int64_t nnz, int *d_ptr, int *d_col,
+                               void *d_val, DeviceCtx **out);
 void ctx_destroy(DeviceCtx *ctx);
 alphasparse_status_t ctx_analyse(DeviceCtx *ctx);
 
@@ -199,11 +237,20 @@ alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T 
 // per (long row, band); launch_band_reduce: y[row] += alpha * (sum of the row's partials), after the merge
 // kernel and its fix-up have written y.
 alphasparse_status_t band_build(DeviceCtx *ctx, const MergeCoord *h_tile, std::vector<char> &skip, cudaStream_t st);
+// The same tables for whole rows (row bins): `rows` are the long rows, h_ptr the host copy of the offsets.
+// Leaves ctx->band.rows == 0 when one of them is not in ascending column order.
+alphasparse_status_t band_build_rows(DeviceCtx *ctx, const int *h_ptr, const std::vector<int> &rows, cudaStream_t st);
+int64_t band_long_min(const DeviceCtx *ctx);  // shortest row the column-band kernel takes
+alphasparse_status_t bins_build(DeviceCtx *ctx, const int *h_ptr, int64_t long_min, std::vector<int> &long_rows,
+                                cudaStream_t st);
+template <typename T>
+void launch_bins(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st);
 void band_destroy(BandTables &b);
 template <typename T>
 void launch_band(DeviceCtx *ctx, const T *x, cudaStream_t st);
+// whole_rows tables: y[row] = alpha * sum + beta * y[row]; otherwise y[row] += alpha * sum (beta unused)
 template <typename T>
-void launch_band_reduce(DeviceCtx *ctx, T alpha, T *y, cudaStream_t st);
+void launch_band_reduce(DeviceCtx *ctx, T alpha, T beta, T *y, cudaStream_t st);
 
 template <typename T>
 void launch_push_rows(int64_t rows, const T *src, const PeerPush &push, cudaStream_t stream);
@@ -216,6 +263,10 @@ alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int co
 template <typename T>
 alphasparse_status_t launch_spmm_col(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx,
                                      T beta, T *Y, int ldy, cudaStream_t stream);
+
+// A^T of a handle's device CSR, built on the device (coo2csr.cu); arrays in ctx_adopt's layout.
+template <typename T>
+alphasparse_status_t transpose_csr_device(const DeviceCtx *c, int **out_ptr, int **out_col, T **out_val);
 
 // COO -> CSR on the device (coo2csr.cu): host arrays in, host 3-array CSR out, same output as the host
 // path in core.cu (ordered by row then column, equal pairs in input order).

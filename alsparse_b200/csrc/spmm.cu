@@ -13,6 +13,8 @@
 // 32 pairs is unrolled so several X rows are in flight per warp.  Bandwidth-bound: the
 // traffic is nnz * columns * sizeof(T) of X rows against 2 flops per element, far below what
 // would justify staging tiles for tensor cores.
+#include <algorithm>
+
 #include "internal.h"
 
 namespace asb {
@@ -49,8 +51,8 @@ constexpr int kSpmmUnroll = 4;     // X rows in flight per lane group (8 and 16 
 constexpr int kSpmmMinBlocks = 8;  // full occupancy (32 registers) measured fastest
 template <typename T, int VEC, int LPR, bool HAS_BETA>
 __global__ void __launch_bounds__(256, kSpmmMinBlocks)
-    spmm_row_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
-                    const T *__restrict__ val, const T *__restrict__ X, int columns,
+    spmm_row_kernel(int rows, const int *__restrict__ row_lo, const int *__restrict__ row_hi,
+                    const int *__restrict__ col, const T *__restrict__ val, const T *__restrict__ X, int columns,
                     long long ldx, T *__restrict__ Y, long long ldy, T alpha, T beta) {
     constexpr int UNROLL = kSpmmUnroll;
     constexpr int RPW = 32 / LPR;  // rows per warp
@@ -59,7 +61,9 @@ __global__ void __launch_bounds__(256, kSpmmMinBlocks)
     const unsigned gmask = LPR == 32 ? 0xffffffffu : (((1u << LPR) - 1u) << (grp * LPR));
     const long long row = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * RPW + grp;
     if (row >= rows) return;  // whole groups leave together; shuffles below name only their group
-    const int s = __ldg(row_ptr + row), e = __ldg(row_ptr + row + 1);
+    // [row_lo[row], row_hi[row]) are the stored elements this launch multiplies: the whole row (row_hi = row_lo + 1
+    // of the offset array) or the part of it that falls into one column block (see SpmmBlocks)
+    const int s = __ldg(row_lo + row), e = __ldg(row_hi + row);
 
     for (int ct = 0; ct < columns; ct += LPR * VEC) {
         const int c = ct + gl * VEC;
@@ -124,26 +128,130 @@ __global__ void __launch_bounds__(256, kSpmmMinBlocks)
     }
 }
 
+// ---- column blocks -----------------------------------------------------------------------------------
+//
+// Every stored element reads one row of X (columns * sizeof(T) bytes).  With unstructured columns and an X far
+// larger than L2 nearly all of these reads come from HBM: 64 fp32 columns on 6.7e7 elements move 17 GB for
+// 1.6 GB of operands.  Cutting the columns of A into P blocks and running the product block by block makes the
+// rows of X a pass touches a slab of 1/P of X that stays in L2, so X crosses HBM about once; the price is that Y
+// is written P times and read P - 1 times.  Rows with ascending columns need no copy of A for this: the part of
+// a row inside a block is a contiguous run, described by P + 1 offsets per row.  (An experiment kept as an
+// option: see spmm_pick_blocks for what it measured.)
+__global__ void rows_ascending_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
+                                      unsigned long long *__restrict__ bad) {
+    unsigned long long n = 0;
+    for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += (long long)gridDim.x * blockDim.x)
+        for (int k = row_ptr[r]; k + 1 < row_ptr[r + 1]; k++) n += col[k] > col[k + 1];
+    for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
+    if ((threadIdx.x & 31) == 0 && n) atomicAdd(bad, n);
+}
+
+// split[p * rows + r] = first element of row r whose column is >= p * width (p = 0 .. blocks)
+__global__ void spmm_split_kernel(int rows, int blocks, int width, const int *__restrict__ row_ptr,
+                                  const int *__restrict__ col, int *__restrict__ split) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * (blocks + 1)) return;
+    const int p = (int)(i / rows), r = (int)(i % rows);
+    int lo = row_ptr[r], hi = row_ptr[r + 1];
+    if (p == 0) hi = lo;
+    else if (p == blocks) lo = hi;
+    const long long want = (long long)p * width;
+    while (lo < hi) {
+        const int mid = lo + ((hi - lo) >> 1);
+        if ((long long)col[mid] < want) lo = mid + 1;
+        else hi = mid;
+    }
+    split[i] = lo;
+}
+
+void spmm_blocks_destroy(SpmmBlocks &b) {
+    cudaFree(b.d_split);
+    b = SpmmBlocks{};
+}
+
+// Column-block table for `blocks` blocks, built on first use and kept until another count is asked for.
+// Leaves b.blocks == 1 (no blocking) when the rows are not in ascending column order.
+static alphasparse_status_t spmm_blocks_ensure(DeviceCtx *ctx, int blocks, cudaStream_t st) {
+    SpmmBlocks &b = ctx->spmm;
+    if (b.blocks == blocks || (b.unsorted && blocks > 1)) return ALPHA_SPARSE_STATUS_SUCCESS;
+    const int64_t old_bytes = b.d_split ? (int64_t)sizeof(int) * ctx->rows * (b.blocks + 1) : 0;
+    spmm_blocks_destroy(b);
+    ctx->device_bytes -= old_bytes;
+    b.blocks = 1;
+    if (blocks <= 1) return ALPHA_SPARSE_STATUS_SUCCESS;
+    unsigned long long *d_bad = nullptr, h_bad = 0;
+    ASB_CUDA_OR(device_alloc(&d_bad, sizeof(h_bad)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    cudaError_t e = cudaMemsetAsync(d_bad, 0, sizeof(h_bad), st);
+    if (e == cudaSuccess) {
+        rows_ascending_kernel<<<148 * 8, 256, 0, st>>>((int)ctx->rows, ctx->d_row_ptr, ctx->d_col, d_bad);
+        count_launch();
+        e = cudaMemcpyAsync(&h_bad, d_bad, sizeof(h_bad), cudaMemcpyDeviceToHost, st);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    cudaFree(d_bad);
+    if (e != cudaSuccess) {
+        record_cuda_error(e, "column blocks");
+        return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+    }
+    if (h_bad) {
+        b.unsorted = true;
+        return ALPHA_SPARSE_STATUS_SUCCESS;
+    }
+    const int width = (int)((ctx->cols + blocks - 1) / blocks);
+    const size_t cells = (size_t)ctx->rows * (size_t)(blocks + 1);
+    ASB_CUDA_OR(device_alloc(&b.d_split, sizeof(int) * cells), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    spmm_split_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, st>>>((int)ctx->rows, blocks, width, ctx->d_row_ptr,
+                                                                     ctx->d_col, b.d_split);
+    count_launch();
+    e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) {
+        spmm_blocks_destroy(b);
+        b.blocks = 1;
+        record_cuda_error(e, "column blocks");
+        return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+    }
+    b.blocks = blocks, b.width = width;
+    ctx->device_bytes += (int64_t)(sizeof(int) * cells);
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+// Column blocks are used only when asked for (option spmm_col_blocks > 1).  Measured on B200 with 64 fp32 columns,
+// 2^21 rows of 32 elements and a 537 MB X: 3.51 ms in one pass, 4.08 / 4.60 / 5.16 / 6.37 ms with 4 / 6 / 8 / 12
+// blocks.  Blocking does take the reads of X off HBM, but every stored element still pulls a whole row of X from
+// L2 into an SM, and that stream (17 GB) already runs at the pace the one-pass kernel reaches from HBM; the
+// extra passes over Y and the shorter per-row runs only add to it.
+static int spmm_pick_blocks(const DeviceCtx *, size_t) {
+    const int64_t blocks = option(kOptSpmmColBlocks);
+    return (int)std::max<int64_t>(1, std::min<int64_t>(blocks, 64));
+}
+
 template <typename T, int VEC, int LPR>
 static void launch_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx, T beta, T *Y,
                        int ldy, cudaStream_t st, const RowWindow *w) {
     constexpr int rows_per_block = 8 * (32 / LPR);
-    // A window is the same kernel on a slice: offsets are absolute, so shifting the offset array and Y
+    // A window is the same kernel on a slice: offsets are absolute, so shifting the offset arrays and Y
     // by the first row is all it takes.
     const int64_t first = w ? w->begin : 0, rows = w ? w->count : ctx->rows;
     const unsigned blocks = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
     const T *val = static_cast<const T *>(ctx->d_val);
-    const int *row_ptr = ctx->d_row_ptr + first;
     Y += first * (int64_t)ldy;
+    const int passes = ctx->spmm.d_split ? ctx->spmm.blocks : 1;
     if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
-    if (beta == T(0))
-        spmm_row_kernel<T, VEC, LPR, false><<<blocks, 256, 0, st>>>(
-            (int)rows, row_ptr, ctx->d_col, val, X, columns, ldx, Y, ldy, alpha, beta);
-    else
-        spmm_row_kernel<T, VEC, LPR, true><<<blocks, 256, 0, st>>>(
-            (int)rows, row_ptr, ctx->d_col, val, X, columns, ldx, Y, ldy, alpha, beta);
+    for (int p = 0; p < passes; p++) {
+        const int *lo = passes > 1 ? ctx->spmm.d_split + (size_t)p * ctx->rows + first : ctx->d_row_ptr + first;
+        const int *hi = passes > 1 ? lo + ctx->rows : lo + 1;
+        // the first pass applies beta, the later ones add to what is there
+        const T b = p == 0 ? beta : T(1);
+        if (b == T(0))
+            spmm_row_kernel<T, VEC, LPR, false><<<blocks, 256, 0, st>>>(
+                (int)rows, lo, hi, ctx->d_col, val, X, columns, ldx, Y, ldy, alpha, b);
+        else
+            spmm_row_kernel<T, VEC, LPR, true><<<blocks, 256, 0, st>>>(
+                (int)rows, lo, hi, ctx->d_col, val, X, columns, ldx, Y, ldy, alpha, b);
+    }
     if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
-    count_launch();
+    count_launch(passes);
 }
 
 template <typename T, int VEC>
@@ -162,6 +270,8 @@ template <typename T>
 alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx,
                                      T beta, T *Y, int ldy, cudaStream_t st, const RowWindow *w) {
     if (ctx->rows == 0 || columns <= 0 || (w && w->count <= 0)) return ALPHA_SPARSE_STATUS_SUCCESS;
+    alphasparse_status_t bs = spmm_blocks_ensure(ctx, spmm_pick_blocks(ctx, sizeof(T) * (size_t)ctx->cols * (size_t)ldx), st);
+    if (bs != ALPHA_SPARSE_STATUS_SUCCESS) return bs;
     auto fits = [&](int vec) {
         const uintptr_t mask = (uintptr_t)(vec * sizeof(T) - 1);
         return columns % vec == 0 && ldx % vec == 0 && ldy % vec == 0 &&

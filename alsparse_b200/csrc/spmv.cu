@@ -180,6 +180,7 @@ __global__ void __launch_bounds__(kRowTile)
     int *s_col = reinterpret_cast<int *>(smem + (size_t)cap * sizeof(T));
     int *s_ptr = s_col + cap;
     unsigned long long *s_bar = reinterpret_cast<unsigned long long *>(s_ptr + kRowTile + 4);
+    __shared__ int s_oversize;
 
     const int tid = threadIdx.x;
     const int r0 = blockIdx.x * kRowTile;
@@ -190,6 +191,7 @@ __global__ void __launch_bounds__(kRowTile)
         const int start = __ldg(row_ptr + r0), end = __ldg(row_ptr + r0 + nr);
         const int a0 = start & ~3;
         int n = ((end + 3) & ~3) - a0;
+        s_oversize = n > cap;
         if (n > cap) {  // cannot happen for a handle analysed by this library; refuse rather than overrun
             atomicExch(status, 1);
             n = 0;
@@ -218,6 +220,7 @@ __global__ void __launch_bounds__(kRowTile)
         if (tid == 0) atomicExch(status, 2);
         return;
     }
+    if (s_oversize) return;  // nothing was staged: the whole block leaves before it touches the tile or x
 
     const int a0 = s_ptr[0] & ~3;
     const int b = tid < nr ? s_ptr[tid] - a0 : 0, e = tid < nr ? s_ptr[tid + 1] - a0 : 0;
@@ -230,7 +233,6 @@ __global__ void __launch_bounds__(kRowTile)
     const bool even = (len & 1) == 0 && len > 0;
     const bool wrap = __any_sync(0xffffffffu, even);
     if (tid < nr) {
-        if (e > cap) return;  // the oversize case flagged above
         T acc0 = T(0), acc1 = T(0), acc2 = T(0), acc3 = T(0);
         if (!wrap) {
             int k = b;
@@ -759,9 +761,11 @@ static alphasparse_status_t build_tile_schedule(DeviceCtx *ctx, cudaStream_t st)
         return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
     }
     std::vector<char> skip((size_t)tiles, 0);
-    alphasparse_status_t s = band_build(ctx, h_tile.data(), skip, st);
-    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
-    const bool banded = ctx->band.rows > 0;
+    if (!ctx->bins.active) {  // a binned handle runs its merge tiles only in the delivering form: all of them
+        alphasparse_status_t s = band_build(ctx, h_tile.data(), skip, st);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    }
+    const bool banded = ctx->band.rows > 0 && !ctx->band.whole_rows;
     const bool by_column = !schedule_disabled() && (size_t)ctx->cols * tsz >= kScheduleMinXBytes;
     if (!banded && !by_column) return ALPHA_SPARSE_STATUS_SUCCESS;
 
@@ -803,6 +807,46 @@ static alphasparse_status_t build_tile_schedule(DeviceCtx *ctx, cudaStream_t st)
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
+// Row bins (spmv_bins.cu) for a matrix the analysis found skewed.  Declined -- the handle then multiplies over merge
+// tiles -- when some row is too long for a lane group yet not long enough for the column-band kernel, when there
+// are long rows but too few (or holding too little) to be worth that kernel, or when a long row is not in ascending
+// column order.
+static alphasparse_status_t try_row_bins(DeviceCtx *ctx, cudaStream_t st) {
+    if (!option(kOptBinEnable)) return ALPHA_SPARSE_STATUS_SUCCESS;
+    std::vector<int> fetched;
+    const int *h_ptr = ctx->h_row_ptr;
+    if (!h_ptr) {  // re-analysis of a live handle: the offsets come back from the device
+        fetched.resize((size_t)ctx->rows + 1);
+        cudaError_t e = cudaMemcpyAsync(fetched.data(), ctx->d_row_ptr, sizeof(int) * ((size_t)ctx->rows + 1),
+                                        cudaMemcpyDeviceToHost, st);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+        if (e != cudaSuccess) {
+            record_cuda_error(e, "row bins");
+            return ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
+        }
+        h_ptr = fetched.data();
+    }
+    const int64_t long_min = option(kOptBandEnable) ? band_long_min(ctx) : INT64_MAX;
+    const int64_t mid_max = option(kOptBinMidMax);
+    for (int64_t r = 0; r < ctx->rows; r++) {
+        const int64_t n = (int64_t)h_ptr[r + 1] - h_ptr[r];
+        if (n > mid_max && n < long_min) return ALPHA_SPARSE_STATUS_SUCCESS;
+    }
+    std::vector<int> long_rows;
+    alphasparse_status_t s = bins_build(ctx, h_ptr, long_min, long_rows, st);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+    if (!long_rows.empty()) {
+        s = band_build_rows(ctx, h_ptr, long_rows, st);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS || ctx->band.rows == 0) {
+            const int64_t freed = (int64_t)sizeof(int) * (ctx->bins.count[0] + ctx->bins.count[1] + ctx->bins.count[2]);
+            bins_destroy(ctx->bins);
+            ctx->device_bytes -= freed;
+            return s;
+        }
+    }
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
 // Merge-path tables of a handle: tile coordinates, carry arrays, chunk counters, block schedule and the
 // column-band tables.  Everything is built into `tmp` and handed to the handle only when all of it exists,
 // so a failure half-way (alphasparse_optimize on a live handle) leaves the handle as it was.
@@ -822,6 +866,7 @@ static alphasparse_status_t build_merge_tables(DeviceCtx *ctx, cudaStream_t st) 
         cudaFree(ctx->d_sched);
         ctx->d_sched = nullptr;
         band_destroy(ctx->band);
+        bins_destroy(ctx->bins);
         ctx->d_tile = nullptr, ctx->d_carry_row = nullptr, ctx->d_carry_val = nullptr, ctx->d_chunk_done = nullptr;
         ctx->merge_tiles = 0, ctx->sched_tiles = 0;
     };
@@ -852,7 +897,8 @@ static alphasparse_status_t build_merge_tables(DeviceCtx *ctx, cudaStream_t st) 
     ctx->merge_items = items, ctx->merge_tiles = tiles;
     ctx->d_tile = d_tile, ctx->d_carry_row = d_carry_row, ctx->d_carry_val = d_carry_val, ctx->d_chunk_done = d_chunk_done;
     ctx->carry_stale = false;
-    alphasparse_status_t s = build_tile_schedule(ctx, st);
+    alphasparse_status_t s = try_row_bins(ctx, st);
+    if (s == ALPHA_SPARSE_STATUS_SUCCESS) s = build_tile_schedule(ctx, st);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) {
         undo();
         return s;
@@ -957,10 +1003,35 @@ static void launch_merge_as(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, c
     T *carry = static_cast<T *>(ctx->d_carry_val);
     // In-kernel delivery wants chunks of neighbouring tiles to finish together: every tile, natural order,
     // and therefore no column-band path either.
-    const bool banded = !PUSH && ctx->band.rows > 0;
+    if (!PUSH && ctx->bins.active) {
+        // bin by bin: the column-band kernel (long rows) first, on its own stream when there is one, then
+        // the short and mid rows; its partial sums are folded into y last
+        BandTables &bt = ctx->band;
+        if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
+        if (bt.rows > 0) {
+            cudaStream_t band_st = st;
+            if (bt.side) {
+                cudaEventRecord(bt.ev_fork, st);
+                cudaStreamWaitEvent(bt.side, bt.ev_fork, 0);
+                band_st = bt.side;
+            }
+            launch_band<T>(ctx, x, band_st);
+        }
+        launch_bins<T>(ctx, alpha, x, beta, y, st);
+        if (bt.rows > 0) {
+            if (bt.side) {
+                cudaEventRecord(bt.ev_join, bt.side);
+                cudaStreamWaitEvent(st, bt.ev_join, 0);
+            }
+            launch_band_reduce<T>(ctx, alpha, beta, y, st);
+        }
+        if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
+        return;
+    }
+    const bool banded = !PUSH && ctx->band.rows > 0 && !ctx->band.whole_rows;
     const int *sched = PUSH ? nullptr : ctx->d_sched;
     const unsigned blocks = (unsigned)(PUSH ? ctx->merge_tiles : ctx->sched_tiles);
-    if (PUSH && ctx->band.rows > 0) ctx->carry_stale = true;  // tiles the schedule leaves out write carries now
+    if (PUSH && ctx->band.rows > 0 && !ctx->band.whole_rows) ctx->carry_stale = true;  // tiles the schedule leaves out write carries now
     if (banded && ctx->carry_stale) {
         cudaMemsetAsync(ctx->d_carry_row, 0x7f, sizeof(int) * (size_t)ctx->merge_tiles, st);
         ctx->carry_stale = false;
@@ -994,7 +1065,7 @@ static void launch_merge_as(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, c
             cudaEventRecord(bt.ev_join, bt.side);
             cudaStreamWaitEvent(st, bt.ev_join, 0);
         }
-        launch_band_reduce<T>(ctx, alpha, y, st);
+        launch_band_reduce<T>(ctx, alpha, beta, y, st);
         // with two large kernels the timed span is the whole product
         if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
     }
@@ -1147,13 +1218,15 @@ alphasparse_status_t noalloc_scratch(unsigned char **out) {
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
-bool on_device(const void *p) {
+// true when `p` is memory the kernels of device `dev` can use: allocated on that device, or managed
+bool on_device(const void *p, int dev) {
     cudaPointerAttributes at;
     if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
         (void)cudaGetLastError();
         return false;
     }
-    return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+    if (at.type == cudaMemoryTypeManaged) return true;
+    return at.type == cudaMemoryTypeDevice && at.device == dev;
 }
 
 }  // namespace
@@ -1162,14 +1235,18 @@ extern "C" alphasparse_status_t alphasparse_cuda_d_csrmv_noalloc(
     ALPHA_INT rows, ALPHA_INT cols, ALPHA_INT nnz, double alpha, const ALPHA_INT *d_row_ptr,
     const ALPHA_INT *d_col_indx, const double *d_values, const double *d_x, double beta, double *d_y) {
     using namespace asb;
-    (void)cols;
-    if (rows < 0 || nnz < 0) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
+    // cols only documents the length of d_x: the stored column indices are NOT checked against it here (a handle
+    // checks them once, at creation; this call would have to read the whole index array on every product)
+    if (rows < 0 || cols < 0 || nnz < 0) return ALPHA_SPARSE_STATUS_INVALID_VALUE;
     if (rows == 0) return ALPHA_SPARSE_STATUS_SUCCESS;
     if (!d_row_ptr || !d_y || (nnz > 0 && (!d_col_indx || !d_values || !d_x)))
         return ALPHA_SPARSE_STATUS_NOT_INITIALIZED;
-    if (!on_device(d_row_ptr) || !on_device(d_y) ||
-        (nnz > 0 && (!on_device(d_col_indx) || !on_device(d_values) || !on_device(d_x)))) {
-        record_cuda_error(cudaErrorInvalidValue, "alphasparse_cuda_d_csrmv_noalloc takes device pointers only");
+    int dev = -1;
+    ASB_CUDA_OR(cudaGetDevice(&dev), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    if (!on_device(d_row_ptr, dev) || !on_device(d_y, dev) ||
+        (nnz > 0 && (!on_device(d_col_indx, dev) || !on_device(d_values, dev) || !on_device(d_x, dev)))) {
+        record_cuda_error(cudaErrorInvalidValue,
+                          "alphasparse_cuda_d_csrmv_noalloc takes pointers to memory of the current device only");
         return ALPHA_SPARSE_STATUS_INVALID_POINTER;
     }
     const long long total = (long long)rows + nnz;
@@ -1219,7 +1296,7 @@ extern "C" alphasparse_status_t alphasparse_cuda_d_csrmv_noalloc(
                                                         beta, tile, nullptr, carry_row, carry_val, nopush);
     spmv_merge_fixup_kernel<double, false><<<(unsigned)((tiles + 255) / 256), 256, 0, st>>>(
         rows, tiles, carry_row, carry_val, d_y, alpha, none);
-    count_launch(3);
+    count_launch(4);
     ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }

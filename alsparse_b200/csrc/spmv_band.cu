@@ -29,91 +29,16 @@
 namespace asb {
 
 constexpr int kBandThreads = 512;
-constexpr int kBandLanes = 8;  // lanes per segment (sizing of the splits)
+constexpr int kBandLanes = 8;  // lanes per segment
 
-// Block (b, s): band b, list positions [s*chunk, (s+1)*chunk).  A group of G lanes takes R segments
-// at a time and keeps U (col, val) pairs per segment in flight in every lane.
-template <typename T, int G, int U, int R, int NT>
-__global__ void __launch_bounds__(NT)
-    spmv_band_kernel(int cols, int width, int bands, int nl, int chunk, const int *__restrict__ seg,
-                     const int *__restrict__ col, const T *__restrict__ val, const T *__restrict__ x,
-                     T *__restrict__ partial) {
-    extern __shared__ __align__(16) unsigned char band_smem[];
-    T *sx = reinterpret_cast<T *>(band_smem);
-    const int b = blockIdx.x, s = blockIdx.y, tid = threadIdx.x;
-    const long long c0l = (long long)b * width;
-    const int c0 = (int)c0l;
-    const int n = (int)(cols - c0l < width ? cols - c0l : width);
-    const T *xb = x + c0l;
-
-    if ((reinterpret_cast<uintptr_t>(xb) & 15) == 0) {
-        constexpr int per = 16 / (int)sizeof(T);
-        const int nv = n / per;
-        const int4 *src = reinterpret_cast<const int4 *>(xb);
-        int4 *dst = reinterpret_cast<int4 *>(sx);
-        for (int i = tid; i < nv; i += NT) dst[i] = __ldg(src + i);
-        for (int i = nv * per + tid; i < n; i += NT) sx[i] = __ldg(xb + i);
-    } else {
-        for (int i = tid; i < n; i += NT) sx[i] = __ldg(xb + i);
-    }
-    __syncthreads();
-
-    constexpr int NG = NT / G;
-    const int g = tid / G, gl = tid % G;
-    const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (((tid & 31) / G) * G));
-    const int p1 = min(nl, (s + 1) * chunk);
-    const int *seg_lo = seg + (size_t)b * nl, *seg_hi = seg_lo + nl;
-
-    for (int p = s * chunk + g; p < p1; p += NG * R) {
-        int k[R], e[R];
-        T acc[R];
-#pragma unroll
-        for (int r = 0; r < R; r++) {
-            const int pp = p + r * NG;
-            k[r] = 0, e[r] = 0, acc[r] = T(0);
-            if (pp < p1) {
-                k[r] = __ldg(seg_lo + pp) + gl;
-                e[r] = __ldg(seg_hi + pp);
-            }
-        }
-        bool more = true;
-        while (more) {
-            int cc[R][U];
-            T vv[R][U];
-#pragma unroll
-            for (int r = 0; r < R; r++)
-#pragma unroll
-                for (int u = 0; u < U; u++) {
-                    const int kk = k[r] + u * G;
-                    if (kk < e[r]) {
-                        cc[r][u] = __ldcs(col + kk);
-                        vv[r][u] = __ldcs(val + kk);
-                    }
-                }
-            more = false;
-#pragma unroll
-            for (int r = 0; r < R; r++) {
-#pragma unroll
-                for (int u = 0; u < U; u++)
-                    if (k[r] + u * G < e[r]) acc[r] = fma(vv[r][u], sx[cc[r][u] - c0], acc[r]);
-                k[r] += G * U;
-                more |= k[r] < e[r];
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < R; r++) {
-#pragma unroll
-            for (int o = G / 2; o > 0; o >>= 1) acc[r] += __shfl_xor_sync(gmask, acc[r], o, G);
-            const int pp = p + r * NG;
-            if (gl == 0 && pp < p1) partial[(size_t)pp * bands + b] = acc[r];
-        }
-    }
-}
-
-// The same work with 16-byte loads: a lane takes whole aligned quads (four consecutive stored elements: one
-// int4 of columns, one or two 16-byte loads of values) and masks the elements that fall outside the
-// segment, as the vector SpMV kernel does for rows.  Four times the bytes in flight per load instruction,
-// which is what a kernel that streams the matrix once needs to cover the latency of HBM.
+// Block (b, s): band b, list positions [s*chunk, (s+1)*chunk).  A group of G lanes takes R segments at a time and
+// keeps U quads per segment in flight in every lane.  A lane takes whole aligned quads (four consecutive stored
+// elements: one int4 of columns, one or two 16-byte loads of values) and masks the elements that fall outside the
+// segment, as the vector SpMV kernel does for rows: the bytes in flight per load instruction are what covers the
+// latency of HBM in a kernel that streams the matrix once.  Measured on B200 (power-law matrix, 1.9e8 elements in
+// 4205 long rows, 1024 bands): 8 lanes x 1 quad x 2 segments and 4 lanes x 2 quads x 1 segment per group, 512
+// threads, two blocks per SM, are the fastest shapes; scalar loads (4 bytes per lane) took twice as long, and
+// forcing three blocks per SM (40 registers, spills) or 32 KB bands with six smaller blocks were slower too.
 template <typename T>
 struct BandQuad {
     T v[4];
@@ -140,6 +65,26 @@ __global__ void __launch_bounds__(NT)
     const int c0 = (int)c0l;
     const int n = (int)(cols - c0l < width ? cols - c0l : width);
     const T *xb = x + c0l;
+
+    constexpr int NG = NT / G;
+    const int g = tid / G, gl = tid % G;
+    const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (((tid & 31) / G) * G));
+    const int p1 = min(nl, (s + 1) * chunk);
+    const int *seg_lo = seg + (size_t)b * nl, *seg_hi = seg_lo + nl;
+
+    // The bounds of the first segments are fetched before the band of x is staged, and those of every later
+    // step while the current one is multiplied: the look-up never sits in front of the matrix loads.
+    int na[R], ne[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+        const int pp = s * chunk + g + r * NG;
+        na[r] = 0, ne[r] = 0;
+        if (pp < p1) {
+            na[r] = __ldg(seg_lo + pp);
+            ne[r] = __ldg(seg_hi + pp);
+        }
+    }
+
     if ((reinterpret_cast<uintptr_t>(xb) & 15) == 0) {
         constexpr int per = 16 / (int)sizeof(T);
         const int nv = n / per;
@@ -152,24 +97,19 @@ __global__ void __launch_bounds__(NT)
     }
     __syncthreads();
 
-    constexpr int NG = NT / G;
-    const int g = tid / G, gl = tid % G;
-    const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (((tid & 31) / G) * G));
-    const int p1 = min(nl, (s + 1) * chunk);
-    const int *seg_lo = seg + (size_t)b * nl, *seg_hi = seg_lo + nl;
-
     for (int p = s * chunk + g; p < p1; p += NG * R) {
         int a[R], e[R], q[R];
         T acc[R];
 #pragma unroll
         for (int r = 0; r < R; r++) {
-            const int pp = p + r * NG;
-            a[r] = 0, e[r] = 0, acc[r] = T(0);
-            if (pp < p1) {
-                a[r] = __ldg(seg_lo + pp);
-                e[r] = __ldg(seg_hi + pp);
-            }
+            a[r] = na[r], e[r] = ne[r], acc[r] = T(0);
             q[r] = (a[r] >> 2) + gl;
+            const int pn = p + (R + r) * NG;  // the segment this slot takes in the next step
+            na[r] = 0, ne[r] = 0;
+            if (pn < p1) {
+                na[r] = __ldg(seg_lo + pn);
+                ne[r] = __ldg(seg_hi + pn);
+            }
         }
         bool more = true;
         while (more) {
@@ -212,11 +152,12 @@ __global__ void __launch_bounds__(NT)
     }
 }
 
-// One warp per long row: its partial sums in band order (lane j takes bands j, j+32, ..., then a fixed
-// tree over the lanes), alpha times the total added to what the merge kernel and its fix-up left in y.
-template <typename T>
+// One warp per long row: its partial sums in band order (lane j takes bands j, j+32, ..., then a fixed tree over
+// the lanes).  ASSIGN: the row belongs to this path alone, y[row] = alpha * total + beta * y[row]; otherwise alpha
+// times the total is added to what the merge kernel and its fix-up left in y.
+template <typename T, bool ASSIGN>
 __global__ void spmv_band_reduce_kernel(int nl, int bands, const int *__restrict__ row,
-                                        const T *__restrict__ partial, T *__restrict__ y, T alpha) {
+                                        const T *__restrict__ partial, T *__restrict__ y, T alpha, T beta) {
     const int p = (int)(((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
     const int lane = threadIdx.x & 31;
     if (p >= nl) return;
@@ -227,7 +168,8 @@ __global__ void spmv_band_reduce_kernel(int nl, int bands, const int *__restrict
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     if (lane == 0) {
         const int r = row[p];
-        y[r] = fma(alpha, acc, y[r]);
+        if (ASSIGN) y[r] = (beta == T(0)) ? alpha * acc : fma(beta, y[r], alpha * acc);
+        else y[r] = fma(alpha, acc, y[r]);
     }
 }
 
@@ -269,47 +211,41 @@ void band_destroy(BandTables &b) {
     b = BandTables{};
 }
 
-alphasparse_status_t band_build(DeviceCtx *ctx, const MergeCoord *h_tile, std::vector<char> &skip, cudaStream_t st) {
-    if (!option(kOptBandEnable)) return ALPHA_SPARSE_STATUS_SUCCESS;
+struct BandCand {
+    int row, a, e;
+    int64_t t0, t1;  // merge tiles covered (interior form only)
+};
+
+static int64_t band_width_of(const DeviceCtx *ctx) {
     const size_t tsz = ctx->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE ? 8 : 4;
-    const int64_t tiles = ctx->merge_tiles;
     int64_t width = option(kOptBandBytes) / (int64_t)tsz & ~31ll;
     if (width < 32) width = 32;
     if (width * (int64_t)tsz > 200 * 1024) width = (200 * 1024 / (int64_t)tsz) & ~31ll;
-    const int64_t bands = (ctx->cols + width - 1) / width;
-    if (bands < 1 || bands > (1 << 20)) return ALPHA_SPARSE_STATUS_SUCCESS;
-    const int64_t min_len = std::max<int64_t>(1, option(kOptBandMinSeg) * bands);
+    return width;
+}
 
-    // Candidates: maximal runs of tiles that lie wholly inside one row.
-    struct Cand {
-        int row, a, e;
-        int64_t t0, t1;
-    };
-    std::vector<Cand> cand;
-    int64_t covered = 0;
-    for (int64_t t = 0; t < tiles;) {
-        if (h_tile[t].row != h_tile[t + 1].row || h_tile[t].row >= ctx->rows) {
-            t++;
-            continue;
-        }
-        int64_t u = t + 1;
-        while (u < tiles && h_tile[u + 1].row == h_tile[t].row) u++;
-        const int a = h_tile[t].nz, e = h_tile[u].nz;
-        if ((int64_t)e - a >= min_len) {
-            cand.push_back({h_tile[t].row, a, e, t, u});
-            covered += e - a;
-        }
-        t = u;
-    }
+int64_t band_long_min(const DeviceCtx *ctx) {
+    const int64_t width = band_width_of(ctx);
+    const int64_t bands = (ctx->cols + width - 1) / width;
+    return std::max<int64_t>(1, option(kOptBandMinSeg) * std::max<int64_t>(bands, 1));
+}
+
+// Builds the tables for the candidates (element ranges of rows).  `all_or_nothing`: one candidate out of
+// ascending column order drops the whole path (row bins need every long row taken) instead of just that row.
+static alphasparse_status_t band_finish(DeviceCtx *ctx, std::vector<BandCand> &cand, int64_t covered, bool all_or_nothing,
+                                        cudaStream_t st) {
+    const size_t tsz = ctx->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE ? 8 : 4;
+    const int64_t width = band_width_of(ctx);
+    const int64_t bands = (ctx->cols + width - 1) / width;
     auto worth = [&] {
         return (int64_t)cand.size() >= std::max<int64_t>(1, option(kOptBandMinRows)) &&
                covered * 100 >= ctx->nnz * option(kOptBandMinSharePct);
     };
-    if (cand.empty() || !worth()) return ALPHA_SPARSE_STATUS_SUCCESS;
+    if (bands < 1 || bands > (1 << 20) || cand.empty() || !worth()) return ALPHA_SPARSE_STATUS_SUCCESS;
 
     // Longest first, dealt round-robin to the `splits` blocks of a band: equal work per block, and the
     // lane groups of a warp meet segments of similar length.
-    std::stable_sort(cand.begin(), cand.end(), [](const Cand &p, const Cand &q) { return p.e - p.a > q.e - q.a; });
+    std::stable_sort(cand.begin(), cand.end(), [](const BandCand &p, const BandCand &q) { return p.e - p.a > q.e - q.a; });
     int nl = (int)cand.size();
     std::vector<int> h_a((size_t)nl), h_e((size_t)nl), h_flag((size_t)nl, 0);
     for (int i = 0; i < nl; i++) h_a[(size_t)i] = cand[(size_t)i].a, h_e[(size_t)i] = cand[(size_t)i].e;
@@ -351,10 +287,14 @@ alphasparse_status_t band_build(DeviceCtx *ctx, const MergeCoord *h_tile, std::v
             }
             cand[keep++] = cand[(size_t)i];
         }
+        if (all_or_nothing && keep != cand.size()) keep = 0;
         cand.resize(keep);
         nl = (int)keep;
     }
-    if (cand.empty() || !worth()) return fail(ALPHA_SPARSE_STATUS_SUCCESS);
+    if (cand.empty() || !worth()) {
+        cand.clear();
+        return fail(ALPHA_SPARSE_STATUS_SUCCESS);
+    }
 
     int64_t splits = option(kOptBandSplits);
     if (splits <= 0) splits = (148 * 3 * 8 + bands - 1) / bands;  // about eight waves of blocks
@@ -363,19 +303,12 @@ alphasparse_status_t band_build(DeviceCtx *ctx, const MergeCoord *h_tile, std::v
     const int chunk = (int)((nl + splits - 1) / splits);
     std::vector<int> h_row((size_t)nl);
     {
-        // sorted index i sits in split i % splits at place i / splits
-        std::vector<int> pos_of((size_t)nl);
-        std::vector<int> filled((size_t)splits, 0);
-        for (int i = 0; i < nl; i++) {
-            const int s = (int)(i % splits);
-            pos_of[(size_t)i] = s * chunk + filled[(size_t)s]++;
-        }
-        // the last splits may hold fewer rows than `chunk`: positions must stay dense, so renumber
+        // sorted index i goes to split i % splits; a stable sort by split number makes the positions dense
         std::vector<int> order((size_t)nl);
         std::iota(order.begin(), order.end(), 0);
-        std::stable_sort(order.begin(), order.end(), [&](int p, int q) { return pos_of[(size_t)p] < pos_of[(size_t)q]; });
+        std::stable_sort(order.begin(), order.end(), [&](int p, int q) { return p % splits < q % splits; });
         for (int p = 0; p < nl; p++) {
-            const Cand &c = cand[(size_t)order[(size_t)p]];
+            const BandCand &c = cand[(size_t)order[(size_t)p]];
             h_row[(size_t)p] = c.row, h_a[(size_t)p] = c.a, h_e[(size_t)p] = c.e;
         }
     }
@@ -404,11 +337,50 @@ alphasparse_status_t band_build(DeviceCtx *ctx, const MergeCoord *h_tile, std::v
     TRY(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
 #undef TRY
     cudaFree(d_a), cudaFree(d_e), cudaFree(d_flag);
-    for (const Cand &c : cand)
-        for (int64_t t = c.t0; t < c.t1; t++) skip[(size_t)t] = 1;
     ctx->band = bt;
     ctx->device_bytes += (int64_t)(sizeof(int) * (size_t)nl * (size_t)(bands + 2) + tsz * (size_t)nl * (size_t)bands);
     return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+alphasparse_status_t band_build(DeviceCtx *ctx, const MergeCoord *h_tile, std::vector<char> &skip, cudaStream_t st) {
+    if (!option(kOptBandEnable)) return ALPHA_SPARSE_STATUS_SUCCESS;
+    const int64_t tiles = ctx->merge_tiles;
+    const int64_t min_len = band_long_min(ctx);
+    // Candidates: maximal runs of tiles that lie wholly inside one row.
+    std::vector<BandCand> cand;
+    int64_t covered = 0;
+    for (int64_t t = 0; t < tiles;) {
+        if (h_tile[t].row != h_tile[t + 1].row || h_tile[t].row >= ctx->rows) {
+            t++;
+            continue;
+        }
+        int64_t u = t + 1;
+        while (u < tiles && h_tile[u + 1].row == h_tile[t].row) u++;
+        const int a = h_tile[t].nz, e = h_tile[u].nz;
+        if ((int64_t)e - a >= min_len) {
+            cand.push_back({h_tile[t].row, a, e, t, u});
+            covered += e - a;
+        }
+        t = u;
+    }
+    alphasparse_status_t s = band_finish(ctx, cand, covered, false, st);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS || ctx->band.rows == 0) return s;
+    for (const BandCand &c : cand)
+        for (int64_t t = c.t0; t < c.t1; t++) skip[(size_t)t] = 1;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+alphasparse_status_t band_build_rows(DeviceCtx *ctx, const int *h_ptr, const std::vector<int> &rows, cudaStream_t st) {
+    std::vector<BandCand> cand;
+    cand.reserve(rows.size());
+    int64_t covered = 0;
+    for (int r : rows) {
+        cand.push_back({r, h_ptr[r], h_ptr[r + 1], 0, 0});
+        covered += (int64_t)h_ptr[r + 1] - h_ptr[r];
+    }
+    alphasparse_status_t s = band_finish(ctx, cand, covered, true, st);
+    if (s == ALPHA_SPARSE_STATUS_SUCCESS && ctx->band.rows > 0) ctx->band.whole_rows = true;
+    return s;
 }
 
 template <typename K, typename T>
@@ -428,29 +400,28 @@ static void launch_band_as(K kernel, int threads, std::atomic<size_t> &granted, 
 
 template <typename T>
 void launch_band(DeviceCtx *ctx, const T *x, cudaStream_t st) {
-    static std::atomic<size_t> granted[6] = {{0}, {0}, {0}, {0}, {0}, {0}};
-    switch (option(kOptBandVariant)) {
-        case 1: launch_band_as(spmv_band_quad_kernel<T, 4, 2, 2, 256>, 256, granted[1], ctx, x, st); break;
-        case 2: launch_band_as(spmv_band_quad_kernel<T, 4, 2, 1, 512>, 512, granted[2], ctx, x, st); break;
-        case 3: launch_band_as(spmv_band_quad_kernel<T, 8, 1, 2, 512>, 512, granted[3], ctx, x, st); break;
-        case 4: launch_band_as(spmv_band_quad_kernel<T, 4, 1, 2, 512>, 512, granted[4], ctx, x, st); break;
-        case 5: launch_band_as(spmv_band_quad_kernel<T, 2, 2, 2, 256>, 256, granted[5], ctx, x, st); break;
-        default: launch_band_as(spmv_band_kernel<T, 8, sizeof(T) == 8 ? 2 : 4, 2, 512>, 512, granted[0], ctx, x, st); break;
-    }
+    static std::atomic<size_t> granted[2] = {};
+    if (option(kOptBandVariant) == 1)
+        launch_band_as(spmv_band_quad_kernel<T, 4, 2, 1, kBandThreads>, kBandThreads, granted[1], ctx, x, st);
+    else
+        launch_band_as(spmv_band_quad_kernel<T, 8, 1, 2, kBandThreads>, kBandThreads, granted[0], ctx, x, st);
 }
 
 template <typename T>
-void launch_band_reduce(DeviceCtx *ctx, T alpha, T *y, cudaStream_t st) {
+void launch_band_reduce(DeviceCtx *ctx, T alpha, T beta, T *y, cudaStream_t st) {
     const BandTables &b = ctx->band;
     const unsigned blocks = (unsigned)(((long long)b.rows * 32 + 255) / 256);
-    spmv_band_reduce_kernel<T><<<blocks, 256, 0, st>>>(b.rows, b.bands, b.d_row, static_cast<const T *>(b.d_partial), y,
-                                                       alpha);
+    const T *partial = static_cast<const T *>(b.d_partial);
+    if (b.whole_rows)
+        spmv_band_reduce_kernel<T, true><<<blocks, 256, 0, st>>>(b.rows, b.bands, b.d_row, partial, y, alpha, beta);
+    else
+        spmv_band_reduce_kernel<T, false><<<blocks, 256, 0, st>>>(b.rows, b.bands, b.d_row, partial, y, alpha, beta);
     count_launch();
 }
 
 template void launch_band<float>(DeviceCtx *, const float *, cudaStream_t);
 template void launch_band<double>(DeviceCtx *, const double *, cudaStream_t);
-template void launch_band_reduce<float>(DeviceCtx *, float, float *, cudaStream_t);
-template void launch_band_reduce<double>(DeviceCtx *, double, double *, cudaStream_t);
+template void launch_band_reduce<float>(DeviceCtx *, float, float, float *, cudaStream_t);
+template void launch_band_reduce<double>(DeviceCtx *, double, double, double *, cudaStream_t);
 
 }  // namespace asb

@@ -151,6 +151,11 @@ def mm(kind, operation, alpha, A, descr_, layout, x, columns, ldx, beta, y, ldy)
                                                            beta, _ptr(y), ldy)
 
 
+def optimize(A):
+    """alphasparse_optimize: re-runs the analysis of the handle."""
+    return capi.load().alphasparse_optimize(A)
+
+
 def mat_info(A):
     info = MatInfo()
     st = capi.load().alphasparse_cuda_get_mat_info(A, C.byref(info))
@@ -200,6 +205,13 @@ def partition_rows_by_nnz(rows_end, parts):
     return out
 
 
+def kernel_status(A, clear=False):
+    """alphasparse_cuda_kernel_status: (status, code) -- the error word of the handle's kernels (0 = fine)."""
+    code = C.c_int()
+    st = capi.load().alphasparse_cuda_kernel_status(A, C.byref(code), 1 if clear else 0)
+    return st, code.value
+
+
 def profile_kernel(A, enable=True):
     return capi.load().alphasparse_cuda_profile_kernel(A, 1 if enable else 0)
 
@@ -217,15 +229,6 @@ def csrmv_noalloc(rows, cols, nnz, alpha, d_row_ptr, d_col_indx, d_values, d_x, 
     (scratch lives in a fixed 4 MiB array inside the library; rows + nnz <= 375,802,112)."""
     return capi.load().alphasparse_cuda_d_csrmv_noalloc(rows, cols, nnz, alpha, _ptr(d_row_ptr), _ptr(d_col_indx),
                                                          _ptr(d_values), _ptr(d_x), beta, _ptr(d_y))
-
-
-def probe_gather_rate(kind, table_elems, gathers=1 << 27):
-    """Random single-element gathers per second the current GPU sustains from a table of that size."""
-    rate = C.c_double()
-    st = capi.load().alphasparse_cuda_probe_gather_rate(capi.FLOAT if kind == "s" else capi.DOUBLE, table_elems,
-                                                         gathers, C.byref(rate))
-    assert st == SUCCESS, (capi.STATUS_NAMES[st], last_error())
-    return rate.value
 
 
 def read_coo(kind, path):

@@ -17,7 +17,10 @@ Workloads (seeded synthetic stand-ins for the user-supplied matrix files the ref
 
 With N > 1 (launched by torch.distributed.run, one process per GPU) the rows are split by the
 reference's nnz-balanced rule, x is replicated, y stays partitioned: total work is fixed, so the
-scaling is "strong".  `--impl reference` times the reference's own OpenMP CPU kernel instead.
+scaling is "strong"; the default run then also measures, in the same process group, the iterated
+power-law SpMV whose y becomes the next x on every GPU (other_workloads.powerlaw_iterated: the
+allgather done inside the SpMV kernels, by a peer-copy kernel, and by NCCL; checked against the
+oracle).  `--impl reference` times the reference's own OpenMP CPU kernel on the same workload.
 """
 import argparse
 import json
@@ -34,11 +37,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only without MEASURED_PEAKS.json
-
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
-# captures summarised under profiles/ (bytes; None where no capture exists yet).
-NCU_TRAFFIC = {"uniform16": 3937436144, "stencil27": 1393600664, "powerlaw": None, "spmm64": 17518304000}
+FALLBACK_HBM_GBS = 6650.0  # B200 copy bandwidth used only when MEASURED_PEAKS.json is absent
 
 WORKLOADS = {
     "uniform16": dict(kind="s", rows_log2=24, alpha=1.5, beta=0.5, op="mv"),
@@ -89,6 +88,22 @@ def algorithmic_bytes(cfg, rows, cols, nnz):
 
 def flops(cfg, nnz):
     return 2 * nnz * cfg.get("columns", 1)
+
+
+def gather_rate(elem_bytes, table_elems, stream_ptr, gathers=1 << 27):
+    """Random single-element gathers per second this GPU sustains from a table of that many elements: the probe
+    built from bench_gather_probe.cu beside this file (python -m alsparse_b200.build)."""
+    import ctypes as C
+    path = os.path.join(ROOT, "libbench_gather_probe.so")
+    if not os.path.exists(path):
+        raise ImportError(f"{path} is missing: run `python -m alsparse_b200.build`")
+    lib = C.CDLL(path, mode=C.RTLD_LOCAL)
+    lib.bench_gather_rate.restype = C.c_int
+    lib.bench_gather_rate.argtypes = [C.c_int, C.c_longlong, C.c_longlong, C.c_void_p, C.POINTER(C.c_double)]
+    rate = C.c_double()
+    err = lib.bench_gather_rate(elem_bytes, table_elems, gathers, stream_ptr, C.byref(rate))
+    assert err == 0, f"gather probe failed (cudaError {err})"
+    return rate.value
 
 
 # ------------------------------------------------------------------------------------------------
@@ -180,35 +195,39 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------
+# what both arms say about the workload (identical dictionaries: the two lines describe the same job)
+# ------------------------------------------------------------------------------------------------
+def workload_config(name, cfg, rows, cols, nnz, reduced):
+    nbytes = algorithmic_bytes(cfg, rows, cols, nnz)
+    return {"workload": name + (" (REDUCED SIZE: development run)" if reduced else ""), "rows": rows, "cols": cols,
+            "nnz": nnz, "alpha": cfg["alpha"], "beta": cfg["beta"], "columns": cfg.get("columns", 1),
+            "l2": f"inputs ({nbytes / 1e6:.0f} MB per step) exceed the 126 MB L2; no flush between steps",
+            "algorithmic_bytes_per_step": nbytes}
+
+
+def metric_name(cfg):
+    return "csr_spmv_effective_gbs" if cfg["op"] == "mv" else "csr_spmm_effective_gbs"
+
+
+# ------------------------------------------------------------------------------------------------
 # the reference arm / CPU baseline
 # ------------------------------------------------------------------------------------------------
-def cpu_reference_run(name, cfg, steps, warmup, sample_rows_log2=22):
-    """The reference's own OpenMP kernel (oracle/_ref) -- or the oracle port of it when those objects
-    are absent -- on a bounded sample: the first 2^sample_rows_log2 rows of the workload's matrix with
-    x at full length, all host threads.  Returns (GB/s, GFLOP/s, ms per step, descriptor dict)."""
+def cpu_reference_time(cfg, m, cols, x, y, steps, warmup):
+    """Times the reference's own OpenMP kernel (oracle/_ref) -- or the oracle port of it when those objects are
+    absent -- on the WHOLE matrix `m` with all host threads.  y is updated in place, as a caller's would be.
+    Returns (ms per call, descriptor dict)."""
     import oracle
-    from alsparse_b200 import synth
-    kind = cfg["kind"]
-    lens = global_row_lengths(name, cfg)
-    rows, cols = len(lens), len(lens)
-    n = min(rows, 1 << sample_rows_log2)
-    if cfg["op"] == "mm":
-        n = min(n, 1 << 19)
-    m = local_block(name, cfg, lens, 0, n)
-    columns = cfg.get("columns", 1)
-    x = synth.vector(kind, 0, 1, cols * columns, 0.0 if name == "stencil27" else -1.0, 1.0)
-    y = synth.vector(kind, 0, 2, n * columns)
+    kind, columns = cfg["kind"], cfg.get("columns", 1)
     use_ref = oracle.ref_available()
     threads = oracle.ref_cores() if use_ref else oracle.max_threads()
-    A = oracle.RefCsr.from_csr(kind, 0, n, cols, m.rows_start, m.rows_end, m.col, m.val) if use_ref else None
+    A = oracle.RefCsr.from_csr(kind, 0, m.nrows, cols, m.rows_start, m.rows_end, m.col, m.val) if use_ref else None
 
     def step():
         if cfg["op"] == "mv":
             if use_ref:
                 A.gemv(cfg["alpha"], x, cfg["beta"], y, omp_threads=threads)
             else:
-                oracle.gemv(kind, m.rows_start, m.rows_end, m.col, m.val, cfg["alpha"], x, cfg["beta"], y,
-                            threads=threads)
+                oracle.gemv(kind, m.rows_start, m.rows_end, m.col, m.val, cfg["alpha"], x, cfg["beta"], y, threads=threads)
         else:
             if use_ref:
                 A.gemm("row", cfg["alpha"], x, columns, columns, cfg["beta"], y, columns, omp_threads=threads)
@@ -222,24 +241,179 @@ def cpu_reference_run(name, cfg, steps, warmup, sample_rows_log2=22):
     for _ in range(steps):
         step()
     dt = (time.perf_counter() - t0) / max(steps, 1)
-    nbytes = algorithmic_bytes(cfg, n, cols, m.nnz)
     desc = {"kind": "reference" if use_ref else "port", "cores": threads,
-            "sample": f"rows [0, {n}) of {rows} ({m.nnz} stored elements), x at full length {cols}"
-                      f"{' x ' + str(columns) if columns > 1 else ''}; {steps} timed calls after {warmup} warm-up"}
-    return nbytes / dt / 1e9, flops(cfg, m.nnz) / dt / 1e9, dt * 1e3, desc
+            "sample": f"the whole matrix ({m.nrows} rows, {m.nnz} stored elements); {steps} timed calls after {warmup} warm-up"}
+    return dt * 1e3, desc
 
 
-def run_reference_arm(args, name, cfg, rank):
+def run_reference_arm(args, name, cfg, reduced, rank):
+    """The reference's CPU implementation of the path on this box's host cores, same workload as the GPU arm.
+    Under torchrun rank 0 alone works."""
     if rank != 0:
         return
-    gbs, gfl, ms, desc = cpu_reference_run(name, cfg, args.steps, max(args.warmup, 1))
-    line = {"impl": "reference", "metric": "csr_spmv_effective_gbs" if cfg["op"] == "mv" else "csr_spmm_effective_gbs",
-            "value": gbs, "unit": "GB/s", "gflops": gfl, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": max(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32" if cfg["kind"] == "s" else "f64", "data": "synthetic",
-            "config": {"workload": name}, "cpu_baseline": dict(value=gbs, unit="GB/s", **desc),
+    from alsparse_b200 import synth
+    kind, columns = cfg["kind"], cfg.get("columns", 1)
+    lens = global_row_lengths(name, cfg)
+    rows = cols = len(lens)
+    m = local_block(name, cfg, lens, 0, rows)
+    x = synth.vector(kind, 0, 1, cols * columns, 0.0 if name == "stencil27" else -1.0, 1.0)
+    y = synth.vector(kind, 0, 2, rows * columns)
+    warmup = max(args.warmup, 1)
+    ms, desc = cpu_reference_time(cfg, m, cols, x, y, args.steps, warmup)
+    nbytes = algorithmic_bytes(cfg, rows, cols, m.nnz)
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    line = {"impl": "reference", "metric": metric_name(cfg), "value": gbs, "unit": "GB/s",
+            "gflops": flops(cfg, m.nnz) / (ms * 1e-3) / 1e9, "n_gpus": args.gpus, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32" if kind == "s" else "f64", "data": "synthetic",
+            "config": workload_config(name, cfg, rows, cols, m.nnz, reduced),
+            "cpu_baseline": dict(value=gbs, unit="GB/s", **desc),
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# ncu traffic figures (profiles/ncu_traffic.json): reported only for the kernel they were captured on
+# ------------------------------------------------------------------------------------------------
+def ncu_traffic(name, kernel, reduced, world):
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    if reduced or world != 1 or not os.path.exists(path):
+        return None, None
+    rec = json.load(open(path)).get(name)
+    if not rec or rec.get("kernel") != kernel:
+        return None, (f"no capture of {kernel} (profiles/ncu_traffic.json has {rec.get('kernel')})" if rec else None)
+    return rec["dram_bytes_per_launch"], f"ncu capture {rec['summary']} ({rec['kernel']}, at commit {rec['commit']})"
+
+
+def sampled_rows(m, rng, n_random):
+    """Sorted distinct local row numbers (first, last, the eight longest, random ones) and those rows as a small
+    CSR with local offsets and the matrix's own columns."""
+    lens = np.diff(m.ptr)
+    longest = np.argpartition(lens, -min(8, len(lens)))[-8:]
+    pick = np.unique(np.concatenate([rng.integers(0, m.nrows, n_random), [0, m.nrows - 1], longest]))
+    ptr = np.concatenate([[0], np.cumsum(lens[pick])]).astype(np.int32)
+    idx = np.concatenate([np.arange(m.ptr[r], m.ptr[r + 1], dtype=np.int64) for r in pick])
+    return pick, ptr, m.col[idx], m.val[idx]
+
+
+# ------------------------------------------------------------------------------------------------
+# iterated power-law SpMV over several GPUs: y of every step becomes the next x on all GPUs
+# ------------------------------------------------------------------------------------------------
+def measure_iterated(args, rank, world, stream, iterations=50):
+    """x_{t+1} = A x_t on the power-law matrix, rows split over the GPUs, the allgather of y done three ways:
+    inside the SpMV kernels (peer stores), by one peer-copy kernel after them, and by a NCCL all_gather.
+    Every way is checked on its first step against the oracle (sampled rows of this rank, x0 known) and timed
+    over `iterations` steps; the time of a step is the maximum over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    import oracle
+    from alsparse_b200 import capi, multi, spblas, synth
+
+    name = "powerlaw"
+    cfg = dict(WORKLOADS[name])
+    if args.iter_rows_log2:
+        cfg["rows_log2"] = args.iter_rows_log2
+    kind, tol = cfg["kind"], 1e-12
+    lens = global_row_lengths(name, cfg)
+    rows = cols = len(lens)
+    rows_end = np.cumsum(lens, dtype=np.int64)
+    nnz_total = int(rows_end[-1])
+    part = multi.row_partition(rows_end, world)
+    r0, r1 = multi.local_rows(part, rank)
+    m = local_block(name, cfg, lens, r0, r1)
+    st, A = spblas.create_csr(kind, capi.BASE_ZERO, m.nrows, cols, m.rows_start, m.rows_end, m.col, m.val)
+    assert st == capi.SUCCESS, (capi.STATUS_NAMES[st], spblas.last_error())
+    x0 = synth.vector(kind, 0, 1, cols)
+    x0_d = torch.from_numpy(x0).cuda()
+    y_d = torch.zeros(m.nrows, dtype=torch.float64, device="cuda")
+    xa, xb = torch.empty_like(x0_d), torch.empty_like(x0_d)
+    descr = spblas.descr()
+
+    # the comparand of step 1: this rank's sampled rows through the oracle's plain kernel
+    pick, sptr, scol, sval = sampled_rows(m, np.random.default_rng(100 + rank), max(64, 4000 // world)) if m.nrows else \
+        (np.zeros(0, np.int64), np.zeros(1, np.int32), m.col[:0], m.val[:0])
+    y_ref = oracle.gemv(kind, sptr[:-1], sptr[1:], scol, sval, 1.0, x0, 0.0, np.zeros(len(pick)))
+    prod = np.abs(sval * x0[scol])
+    scale = np.add.reduceat(np.concatenate([prod, [0.0]]), np.minimum(sptr[:-1], len(prod))) * (np.diff(sptr) > 0)
+
+    def all_max(v):
+        t = torch.tensor([float(v)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def barrier():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    out = {"iterations": iterations, "rows": rows, "nnz": nnz_total, "dtype": "f64", "alpha": 1.0, "beta": 0.0,
+           "rows_of_rank0": int(part[1] - part[0]),
+           "nvlink_bytes_per_gpu_per_iteration": {"sent": int(m.nrows) * 8 * (world - 1), "received": int(rows - m.nrows) * 8},
+           "parity": {"against": "oracle plain kernel, sampled rows of every rank, step 1 (x0 known)", "tolerance": tol,
+                      "rows_checked_on_rank0": int(len(pick))}, "modes": {}}
+    nbytes = algorithmic_bytes(cfg, rows, cols, nnz_total)
+    collectives = {"fused": "peer stores from inside the SpMV kernels + flag exchange",
+                   "push": "one peer-copy kernel after the SpMV + flag exchange",
+                   "nccl": "torch.distributed all_gather (NCCL) after the SpMV"}
+    with torch.cuda.stream(stream):
+        for mode in ("fused", "push", "nccl"):
+            ex = None
+            cur, nxt = xa, xb
+            if mode != "nccl":
+                ex = multi.FusedExchange(kind, part, rank, world, deliver_after=(mode == "push"))
+                ex.x_tensor().copy_(x0_d)
+            else:
+                cur.copy_(x0_d)
+            barrier()
+
+            def step():
+                nonlocal cur, nxt
+                if ex is not None:
+                    s = ex.step(1.0, A, 0.0, y_d)
+                else:
+                    s = spblas.mv(kind, 0, 1.0, A, descr, cur, 0.0, y_d)
+                    multi.allgather_rows(y_d, nxt, part)
+                    cur, nxt = nxt, cur
+                assert s == capi.SUCCESS, capi.STATUS_NAMES[s]
+
+            step()
+            barrier()
+            y1 = y_d.cpu().numpy()
+            x1 = (ex.x_tensor() if ex is not None else cur)
+            err = np.abs(y1[pick] - y_ref)
+            rows_ok = bool((err <= tol * scale + 1e-300).all()) if len(pick) else True
+            worst = float(np.max(err / np.maximum(tol * scale, 1e-300))) if len(pick) else 0.0
+            own_ok = bool(torch.equal(x1[r0:r1], y_d))                   # my rows arrived in my own next x
+            # every rank must hold the same gathered vector: compare a checksum of it across ranks
+            chk = float(x1.double().abs().sum().item())
+            same = all_max(chk) == -all_max(-chk)
+            ok = all_max(0.0 if (rows_ok and own_ok and same) else 1.0) == 0.0
+            for _ in range(max(args.warmup, 3)):
+                step()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(iterations):
+                step()
+            e1.record(stream)
+            e1.synchronize()
+            barrier()
+            ms = all_max(e0.elapsed_time(e1) / iterations)
+            status = 0
+            if ex is not None:
+                st_, status = ex.status()
+                ex.destroy()
+            status = int(all_max(status))
+            finite = all_max(0.0 if bool(torch.isfinite(y_d).all()) else 1.0) == 0.0
+            out["modes"][mode] = {"ms_per_iteration": ms, "value": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s",
+                                  "collective": collectives[mode], "parity_ok": ok,
+                                  "worst_row_error_over_tolerance": all_max(worst), "exchange_status": status,
+                                  "finite_after_all_iterations": finite}
+    out["parity"]["ok"] = all(v["parity_ok"] and v["exchange_status"] == 0 for v in out["modes"].values())
+    out["fused_vs_nccl"] = out["modes"]["nccl"]["ms_per_iteration"] / out["modes"]["fused"]["ms_per_iteration"]
+    spblas.destroy(A)
+    return out
 
 
 # ------------------------------------------------------------------------------------------------
@@ -254,6 +428,8 @@ def main():
     ap.add_argument("--workload", default="uniform16", choices=sorted(WORKLOADS))
     ap.add_argument("--rows-log2", type=int, default=None, help="shrink the matrix (development only)")
     ap.add_argument("--grid", type=int, default=None, help="shrink the stencil grid (development only)")
+    ap.add_argument("--iter-rows-log2", type=int, default=None,
+                    help="shrink the iterated power-law matrix of multi-GPU runs (development only)")
     ap.add_argument("--alg", default="auto", choices=["auto", "vector", "merge", "rowtile"])
     ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "push", "nccl"],
                     help="iterated workload with several GPUs: y reaches the next x from inside the SpMV kernels "
@@ -261,8 +437,10 @@ def main():
                          "whichever of the two the library prefers for this many GPUs (auto) or by a NCCL allgather (nccl)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cold", action="store_true", help="skip the cold-L2 variant")
     ap.add_argument("--no-others", action="store_true",
-                    help="do not append the short device-resident runs of the other three workloads (N=1 only)")
+                    help="do not append the other workloads (N=1: the three other configurations, each in a fresh "
+                         "process; N>1: the iterated power-law SpMV with its allgather, in this process group)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -279,7 +457,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     if args.impl == "reference":
-        run_reference_arm(args, name, cfg, rank)
+        run_reference_arm(args, name, cfg, reduced, rank)
         return
 
     import torch
@@ -293,7 +471,6 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
     kind, alpha, beta, op = cfg["kind"], cfg["alpha"], cfg["beta"], cfg["op"]
-    tdt = torch.float32 if kind == "s" else torch.float64
     columns = cfg.get("columns", 1)
     # y becomes the next x through an allgather; on one GPU only when the in-library exchange is asked for
     # by name (its kernels then deliver into this GPU's own next-x buffer: the form an ncu capture can take)
@@ -317,8 +494,10 @@ def main():
     _, info = spblas.mat_info(A)
 
     x_lo = 0.0 if name == "stencil27" else -1.0
-    x_h = torch.from_numpy(synth.vector(kind, 0, 1, cols * columns, x_lo, 1.0)).pin_memory()
-    y0_h = torch.from_numpy(synth.vector(kind, 0, 2, rows * columns)[r0 * columns:r1 * columns].copy()).pin_memory()
+    x_np = synth.vector(kind, 0, 1, cols * columns, x_lo, 1.0)
+    y0_np = synth.vector(kind, 0, 2, rows * columns)[r0 * columns:r1 * columns].copy()
+    x_h = torch.from_numpy(x_np).pin_memory()
+    y0_h = torch.from_numpy(y0_np).pin_memory()
     y_h = torch.empty_like(y0_h).pin_memory()
     x_d = x_h.cuda()
     y_d = y0_h.cuda()
@@ -394,10 +573,12 @@ def main():
         launches = spblas.launch_count() - launches0
         ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
 
-        # ---- duration of the dominant kernel, launch by launch, same stream -----------------------
-        # The library brackets the kernel with one pair of events per handle; reading them waits for the
-        # stream.  Launches are queued back to back, as in the timed region, and the events of the last one
-        # of each batch are read, so that no sample comes from a kernel started on an idle GPU.
+        # ---- duration of the product's kernels, launch by launch, same stream -----------------------
+        # The library brackets the kernels of the product with one pair of events per handle (one kernel for
+        # the vector and row-tile families; for a skewed matrix the span from the first to the last kernel of
+        # the product, since two large kernels share the work); reading them waits for the stream.  Launches
+        # are queued back to back, as in the timed region, and the events of the last one of each batch are
+        # read, so that no sample comes from a kernel started on an idle GPU.
         spblas.profile_kernel(A, True)
         kms = []
         batches = min(args.steps, 5)
@@ -408,6 +589,23 @@ def main():
         spblas.profile_kernel(A, False)
         barrier()
         kernel_ms = max_over_ranks(sum(kms) / len(kms))
+
+        # ---- cold L2: 256 MB are overwritten on the device before every timed step ---------------------
+        cold = None
+        if not args.no_cold and not iterate:
+            flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+            n_cold = max(3, min(args.steps, 10))
+            pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_cold)]
+            for a, b in pairs:
+                flush.fill_(1)
+                a.record(stream)
+                step()
+                b.record(stream)
+            torch.cuda.synchronize()
+            cold_ms = max_over_ranks(statistics.median(a.elapsed_time(b) for a, b in pairs))
+            del flush
+            barrier()
+            cold = cold_ms
 
         # ---- end to end: host vectors through the same entry point ----------------------------------
         e2e = None
@@ -428,16 +626,25 @@ def main():
                     print(f"[bench] sharded upload of x unavailable: {exc}", file=sys.stderr)
                     loader = None
 
-            def step_host():  # y is updated in place; with beta = 0.5 it converges, no reset needed
+            phase = {"load_x_ms": 0.0, "product_ms": 0.0}
+
+            def step_host(timed=False):  # y is updated in place; with beta = 0.5 it converges, no reset needed
+                t0 = time.perf_counter()
                 if loader is not None:
                     s = loader.load_x(x_block_h)
                     assert s == capi.SUCCESS, capi.STATUS_NAMES[s]
+                    if timed:
+                        torch.cuda.synchronize()
+                        phase["load_x_ms"] += (time.perf_counter() - t0) * 1e3
+                        t0 = time.perf_counter()
                     s = spblas.mv(kind, 0, alpha, A, descr, loader.x_ptr(), beta, yh)
                 elif op == "mv":
                     s = spblas.mv(kind, 0, alpha, A, descr, xh, beta, yh)
                 else:
                     s = spblas.mm(kind, 0, alpha, A, descr, capi.ROW_MAJOR, xh, columns, columns, beta, yh, columns)
                 assert s == capi.SUCCESS
+                if timed:
+                    phase["product_ms"] += (time.perf_counter() - t0) * 1e3
             for _ in range(2):
                 step_host()
             barrier()
@@ -451,6 +658,16 @@ def main():
             wall = (time.perf_counter() - t0) / n_e2e * 1e3
             barrier()
             ms_e2e = max_over_ranks(max(e0.elapsed_time(e1) / n_e2e, wall))
+            # the same steps once more with a host-side wait between their two halves: where the time goes
+            # (outside the timed region; the extra wait makes these steps slower than the timed ones)
+            breakdown = None
+            if loader is not None:
+                for _ in range(3):
+                    step_host(timed=True)
+                barrier()
+                breakdown = {"x_piece_upload_and_nvlink_exchange_ms": max_over_ranks(phase["load_x_ms"] / 3),
+                             "product_with_y_copies_ms": max_over_ranks(phase["product_ms"] / 3),
+                             "note": "measured in separate steps with a wait between the two halves (max over ranks)"}
             x_bytes = (x_block_h if loader is not None else x_h)
             h2d = x_bytes.numel() * x_bytes.element_size() + (y0_h.numel() * y0_h.element_size() if beta != 0.0 else 0)
             d2h = y_h.numel() * y_h.element_size()
@@ -459,7 +676,7 @@ def main():
                 assert st_code == capi.SUCCESS and code == 0, f"a bounded wait of the exchange ran out (status {code})"
                 loader.destroy()
             # bytes of the whole job: every rank's copies added up
-            e2e = (ms_e2e, sum_over_ranks(h2d), sum_over_ranks(d2h), x_upload)
+            e2e = (ms_e2e, sum_over_ranks(h2d), sum_over_ranks(d2h), x_upload, breakdown)
     if sampler:
         sampler.stop()
 
@@ -475,73 +692,99 @@ def main():
         peak, peak_src = FALLBACK_HBM_GBS, "fallback"
     achieved = launch_bytes / (kernel_ms * 1e-3) / 1e9
     # Matrices with unstructured columns: one gather of x per stored element.  The measured gather rate
-    # of this GPU gives a floor for the kernel that no SpMV can beat, whatever its HBM traffic.
+    # of this GPU gives a floor for a kernel that gathers every element of x from L2, whatever its HBM traffic.
     gather = None
     if op == "mv" and name != "stencil27":
-        rate = spblas.probe_gather_rate(kind, cols)
-        floor_ms = m.nnz / rate * 1e3
-        gather = {"gathers_per_s": rate, "table_elems": cols, "kernel_floor_ms": floor_ms,
-                  "kernel_vs_floor": floor_ms / kernel_ms}
+        rate = gather_rate(TSIZE[kind], cols, stream.cuda_stream)
+        through_l2 = m.nnz - int(info.band_elements)
+        floor_ms = through_l2 / rate * 1e3
+        gather = {"gathers_per_s": rate, "table_elems": cols, "elements_gathered_from_l2": through_l2,
+                  "elements_gathered_from_shared_memory": int(info.band_elements),
+                  "kernel_floor_ms": floor_ms, "kernel_vs_floor": floor_ms / kernel_ms}
 
+    algorithm = ["auto", "vector", "merge", "rowtile"][info.algorithm]
+    kernel = {"vector": f"spmv_vector_kernel lanes={info.lanes_per_row}", "rowtile": "spmv_rowtile_kernel",
+              "merge": "spmv_merge_kernel" + (" + spmv_band_quad_kernel" if info.band_rows else "")}[algorithm] \
+        if op == "mv" else "spmm_row_kernel"
+    if op == "mm":
+        kernel += f" column_blocks={spblas.mat_info(A)[1].spmm_col_blocks}" if False else ""
     if rank == 0:
+        traffic, traffic_src = ncu_traffic(name, kernel, reduced, world)
         line = {
-            "metric": "csr_spmv_effective_gbs" if op == "mv" else "csr_spmm_effective_gbs",
+            "metric": metric_name(cfg),
             "value": nbytes / (ms_step * 1e-3) / 1e9, "unit": "GB/s", "gflops": fl / (ms_step * 1e-3) / 1e9,
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32" if kind == "s" else "f64", "data": "synthetic",
-            "config": {"workload": name + (" (REDUCED SIZE: development run)" if reduced else ""), "rows": rows,
-                       "cols": cols, "nnz": nnz_total, "alpha": alpha, "beta": beta, "columns": columns,
-                       "partition": f"nnz-balanced contiguous row blocks over {world} GPU(s), x replicated",
-                       "collective": ("none" if not iterate else
-                                      "allgather of y into the next x each step: " +
-                                      ({"fused": "peer stores from inside the SpMV kernel + flag exchange",
-                                        "push": "peer-copy kernel after the SpMV + flag exchange"}[args.exchange]
-                                       if fused is not None
-                                       else "NCCL all_gather after the SpMV")),
-                       "algorithm": ["auto", "vector", "merge", "rowtile"][info.algorithm], "lanes_per_row": info.lanes_per_row,
-                       "l2": f"inputs ({nbytes / 1e6:.0f} MB per step) exceed the 126 MB L2; no flush between steps",
-                       "algorithmic_bytes_per_step": nbytes},
+            "config": workload_config(name, cfg, rows, cols, nnz_total, reduced),
+            "execution": {"partition": f"nnz-balanced contiguous row blocks over {world} GPU(s), x replicated",
+                          "collective": ("none" if not iterate else
+                                         "allgather of y into the next x each step: " +
+                                         ({"fused": "peer stores from inside the SpMV kernel + flag exchange",
+                                           "push": "peer-copy kernel after the SpMV + flag exchange"}[args.exchange]
+                                          if fused is not None
+                                          else "NCCL all_gather after the SpMV")),
+                          "algorithm": algorithm, "lanes_per_row": info.lanes_per_row, "kernel": kernel,
+                          "rows_in_column_band_kernel": info.band_rows, "elements_in_column_band_kernel": int(info.band_elements)},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": NCU_TRAFFIC.get(name) if not reduced and world == 1 else None,
+                         "traffic": traffic, "traffic_source": traffic_src,
                          "peak_source": peak_src, "kernel_ms": kernel_ms, "bytes_per_launch": launch_bytes,
                          "gather_bound": gather},
             "clocks": sampler.summary(t_wall0, t_wall1) if sampler else None,
         }
+        if cold is not None:
+            line["cold_l2"] = {"ms_per_step": cold, "value": nbytes / (cold * 1e-3) / 1e9, "unit": "GB/s",
+                               "how": "256 MB overwritten on the device before every timed step; median of the steps"}
         if e2e:
             line["e2e"] = {"value": nbytes / (e2e[0] * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e[0],
                            "h2d_bytes_per_step": int(e2e[1]), "d2h_bytes_per_step": int(e2e[2]), "x_upload": e2e[3]}
+            if e2e[4]:
+                line["e2e"]["phases"] = e2e[4]
         else:
             line["e2e"] = None
         if world == 1 and not args.no_cpu_baseline:
-            gbs, gfl, ms, desc = cpu_reference_run(name, cfg, 3, 1)
-            line["cpu_baseline"] = dict(value=gbs, unit="GB/s", gflops=gfl, ms_per_step=ms, **desc)
-        if world == 1 and not args.no_others and not reduced:
-            # The other single-GPU configurations, each in a fresh process, device-resident numbers only:
-            # context for the headline above (they are parity-test cases, not separate bench lines).
-            others = {}
-            for w in sorted(WORKLOADS):
-                if w == name:
-                    continue
-                try:
-                    out = subprocess.run([sys.executable, os.path.abspath(__file__), "--workload", w, "--steps", "10",
-                                          "--warmup", "3", "--no-e2e", "--no-cpu-baseline", "--no-others"],
-                                         capture_output=True, text=True, timeout=600)
-                    d = json.loads(out.stdout.strip().splitlines()[-1])
-                    others[w] = {"value": d["value"], "unit": d["unit"], "ms_per_step": d["ms_per_step"],
-                                 "gflops": d["gflops"], "roofline_frac": d["roofline"]["frac"],
-                                 "algorithm": d["config"]["algorithm"], "nnz": d["config"]["nnz"]}
-                except Exception as exc:  # the headline must not depend on these
-                    others[w] = {"error": repr(exc)[:200]}
-            line["other_workloads"] = others
-        print(json.dumps(line), flush=True)
+            # the reference's OpenMP kernel on this box's host cores, the whole matrix, the same vectors
+            ms_cpu, desc = cpu_reference_time(cfg, m, cols, x_np, y0_np.copy(), 3, 1)
+            line["cpu_baseline"] = dict(value=nbytes / (ms_cpu * 1e-3) / 1e9, unit="GB/s",
+                                        gflops=fl / (ms_cpu * 1e-3) / 1e9, ms_per_step=ms_cpu, **desc)
 
     if fused is not None:
         st_, code = fused.status()
         assert code == 0, f"a bounded wait of the exchange ran out (status {code})"
         fused.destroy()
     spblas.destroy(A)
+    del x_d, y_d, xn_d
+    torch.cuda.empty_cache()
+
+    others = None
+    if world > 1 and not args.no_others and not reduced and name == "uniform16":
+        # the iterated configuration, in the same process group: SpMV fused with its allgather against NCCL
+        try:
+            others = {"powerlaw_iterated": measure_iterated(args, rank, world, stream)}
+        except Exception as exc:  # the headline must not depend on it; all ranks fail or pass together
+            others = {"powerlaw_iterated": {"error": repr(exc)[:300]}}
+    if rank == 0:
+        if world == 1 and not args.no_others and not reduced:
+            # The other single-GPU configurations, each in a fresh process with its own end-to-end, CPU-baseline
+            # and roofline figures: context for the headline above (parity-test cases, not separate bench lines).
+            others = {}
+            for w in sorted(WORKLOADS):
+                if w == name:
+                    continue
+                try:
+                    out = subprocess.run([sys.executable, os.path.abspath(__file__), "--workload", w, "--steps", "10",
+                                          "--warmup", "3", "--no-others"], capture_output=True, text=True, timeout=900)
+                    d = json.loads(out.stdout.strip().splitlines()[-1])
+                    others[w] = {k: d.get(k) for k in ("value", "unit", "ms_per_step", "gflops", "dtype", "config",
+                                                        "execution", "roofline", "e2e", "cpu_baseline", "cold_l2",
+                                                        "gpu_launches")}
+                except Exception as exc:  # the headline must not depend on these
+                    others[w] = {"error": repr(exc)[:200]}
+        if others is not None:
+            line["other_workloads"] = others
+        print(json.dumps(line), flush=True)
+
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -1,11 +1,16 @@
-// A device probe used by the benchmark to put the SpMV numbers in context: the rate at which the
-// GPU sustains independent gathers of single elements from random addresses of a table (what a CSR
-// matrix with unstructured columns asks of x).  On B200 this rate, not HBM bandwidth, bounds SpMV on
-// such matrices: every gather is its own L1->L2 request and the SMs issue one per clock each.
-#include "alphasparse/spapi_cuda.h"
-#include "internal.h"
+// Benchmark-side probe (not part of the library): the rate at which the GPU sustains independent
+// gathers of single elements from random addresses of a table, which is what a CSR matrix with
+// unstructured columns asks of x.  On B200 this rate, not HBM bandwidth, bounds an SpMV that takes
+// every x element from L2: each gather is its own L1 -> L2 request.  bench.py loads the shared
+// object built from this file (libbench_gather_probe.so, beside it) and reports the rate next to the
+// kernel's time.
+//
+//   int bench_gather_rate(int elem_bytes, long long table_elems, long long gathers, void *stream,
+//                         double *per_second)         returns 0 on success, a cudaError_t otherwise
+#include <cuda_runtime.h>
+#include <stdint.h>
 
-namespace asb {
+namespace {
 
 __global__ void probe_fill_kernel(int *idx, size_t n, unsigned long long range) {
     const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
@@ -29,16 +34,14 @@ __global__ void __launch_bounds__(256) probe_gather_kernel(const int *__restrict
 }
 
 template <typename T>
-static alphasparse_status_t probe(int64_t table_elems, int64_t gathers, double *per_second) {
+int probe(long long table_elems, long long gathers, cudaStream_t st, double *per_second) {
     int *idx = nullptr;
     T *table = nullptr, *sink = nullptr;
     cudaEvent_t e0 = nullptr, e1 = nullptr;
-    cudaStream_t st = current_stream();
     const size_t n = (size_t)gathers & ~(size_t)3, quads = n / 4;
-    alphasparse_status_t status = ALPHA_SPARSE_STATUS_SUCCESS;
-    cudaError_t err = device_alloc(&idx, n * sizeof(int));
-    if (err == cudaSuccess) err = device_alloc(&table, (size_t)table_elems * sizeof(T));
-    if (err == cudaSuccess) err = device_alloc(&sink, sizeof(T) * 4);
+    cudaError_t err = cudaMalloc(&idx, n * sizeof(int));
+    if (err == cudaSuccess) err = cudaMalloc(&table, (size_t)table_elems * sizeof(T));
+    if (err == cudaSuccess) err = cudaMalloc(&sink, sizeof(T) * 4);
     if (err == cudaSuccess) err = cudaMemsetAsync(table, 0, (size_t)table_elems * sizeof(T), st);
     if (err == cudaSuccess) err = cudaEventCreate(&e0);
     if (err == cudaSuccess) err = cudaEventCreate(&e1);
@@ -55,26 +58,22 @@ static alphasparse_status_t probe(int64_t table_elems, int64_t gathers, double *
             if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, e0, e1);
             if (rep > 0 && ms < best) best = ms;
         }
-        count_launch(5);
         if (err == cudaSuccess) *per_second = (double)n / ((double)best * 1e-3);
     }
-    if (err != cudaSuccess) {
-        record_cuda_error(err, "gather probe");
-        status = ALPHA_SPARSE_STATUS_EXECUTION_FAILED;
-    }
+    if (err != cudaSuccess) (void)cudaGetLastError();
     if (e0) cudaEventDestroy(e0);
     if (e1) cudaEventDestroy(e1);
     cudaFree(idx), cudaFree(table), cudaFree(sink);
-    return status;
+    return (int)err;
 }
 
-}  // namespace asb
+}  // namespace
 
-extern "C" alphasparse_status_t alphasparse_cuda_probe_gather_rate(alphasparse_datatype_t datatype, int64_t table_elems,
-                                                                   int64_t gathers, double *per_second) {
-    if (!per_second || table_elems <= 0 || table_elems > 0x7fffffff || gathers < 1024)
-        return ALPHA_SPARSE_STATUS_INVALID_VALUE;
-    if (datatype == ALPHA_SPARSE_DATATYPE_FLOAT) return asb::probe<float>(table_elems, gathers, per_second);
-    if (datatype == ALPHA_SPARSE_DATATYPE_DOUBLE) return asb::probe<double>(table_elems, gathers, per_second);
-    return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+extern "C" int bench_gather_rate(int elem_bytes, long long table_elems, long long gathers, void *stream,
+                                 double *per_second) {
+    if (!per_second || table_elems <= 0 || table_elems > 0x7fffffff || gathers < 1024) return (int)cudaErrorInvalidValue;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (elem_bytes == 4) return probe<float>(table_elems, gathers, st, per_second);
+    if (elem_bytes == 8) return probe<double>(table_elems, gathers, st, per_second);
+    return (int)cudaErrorInvalidValue;
 }

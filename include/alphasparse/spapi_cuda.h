@@ -43,9 +43,16 @@ alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg);
  *   band_min_rows (128)     fewer long rows than this are left to the merge kernel
  *   band_min_share_pct (10) ... and so are long rows holding less than this share of the elements
  *   band_splits (0)         thread blocks per band, 0 = about eight waves of blocks
- *   band_overlap (1)        the column-band kernel runs on a second stream beside the merge kernel
- *   spmm_col_blocks (0)     column blocks of the row-major dense-block product, 0 = from the size of X
- *   spmm_block_bytes (48Mi) bytes of X per column block when the count is chosen automatically
+ *   band_overlap (0)        1: the column-band kernel runs on a second stream beside the other kernels
+ *   band_variant (0)        shape of the column-band kernel: 0 = 8 lanes x 1 quad x 2 segments per lane group,
+ *                           1 = 4 lanes x 2 quads x 1 segment
+ *   bin_overlap (1)         the kernels of the mid bins run on streams of their own, side by side
+ *   bin_enable (1)          skewed matrices are multiplied bin by bin: thread per row up to bin_short (8)
+ *                           elements, a lane group per row above, the column-band kernel for long rows; merge
+ *                           tiles remain for matrices with rows above bin_mid_max (16384) that are not long
+ *                           enough for the band kernel, with too few long rows, or with unsorted long rows
+ *   spmm_col_blocks (0)     row-major dense-block product in this many column blocks (X slab by slab, Y
+ *                           accumulated over the passes); 0 or 1 = one pass, which measured faster on B200
  * Unknown names return ALPHA_SPARSE_STATUS_INVALID_VALUE. */
 alphasparse_status_t alphasparse_cuda_set_option(const char *name, int64_t value);
 alphasparse_status_t alphasparse_cuda_get_option(const char *name, int64_t *value);
@@ -67,6 +74,9 @@ typedef struct {
     int32_t band_count;    /* column bands of band_width columns each */
     int32_t band_width;
     int64_t band_elements; /* stored elements the column-band kernel multiplies */
+    int32_t spmm_col_blocks; /* column blocks the last row-major mm call on this handle ran in (0: none yet) */
+    int32_t binned;          /* 1: products of this handle run bin by bin (thread per short row, lane group per mid
+                                row, column-band kernel for long rows) instead of over merge tiles */
 } alphasparse_cuda_mat_info_t;
 
 alphasparse_status_t alphasparse_cuda_get_mat_info(const alphasparse_matrix_t A,
@@ -86,8 +96,14 @@ alphasparse_status_t alphasparse_cuda_get_device_csr(const alphasparse_matrix_t 
  * service that cannot tolerate the device-wide synchronisation cudaMalloc / cudaFree carry.
  *
  * d_row_ptr has rows+1 zero-based offsets, d_col_indx / d_values have nnz entries, d_x has cols
- * and d_y rows entries; all five live on the current device.  Work is enqueued on the library
- * stream and the call returns without waiting.
+ * and d_y rows entries; all five live on the current device (memory of another GPU is refused with
+ * ALPHA_SPARSE_STATUS_INVALID_POINTER).  Work is enqueued on the library stream and the call returns
+ * without waiting.
+ *
+ * The matrix is taken as it is: offsets must be non-decreasing and every column index must lie in
+ * [0, cols).  Unlike handle creation, which checks both once and refuses a bad matrix, this call does
+ * NOT validate them (it would have to read the whole index array on every product): an index outside
+ * the range reads outside d_x.  Validate untrusted matrices by creating a handle from them once.
  *
  * Scratch (the merge-path tile table and carries that a handle would own) comes from one fixed
  * 4 MiB array inside the library image, present on every GPU that loads the library until the
@@ -150,20 +166,20 @@ alphasparse_status_t alphasparse_d_mv_exchange(const double alpha, const alphasp
                                                const struct alpha_matrix_descr descr,
                                                alphasparse_cuda_exchange_t ex, const double beta, double *y);
 
+/* Error word of a handle's kernels.  Kernels that wait (the row-tile kernel waits for its bulk copies) give up
+ * after a bounded number of polls, leave y untouched for their tile and record a code here: 1 = a tile larger
+ * than the kernel was configured for, 2 = a bulk copy did not complete in time.  A call with host vectors
+ * reports it as ALPHA_SPARSE_STATUS_EXECUTION_FAILED by itself; a caller that passes device pointers (calls
+ * only enqueue) asks here: waits for the library stream, stores the code (0 = fine) and, with clear != 0,
+ * resets it so that later calls start clean. */
+alphasparse_status_t alphasparse_cuda_kernel_status(const alphasparse_matrix_t A, int *status, int clear);
+
 /* Kernel timing for benchmarks.  With profiling enabled on a handle, every mv / mm call on it
  * brackets its dominant kernel (the SpMV or SpMM kernel itself, not the small fix-up or any
  * copies) with CUDA events on the library stream; alphasparse_cuda_kernel_ms waits for the
  * last such kernel and returns its duration in milliseconds. */
 alphasparse_status_t alphasparse_cuda_profile_kernel(const alphasparse_matrix_t A, int enable);
 alphasparse_status_t alphasparse_cuda_kernel_ms(const alphasparse_matrix_t A, float *ms);
-
-/* Benchmark aid: measures on the current device how many independent single-element gathers per
- * second the GPU sustains from uniformly random positions of a zero-filled table of `table_elems`
- * elements of the given precision (`gathers` of them, shaped like the SpMV inner loop).  For matrices
- * with unstructured columns this rate, not HBM bandwidth, is what bounds SpMV.  Allocates and frees
- * 4*gathers + table bytes on the device. */
-alphasparse_status_t alphasparse_cuda_probe_gather_rate(alphasparse_datatype_t datatype, int64_t table_elems,
-                                                        int64_t gathers, double *per_second);
 
 /* Test aid: makes the nth device allocation the library performs from now on fail as if the device
  * were out of memory (0 cancels).  The failing call returns ALPHA_SPARSE_STATUS_ALLOC_FAILED and

@@ -103,6 +103,51 @@ def gemv_exact(rows_start, rows_end, col, val, alpha, x, beta, y0):
     return beta * np.asarray(y0, dtype=np.float64) + alpha * out
 
 
+CHECK_THRESHOLD = 50.0   # THRESH of the reference's checks (include/alphasparse/util/check.h:39)
+
+
+def _check_eps(kind):
+    # CalEpisilon_{s,d} (src/util/norm.c:6-32): ten times the machine epsilon of the type
+    return 10.0 * float(np.finfo(np.float32 if kind == "s" else np.float64).eps)
+
+
+def _norm1_of_columns(cols, col, val):
+    # GeNorm1_{s,d} (src/util/norm.c:207-222): the largest column sum of |a|
+    return float(np.bincount(np.asarray(col), weights=np.abs(np.asarray(val, dtype=np.float64)), minlength=cols).max()) \
+        if len(col) else 0.0
+
+
+def check_l2_residual(kind, answer, result, x, alpha, beta, rows, cols, col, val):
+    """The figure the reference's own mv tests judge a result by (check_{s,d}_l2, src/util/check.c:7-57 and its
+    double twin): max|answer - result| over (max(|A|_1, 1) * max(|x|_inf, 1) * max(|result|_inf, 1) * eps * max(rows,
+    cols)), with |x|_inf multiplied by alpha and |result|_inf by beta when their magnitude exceeds one (by the signed
+    scalar, as the reference does) and eps ten machine epsilons.  A result passes when the residual is <= 50."""
+    a, r = np.asarray(answer, dtype=np.float64), np.asarray(result, dtype=np.float64)
+    norm_d = float(np.abs(a - r).max()) if len(a) else 0.0
+    norm_x = float(np.abs(np.asarray(x, dtype=np.float64)).max()) if len(x) else 0.0
+    if abs(alpha) > 1.0:
+        norm_x *= alpha
+    norm_y = float(np.abs(r).max()) if len(r) else 0.0
+    if abs(beta) > 1.0:
+        norm_y *= beta
+    norm_a = _norm1_of_columns(cols, col, val)
+    return norm_d / (max(norm_a, 1.0) * max(norm_x, 1.0) * max(norm_y, 1.0) * _check_eps(kind) * max(rows, cols))
+
+
+def check_l3_residual(kind, answer, result, X, rows, cols, columns, ld_answer, ld_result, ldx, col, val):
+    """check_{s,d}_l3 for row-major mm (src/util/check.c:217-334, the branch with one matrix file): the largest column
+    sum of |answer - result| over (max(|A|_1, 1) * max(|X|_1, 1) * max(|result|_1, 1) * eps * max(rows, cols, columns)),
+    |.|_1 the largest column sum of magnitudes (DesNorm1, DesDiffNorm1 of src/util/norm.c:303-354)."""
+    def dense(v, n, ld):
+        return np.asarray(v, dtype=np.float64).reshape(-1)[: n * ld].reshape(n, ld)[:, :columns]
+    A_, R_, X_ = dense(answer, rows, ld_answer), dense(result, rows, ld_result), dense(X, cols, ldx)
+    norm_d = float(np.abs(A_ - R_).sum(axis=0).max())
+    norm_x = float(np.abs(X_).sum(axis=0).max())
+    norm_y = float(np.abs(R_).sum(axis=0).max())
+    norm_a = _norm1_of_columns(cols, col, val)
+    return norm_d / (max(norm_a, 1.0) * max(norm_x, 1.0) * max(norm_y, 1.0) * _check_eps(kind) * max(rows, cols, columns))
+
+
 def gemv_trans(kind, cols, rows_start, rows_end, col, val, alpha, x, beta, y):
     rs, re_, ci = _i(rows_start), _i(rows_end), _i(col)
     getattr(lib(), f"oracle_gemv_csr_trans_{kind}")(len(rs), cols, _a(rs), _a(re_), _a(ci), _a(val), alpha, _a(x),

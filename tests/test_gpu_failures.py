@@ -21,7 +21,7 @@ def test_allocation_failures_leave_nothing_behind():
     m = synth.zipf("d", 3, 20000, 20000, 1.8, 1, 5000)      # merge path: the creation allocates its tables too
     free0 = torch.cuda.mem_get_info()[0]
     failures = 0
-    for nth in range(1, 12):
+    for nth in range(1, 40):
         lib.alphasparse_cuda_debug_fail_alloc(nth)
         st, A = spblas.create_csr("d", 0, m.nrows, m.cols, m.rows_start, m.rows_end, m.col, m.val)
         lib.alphasparse_cuda_debug_fail_alloc(0)
@@ -30,7 +30,8 @@ def test_allocation_failures_leave_nothing_behind():
             break
         assert st == capi.ALLOC_FAILED and not A.value and "device_alloc" in spblas.last_error()
         failures += 1
-    assert failures >= 8                 # row_ptr, status, col, val, analysis scratch, tile table, carries, chunk counters
+    # row_ptr, status, col, val, analysis scratch, tile table, carries, chunk counters, row lists, band tables
+    assert 8 <= failures < 39
     torch.cuda.synchronize()
     assert torch.cuda.mem_get_info()[0] >= free0 - (4 << 20)   # nothing leaked (allow allocator granularity)
     # a staging-buffer failure inside mv is reported and the handle keeps working

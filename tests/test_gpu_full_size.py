@@ -4,7 +4,9 @@
   fed with those rows cut out of the same matrix and the full-length x;
 * identical bits from one call to the next;
 * linearity, A(2 x1 - 3 x2) = 2 A x1 - 3 A x2, within the parity tolerance on every row;
-* a checksum, sum(A x) = (column sums of A) . x, within the tolerance on the whole sum.
+* a checksum, sum(A x) = (column sums of A) . x, within the tolerance on the whole sum;
+* the reference's own pass criterion (the residual of its check_{s,d}_l2 / _l3, at most 50), computed on the whole
+  result against the oracle's OpenMP kernel on the whole matrix, and printed beside the per-row gate.
 
 The per-row scale |A||x| that the tolerances multiply is computed with torch on the GPU from the same arrays.
 """
@@ -68,6 +70,11 @@ def test_full_size_mv(name):
     y_host = y.cpu().numpy()
     assert_rows_close(kind, y_host[pick], y_ref, row_scale(sptr, scol, sval, x1, alpha, beta, y0[pick]), f"{name} sampled rows")
     assert np.isfinite(y_host).all()
+    # the reference's own criterion on the whole vector (its tests compare two implementations this way)
+    y_all = oracle.gemv(kind, m.rows_start, m.rows_end, m.col, m.val, alpha, x1, beta, y0.copy(), threads=oracle.max_threads())
+    resid = oracle.check_l2_residual(kind, y_all, y_host, x1, alpha, beta, m.nrows, m.cols, m.col, m.val)
+    print(f"{name}: reference check_{kind}_l2 residual {resid:.3g} (passes at <= {oracle.CHECK_THRESHOLD:g})")
+    assert resid <= oracle.CHECK_THRESHOLD
     # identical bits on a second call
     assert torch.equal(y, product(dx1, alpha, beta))
 
@@ -107,6 +114,12 @@ def test_full_size_mm():
     got = Y.cpu().numpy().reshape(m.nrows, columns)[pick].reshape(-1)
     scale = mm_scale(sptr, scol, sval, X, columns, columns, 1.5, 0.5, Y0s, columns)
     assert_rows_close(kind, got, Y_ref, scale.reshape(-1), "spmm64 sampled rows")
+    Y_all = oracle.gemm(kind, "row", m.rows_start, m.rows_end, m.col, m.val, 1.5, X, columns, columns, 0.5, Y0.copy(), columns,
+                        threads=oracle.max_threads())
+    resid = oracle.check_l3_residual(kind, Y_all, Y.cpu().numpy(), X, m.nrows, m.cols, columns, columns, columns, columns,
+                                     m.col, m.val)
+    print(f"spmm64: reference check_{kind}_l3 residual {resid:.3g} (passes at <= {oracle.CHECK_THRESHOLD:g})")
+    assert resid <= oracle.CHECK_THRESHOLD
     assert torch.equal(Y, product(1.5, 0.5))
     assert TORCH[kind] == Y.dtype
     spblas.destroy(A)

@@ -66,6 +66,50 @@ def test_widths_and_leading_dimensions(kind, columns, ldx, ldy):
     spblas.destroy(A)
 
 
+@pytest.mark.parametrize("kind", ["s", "d"])
+def test_column_blocks_give_the_same_product(kind):
+    """Row-major mm in column blocks (X slab by slab, Y accumulated over the passes): forced block counts on a
+    small matrix against the oracle, with beta != 0 (applied by the first pass only), padded leading dimensions,
+    empty rows, more blocks than some rows have elements, host operands; a matrix whose rows are not in ascending
+    column order must fall back to one pass."""
+    lens = synth.rowlen_poisson(13, 4000, 12.0, 3000).copy()
+    lens[::40] = 0
+    lens[11] = 900
+    m = synth.from_lengths(kind, 13, lens, 3000)
+    columns, ldx, ldy = 24, 28, 26
+    X, Y0 = synth.vector(kind, 13, 3, m.cols * ldx), synth.vector(kind, 13, 4, m.nrows * ldy)
+    A = make_handle(kind, m)
+    try:
+        for blocks in (1, 2, 5, 16):
+            assert spblas.set_option("spmm_col_blocks", blocks) == capi.SUCCESS
+            for alpha, beta in ((1.0, 0.0), (1.5, 0.5)):
+                Yref = oracle.gemm(kind, "row", m.rows_start, m.rows_end, m.col, m.val, alpha, X, columns, ldx, beta,
+                                   Y0.copy(), ldy)
+                for device in (False, True):
+                    Y = run_mm(kind, A, m, X, columns, ldx, alpha, beta, Y0, ldy, device)
+                    compare(kind, m, Y, Yref, X, columns, ldx, alpha, beta, Y0, ldy, f"{blocks} column blocks dev={device}")
+            assert spblas.mat_info(A)[1].spmm_col_blocks == blocks
+        spblas.destroy(A)
+        A = None
+        # descending columns inside the rows: the blocks cannot be cut by searching, one pass it is
+        ptr = m.ptr
+        col, val = m.col.copy(), m.val.copy()
+        for r in range(m.nrows):
+            col[ptr[r]:ptr[r + 1]] = col[ptr[r]:ptr[r + 1]][::-1]
+            val[ptr[r]:ptr[r + 1]] = val[ptr[r]:ptr[r + 1]][::-1]
+        mr = synth.Csr(m.nrows, m.cols, 0, ptr, col, val)
+        A = make_handle(kind, mr)
+        assert spblas.set_option("spmm_col_blocks", 4) == capi.SUCCESS
+        Yref = oracle.gemm(kind, "row", mr.rows_start, mr.rows_end, mr.col, mr.val, 2.0, X, columns, ldx, -1.0, Y0.copy(), ldy)
+        Y = run_mm(kind, A, mr, X, columns, ldx, 2.0, -1.0, Y0, ldy, True)
+        compare(kind, mr, Y, Yref, X, columns, ldx, 2.0, -1.0, Y0, ldy, "unsorted rows")
+        assert spblas.mat_info(A)[1].spmm_col_blocks == 1
+    finally:
+        spblas.set_option("spmm_col_blocks", -1)
+        if A is not None:
+            spblas.destroy(A)
+
+
 def test_status_codes():
     m = synth.poisson("s", 8, 30, 40, 4.0)
     A = make_handle("s", m)

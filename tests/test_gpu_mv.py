@@ -110,8 +110,8 @@ def test_shapes_and_scalars(kind, alg, pointers):
     mats = [synth.uniform_fixed(kind, 1, 20000, 20000, 16), synth.poisson(kind, 2, 9000, 7000, 32.0),
             synth.stencil27(kind, 14), synth.uniform_fixed(kind, 3, 5000, 300, 1),
             synth.uniform_fixed(kind, 4, 777, 50, 3)]
-    hi = 200000 if kind == "d" else 1500  # single precision: keep the oracle's own rounding inside tolerance
-    mats.append(synth.zipf(kind, 5, 30000, 250000, 1.8, 1, hi))
+    # rows of up to 200,000 elements in both precisions (single precision is compared with a double-precision sum)
+    mats.append(synth.zipf(kind, 5, 30000, 250000, 1.8, 1, 200000))
     for m in mats:
         for alpha, beta in ((1.0, 0.0), (1.5, 0.5), (-2.0, 1.0), (0.0, 3.0)):
             check_mv(kind, m, alpha, beta, pointers=pointers, alg=alg)
@@ -375,7 +375,9 @@ def test_large_coo_is_sorted_on_the_device(kind):
 
 def test_merge_kernel_delivers_into_page_locked_host_y():
     """Large skewed matrix + page-locked host y: finished chunks of y are stored into the host buffer from
-    inside the kernel.  Same bits as the device-pointer call, and as with pageable memory."""
+    inside the merge kernel, which then runs over all tiles (the delivering form has no column-band path, so
+    long rows are summed in another order than in the device-pointer call: equal within the tolerance, and
+    bit-identical from one such call to the next).  Pageable host memory takes the device-pointer kernels."""
     kind = "d"
     m = synth.zipf(kind, 91, (1 << 20) + 777, 1 << 20, 1.8, 1, 100000)
     A = make_handle(kind, m)
@@ -387,9 +389,14 @@ def test_merge_kernel_delivers_into_page_locked_host_y():
         dx, dy = torch.from_numpy(x).cuda(), torch.from_numpy(y0).cuda()
         assert spblas.mv(kind, 0, alpha, A, spblas.descr(), dx, beta, dy) == capi.SUCCESS
         want = dy.cpu().numpy()
+        scale = row_scale(m.ptr, m.col, m.val, x, alpha, beta, y0)
+        exact = oracle.gemv_exact(m.rows_start, m.rows_end, m.col, m.val, alpha, x, beta, y0)
         pinned = torch.from_numpy(y0.copy()).pin_memory()
         assert spblas.mv(kind, 0, alpha, A, spblas.descr(), x, beta, pinned.numpy()) == capi.SUCCESS
-        assert np.array_equal(pinned.numpy(), want)
+        assert_rows_close(kind, pinned.numpy(), exact, scale, "delivered into page-locked y")
+        again = torch.from_numpy(y0.copy()).pin_memory()
+        assert spblas.mv(kind, 0, alpha, A, spblas.descr(), x, beta, again.numpy()) == capi.SUCCESS
+        assert np.array_equal(pinned.numpy(), again.numpy())
         pageable = y0.copy()
         assert spblas.mv(kind, 0, alpha, A, spblas.descr(), x, beta, pageable) == capi.SUCCESS
         assert np.array_equal(pageable, want)
@@ -515,12 +522,18 @@ class _Options:
 
 @pytest.mark.parametrize("kind", ["s", "d"])
 @pytest.mark.parametrize("overlap", [0, 1])
-def test_long_rows_take_the_column_band_path(kind, overlap):
-    """Row binning of the analysis: rows long enough to average several elements per column band leave the merge
-    tiles and go through the column-band kernel (x bands staged in shared memory).  Tiny limits make a small
-    matrix take every branch: several splits per band, a ragged last band, long rows first / last / adjacent,
-    an unsorted long row (must stay with the merge kernel), all scalar combinations, bit-identical repeats, and
-    a run over all tiles (the delivering form of the merge kernel) in between two banded runs."""
+@pytest.mark.parametrize("mode", ["binned", "binned_unsorted", "tiles", "tiles_unsorted"])
+def test_row_bins_and_the_column_band_path(kind, overlap, mode):
+    """Row binning of the analysis on a skewed matrix, with limits small enough for a small matrix to fill every bin.
+
+    binned: thread per row up to 2 elements, lane groups for the three mid lists, and the five long rows (long = at
+    least 30 elements per column band on average) whole in the column-band kernel (bands of x staged in shared
+    memory; several splits per band, a ragged last band, long rows first / last / adjacent).
+    binned_unsorted: one long row has two columns swapped; it cannot be cut into bands, so the handle must fall back
+    to merge tiles, where the other four long rows still give their inner tiles to the band kernel.
+    tiles / tiles_unsorted: the same with binning switched off.
+    All scalar combinations, host and device vectors, bit-identical repeats, and a run of the delivering merge kernel
+    (every tile) in between."""
     cols = 70001
     body = np.concatenate([[40000], synth.rowlen_zipf(9, 6000, 1.8, 1, 900), [9000, 25000, 3],
                            synth.rowlen_zipf(10, 3000, 1.8, 1, 50), [12000, 1, 1]])
@@ -528,13 +541,16 @@ def test_long_rows_take_the_column_band_path(kind, overlap):
     lens = np.concatenate([body, np.zeros(cols - len(body) - 1), [30000]]).astype(np.int32)
     m = synth.from_lengths(kind, 9, lens, cols)
     ptr = m.ptr
-    unsorted_row = 6002                                        # the 25000-element row: swap two of its columns
-    assert ptr[unsorted_row + 1] - ptr[unsorted_row] == 25000
-    a = int(ptr[unsorted_row]) + 7000
-    m.col[a], m.col[a + 1] = m.col[a + 1], m.col[a]
-    m.val[a], m.val[a + 1] = m.val[a + 1], m.val[a]
-    with _Options(band_bytes=4096, band_min_seg=1, band_min_rows=1, band_min_share_pct=0, band_splits=3,
-                  band_overlap=overlap):
+    unsorted = mode.endswith("unsorted")
+    if unsorted:
+        row = 6002                                               # the 25000-element row: swap two of its columns
+        assert ptr[row + 1] - ptr[row] == 25000
+        a = int(ptr[row]) + 7000
+        m.col[a], m.col[a + 1] = m.col[a + 1], m.col[a]
+        m.val[a], m.val[a + 1] = m.val[a + 1], m.val[a]
+    binned = mode.startswith("binned")
+    with _Options(band_bytes=4096, band_min_seg=30, band_min_rows=1, band_min_share_pct=0, band_splits=3,
+                  band_overlap=overlap, bin_enable=int(binned), bin_short=2):
         spblas.set_algorithm(capi.ALG_MERGE)
         try:
             A = make_handle(kind, m)
@@ -542,10 +558,15 @@ def test_long_rows_take_the_column_band_path(kind, overlap):
             spblas.set_algorithm(capi.ALG_AUTO)
     st, info = spblas.mat_info(A)
     assert st == capi.SUCCESS and info.algorithm == capi.ALG_MERGE
-    assert info.band_rows == 4 and info.band_width == 4096 // m.val.itemsize, (info.band_rows, info.band_width)
-    assert info.band_count == -(-cols // info.band_width) and info.scheduled == 1
-    tile = 256 * (7 if kind == "d" else 9)
-    assert 40000 + 9000 + 12000 + 30000 - 8 * tile <= info.band_elements <= 40000 + 9000 + 12000 + 30000
+    assert info.band_width == 4096 // m.val.itemsize and info.band_count == -(-cols // info.band_width)
+    long_total = 40000 + 9000 + 12000 + 30000 + (0 if unsorted else 25000)
+    assert info.band_rows == (4 if unsorted else 5), info.band_rows
+    if binned and not unsorted:
+        assert info.binned == 1 and info.band_elements == long_total
+    else:
+        tile = 256 * (7 if kind == "d" else 9)
+        assert info.binned == 0 and info.scheduled == 1
+        assert long_total - 2 * info.band_rows * tile <= info.band_elements <= long_total
     x, y0 = synth.vector(kind, 9, 1, cols), synth.vector(kind, 9, 2, m.nrows)
     dx = torch.from_numpy(x).cuda()
     results = {}
@@ -554,12 +575,12 @@ def test_long_rows_take_the_column_band_path(kind, overlap):
         dy = torch.from_numpy(y0).cuda()
         assert spblas.mv(kind, 0, alpha, A, spblas.descr(), dx, beta, dy) == capi.SUCCESS
         y = dy.cpu().numpy()
-        assert_rows_close(kind, y, y_ref, row_scale(m.ptr, m.col, m.val, x, alpha, beta, y0), f"band {kind} {alpha} {beta}")
+        assert_rows_close(kind, y, y_ref, row_scale(m.ptr, m.col, m.val, x, alpha, beta, y0), f"{mode} {kind} {alpha} {beta}")
         results[(alpha, beta)] = y
         yh = y0.copy()                                           # host vectors through the same handle
         assert spblas.mv(kind, 0, alpha, A, spblas.descr(), x, beta, yh) == capi.SUCCESS
         assert np.array_equal(yh, y)
-    # the delivering merge kernel runs every tile and leaves carries behind for the tiles the schedule skips
+    # the delivering merge kernel runs every tile (and leaves carries behind for the tiles a schedule skips)
     from alsparse_b200 import multi
     ex = multi.FusedExchange(kind, np.array([0, m.nrows], np.int32), 0, 1, deliver_after=False)
     ex.x_tensor().copy_(dx)
@@ -573,6 +594,29 @@ def test_long_rows_take_the_column_band_path(kind, overlap):
     assert spblas.mv(kind, 0, 1.5, A, spblas.descr(), dx, 0.5, dy) == capi.SUCCESS
     assert np.array_equal(dy.cpu().numpy(), results[(1.5, 0.5)])
     spblas.destroy(A)
+
+
+@pytest.mark.parametrize("kind", ["s", "d"])
+def test_row_bins_without_long_rows_and_declined_bins(kind):
+    """A skewed matrix whose longest rows stay below the column-band kernel's threshold is binned without that kernel;
+    a row longer than the lane-group kernels may take (bin_mid_max) but too short for the band kernel keeps the handle
+    on merge tiles."""
+    lens = np.concatenate([synth.rowlen_zipf(3, 20000, 1.8, 1, 2500), np.zeros(50), [2999, 1]]).astype(np.int32)
+    m = synth.from_lengths(kind, 3, lens, 1 << 23)              # 512 / 1024 bands: a row is long from 4096 / 8192 elements
+    for mid_max, expect in ((16384, 1), (2000, 0)):
+        with _Options(bin_mid_max=mid_max):
+            spblas.set_algorithm(capi.ALG_MERGE)
+            try:
+                A = make_handle(kind, m)
+            finally:
+                spblas.set_algorithm(capi.ALG_AUTO)
+        _, info = spblas.mat_info(A)
+        assert info.binned == expect and info.band_rows == 0, (info.binned, info.band_rows)
+        check_mv(kind, m, 1.5, 0.5, pointers="device", A=A)
+        check_mv(kind, m, 1.0, 0.0, pointers="host", A=A)
+        assert spblas.optimize(A) == capi.SUCCESS                # re-analysis of a live handle keeps it usable
+        check_mv(kind, m, -1.0, 2.0, pointers="device", A=A)
+        spblas.destroy(A)
 
 
 @pytest.mark.parametrize("kind", ["s", "d"])

@@ -1,22 +1,24 @@
-"""alphasparse_cuda_d_csrmv_noalloc against alphasparse_d_mv.
+"""alphasparse_cuda_d_csrmv_noalloc against the oracle's plain kernel and against alphasparse_d_mv.
 
 The no-allocation entry point exists for callers that cannot call cudaMalloc when they need a
 product (a memory pool already owns the device, or the device-wide synchronisation of an
-allocation is not acceptable).  It must give what the handle-based call gives.  This file sorts
+allocation is not acceptable).  It must give what the reference's kernel gives (the oracle, within
+the parity tolerance) and what the handle-based call gives.  This file sorts
 last on purpose: a run that stops at the first failure has then already run every other test.
 """
 import numpy as np
 import pytest
 import torch
 
+import oracle
 from alsparse_b200 import capi, spblas, synth
-from helpers import TOL, row_scale
+from helpers import TOL, assert_rows_close, row_scale
 
 pytestmark = pytest.mark.gpu
 
 
 def _both(m, alpha, beta, seed, check_free_memory=False):
-    """(y from the handle-based mv, y from the no-allocation call, per-row tolerance scale)."""
+    """(y from the handle-based mv, y from the no-allocation call, y from the oracle, per-row tolerance scale)."""
     x = synth.vector("d", seed, 1, m.cols)
     y0 = synth.vector("d", seed, 2, m.nrows)
     st, A = spblas.create_csr("d", 0, m.nrows, m.cols, m.rows_start, m.rows_end, m.col, m.val)
@@ -36,7 +38,8 @@ def _both(m, alpha, beta, seed, check_free_memory=False):
     if check_free_memory:  # once every kernel involved has been loaded, device free memory does not move
         assert torch.cuda.mem_get_info()[0] == free_before
     spblas.destroy(A)
-    return y_handle.cpu().numpy(), y_noalloc.cpu().numpy(), row_scale(m.ptr, m.col, m.val, x, alpha, beta, y0)
+    y_oracle = oracle.gemv("d", m.rows_start, m.rows_end, m.col, m.val, alpha, x, beta, y0.copy())
+    return y_handle.cpu().numpy(), y_noalloc.cpu().numpy(), y_oracle, row_scale(m.ptr, m.col, m.val, x, alpha, beta, y0)
 
 
 def test_two_calls_in_a_row_match_the_handle_based_mv():
@@ -48,7 +51,8 @@ def test_two_calls_in_a_row_match_the_handle_based_mv():
     second = synth.from_lengths("d", 22, lens, 1000)                   # short and empty rows, fewer tiles
     for m, alpha, beta, seed, settled in ((first, 1.5, 0.5, 21, False), (second, -2.0, 0.0, 22, False),
                                           (first, 1.0, 0.0, 23, True)):
-        y_handle, y_noalloc, scale = _both(m, alpha, beta, seed, settled)
+        y_handle, y_noalloc, y_oracle, scale = _both(m, alpha, beta, seed, settled)
+        assert_rows_close("d", y_noalloc, y_oracle, scale, "no-allocation call against the oracle")
         err = np.abs(y_noalloc - y_handle)
         assert (err <= 2 * TOL["d"] * scale).all(), f"max ratio {np.max(err / np.maximum(scale, 1e-300)):.3g}"
 
@@ -59,6 +63,9 @@ def test_limits_and_pointer_checks():
     # beyond the fixed scratch: refused with a message, nothing launched
     st = spblas.csrmv_noalloc(2_000_000_000, 8, 0x7fffffff, 1.0, ip, ip, x, x, 0.0, x)
     assert st == capi.INVALID_VALUE and "exceeds the fixed scratch" in spblas.last_error()
+    if torch.cuda.device_count() > 1:  # memory of another GPU is refused, not dereferenced
+        other = torch.zeros(8, dtype=torch.float64, device="cuda:1")
+        assert spblas.csrmv_noalloc(8, 8, 8, 1.0, ip, ip, x, other, 0.0, x) == capi.INVALID_POINTER
     # host memory is not accepted
     hx = np.zeros(8)
     assert spblas.csrmv_noalloc(8, 8, 8, 1.0, ip, ip, x, hx, 0.0, x) == capi.INVALID_POINTER
