@@ -244,13 +244,13 @@ int64_t band_long_min(const DeviceCtx *ctx);  // shortest row the column-band ke
 alphasparse_status_t bins_build(DeviceCtx *ctx, const int *h_ptr, int64_t long_min, std::vector<int> &long_rows,
                                 cudaStream_t st);
 template <typename T>
-void launch_bins(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st);
+void launch_bins(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st, const PeerPush *push = nullptr);
 void band_destroy(BandTables &b);
 template <typename T>
 void launch_band(DeviceCtx *ctx, const T *x, cudaStream_t st);
 // whole_rows tables: y[row] = alpha * sum + beta * y[row]; otherwise y[row] += alpha * sum (beta unused)
 template <typename T>
-void launch_band_reduce(DeviceCtx *ctx, T alpha, T beta, T *y, cudaStream_t st);
+void launch_band_reduce(DeviceCtx *ctx, T alpha, T beta, T *y, cudaStream_t st, const PeerPush *push = nullptr);
 
 template <typename T>
 void launch_push_rows(int64_t rows, const T *src, const PeerPush &push, cudaStream_t stream);

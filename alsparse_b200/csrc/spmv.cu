@@ -1003,9 +1003,11 @@ static void launch_merge_as(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, c
     T *carry = static_cast<T *>(ctx->d_carry_val);
     // In-kernel delivery wants chunks of neighbouring tiles to finish together: every tile, natural order,
     // and therefore no column-band path either.
-    if (!PUSH && ctx->bins.active) {
+    if (ctx->bins.active) {
         // bin by bin: the column-band kernel (long rows) first, on its own stream when there is one, then
-        // the short and mid rows; its partial sums are folded into y last
+        // the short and mid rows; its partial sums are folded into y last.  In an exchange call (PUSH) every
+        // kernel that finishes rows stores them into the peers' buffers itself.
+        const PeerPush *deliver = PUSH ? &push : nullptr;
         BandTables &bt = ctx->band;
         if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
         if (bt.rows > 0) {
@@ -1017,13 +1019,13 @@ static void launch_merge_as(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, c
             }
             launch_band<T>(ctx, x, band_st);
         }
-        launch_bins<T>(ctx, alpha, x, beta, y, st);
+        launch_bins<T>(ctx, alpha, x, beta, y, st, deliver);
         if (bt.rows > 0) {
             if (bt.side) {
                 cudaEventRecord(bt.ev_join, bt.side);
                 cudaStreamWaitEvent(st, bt.ev_join, 0);
             }
-            launch_band_reduce<T>(ctx, alpha, beta, y, st);
+            launch_band_reduce<T>(ctx, alpha, beta, y, st, deliver);
         }
         if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
         return;

@@ -157,7 +157,8 @@ __global__ void __launch_bounds__(NT)
 // times the total is added to what the merge kernel and its fix-up left in y.
 template <typename T, bool ASSIGN>
 __global__ void spmv_band_reduce_kernel(int nl, int bands, const int *__restrict__ row,
-                                        const T *__restrict__ partial, T *__restrict__ y, T alpha, T beta) {
+                                        const T *__restrict__ partial, T *__restrict__ y, T alpha, T beta,
+                                        const PeerPush push) {
     const int p = (int)(((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5);
     const int lane = threadIdx.x & 31;
     if (p >= nl) return;
@@ -168,8 +169,14 @@ __global__ void spmv_band_reduce_kernel(int nl, int bands, const int *__restrict
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     if (lane == 0) {
         const int r = row[p];
-        if (ASSIGN) y[r] = (beta == T(0)) ? alpha * acc : fma(beta, y[r], alpha * acc);
-        else y[r] = fma(alpha, acc, y[r]);
+        if (ASSIGN) {
+            const T out = (beta == T(0)) ? alpha * acc : fma(beta, y[r], alpha * acc);
+            y[r] = out;
+            // exchange calls: the finished row also goes to every GPU's next x (push.n == 0 otherwise)
+            for (int q = 0; q < push.n; q++) static_cast<T *>(push.dst[q])[push.row_off + r] = out;
+        } else {
+            y[r] = fma(alpha, acc, y[r]);
+        }
     }
 }
 
@@ -408,20 +415,22 @@ void launch_band(DeviceCtx *ctx, const T *x, cudaStream_t st) {
 }
 
 template <typename T>
-void launch_band_reduce(DeviceCtx *ctx, T alpha, T beta, T *y, cudaStream_t st) {
+void launch_band_reduce(DeviceCtx *ctx, T alpha, T beta, T *y, cudaStream_t st, const PeerPush *push) {
     const BandTables &b = ctx->band;
     const unsigned blocks = (unsigned)(((long long)b.rows * 32 + 255) / 256);
     const T *partial = static_cast<const T *>(b.d_partial);
+    const PeerPush none{};
     if (b.whole_rows)
-        spmv_band_reduce_kernel<T, true><<<blocks, 256, 0, st>>>(b.rows, b.bands, b.d_row, partial, y, alpha, beta);
+        spmv_band_reduce_kernel<T, true><<<blocks, 256, 0, st>>>(b.rows, b.bands, b.d_row, partial, y, alpha, beta,
+                                                                 push ? *push : none);
     else
-        spmv_band_reduce_kernel<T, false><<<blocks, 256, 0, st>>>(b.rows, b.bands, b.d_row, partial, y, alpha, beta);
+        spmv_band_reduce_kernel<T, false><<<blocks, 256, 0, st>>>(b.rows, b.bands, b.d_row, partial, y, alpha, beta, none);
     count_launch();
 }
 
 template void launch_band<float>(DeviceCtx *, const float *, cudaStream_t);
 template void launch_band<double>(DeviceCtx *, const double *, cudaStream_t);
-template void launch_band_reduce<float>(DeviceCtx *, float, float, float *, cudaStream_t);
-template void launch_band_reduce<double>(DeviceCtx *, double, double, double *, cudaStream_t);
+template void launch_band_reduce<float>(DeviceCtx *, float, float, float *, cudaStream_t, const PeerPush *);
+template void launch_band_reduce<double>(DeviceCtx *, double, double, double *, cudaStream_t, const PeerPush *);
 
 }  // namespace asb

@@ -21,19 +21,35 @@
 // its adaptive variant cuts the rows into blocks of similar work at analysis time
 // (src/util_cpp/alphasparse_dcu_x_csrmv_analysis.cpp:58-267).  This is the same idea with other bins.
 #include <algorithm>
+#include <type_traits>
 #include <vector>
 
 #include "internal.h"
 
 namespace asb {
 
+// Delivery of finished rows to the peers; kernels instantiated without PUSH carry no such argument at all.
+struct BinNoPush {};
+template <bool PUSH>
+using BinPushArg = typename std::conditional<PUSH, PeerPush, BinNoPush>::type;
+template <typename T>
+__device__ __forceinline__ void bin_push_row(const PeerPush &push, long long r, T out) {
+#pragma unroll 1
+    for (int p = 0; p < push.n; p++) static_cast<T *>(push.dst[p])[push.row_off + r] = out;
+}
+template <typename T>
+__device__ __forceinline__ void bin_push_row(const BinNoPush &, long long, T) {}
+
 // ---- short rows: one thread per row -------------------------------------------------------------
 // A thread takes R rows, 256 rows apart (so that every load instruction of a warp covers consecutive rows), and walks
 // them together, two elements of each per step.  R = 1 is what is used: see launch_bins.
-template <typename T, int R, bool HAS_BETA>
+// PUSH: every finished row also goes into the next-x buffer of every GPU of the row partition (peer-mapped pointers,
+// plain stores over NVLink; see PeerPush).  Neighbouring lanes hold neighbouring rows, so these are coalesced.
+template <typename T, int R, bool HAS_BETA, bool PUSH>
 __global__ void __launch_bounds__(256)
     spmv_short_kernel(int rows, int limit, const int *__restrict__ row_ptr, const int *__restrict__ col,
-                      const T *__restrict__ val, const T *__restrict__ x, T *__restrict__ y, T alpha, T beta) {
+                      const T *__restrict__ val, const T *__restrict__ x, T *__restrict__ y, T alpha, T beta,
+                      const __grid_constant__ BinPushArg<PUSH> push) {
     const long long base = (long long)blockIdx.x * (256 * R) + threadIdx.x;
     int s[R], n[R];
     T acc[R];
@@ -73,6 +89,7 @@ __global__ void __launch_bounds__(256)
             T out = alpha * acc[u];
             if (HAS_BETA) out = fma(beta, y[r], out);
             __stcs(y + r, out);
+            bin_push_row<T>(push, r, out);
         }
     }
 }
@@ -106,11 +123,11 @@ __device__ __forceinline__ T bin_quad_dot(const int4 c, const BinQuad<T> &v, int
 
 // 256 threads = 256 / LANES groups; group g of block b takes list entries b * (GROUPS * R) + g + u * GROUPS,
 // u = 0 .. R-1: R rows in flight per group.  U quads per row are requested before any is consumed.
-template <typename T, int LANES, int R, int U, bool HAS_BETA>
+template <typename T, int LANES, int R, int U, bool HAS_BETA, bool PUSH>
 __global__ void __launch_bounds__(256)
     spmv_rowlist_kernel(int count, const int *__restrict__ list, const int *__restrict__ row_ptr,
                         const int *__restrict__ col, const T *__restrict__ val, const T *__restrict__ x,
-                        T *__restrict__ y, T alpha, T beta) {
+                        T *__restrict__ y, T alpha, T beta, const __grid_constant__ BinPushArg<PUSH> push) {
     constexpr int GROUPS = 256 / LANES;
     const int lane = threadIdx.x % LANES, grp = threadIdx.x / LANES;
     const long long i0 = (long long)blockIdx.x * (GROUPS * R) + grp;
@@ -161,6 +178,7 @@ __global__ void __launch_bounds__(256)
             T out = alpha * sum[u];
             if (HAS_BETA) out = fma(beta, y[row[u]], out);
             y[row[u]] = out;
+            bin_push_row<T>(push, row[u], out);  // the listed rows are few and far apart: single stores
         }
     }
 }
@@ -248,8 +266,9 @@ alphasparse_status_t bins_build(DeviceCtx *ctx, const int *h_ptr, int64_t long_m
 
 // ---- launch --------------------------------------------------------------------------------------
 
-template <typename T, int LANES, int R, int U>
-static void launch_list(DeviceCtx *ctx, int k, T alpha, const T *x, T beta, T *y, cudaStream_t st) {
+template <typename T, int LANES, int R, int U, bool PUSH>
+static void launch_list(DeviceCtx *ctx, int k, T alpha, const T *x, T beta, T *y, cudaStream_t st,
+                        const BinPushArg<PUSH> &push) {
     const RowBins &b = ctx->bins;
     if (b.count[k] == 0) return;
     if (b.side[k]) st = b.side[k];
@@ -257,34 +276,32 @@ static void launch_list(DeviceCtx *ctx, int k, T alpha, const T *x, T beta, T *y
     const unsigned blocks = (unsigned)((b.count[k] + per_block - 1) / per_block);
     const T *val = static_cast<const T *>(ctx->d_val);
     if (beta == T(0))
-        spmv_rowlist_kernel<T, LANES, R, U, false><<<blocks, 256, 0, st>>>(
-            (int)b.count[k], b.d_list + b.offset[k], ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta);
+        spmv_rowlist_kernel<T, LANES, R, U, false, PUSH><<<blocks, 256, 0, st>>>(
+            (int)b.count[k], b.d_list + b.offset[k], ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta, push);
     else
-        spmv_rowlist_kernel<T, LANES, R, U, true><<<blocks, 256, 0, st>>>(
-            (int)b.count[k], b.d_list + b.offset[k], ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta);
+        spmv_rowlist_kernel<T, LANES, R, U, true, PUSH><<<blocks, 256, 0, st>>>(
+            (int)b.count[k], b.d_list + b.offset[k], ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta, push);
     count_launch();
 }
 
-template <typename T, int R>
-static void launch_short(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st) {
+template <typename T, bool PUSH>
+static void launch_short(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st,
+                         const BinPushArg<PUSH> &push) {
     const RowBins &b = ctx->bins;
     const T *val = static_cast<const T *>(ctx->d_val);
-    const unsigned blocks = (unsigned)((ctx->rows + 256 * R - 1) / (256 * R));
+    const unsigned blocks = (unsigned)((ctx->rows + 255) / 256);
     if (beta == T(0))
-        spmv_short_kernel<T, R, false><<<blocks, 256, 0, st>>>((int)ctx->rows, b.short_limit, ctx->d_row_ptr, ctx->d_col,
-                                                               val, x, y, alpha, beta);
+        spmv_short_kernel<T, 1, false, PUSH><<<blocks, 256, 0, st>>>((int)ctx->rows, b.short_limit, ctx->d_row_ptr,
+                                                                     ctx->d_col, val, x, y, alpha, beta, push);
     else
-        spmv_short_kernel<T, R, true><<<blocks, 256, 0, st>>>((int)ctx->rows, b.short_limit, ctx->d_row_ptr, ctx->d_col,
-                                                              val, x, y, alpha, beta);
+        spmv_short_kernel<T, 1, true, PUSH><<<blocks, 256, 0, st>>>((int)ctx->rows, b.short_limit, ctx->d_row_ptr,
+                                                                    ctx->d_col, val, x, y, alpha, beta, push);
     count_launch();
 }
 
-// Short and mid rows of a binned handle (the long rows are the column-band kernel's).
-// Shapes from a sweep on B200 (power-law matrix): one row per thread / two rows per lane group at 32..48 registers
-// beat every shape with more rows in flight per thread (4 rows per thread or group: 80..93 registers, 15..25 %
-// slower): these kernels live on resident warps, not on loads per thread.
-template <typename T>
-void launch_bins(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st) {
+template <typename T, bool PUSH>
+static void launch_bins_as(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st,
+                           const BinPushArg<PUSH> &push) {
     const RowBins &b = ctx->bins;
     if (b.ev_fork) {
         cudaEventRecord(b.ev_fork, st);
@@ -292,10 +309,10 @@ void launch_bins(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t
             if (b.side[k]) cudaStreamWaitEvent(b.side[k], b.ev_fork, 0);
     }
     // the longest-running list first, so that the shorter kernels fill in behind it
-    launch_list<T, 32, 1, 2>(ctx, 2, alpha, x, beta, y, st);
-    if (b.short_rows > 0) launch_short<T, 1>(ctx, alpha, x, beta, y, st);
-    launch_list<T, 4, 2, 1>(ctx, 0, alpha, x, beta, y, st);
-    launch_list<T, 16, 2, 1>(ctx, 1, alpha, x, beta, y, st);
+    launch_list<T, 32, 1, 2, PUSH>(ctx, 2, alpha, x, beta, y, st, push);
+    if (b.short_rows > 0) launch_short<T, PUSH>(ctx, alpha, x, beta, y, st, push);
+    launch_list<T, 4, 2, 1, PUSH>(ctx, 0, alpha, x, beta, y, st, push);
+    launch_list<T, 16, 2, 1, PUSH>(ctx, 1, alpha, x, beta, y, st, push);
     for (int k = 0; k < kMidBins; k++)
         if (b.side[k]) {
             cudaEventRecord(b.ev_join[k], b.side[k]);
@@ -303,7 +320,18 @@ void launch_bins(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t
         }
 }
 
-template void launch_bins<float>(DeviceCtx *, float, const float *, float, float *, cudaStream_t);
-template void launch_bins<double>(DeviceCtx *, double, const double *, double, double *, cudaStream_t);
+// Short and mid rows of a binned handle (the long rows are the column-band kernel's).  With `push` every kernel
+// also stores its rows into the peers' buffers as it finishes them: the exchange overlaps the product.
+// Shapes from a sweep on B200 (power-law matrix): one row per thread / two rows per lane group at 32..48 registers
+// beat every shape with more rows in flight per thread (4 rows per thread or group: 80..93 registers, 15..25 %
+// slower): these kernels live on resident warps, not on loads per thread.
+template <typename T>
+void launch_bins(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cudaStream_t st, const PeerPush *push) {
+    if (push) launch_bins_as<T, true>(ctx, alpha, x, beta, y, st, *push);
+    else launch_bins_as<T, false>(ctx, alpha, x, beta, y, st, BinNoPush{});
+}
+
+template void launch_bins<float>(DeviceCtx *, float, const float *, float, float *, cudaStream_t, const PeerPush *);
+template void launch_bins<double>(DeviceCtx *, double, const double *, double, double *, cudaStream_t, const PeerPush *);
 
 }  // namespace asb
