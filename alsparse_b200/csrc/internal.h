@@ -37,6 +37,7 @@ enum Option {
     kOptBinShort,         // rows of at most this many elements take the thread-per-row kernel
     kOptBinOverlap,       // 1: the kernels of the bins run on streams of their own, side by side
     kOptBinMidMax,        // longest row the lane-group kernels may be given; longer non-band rows: merge tiles instead
+    kOptBinPushMaxPeers,  // exchange calls to more GPUs than this run over merge tiles instead of bins
     kOptSpmmColBlocks,    // column blocks of the row-major dense-block product (0 or 1: one pass)
     kOptCount
 };

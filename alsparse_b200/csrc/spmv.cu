@@ -1003,7 +1003,12 @@ static void launch_merge_as(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, c
     T *carry = static_cast<T *>(ctx->d_carry_val);
     // In-kernel delivery wants chunks of neighbouring tiles to finish together: every tile, natural order,
     // and therefore no column-band path either.
-    if (ctx->bins.active) {
+    // Exchange calls over many GPUs stay on the merge tiles: their chunk-by-chunk delivery spreads the NVLink traffic
+    // over the whole product, while the bins would send 88 % of the rows in one burst from the short-row kernel
+    // (iterated power-law step on 8 GPUs: 0.32 ms with tiles, 0.47 ms with bins; on 2 GPUs 0.99 against 0.78 ms).
+    bool binned = ctx->bins.active;
+    if constexpr (PUSH) binned = binned && push.n <= (int)option(kOptBinPushMaxPeers);
+    if (binned) {
         // bin by bin: the column-band kernel (long rows) first, on its own stream when there is one, then
         // the short and mid rows; its partial sums are folded into y last.  In an exchange call (PUSH) every
         // kernel that finishes rows stores them into the peers' buffers itself.

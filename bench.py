@@ -280,9 +280,11 @@ def ncu_traffic(name, kernel, reduced, world):
     if reduced or world != 1 or not os.path.exists(path):
         return None, None
     rec = json.load(open(path)).get(name)
-    if not rec or rec.get("kernel") != kernel:
-        return None, (f"no capture of {kernel} (profiles/ncu_traffic.json has {rec.get('kernel')})" if rec else None)
-    return rec["dram_bytes_per_launch"], f"ncu capture {rec['summary']} ({rec['kernel']}, at commit {rec['commit']})"
+    if not isinstance(rec, dict) or rec.get("kernel") != kernel:
+        return None, (f"no capture of {kernel} (profiles/ncu_traffic.json has {rec.get('kernel')})"
+                      if isinstance(rec, dict) else None)
+    how = "scaled from a capture at reduced size, see the summary" if rec.get("scaled") else "full-size capture"
+    return rec["dram_bytes_per_launch"], f"ncu: {rec['summary']} ({rec['kernel']}, at commit {rec['commit']}; {how})"
 
 
 def sampled_rows(m, rng, n_random):
@@ -671,12 +673,38 @@ def main():
             x_bytes = (x_block_h if loader is not None else x_h)
             h2d = x_bytes.numel() * x_bytes.element_size() + (y0_h.numel() * y0_h.element_size() if beta != 0.0 else 0)
             d2h = y_h.numel() * y_h.element_size()
+            # What the host side of the box allows for these copies alone: every rank moves the bytes of one step
+            # (same pinned buffers, inbound and outbound on two streams at once, no kernel), all ranks at the same
+            # time.  With several GPUs the ranks share the host's memory and PCIe root, so this floor does not
+            # shrink like the per-GPU byte count does.
+            up, down = torch.cuda.Stream(), torch.cuda.Stream()
+            dev_in = [torch.empty_like(x_bytes, device="cuda"), torch.empty_like(y0_h, device="cuda")]
+            dev_out = torch.empty_like(y_h, device="cuda")
+
+            def copies():
+                with torch.cuda.stream(up):
+                    dev_in[0].copy_(x_bytes, non_blocking=True)
+                    if beta != 0.0:
+                        dev_in[1].copy_(y0_h, non_blocking=True)
+                with torch.cuda.stream(down):
+                    y_h.copy_(dev_out, non_blocking=True)
+                up.synchronize()
+                down.synchronize()
+            for _ in range(2):
+                copies()
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(5):
+                copies()
+            copy_floor = max_over_ranks((time.perf_counter() - t0) / 5 * 1e3)
+            del dev_in, dev_out
+            barrier()
             if loader is not None:
                 st_code, code = loader.status()
                 assert st_code == capi.SUCCESS and code == 0, f"a bounded wait of the exchange ran out (status {code})"
                 loader.destroy()
             # bytes of the whole job: every rank's copies added up
-            e2e = (ms_e2e, sum_over_ranks(h2d), sum_over_ranks(d2h), x_upload, breakdown)
+            e2e = (ms_e2e, sum_over_ranks(h2d), sum_over_ranks(d2h), x_upload, breakdown, copy_floor)
     if sampler:
         sampler.stop()
 
@@ -704,10 +732,9 @@ def main():
 
     algorithm = ["auto", "vector", "merge", "rowtile"][info.algorithm]
     kernel = {"vector": f"spmv_vector_kernel lanes={info.lanes_per_row}", "rowtile": "spmv_rowtile_kernel",
-              "merge": "spmv_merge_kernel" + (" + spmv_band_quad_kernel" if info.band_rows else "")}[algorithm] \
+              "merge": ("row bins: spmv_short_kernel + spmv_rowlist_kernel x3" if info.binned else "spmv_merge_kernel") +
+                       (" + spmv_band_quad_kernel" if info.band_rows else "")}[algorithm] \
         if op == "mv" else "spmm_row_kernel"
-    if op == "mm":
-        kernel += f" column_blocks={spblas.mat_info(A)[1].spmm_col_blocks}" if False else ""
     if rank == 0:
         traffic, traffic_src = ncu_traffic(name, kernel, reduced, world)
         line = {
@@ -741,6 +768,10 @@ def main():
                            "h2d_bytes_per_step": int(e2e[1]), "d2h_bytes_per_step": int(e2e[2]), "x_upload": e2e[3]}
             if e2e[4]:
                 line["e2e"]["phases"] = e2e[4]
+            line["e2e"]["copies_alone_ms"] = e2e[5]
+            line["e2e"]["copies_alone_note"] = ("the same host<->device bytes moved by plain copies on two streams, all "
+                                                "ranks at once, no kernel: the share of the step that belongs to the "
+                                                "host's memory and PCIe links")
         else:
             line["e2e"] = None
         if world == 1 and not args.no_cpu_baseline:

@@ -51,6 +51,8 @@ alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg);
  *                           elements, a lane group per row above, the column-band kernel for long rows; merge
  *                           tiles remain for matrices with rows above bin_mid_max (16384) that are not long
  *                           enough for the band kernel, with too few long rows, or with unsorted long rows
+ *   bin_push_max_peers (3)  exchange calls (alphasparse_?_mv_exchange) that deliver to more GPUs than this run over
+ *                           merge tiles, whose chunk-wise delivery spreads the NVLink traffic, instead of bins
  *   spmm_col_blocks (0)     row-major dense-block product in this many column blocks (X slab by slab, Y
  *                           accumulated over the passes); 0 or 1 = one pass, which measured faster on B200
  * Unknown names return ALPHA_SPARSE_STATUS_INVALID_VALUE. */
