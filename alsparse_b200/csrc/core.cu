@@ -917,7 +917,7 @@ static alphasparse_status_t mv_on_ctx(DeviceCtx *c, T alpha, const T *x, T beta,
         y_alias = device_alias_of_pinned(y);
     if (y_alias) {
         PeerPush push{};
-        push.n = 1, push.dst[0] = y_alias, push.row_off = 0, push.after = 0;
+        push.n = 1, push.dst[0] = y_alias, push.row_off = 0, push.after = 0, push.runs = 1;
         s = launch_spmv<T>(c, alpha, dx, beta, dy, st, &push);
         if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     } else {

@@ -88,6 +88,8 @@ struct PeerPush {
     int n;
     long long row_off;
     int after;  // 1: deliver with a separate bulk copy after the product instead of from inside it
+    int runs;   // 1: the destination wants long contiguous runs (host memory behind PCIe): a binned handle then
+                // delivers through its merge tiles, chunk by chunk, not row by row from the bin kernels
     // merge kernel only: progress counters of its chunks of consecutive tiles
     int tiles, chunk_tiles;
     unsigned *chunk_done;  // tiles finished per chunk; reset by the block that completes the chunk

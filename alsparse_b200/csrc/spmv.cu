@@ -1006,8 +1006,10 @@ static void launch_merge_as(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, c
     // Exchange calls over many GPUs stay on the merge tiles: their chunk-by-chunk delivery spreads the NVLink traffic
     // over the whole product, while the bins would send 88 % of the rows in one burst from the short-row kernel
     // (iterated power-law step on 8 GPUs: 0.32 ms with tiles, 0.47 ms with bins; on 2 GPUs 0.99 against 0.78 ms).
+    // So do deliveries into page-locked host memory: single 8-byte stores over PCIe made the end-to-end power-law
+    // product 5.4 ms, the tiles' 16-byte runs 3.1 ms.
     bool binned = ctx->bins.active;
-    if constexpr (PUSH) binned = binned && push.n <= (int)option(kOptBinPushMaxPeers);
+    if constexpr (PUSH) binned = binned && !push.runs && push.n <= (int)option(kOptBinPushMaxPeers);
     if (binned) {
         // bin by bin: the column-band kernel (long rows) first, on its own stream when there is one, then
         // the short and mid rows; its partial sums are folded into y last.  In an exchange call (PUSH) every
