@@ -35,6 +35,8 @@ enum Option {
     kOptBandVariant,      // shape of the band kernel: 0 = 8 lanes x 1 quad x 2 segments, 1 = 4 lanes x 2 quads x 1 segment
     kOptBinEnable,        // 1: skewed matrices are multiplied bin by bin (short / mid / long rows) instead of merge tiles
     kOptBinShort,         // rows of at most this many elements take the thread-per-row kernel
+    kOptBinMid0,          // longest row of the first mid list (4 lanes per row)
+    kOptBinMid1,          // longest row of the second mid list (16 lanes per row); longer rows: 32 lanes
     kOptBinOverlap,       // 1: the kernels of the bins run on streams of their own, side by side
     kOptBinMidMax,        // longest row the lane-group kernels may be given; longer non-band rows: merge tiles instead
     kOptBinPushMaxPeers,  // exchange calls to more GPUs than this run over merge tiles instead of bins

@@ -57,7 +57,7 @@ template <typename T, int G, int U, int R, int NT>
 __global__ void __launch_bounds__(NT)
     spmv_band_quad_kernel(int cols, int width, int bands, int nl, int chunk, const int *__restrict__ seg,
                           const int *__restrict__ col, const T *__restrict__ val, const T *__restrict__ x,
-                          T *__restrict__ partial) {
+                          T *__restrict__ partial, int *__restrict__ status) {
     extern __shared__ __align__(16) unsigned char band_smem[];
     T *sx = reinterpret_cast<T *>(band_smem);
     const int b = blockIdx.x, s = blockIdx.y, tid = threadIdx.x;
@@ -85,17 +85,47 @@ __global__ void __launch_bounds__(NT)
         }
     }
 
-    if ((reinterpret_cast<uintptr_t>(xb) & 15) == 0) {
-        constexpr int per = 16 / (int)sizeof(T);
-        const int nv = n / per;
-        const int4 *src = reinterpret_cast<const int4 *>(xb);
-        int4 *dst = reinterpret_cast<int4 *>(sx);
-        for (int i = tid; i < nv; i += NT) dst[i] = __ldg(src + i);
-        for (int i = nv * per + tid; i < n; i += NT) sx[i] = __ldg(xb + i);
+    // The band of x comes in by bulk asynchronous copies (cp.async.bulk global -> shared, completion counted in
+    // bytes on an mbarrier) issued by one thread, so that every thread goes straight on to its first matrix loads
+    // and meets the band only when it needs it.  A band that does not start on a 16-byte boundary or has a ragged
+    // length (the last one) is loaded by all threads instead.  `ready` is uniform over the block until the wait.
+    __shared__ __align__(8) unsigned long long s_bar;
+    const unsigned bar = (unsigned)__cvta_generic_to_shared(&s_bar);
+    const unsigned band_bytes = (unsigned)n * (unsigned)sizeof(T);
+    const bool bulk = (reinterpret_cast<uintptr_t>(xb) & 15) == 0 && (band_bytes & 15u) == 0 && band_bytes > 0;
+    bool ready = !bulk;
+    if (bulk) {
+        if (tid == 0) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(band_bytes) : "memory");
+            constexpr unsigned kPiece = 16 * 1024;
+            for (unsigned off = 0; off < band_bytes; off += kPiece) {
+                const unsigned bytes = band_bytes - off < kPiece ? band_bytes - off : kPiece;
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 (unsigned)__cvta_generic_to_shared(band_smem + off)),
+                             "l"(reinterpret_cast<const unsigned char *>(xb) + off), "r"(bytes), "r"(bar)
+                             : "memory");
+            }
+        }
     } else {
         for (int i = tid; i < n; i += NT) sx[i] = __ldg(xb + i);
     }
-    __syncthreads();
+    __syncthreads();  // the barrier is initialised (or the band is in place) for everyone
+
+    // Bounded wait for the band; on a time-out the block records the error word and gives up its segments.
+    auto wait_band = [&]() -> bool {
+        for (int spin = 0; spin < (1 << 22); spin++) {
+            unsigned ok;
+            asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                         : "=r"(ok)
+                         : "r"(bar), "r"(0u)
+                         : "memory");
+            if (ok) return true;
+        }
+        atomicExch(status, 2);
+        return false;
+    };
 
     for (int p = s * chunk + g; p < p1; p += NG * R) {
         int a[R], e[R], q[R];
@@ -125,6 +155,10 @@ __global__ void __launch_bounds__(NT)
                         vv[r][u] = band_load_val(val, qq);
                     }
                 }
+            if (!ready) {  // the first matrix loads are on their way: now the band is needed
+                if (!wait_band()) return;
+                ready = true;
+            }
             more = false;
 #pragma unroll
             for (int r = 0; r < R; r++) {
@@ -150,6 +184,9 @@ __global__ void __launch_bounds__(NT)
             if (gl == 0 && pp < p1) partial[(size_t)pp * bands + b] = acc[r];
         }
     }
+    // a thread without segments has not met the band yet: nobody leaves while the copies may still be writing
+    // into this block's shared memory
+    if (!ready) wait_band();
 }
 
 // One warp per long row: its partial sums in band order (lane j takes bands j, j+32, ..., then a fixed tree over
@@ -401,7 +438,8 @@ static void launch_band_as(K kernel, int threads, std::atomic<size_t> &granted, 
     }
     const dim3 grid((unsigned)b.bands, (unsigned)b.splits);
     kernel<<<grid, threads, smem, st>>>((int)ctx->cols, b.width, b.bands, b.rows, b.chunk, b.d_seg, ctx->d_col,
-                                        static_cast<const T *>(ctx->d_val), x, static_cast<T *>(b.d_partial));
+                                        static_cast<const T *>(ctx->d_val), x, static_cast<T *>(b.d_partial),
+                                        ctx->d_status);
     count_launch();
 }
 

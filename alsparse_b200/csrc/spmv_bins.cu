@@ -5,7 +5,7 @@
 // bins once per handle -- lists of row numbers; the CSR arrays stay as the caller gave them -- and a
 // product launches one kernel per non-empty bin on the same stream:
 //
-//   short   rows of at most kBinShort elements (empty rows included): one thread per row, straight
+//   short   rows of at most 16 elements (option bin_short; empty rows included): one thread per row, straight
 //           from the CSR arrays.  Neighbouring threads take neighbouring rows, whose elements are
 //           neighbours in memory, so the loads of a warp stay within a few cache lines.
 //   mid     three lists (up to 32, up to 256, longer): a group of 4 / 16 / 32 lanes per row, every lane
@@ -201,7 +201,7 @@ alphasparse_status_t bins_build(DeviceCtx *ctx, const int *h_ptr, int64_t long_m
                                 cudaStream_t st) {
     RowBins b;
     b.short_limit = (int)std::max<int64_t>(0, option(kOptBinShort));
-    const int bounds[kMidBins] = {32, 256, INT32_MAX};
+    const int bounds[kMidBins] = {(int)option(kOptBinMid0), (int)option(kOptBinMid1), INT32_MAX};
     std::vector<int> lists[kMidBins];
     long_rows.clear();
     for (int64_t r = 0; r < ctx->rows; r++) {

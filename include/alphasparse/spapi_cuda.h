@@ -39,7 +39,7 @@ alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg);
  * call; a negative value restores the default.  ALPHASPARSE_CUDA_OPTIONS="name=value,..." sets initial values.
  *   band_enable (1)         long rows of a skewed matrix go through the column-band kernel
  *   band_bytes (65536)      bytes of x one column band stages in shared memory
- *   band_min_seg (8)        a row is long when it averages at least this many elements per band
+ *   band_min_seg (12)       a row is long when it averages at least this many elements per band
  *   band_min_rows (128)     fewer long rows than this are left to the merge kernel
  *   band_min_share_pct (10) ... and so are long rows holding less than this share of the elements
  *   band_splits (0)         thread blocks per band, 0 = about eight waves of blocks
@@ -47,8 +47,9 @@ alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg);
  *   band_variant (0)        shape of the column-band kernel: 0 = 8 lanes x 1 quad x 2 segments per lane group,
  *                           1 = 4 lanes x 2 quads x 1 segment
  *   bin_overlap (1)         the kernels of the mid bins run on streams of their own, side by side
- *   bin_enable (1)          skewed matrices are multiplied bin by bin: thread per row up to bin_short (8)
- *                           elements, a lane group per row above, the column-band kernel for long rows; merge
+ *   bin_enable (1)          skewed matrices are multiplied bin by bin: thread per row up to bin_short (16)
+ *                           elements, a lane group (4 / 16 / 32 lanes for rows up to bin_mid0 (32) / bin_mid1 (256) /
+ *                           longer) per row above, the column-band kernel for long rows; merge
  *                           tiles remain for matrices with rows above bin_mid_max (16384) that are not long
  *                           enough for the band kernel, with too few long rows, or with unsorted long rows
  *   bin_push_max_peers (3)  exchange calls (alphasparse_?_mv_exchange) that deliver to more GPUs than this run over
