@@ -32,6 +32,7 @@ enum Option {
     kOptBandMinSharePct,  // long rows must hold at least this share of the stored elements
     kOptBandSplits,       // thread blocks per band (0: chosen from the band count)
     kOptBandOverlap,      // 1: the band kernel runs on a second stream beside the merge kernel
+    kOptBandPacked,       // 1: the band kernel streams a packed, band-major copy of the long rows (16-bit columns)
     kOptBandVariant,      // shape of the band kernel: 0 = 8 lanes x 1 quad x 2 segments, 1 = 4 lanes x 2 quads x 1 segment
     kOptBinEnable,        // 1: skewed matrices are multiplied bin by bin (short / mid / long rows) instead of merge tiles
     kOptBinShort,         // rows of at most this many elements take the thread-per-row kernel
@@ -119,6 +120,13 @@ struct BandTables {
     int *d_row = nullptr;      // rows
     int *d_seg = nullptr;      // (bands + 1) * rows
     void *d_partial = nullptr; // rows * bands sums, written by every call
+    // Packed copy of the long rows' elements, band-major (optional): the segments of band b follow each other in
+    // list order, each padded to whole quads; columns are stored relative to the band in 16 bits (0xffff = padding).
+    // d_pk_start[b * rows + p] is the first quad of segment (b, p); one more entry closes the last segment.
+    int *d_pk_start = nullptr;
+    void *d_pk_val = nullptr;
+    unsigned short *d_pk_col = nullptr;
+    int64_t pk_quads = 0;
     cudaStream_t side = nullptr;  // second stream + fork / join events when the kernels overlap
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 };

@@ -189,6 +189,176 @@ __global__ void __launch_bounds__(NT)
     if (!ready) wait_band();
 }
 
+// ---- the same product from the packed copy ------------------------------------------------------------
+//
+// The long rows are static, so the analysis can lay their elements out the way this kernel walks them: band by band,
+// inside a band segment after segment in list order, every segment padded to whole quads.  The block (b, s) then
+// streams ONE contiguous piece of memory, neighbouring lane groups read neighbouring addresses, no element has to be
+// masked against the row's ends, and the column of an element is its offset inside the band: 16 bits instead of 32
+// (10 instead of 12 bytes per fp64 element, 6 instead of 8 per fp32 element).  Padding carries the column 0xffff
+// and is skipped, so nothing of x is ever read for it.  The copy costs (sizeof(T) + 2) bytes per long-row element
+// of device memory; the caller's CSR arrays stay as they are.
+// (Feeding the packed piece through shared memory with a pipeline of bulk copies -- stages of 256 quads on
+// mbarriers, one quad per thread, segmented scan over the lanes, run sums combined in warp order -- was built and
+// measured too: 1.86 ms per power-law product against 1.24 ms with the lane groups below.  With ~60 elements per
+// segment the two block-wide barriers and the ordered combine of every 10 KB stage cost more than the loads they
+// take out of the registers.)
+template <typename T>
+__device__ __forceinline__ BandQuad<T> band_load_packed(const T *__restrict__ val, int q);
+template <>
+__device__ __forceinline__ BandQuad<float> band_load_packed<float>(const float *__restrict__ val, int q) {
+    const float4 t = __ldcs(reinterpret_cast<const float4 *>(val) + q);
+    return {{t.x, t.y, t.z, t.w}};
+}
+template <>
+__device__ __forceinline__ BandQuad<double> band_load_packed<double>(const double *__restrict__ val, int q) {
+    const double2 a = __ldcs(reinterpret_cast<const double2 *>(val) + 2 * (size_t)q);
+    const double2 b = __ldcs(reinterpret_cast<const double2 *>(val) + 2 * (size_t)q + 1);
+    return {{a.x, a.y, b.x, b.y}};
+}
+
+template <typename T, int G, int U, int R, int NT>
+__global__ void __launch_bounds__(NT)
+    spmv_band_packed_kernel(int cols, int width, int bands, int nl, int chunk, const int *__restrict__ pk_start,
+                            const unsigned short *__restrict__ pk_col, const T *__restrict__ pk_val,
+                            const T *__restrict__ x, T *__restrict__ partial, int *__restrict__ status) {
+    extern __shared__ __align__(16) unsigned char band_smem[];
+    T *sx = reinterpret_cast<T *>(band_smem);
+    const int b = blockIdx.x, s = blockIdx.y, tid = threadIdx.x;
+    const long long c0l = (long long)b * width;
+    const int n = (int)(cols - c0l < width ? cols - c0l : width);
+    const T *xb = x + c0l;
+
+    constexpr int NG = NT / G;
+    const int g = tid / G, gl = tid % G;
+    const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (((tid & 31) / G) * G));
+    const int p1 = min(nl, (s + 1) * chunk);
+    const int *start = pk_start + (size_t)b * nl;
+
+    int nq[R], ne[R];  // first quad / end quad of the segments of the next step
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+        const int pp = s * chunk + g + r * NG;
+        nq[r] = 0, ne[r] = 0;
+        if (pp < p1) {
+            nq[r] = __ldg(start + pp);
+            ne[r] = __ldg(start + pp + 1);
+        }
+    }
+
+    __shared__ __align__(8) unsigned long long s_bar;
+    const unsigned bar = (unsigned)__cvta_generic_to_shared(&s_bar);
+    const unsigned band_bytes = (unsigned)n * (unsigned)sizeof(T);
+    const bool bulk = (reinterpret_cast<uintptr_t>(xb) & 15) == 0 && (band_bytes & 15u) == 0 && band_bytes > 0;
+    bool ready = !bulk;
+    if (bulk) {
+        if (tid == 0) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(band_bytes) : "memory");
+            constexpr unsigned kPiece = 16 * 1024;
+            for (unsigned off = 0; off < band_bytes; off += kPiece) {
+                const unsigned bytes = band_bytes - off < kPiece ? band_bytes - off : kPiece;
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 (unsigned)__cvta_generic_to_shared(band_smem + off)),
+                             "l"(reinterpret_cast<const unsigned char *>(xb) + off), "r"(bytes), "r"(bar)
+                             : "memory");
+            }
+        }
+    } else {
+        for (int i = tid; i < n; i += NT) sx[i] = __ldg(xb + i);
+    }
+    __syncthreads();
+    auto wait_band = [&]() -> bool {
+        for (int spin = 0; spin < (1 << 22); spin++) {
+            unsigned ok;
+            asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+                         : "=r"(ok)
+                         : "r"(bar), "r"(0u)
+                         : "memory");
+            if (ok) return true;
+        }
+        atomicExch(status, 2);
+        return false;
+    };
+
+    for (int p = s * chunk + g; p < p1; p += NG * R) {
+        int q[R], e[R];
+        T acc[R];
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+            q[r] = nq[r] + gl, e[r] = ne[r], acc[r] = T(0);
+            const int pn = p + (R + r) * NG;
+            nq[r] = 0, ne[r] = 0;
+            if (pn < p1) {
+                nq[r] = __ldg(start + pn);
+                ne[r] = __ldg(start + pn + 1);
+            }
+        }
+        bool more = true;
+        while (more) {
+            uint2 cc[R][U];
+            BandQuad<T> vv[R][U];
+#pragma unroll
+            for (int r = 0; r < R; r++)
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    const int qq = q[r] + u * G;
+                    if (qq < e[r]) {
+                        cc[r][u] = __ldcs(reinterpret_cast<const uint2 *>(pk_col) + qq);
+                        vv[r][u] = band_load_packed<T>(pk_val, qq);
+                    }
+                }
+            if (!ready) {
+                if (!wait_band()) return;
+                ready = true;
+            }
+            more = false;
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+#pragma unroll
+                for (int u = 0; u < U; u++) {
+                    if (q[r] + u * G < e[r]) {
+                        const unsigned c0 = cc[r][u].x & 0xffffu, c1 = cc[r][u].x >> 16;
+                        const unsigned c2 = cc[r][u].y & 0xffffu, c3 = cc[r][u].y >> 16;
+                        if (c0 != 0xffffu) acc[r] = fma(vv[r][u].v[0], sx[c0], acc[r]);
+                        if (c1 != 0xffffu) acc[r] = fma(vv[r][u].v[1], sx[c1], acc[r]);
+                        if (c2 != 0xffffu) acc[r] = fma(vv[r][u].v[2], sx[c2], acc[r]);
+                        if (c3 != 0xffffu) acc[r] = fma(vv[r][u].v[3], sx[c3], acc[r]);
+                    }
+                }
+                q[r] += G * U;
+                more |= q[r] < e[r];
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+#pragma unroll
+            for (int o = G / 2; o > 0; o >>= 1) acc[r] += __shfl_xor_sync(gmask, acc[r], o, G);
+            const int pp = p + r * NG;
+            if (gl == 0 && pp < p1) partial[(size_t)pp * bands + b] = acc[r];
+        }
+    }
+    if (!ready) wait_band();
+}
+
+// Fills the packed copy: block p copies the elements [a[p], e[p]) of long row p to their places.
+template <typename T>
+__global__ void band_pack_kernel(int nl, int width, const int *__restrict__ a, const int *__restrict__ e,
+                                 const int *__restrict__ seg, const int *__restrict__ pk_start,
+                                 const int *__restrict__ col, const T *__restrict__ val,
+                                 unsigned short *__restrict__ pk_col, T *__restrict__ pk_val) {
+    const int p = blockIdx.x;
+    for (long long k = (long long)a[p] + threadIdx.x; k < e[p]; k += blockDim.x) {
+        const int c = col[k];
+        const int b = c / width;
+        const size_t cell = (size_t)b * nl + p;
+        const size_t dst = 4 * (size_t)pk_start[cell] + (size_t)(k - seg[cell]);
+        pk_col[dst] = (unsigned short)(c - b * width);
+        pk_val[dst] = val[k];
+    }
+}
+
 // One warp per long row: its partial sums in band order (lane j takes bands j, j+32, ..., then a fixed tree over
 // the lanes).  ASSIGN: the row belongs to this path alone, y[row] = alpha * total + beta * y[row]; otherwise alpha
 // times the total is added to what the merge kernel and its fix-up left in y.
@@ -249,6 +419,9 @@ void band_destroy(BandTables &b) {
     cudaFree(b.d_row);
     cudaFree(b.d_seg);
     cudaFree(b.d_partial);
+    cudaFree(b.d_pk_start);
+    cudaFree(b.d_pk_val);
+    cudaFree(b.d_pk_col);
     if (b.side) cudaStreamDestroy(b.side);
     if (b.ev_fork) cudaEventDestroy(b.ev_fork);
     if (b.ev_join) cudaEventDestroy(b.ev_join);
@@ -373,6 +546,44 @@ static alphasparse_status_t band_finish(DeviceCtx *ctx, std::vector<BandCand> &c
                                                                    bt.d_seg);
     count_launch();
     TRY(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    if (option(kOptBandPacked) && width < 65535) {
+        // quads per segment, band-major, from the segment table (a few MB: summed on the host)
+        std::vector<int> h_seg((size_t)cells);
+        TRY(cudaMemcpyAsync(h_seg.data(), bt.d_seg, sizeof(int) * (size_t)cells, cudaMemcpyDeviceToHost, st),
+            ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        TRY(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        const size_t segs = (size_t)nl * (size_t)bands;
+        std::vector<int> h_start(segs + 1);
+        long long quads = 0;
+        for (size_t i = 0; i < segs && quads <= (long long)INT32_MAX / 4; i++) {
+            h_start[i] = (int)quads;
+            quads += ((long long)h_seg[i + (size_t)nl] - h_seg[i] + 3) >> 2;
+        }
+        if (quads <= (long long)INT32_MAX / 4) {
+            h_start[segs] = (int)quads;
+            const size_t slots = 4 * (size_t)quads + 8;  // a little slack behind the last quad
+            TRY(device_alloc(&bt.d_pk_start, sizeof(int) * (segs + 1)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+            TRY(device_alloc(&bt.d_pk_val, tsz * slots), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+            TRY(device_alloc(&bt.d_pk_col, sizeof(unsigned short) * slots), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+
+            TRY(cudaMemcpyAsync(bt.d_pk_start, h_start.data(), sizeof(int) * (segs + 1), cudaMemcpyHostToDevice, st),
+                ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+            TRY(cudaMemsetAsync(bt.d_pk_val, 0, tsz * slots, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+            TRY(cudaMemsetAsync(bt.d_pk_col, 0xff, sizeof(unsigned short) * slots, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+            if (tsz == 8)
+                band_pack_kernel<double><<<(unsigned)nl, 256, 0, st>>>(nl, (int)width, d_a, d_e, bt.d_seg, bt.d_pk_start,
+                                                                      ctx->d_col, static_cast<const double *>(ctx->d_val),
+                                                                      bt.d_pk_col, static_cast<double *>(bt.d_pk_val));
+            else
+                band_pack_kernel<float><<<(unsigned)nl, 256, 0, st>>>(nl, (int)width, d_a, d_e, bt.d_seg, bt.d_pk_start,
+                                                                     ctx->d_col, static_cast<const float *>(ctx->d_val),
+                                                                     bt.d_pk_col, static_cast<float *>(bt.d_pk_val));
+            count_launch();
+            TRY(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+            TRY(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);  // h_start goes out of scope
+            bt.pk_quads = quads;
+        }
+    }
     if (option(kOptBandOverlap)) {
         TRY(cudaStreamCreateWithFlags(&bt.side, cudaStreamNonBlocking), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
         TRY(cudaEventCreateWithFlags(&bt.ev_fork, cudaEventDisableTiming), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
@@ -383,6 +594,8 @@ static alphasparse_status_t band_finish(DeviceCtx *ctx, std::vector<BandCand> &c
     cudaFree(d_a), cudaFree(d_e), cudaFree(d_flag);
     ctx->band = bt;
     ctx->device_bytes += (int64_t)(sizeof(int) * (size_t)nl * (size_t)(bands + 2) + tsz * (size_t)nl * (size_t)bands);
+    if (bt.pk_quads > 0)
+        ctx->device_bytes += (int64_t)((tsz + 2) * 4 * (size_t)bt.pk_quads + sizeof(int) * (size_t)nl * (size_t)bands);
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
@@ -443,8 +656,36 @@ static void launch_band_as(K kernel, int threads, std::atomic<size_t> &granted, 
     count_launch();
 }
 
+template <typename K, typename T>
+static void launch_band_packed_as(K kernel, std::atomic<size_t> &granted, DeviceCtx *ctx, const T *x, cudaStream_t st) {
+    const BandTables &b = ctx->band;
+    const size_t smem = sizeof(T) * (size_t)b.width;
+    if (smem > 48 * 1024 && granted.load() < smem) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) == cudaSuccess)
+            granted.store(200 * 1024);
+    }
+    const dim3 grid((unsigned)b.bands, (unsigned)b.splits);
+    kernel<<<grid, kBandThreads, smem, st>>>((int)ctx->cols, b.width, b.bands, b.rows, b.chunk, b.d_pk_start, b.d_pk_col,
+                                             static_cast<const T *>(b.d_pk_val), x, static_cast<T *>(b.d_partial),
+                                             ctx->d_status);
+    count_launch();
+}
+
+template <typename T>
+static void launch_band_packed(DeviceCtx *ctx, const T *x, cudaStream_t st) {
+    static std::atomic<size_t> granted[2] = {};
+    if (option(kOptBandVariant) == 1)
+        launch_band_packed_as(spmv_band_packed_kernel<T, 8, 2, 2, kBandThreads>, granted[1], ctx, x, st);
+    else
+        launch_band_packed_as(spmv_band_packed_kernel<T, 8, 2, 1, kBandThreads>, granted[0], ctx, x, st);
+}
+
 template <typename T>
 void launch_band(DeviceCtx *ctx, const T *x, cudaStream_t st) {
+    if (ctx->band.pk_quads > 0) {
+        launch_band_packed<T>(ctx, x, st);
+        return;
+    }
     static std::atomic<size_t> granted[2] = {};
     if (option(kOptBandVariant) == 1)
         launch_band_as(spmv_band_quad_kernel<T, 4, 2, 1, kBandThreads>, kBandThreads, granted[1], ctx, x, st);

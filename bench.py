@@ -733,7 +733,7 @@ def main():
     algorithm = ["auto", "vector", "merge", "rowtile"][info.algorithm]
     kernel = {"vector": f"spmv_vector_kernel lanes={info.lanes_per_row}", "rowtile": "spmv_rowtile_kernel",
               "merge": ("row bins: spmv_short_kernel + spmv_rowlist_kernel x3" if info.binned else "spmv_merge_kernel") +
-                       (" + spmv_band_quad_kernel" if info.band_rows else "")}[algorithm] \
+                       (" + spmv_band_packed_kernel + spmv_band_reduce_kernel" if info.band_rows else "")}[algorithm] \
         if op == "mv" else "spmm_row_kernel"
     if rank == 0:
         traffic, traffic_src = ncu_traffic(name, kernel, reduced, world)

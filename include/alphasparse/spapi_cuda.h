@@ -44,8 +44,11 @@ alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg);
  *   band_min_share_pct (10) ... and so are long rows holding less than this share of the elements
  *   band_splits (0)         thread blocks per band, 0 = about eight waves of blocks
  *   band_overlap (0)        1: the column-band kernel runs on a second stream beside the other kernels
- *   band_variant (0)        shape of the column-band kernel: 0 = 8 lanes x 1 quad x 2 segments per lane group,
- *                           1 = 4 lanes x 2 quads x 1 segment
+ *   band_packed (1)         the band kernel streams a packed band-major copy of the long rows (columns relative to
+ *                           the band in 16 bits, segments padded to quads): (sizeof(T) + 2) bytes of device
+ *                           memory per long-row element; 0 = read the CSR arrays
+ *   band_variant (0)        shape of the column-band kernel (lanes x quads in flight x segments per lane group):
+ *                           packed copy 0 = 8 x 2 x 1, 1 = 8 x 2 x 2; CSR arrays 0 = 8 x 1 x 2, 1 = 4 x 2 x 1
  *   bin_overlap (1)         the kernels of the mid bins run on streams of their own, side by side
  *   bin_enable (1)          skewed matrices are multiplied bin by bin: thread per row up to bin_short (16)
  *                           elements, a lane group (4 / 16 / 32 lanes for rows up to bin_mid0 (32) / bin_mid1 (256) /

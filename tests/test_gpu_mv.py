@@ -522,7 +522,7 @@ class _Options:
 
 @pytest.mark.parametrize("kind", ["s", "d"])
 @pytest.mark.parametrize("overlap", [0, 1])
-@pytest.mark.parametrize("mode", ["binned", "binned_unsorted", "tiles", "tiles_unsorted"])
+@pytest.mark.parametrize("mode", ["binned", "binned_unpacked", "binned_unsorted", "tiles", "tiles_unsorted"])
 def test_row_bins_and_the_column_band_path(kind, overlap, mode):
     """Row binning of the analysis on a skewed matrix, with limits small enough for a small matrix to fill every bin.
 
@@ -531,6 +531,8 @@ def test_row_bins_and_the_column_band_path(kind, overlap, mode):
     memory; several splits per band, a ragged last band, long rows first / last / adjacent).
     binned_unsorted: one long row has two columns swapped; it cannot be cut into bands, so the handle must fall back
     to merge tiles, where the other four long rows still give their inner tiles to the band kernel.
+    binned_unpacked: the band kernel reads the long rows from the CSR arrays instead of from its packed band-major
+    copy (16-bit columns relative to the band, segments padded to quads).
     tiles / tiles_unsorted: the same with binning switched off.
     All scalar combinations, host and device vectors, bit-identical repeats, and a run of the delivering merge kernel
     (every tile) in between."""
@@ -550,7 +552,7 @@ def test_row_bins_and_the_column_band_path(kind, overlap, mode):
         m.val[a], m.val[a + 1] = m.val[a + 1], m.val[a]
     binned = mode.startswith("binned")
     with _Options(band_bytes=4096, band_min_seg=30, band_min_rows=1, band_min_share_pct=0, band_splits=3,
-                  band_overlap=overlap, bin_enable=int(binned), bin_short=2):
+                  band_overlap=overlap, bin_enable=int(binned), bin_short=2, band_packed=int(mode != "binned_unpacked")):
         spblas.set_algorithm(capi.ALG_MERGE)
         try:
             A = make_handle(kind, m)
