@@ -41,6 +41,7 @@ enum Option {
     kOptBinOverlap,       // 1: the kernels of the bins run on streams of their own, side by side
     kOptBinMidMax,        // longest row the lane-group kernels may be given; longer non-band rows: merge tiles instead
     kOptBinPushMaxPeers,  // exchange calls to more GPUs than this run over merge tiles instead of bins
+    kOptBinSort,          // 1: the lists of the two longer mid bins are ordered longest row first
     kOptSpmmColBlocks,    // column blocks of the row-major dense-block product (0 or 1: one pass)
     kOptCount
 };

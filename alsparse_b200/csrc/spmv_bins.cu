@@ -220,6 +220,14 @@ alphasparse_status_t bins_build(DeviceCtx *ctx, const int *h_ptr, int64_t long_m
                 break;
             }
     }
+    if (option(kOptBinSort)) {
+        // A block of the list kernels is busy until its longest row is done: longest rows first, so that the rows
+        // of one block are of about one length and the blocks that start last are the short ones.
+        for (int k = 1; k < kMidBins; k++)
+            std::stable_sort(lists[k].begin(), lists[k].end(), [h_ptr](int a, int c) {
+                return h_ptr[a + 1] - h_ptr[a] > h_ptr[c + 1] - h_ptr[c];
+            });
+    }
     size_t total = 0;
     for (int k = 0; k < kMidBins; k++) {
         b.offset[k] = (int64_t)total;

@@ -55,6 +55,8 @@ alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg);
  *                           longer) per row above, the column-band kernel for long rows; merge
  *                           tiles remain for matrices with rows above bin_mid_max (16384) that are not long
  *                           enough for the band kernel, with too few long rows, or with unsorted long rows
+ *   bin_sort (1)            the two lists of rows above bin_mid0 elements are ordered longest row first, so that the
+ *                           rows of one thread block are of about one length; 0 = row order
  *   bin_push_max_peers (3)  exchange calls (alphasparse_?_mv_exchange) that deliver to more GPUs than this run over
  *                           merge tiles, whose chunk-wise delivery spreads the NVLink traffic, instead of bins
  *   spmm_col_blocks (0)     row-major dense-block product in this many column blocks (X slab by slab, Y
