@@ -420,6 +420,228 @@ alphasparse_status_t transpose_csr_device(const DeviceCtx *c, int **out_ptr, int
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
+// ---- matrices derived from the device copy of A for structured descriptors -----------------------------
+//
+// What a SYMMETRIC / TRIANGULAR / DIAGONAL descriptor makes of the stored matrix (the reference's symv / trmv /
+// diagmv and symm / trmm / diagmm kernels, src/plain/kernel/level2/mv/{symv,trmv,diagmv},
+// src/plain/kernel/level3/mm/{symm,trmm,diagmm}) is an ordinary matrix: the kept triangle, its mirror image for
+// SYMMETRIC, its transpose for TRIANGULAR with op = TRANSPOSE, an explicit unit diagonal, or only the diagonal.
+// Every stored element emits 0, 1 or 2 (row, column) keys, an exclusive scan places them, the stable radix sort
+// orders them by (row, column) -- equal pairs keep storage order -- and the values are gathered at the end.
+// Payload of a key: the position of the stored element, or kUnitPayload for an explicit 1 on the diagonal.
+constexpr unsigned kUnitPayload = 0xffffffffu;
+
+struct DeriveRule {
+    int type;       // ALPHA_SPARSE_MATRIX_TYPE_SYMMETRIC / TRIANGULAR / DIAGONAL
+    int upper;      // kept triangle
+    int unit;       // unit diagonal: stored diagonal entries are ignored
+    int flip;       // TRIANGULAR under op = TRANSPOSE: (i, j) becomes (j, i)
+    int diag_rule;  // DIAGONAL, rows storing their diagonal more than once: 0 first entry, 1 all, 2 last
+};
+
+__device__ __forceinline__ int derive_row_of(const int *__restrict__ row_ptr, int rows, int k) {
+    int lo = 0, hi = rows;  // last row whose first element is <= k (empty rows share an offset: take the last)
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (row_ptr[mid] <= k) lo = mid;
+        else hi = mid;
+    }
+    return lo;
+}
+
+// DIAGONAL with the first / last rule: the smallest / largest position of a stored diagonal entry per row.
+__global__ void derive_diag_pick_kernel(long long nnz, int rows, const int *__restrict__ row_ptr,
+                                        const int *__restrict__ col, int last, int *__restrict__ pick) {
+    const long long k = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= nnz) return;
+    const int i = derive_row_of(row_ptr, rows, (int)k);
+    if (col[k] != i) return;
+    if (last) atomicMax(pick + i, (int)k);
+    else atomicMin(pick + i, (int)k);
+}
+
+__device__ __forceinline__ unsigned derive_emits(const DeriveRule &r, int i, int j, int k, const int *__restrict__ pick) {
+    if (r.type == ALPHA_SPARSE_MATRIX_TYPE_DIAGONAL) {
+        if (r.unit || j != i) return 0;
+        return r.diag_rule == 1 || pick[i] == k ? 1u : 0u;
+    }
+    const bool off = r.upper ? j > i : j < i;
+    if (off) return r.type == ALPHA_SPARSE_MATRIX_TYPE_SYMMETRIC ? 2u : 1u;
+    return j == i && !r.unit ? 1u : 0u;
+}
+
+__global__ void derive_count_kernel(long long nnz, int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
+                                    DeriveRule rule, const int *__restrict__ pick, unsigned *__restrict__ count) {
+    const long long k = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= nnz) return;
+    const int i = derive_row_of(row_ptr, rows, (int)k);
+    count[k] = derive_emits(rule, i, col[k], (int)k, pick);
+}
+
+// `offset` holds the exclusive scan of the counts; the explicit unit diagonal takes the first `rows` places.
+__global__ void derive_emit_kernel(long long nnz, int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
+                                   DeriveRule rule, const int *__restrict__ pick, const unsigned *__restrict__ offset,
+                                   unsigned long long *__restrict__ keys, unsigned *__restrict__ pos) {
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned first = rule.unit ? (unsigned)rows : 0u;
+    if (rule.unit && t < rows) {
+        keys[t] = ((unsigned long long)(unsigned)t << 32) | (unsigned)t;
+        pos[t] = kUnitPayload;
+    }
+    if (t >= nnz) return;
+    const int k = (int)t, i = derive_row_of(row_ptr, rows, k), j = col[k];
+    const unsigned n = derive_emits(rule, i, j, k, pick);
+    if (n == 0) return;
+    const unsigned o = first + offset[k];
+    const bool flip = rule.flip && j != i;
+    keys[o] = flip ? ((unsigned long long)(unsigned)j << 32) | (unsigned)i : ((unsigned long long)(unsigned)i << 32) | (unsigned)j;
+    pos[o] = (unsigned)k;
+    if (n == 2) {
+        keys[o + 1] = ((unsigned long long)(unsigned)j << 32) | (unsigned)i;
+        pos[o + 1] = (unsigned)k;
+    }
+}
+
+template <typename T>
+__global__ void derive_fill_kernel(long long m, int rows, const unsigned long long *__restrict__ keys,
+                                   const unsigned *__restrict__ pos, const T *__restrict__ val, int *__restrict__ ptr,
+                                   int *__restrict__ col_out, T *__restrict__ val_out) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i <= rows) {  // first sorted key whose row is >= i
+        long long lo = 0, hi = m;
+        while (lo < hi) {
+            const long long mid = (lo + hi) >> 1;
+            if ((long long)(keys[mid] >> 32) < i) lo = mid + 1;
+            else hi = mid;
+        }
+        ptr[i] = (int)lo;
+    }
+    if (i < m) {
+        col_out[i] = (int)(unsigned)keys[i];
+        val_out[i] = pos[i] == kUnitPayload ? T(1) : val[pos[i]];
+    }
+}
+
+// Device arrays of the derived square matrix in the layout ctx_adopt expects, allocated here and handed to the
+// caller with the number of stored elements.
+template <typename T>
+alphasparse_status_t derive_csr_device(const DeviceCtx *c, int type, int upper, int unit, int flip, int diag_rule,
+                                       int **out_ptr, int **out_col, T **out_val, int64_t *out_nnz) {
+    cudaStream_t st = current_stream();
+    const int64_t nnz = c->nnz, rows = c->rows;
+    const DeriveRule rule{type, upper, unit, flip, diag_rule};
+    unsigned long long *d_keys[2] = {nullptr, nullptr};
+    unsigned *d_pos[2] = {nullptr, nullptr}, *d_hist = nullptr, *d_sums = nullptr, *d_count = nullptr;
+    int *d_pick = nullptr, *dptr = nullptr, *dcol = nullptr;
+    T *dval = nullptr;
+    auto release = [&](bool all) {
+        cudaFree(d_keys[0]), cudaFree(d_keys[1]), cudaFree(d_pos[0]), cudaFree(d_pos[1]), cudaFree(d_hist), cudaFree(d_sums);
+        cudaFree(d_count), cudaFree(d_pick);
+        if (all) cudaFree(dptr), cudaFree(dcol), cudaFree(dval);
+    };
+#define TRY(expr, code)                   \
+    do {                                  \
+        cudaError_t _e = (expr);          \
+        if (_e != cudaSuccess) {          \
+            record_cuda_error(_e, #expr); \
+            release(true);                \
+            return (code);                \
+        }                                 \
+    } while (0)
+    const unsigned eblocks = (unsigned)((std::max<int64_t>(nnz, 1) + 255) / 256);
+    const bool picks = type == ALPHA_SPARSE_MATRIX_TYPE_DIAGONAL && !unit && diag_rule != 1 && nnz > 0;
+    if (picks) {
+        TRY(device_alloc(&d_pick, sizeof(int) * (size_t)rows), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        // bytes 0x7f.. = a large positive int for the minimum, 0xff.. = -1 for the maximum
+        TRY(cudaMemsetAsync(d_pick, diag_rule == 2 ? 0xff : 0x7f, sizeof(int) * (size_t)rows, st),
+            ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        derive_diag_pick_kernel<<<eblocks, 256, 0, st>>>(nnz, (int)rows, c->d_row_ptr, c->d_col, diag_rule == 2, d_pick);
+        count_launch();
+    }
+    // how many keys every stored element emits, and where
+    unsigned long long emitted = 0;
+    if (nnz > 0) {
+        const int scan_blocks = (int)((nnz + kScanTile - 1) / kScanTile);
+        unsigned last_count = 0, last_offset = 0;
+        TRY(device_alloc(&d_count, sizeof(unsigned) * (size_t)nnz), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        TRY(device_alloc(&d_sums, sizeof(unsigned) * (size_t)(scan_blocks + 1)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        derive_count_kernel<<<eblocks, 256, 0, st>>>(nnz, (int)rows, c->d_row_ptr, c->d_col, rule, d_pick, d_count);
+        count_launch();
+        TRY(cudaMemcpyAsync(&last_count, d_count + nnz - 1, 4, cudaMemcpyDeviceToHost, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        alphasparse_status_t s = device_exclusive_scan(d_count, nnz, d_sums, st);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) {
+            release(true);
+            return s;
+        }
+        TRY(cudaMemcpyAsync(&last_offset, d_count + nnz - 1, 4, cudaMemcpyDeviceToHost, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        TRY(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        emitted = (unsigned long long)last_offset + last_count;  // at most 2 * nnz < 2^32: the 32-bit scan is exact
+        cudaFree(d_sums), d_sums = nullptr;
+    }
+    // 32-bit offsets, as for every handle; a symmetric matrix may double its stored elements
+    if (emitted + (unit ? (unsigned long long)rows : 0ull) > (unsigned long long)(INT32_MAX - 64)) {
+        release(true);
+        record_error("the matrix derived for this descriptor would hold more than 2^31 - 65 elements");
+        return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    }
+    const int64_t m = (int64_t)emitted + (unit ? rows : 0);
+    const size_t n = (size_t)m, padded = n + kTailPad;
+    TRY(device_alloc(&dptr, sizeof(int) * (size_t)(rows + 1 + 4)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&dcol, sizeof(int) * padded), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(device_alloc(&dval, sizeof(T) * padded), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    TRY(cudaMemsetAsync(dptr, 0, sizeof(int) * (size_t)(rows + 1 + 4), st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaMemsetAsync(dcol + n, 0, sizeof(int) * kTailPad, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    TRY(cudaMemsetAsync(dval + n, 0, sizeof(T) * kTailPad, st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    if (m > 0) {
+        const long long nblocks = (m + kSortTile - 1) / kSortTile;
+        const long long hist_n = 16 * nblocks;
+        const int scan_blocks = (int)((hist_n + kScanTile - 1) / kScanTile);
+        TRY(device_alloc(&d_keys[0], 8 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        TRY(device_alloc(&d_keys[1], 8 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        TRY(device_alloc(&d_pos[0], 4 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        TRY(device_alloc(&d_pos[1], 4 * n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        TRY(device_alloc(&d_hist, sizeof(unsigned) * (size_t)hist_n), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        TRY(device_alloc(&d_sums, sizeof(unsigned) * (size_t)(scan_blocks + 1)), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        const long long work = std::max<long long>(nnz, unit ? rows : 0);
+        derive_emit_kernel<<<(unsigned)((work + 255) / 256), 256, 0, st>>>(nnz, (int)rows, c->d_row_ptr, c->d_col, rule,
+                                                                          d_pick, d_count, d_keys[0], d_pos[0]);
+        count_launch();
+        int cur = 0;
+        const int bits = bits_for(rows);  // square: rows == cols
+        for (int part = 0; part < 2; part++) {
+            const int first = part == 0 ? 0 : 32;
+            for (int shift = first; shift < first + bits; shift += 4) {
+                radix_hist_kernel<<<(unsigned)nblocks, kSortThreads, 0, st>>>(m, d_keys[cur], shift, d_hist);
+                count_launch();
+                alphasparse_status_t s = device_exclusive_scan(d_hist, hist_n, d_sums, st);
+                if (s != ALPHA_SPARSE_STATUS_SUCCESS) {
+                    release(true);
+                    return s;
+                }
+                radix_scatter_kernel<<<(unsigned)nblocks, kSortThreads, 0, st>>>(m, d_keys[cur], d_pos[cur], shift, d_hist,
+                                                                                d_keys[cur ^ 1], d_pos[cur ^ 1]);
+                count_launch();
+                cur ^= 1;
+            }
+        }
+        const long long fill = std::max<long long>(m, rows + 1);
+        derive_fill_kernel<T><<<(unsigned)((fill + 255) / 256), 256, 0, st>>>(
+            m, (int)rows, d_keys[cur], d_pos[cur], static_cast<const T *>(c->d_val), dptr, dcol, dval);
+        count_launch();
+        TRY(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    }
+    TRY(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+#undef TRY
+    release(false);
+    *out_ptr = dptr, *out_col = dcol, *out_val = dval, *out_nnz = m;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
+template alphasparse_status_t derive_csr_device<float>(const DeviceCtx *, int, int, int, int, int, int **, int **, float **,
+                                                       int64_t *);
+template alphasparse_status_t derive_csr_device<double>(const DeviceCtx *, int, int, int, int, int, int **, int **, double **,
+                                                        int64_t *);
+
 template alphasparse_status_t transpose_csr_device<float>(const DeviceCtx *, int **, int **, float **);
 template alphasparse_status_t transpose_csr_device<double>(const DeviceCtx *, int **, int **, double **);
 

@@ -104,6 +104,8 @@ void record_cuda_error(cudaError_t e, const char *what) {
     (void)cudaGetLastError();  // clear the sticky-free error so later calls start clean
 }
 
+void record_error(const char *what) { snprintf(t_error, sizeof(t_error), "%s", what); }
+
 // ---- device context ----------------------------------------------------------------------------
 
 DeviceCtx *ctx_of(const alphasparse_matrix_t A) {
@@ -445,6 +447,7 @@ static alphasparse_status_t create_coo(alphasparse_matrix_t *A, alphasparse_inde
         free(h), free(m), free(ri), free(ci), free(v);
         return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
     }
+#pragma omp parallel for schedule(static) if (nnz > (1 << 16))
     for (int64_t i = 0; i < nnz; i++) {
         ri[i] = row_indx[i] - shift;
         ci[i] = col_indx[i] - shift;
@@ -573,8 +576,8 @@ static alphasparse_status_t ensure_transposed(DeviceCtx *c, const typename CsrOf
 // alphasparse_?_mv, src/core/op/level2/alphasparse_x_mv.c:1693-1716; kernels under
 // src/plain/kernel/level2/mv/{symv,trmv,diagmv}) is an ordinary SpMV with a matrix DERIVED from the
 // stored one: the kept triangle (plus an explicit unit diagonal), its mirror image for SYMMETRIC, its
-// transpose for op = TRANSPOSE, or just the diagonal.  Each variant is built once from the host copy,
-// uploaded as its own device CSR, analysed like any matrix and kept with the handle.
+// transpose for op = TRANSPOSE, or just the diagonal.  Each variant is built once on the device from the device
+// copy of the stored matrix (derive_csr_device), analysed like any matrix and kept with the handle.
 //
 // The same matrices serve mm (symm / trmm / diagmm, src/core/op/level3/alphasparse_x_mm.c:2345-2368;
 // kernels under src/plain/kernel/level3/mm/{symm,trmm,diagmm}).  Only rows that store their diagonal
@@ -598,45 +601,16 @@ static alphasparse_status_t ensure_derived(DeviceCtx *c, const typename CsrOf<T>
         *out = slot;
         return ALPHA_SPARSE_STATUS_SUCCESS;
     }
+    (void)m;
     const int64_t n = c->rows;
-    const int *ptr = m->rows_start, *col = m->col_indx;
-    const T *val = m->values;
-    std::vector<int> ri, ci;
-    std::vector<T> v;
-    try {
-        for (int64_t i = 0; i < n; i++) {
-            if (unit) ri.push_back((int)i), ci.push_back((int)i), v.push_back(T(1));
-            bool diag_seen = false;
-            for (int k = ptr[i]; k < ptr[i + 1]; k++) {
-                const int j = col[k];
-                if (type == ALPHA_SPARSE_MATRIX_TYPE_DIAGONAL) {
-                    if (!unit && j == i) {
-                        if (diag_seen && diag_rule == kDiagLast) v.back() = val[k];
-                        else if (!diag_seen || diag_rule == kDiagAll) ri.push_back((int)i), ci.push_back(j), v.push_back(val[k]);
-                        diag_seen = true;
-                    }
-                    continue;
-                }
-                const bool off = upper ? j > i : j < i;
-                if (off) {
-                    const bool flip = type == ALPHA_SPARSE_MATRIX_TYPE_TRIANGULAR && trans;
-                    ri.push_back(flip ? j : (int)i), ci.push_back(flip ? (int)i : j), v.push_back(val[k]);
-                    if (type == ALPHA_SPARSE_MATRIX_TYPE_SYMMETRIC) ri.push_back(j), ci.push_back((int)i), v.push_back(val[k]);
-                } else if (j == i && !unit) {
-                    ri.push_back((int)i), ci.push_back(j), v.push_back(val[k]);
-                }
-            }
-        }
-    } catch (...) {
-        return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
-    }
+    const bool flip = type == ALPHA_SPARSE_MATRIX_TYPE_TRIANGULAR && trans;
     int *dptr = nullptr, *dcol = nullptr;
     T *dval = nullptr;
-    alphasparse_status_t s = triples_to_csr<T>(n, (int64_t)v.size(), ri.data(), ci.data(), v.data(), &dptr, &dcol, &dval);
+    int64_t dnnz = 0;
+    alphasparse_status_t s = derive_csr_device<T>(c, type, upper, unit, flip, diag_rule, &dptr, &dcol, &dval, &dnnz);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     DeviceCtx *d = nullptr;
-    s = ctx_create(c->datatype, n, n, dptr, dcol, dval, &d);
-    free(dptr), free(dcol), free(dval);
+    s = ctx_adopt(c->datatype, n, n, dnnz, dptr, dcol, dval, &d);
     if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     c->device_bytes += d->device_bytes;
     slot = d;

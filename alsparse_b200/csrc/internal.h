@@ -21,6 +21,7 @@ cudaStream_t current_stream();
 alphasparse_cuda_alg_t forced_algorithm();
 void count_launch(int n = 1);
 void record_cuda_error(cudaError_t e, const char *what);
+void record_error(const char *what);  // text for alphasparse_cuda_last_error without a CUDA error behind it
 
 // Tuning values of the analysis (alphasparse_cuda_set_option / ALPHASPARSE_CUDA_OPTIONS); each has a
 // default that measurements on B200 chose, tests shrink them to reach every branch on small matrices.
@@ -281,6 +282,10 @@ alphasparse_status_t launch_spmm_col(DeviceCtx *ctx, T alpha, const T *X, int co
 // A^T of a handle's device CSR, built on the device (coo2csr.cu); arrays in ctx_adopt's layout.
 template <typename T>
 alphasparse_status_t transpose_csr_device(const DeviceCtx *c, int **out_ptr, int **out_col, T **out_val);
+// Device CSR (ctx_adopt layout) of what a SYMMETRIC / TRIANGULAR / DIAGONAL descriptor makes of the square matrix in `c`.
+template <typename T>
+alphasparse_status_t derive_csr_device(const DeviceCtx *c, int type, int upper, int unit, int flip, int diag_rule,
+                                       int **out_ptr, int **out_col, T **out_val, int64_t *out_nnz);
 
 // COO -> CSR on the device (coo2csr.cu): host arrays in, host 3-array CSR out, same output as the host
 // path in core.cu (ordered by row then column, equal pairs in input order).

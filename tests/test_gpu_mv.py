@@ -337,6 +337,55 @@ def test_structured_descriptors():
         spblas.destroy(A)
 
 
+def test_structured_descriptors_on_unsorted_rows_with_repeated_diagonals():
+    """The derived matrices are built on the device from the device copy (key emission, scan, radix sort over more
+    than one block of keys).  Rows in shuffled column order, diagonals stored up to three times (diagmv takes the
+    FIRST stored one, the row-major diagmm ALL, the column-major diagmm the LAST), pairs stored twice, empty rows."""
+    n = 60000
+    base = synth.poisson("d", 91, n, n, 20.0)
+    assert base.nnz > 1 << 20
+    rng = np.random.default_rng(91)
+    rows_of = np.repeat(np.arange(n, dtype=np.int64), np.diff(base.ptr))
+    extra_diag = np.concatenate([rng.integers(0, n, 9000), rng.integers(0, n, 4000)])  # some rows get 2 or 3
+    dup = rng.integers(0, base.nnz, 3000)
+    ri = np.concatenate([rows_of, extra_diag, rows_of[dup]])
+    ci = np.concatenate([base.col.astype(np.int64), extra_diag, base.col[dup].astype(np.int64)])
+    v = np.concatenate([base.val, rng.uniform(-1, 1, len(extra_diag)), rng.uniform(-1, 1, len(dup))])
+    keep = ri % 97 != 5  # empty rows
+    ri, ci, v = ri[keep], ci[keep], v[keep]
+    order = np.lexsort((rng.random(len(ri)), ri))  # rows ascending, random order inside a row
+    ri, ci, v = ri[order], ci[order].astype(np.int32), v[order]
+    ptr = np.concatenate([[0], np.cumsum(np.bincount(ri, minlength=n))]).astype(np.int32)
+    m = synth.Csr(n, n, 0, ptr, ci, v)
+    A = make_handle("d", m)
+    x, y0 = synth.vector("d", 91, 1, n), synth.vector("d", 91, 2, n)
+    rid = np.repeat(np.arange(n), np.diff(ptr))
+    sc = np.abs(0.5 * y0) + 1.25 * (np.bincount(rid, weights=np.abs(v * x[ci]), minlength=n) +
+                                    np.bincount(ci, weights=np.abs(v * x[rid]), minlength=n) + np.abs(x))
+    for t, transes in ((capi.SYMMETRIC, (0,)), (capi.TRIANGULAR, (0, 1)), (capi.DIAGONAL, (0,))):
+        for upper in (0, 1):
+            for unit in (0, 1):
+                for tr in transes:
+                    y_ref = oracle.structured_mv("d", t, upper, unit, tr, m.rows_start, m.rows_end, m.col, m.val, 1.25, x,
+                                                 0.5, y0.copy())
+                    dx, dy = torch.from_numpy(x).cuda(), torch.from_numpy(y0).cuda()
+                    assert spblas.mv("d", tr, 1.25, A, spblas.descr(t, upper, unit), dx, 0.5, dy) == capi.SUCCESS, spblas.last_error()
+                    assert_rows_close("d", dy.cpu().numpy(), y_ref, sc, f"type {t} {upper}{unit}{tr}")
+    # the two diagmm rules for repeated diagonals
+    columns = 4
+    X, Y0 = synth.vector("d", 92, 1, n * columns), synth.vector("d", 92, 2, n * columns)
+    for lay, layout in (("row", capi.ROW_MAJOR), ("col", capi.COLUMN_MAJOR)):
+        ld = columns if lay == "row" else n
+        Yref = oracle.structured_mm("d", capi.DIAGONAL, 0, 0, 0, lay, m.rows_start, m.rows_end, m.col, m.val, 1.25, X, columns,
+                                    ld, 0.5, Y0.copy(), ld)
+        dX, dY = torch.from_numpy(X).cuda(), torch.from_numpy(Y0).cuda()
+        assert spblas.mm("d", 0, 1.25, A, spblas.descr(capi.DIAGONAL, 0, 0), layout, dX, columns, ld, 0.5, dY, ld) == capi.SUCCESS
+        d_abs = np.bincount(rid[ci == rid], weights=np.abs(v[ci == rid]), minlength=n)
+        scm = np.abs(0.5 * Y0) + 1.25 * np.abs(X) * (np.repeat(d_abs, columns) if lay == "row" else np.tile(d_abs, columns))
+        assert_rows_close("d", dY.cpu().numpy(), Yref, scm, f"diagmm {lay}")
+    spblas.destroy(A)
+
+
 @pytest.mark.parametrize("kind", ["s", "d"])
 def test_large_coo_is_sorted_on_the_device(kind):
     """More than 2^20 COO entries take the GPU radix-sort path of alphasparse_convert_csr; the CSR must be
