@@ -412,6 +412,19 @@ def measure_iterated(args, rank, world, stream, iterations=50):
                                   "collective": collectives[mode], "parity_ok": ok,
                                   "worst_row_error_over_tolerance": all_max(worst), "exchange_status": status,
                                   "finite_after_all_iterations": finite}
+        # the product alone on the same handle (x fixed, nothing exchanged): what the three modes add to it
+        xa.copy_(x0_d)
+        for _ in range(max(args.warmup, 3)):
+            assert spblas.mv(kind, 0, 1.0, A, descr, xa, 0.0, y_d) == capi.SUCCESS
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iterations):
+            spblas.mv(kind, 0, 1.0, A, descr, xa, 0.0, y_d)
+        e1.record(stream)
+        e1.synchronize()
+        barrier()
+        out["product_without_exchange_ms"] = all_max(e0.elapsed_time(e1) / iterations)
     out["parity"]["ok"] = all(v["parity_ok"] and v["exchange_status"] == 0 for v in out["modes"].values())
     out["fused_vs_nccl"] = out["modes"]["nccl"]["ms_per_iteration"] / out["modes"]["fused"]["ms_per_iteration"]
     spblas.destroy(A)
