@@ -83,6 +83,7 @@ static void options_init() {
         // ALPHASPARSE_CUDA_OPTIONS="name=value,name=value": initial values
         const char *env = getenv("ALPHASPARSE_CUDA_OPTIONS");
         while (env && *env) {
+            while (*env == ' ') env++;  // blanks after a comma
             const char *eq = strchr(env, '='), *end = strchr(env, ',');
             if (!end) end = env + strlen(env);
             if (eq && eq < end) {

@@ -1,5 +1,6 @@
 """Host-side pieces of the library that need no GPU: the row partition, COO handles, generators."""
 import ctypes as C
+import os
 
 import numpy as np
 import pytest
@@ -119,3 +120,30 @@ def test_matrix_file_reader(tmp_path):
                 assert np.array_equal(v.view(np.uint8), rv.view(np.uint8))
     with pytest.raises(OSError):
         spblas.read_coo("s", str(tmp_path / "missing.mtx"))
+
+
+def test_tuning_options_table_matches_the_header():
+    """Every option the public header documents as `name (default)` exists with that default, set / restore work
+    without a GPU, unknown names are refused, and ALPHASPARSE_CUDA_OPTIONS seeds the values of a fresh process."""
+    import re
+    import subprocess
+    import sys
+    from helpers import ROOT
+    text = open(os.path.join(ROOT, "include", "alphasparse", "spapi_cuda.h")).read()
+    block = text[text.index("ALPHASPARSE_CUDA_OPTIONS="):text.index("alphasparse_cuda_set_option(const char")]
+    documented = {n: int(d) for n, d in re.findall(r"\*\s+([a-z][a-z0-9_]+) \((\d+)\)", block)}
+    documented.update({n: int(d) for n, d in re.findall(r"\b(bin_[a-z0-9_]+) \((\d+)\)", block)})  # named inside a sentence
+    assert len(documented) >= 15, documented
+    for name, default in documented.items():
+        assert spblas.get_option(name) == default, name
+        assert spblas.set_option(name, default + 3) == capi.SUCCESS
+        assert spblas.get_option(name) == default + 3
+        assert spblas.set_option(name, -1) == capi.SUCCESS
+        assert spblas.get_option(name) == default, name
+    assert spblas.set_option("no_such_option", 1) == capi.INVALID_VALUE
+    code = ("from alsparse_b200 import spblas; "
+            "print(spblas.get_option('band_min_seg'), spblas.get_option('bin_short'), spblas.get_option('band_bytes'))")
+    env = dict(os.environ, ALPHASPARSE_CUDA_OPTIONS="band_min_seg=7, bin_short=9,bogus=1")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd=ROOT, timeout=120)
+    assert out.returncode == 0, out.stderr
+    assert out.stdout.split() == ["7", "9", str(documented["band_bytes"])]
