@@ -66,7 +66,7 @@ struct OptionDef {
 };
 static const OptionDef kOptionDefs[kOptCount] = {
     {"band_enable", 1},       {"band_bytes", 64 * 1024}, {"band_min_seg", 12},      {"band_min_rows", 128},
-    {"band_min_share_pct", 10}, {"band_splits", 0},      {"band_overlap", 0},      {"band_packed", 1},      {"band_variant", 0},     {"bin_enable", 1},        {"bin_short", 16},         {"bin_mid0", 32},          {"bin_mid1", 256},        {"bin_overlap", 1},      {"bin_mid_max", 16384},   {"bin_push_max_peers", 4}, {"bin_sort", 1}, {"spmm_col_blocks", 0},
+    {"band_min_share_pct", 10}, {"band_splits", 0},      {"band_overlap", 0},      {"band_packed", 1},      {"band_variant", 0},     {"bin_enable", 1},        {"bin_short", 16},         {"bin_mid0", 32},          {"bin_mid1", 256},        {"bin_overlap", 1},      {"bin_mid_max", 16384},   {"bin_push_max_peers", 4}, {"bin_sort", 1}, {"pipe_max_windows", 12}, {"pipe_min_piece_kb", 4096}, {"spmm_col_blocks", 0},
 };
 static std::atomic<int64_t> g_options[kOptCount];
 static std::once_flag g_options_once;
@@ -754,17 +754,17 @@ static alphasparse_status_t csr_shadow_of(const alphasparse_matrix_t A, alphaspa
 // overlap.  Three streams: x and the y0 pieces go in on one, the windows run on the library stream as their inputs
 // land, every finished piece of y leaves on the third while the next window is being multiplied (PCIe is full
 // duplex).  The call still returns only when all of y is back in host memory.
-// The number of windows follows the size of y: pieces of at least kPipelineMinPiece bytes, at most kPipelineChunks of
-// them (on B200 4 -> 8 windows took a 64 MB y from 3.14 to 2.90 ms end to end, 16 changed nothing; an 8 MB y --
+// The number of windows follows the size of y: pieces of at least pipe_min_piece_kb, at most pipe_max_windows of
+// them (on B200 4 / 8 / 12 / 16 windows took a 64 MB y to 3.18 / 2.93 / 2.86 / 2.88 ms end to end; an 8 MB y --
 // one GPU's share of the same vector on eight GPUs -- is quicker in two pieces than in eight, where the seventeen
-// events and copies of 1 MB cost more than they hide).
+// events and copies of 1 MB cost more than they hide).  The dense-block product keeps kPipelineChunks windows.
 constexpr int64_t kPipelineMinRows = 1 << 20;
 constexpr int kPipelineChunks = 8;
-constexpr size_t kPipelineMinPiece = (size_t)4 << 20;
 
 static int pipeline_windows(size_t y_bytes) {
-    const size_t n = y_bytes / kPipelineMinPiece;
-    return (int)std::max<size_t>(1, std::min<size_t>(n, kPipelineChunks));
+    const size_t piece = (size_t)std::max<int64_t>(64, option(kOptPipeMinPieceKb)) << 10;
+    const size_t most = (size_t)std::max<int64_t>(1, std::min<int64_t>(16, option(kOptPipeMaxWindows)));
+    return (int)std::max<size_t>(1, std::min<size_t>(y_bytes / piece, most));
 }
 
 // the two copy streams and the events of the host-operand pipelines, created on first use

@@ -43,6 +43,8 @@ enum Option {
     kOptBinMidMax,        // longest row the lane-group kernels may be given; longer non-band rows: merge tiles instead
     kOptBinPushMaxPeers,  // exchange calls to more GPUs than this run over merge tiles instead of bins
     kOptBinSort,          // 1: the lists of the two longer mid bins are ordered longest row first
+    kOptPipeMaxWindows,   // host-vector mv: most row windows the product is cut into (1..16)
+    kOptPipeMinPieceKb,   // ... and the smallest piece of y per window, in KB
     kOptSpmmColBlocks,    // column blocks of the row-major dense-block product (0 or 1: one pass)
     kOptCount
 };

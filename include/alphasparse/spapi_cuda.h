@@ -60,6 +60,8 @@ alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg);
  *   bin_push_max_peers (4)  exchange calls (alphasparse_?_mv_exchange) over more GPUs than this run over merge tiles,
  *                           whose chunk-wise delivery spreads the NVLink traffic, instead of bins (measured: bins
  *                           0.49 against 0.53 ms per iteration at 4 GPUs, 0.47 against 0.32 ms at 8)
+ *   pipe_max_windows (12)   mv with host vectors: the product runs in up to this many row windows (at most 16) that
+ *                           overlap the copies of y, each window covering at least pipe_min_piece_kb (4096) KB of y
  *   spmm_col_blocks (0)     row-major dense-block product in this many column blocks (X slab by slab, Y
  *                           accumulated over the passes); 0 or 1 = one pass, which measured faster on B200
  * Unknown names return ALPHA_SPARSE_STATUS_INVALID_VALUE. */
