@@ -223,10 +223,22 @@ alphasparse_status_t bins_build(DeviceCtx *ctx, const int *h_ptr, int64_t long_m
     if (option(kOptBinSort)) {
         // A block of the list kernels is busy until its longest row is done: longest rows first, so that the rows
         // of one block are of about one length and the blocks that start last are the short ones.
-        for (int k = 1; k < kMidBins; k++)
-            std::stable_sort(lists[k].begin(), lists[k].end(), [h_ptr](int a, int c) {
-                return h_ptr[a + 1] - h_ptr[a] > h_ptr[c + 1] - h_ptr[c];
-            });
+        // (a counting sort over the lengths, stable in the row number: linear in the list, whatever its size)
+        for (int k = 1; k < kMidBins; k++) {
+            std::vector<int> &l = lists[k];
+            if (l.size() < 2) continue;
+            int lo = INT32_MAX, hi = 0;
+            for (int r : l) {
+                const int n = h_ptr[r + 1] - h_ptr[r];
+                lo = std::min(lo, n), hi = std::max(hi, n);
+            }
+            std::vector<size_t> first((size_t)(hi - lo) + 2, 0);  // first[hi - n + 1]: rows of length n, longest first
+            for (int r : l) first[(size_t)(hi - (h_ptr[r + 1] - h_ptr[r])) + 1]++;
+            for (size_t i = 1; i < first.size(); i++) first[i] += first[i - 1];
+            std::vector<int> sorted(l.size());
+            for (int r : l) sorted[first[(size_t)(hi - (h_ptr[r + 1] - h_ptr[r]))]++] = r;
+            l.swap(sorted);
+        }
     }
     size_t total = 0;
     for (int k = 0; k < kMidBins; k++) {
