@@ -514,7 +514,14 @@ static alphasparse_status_t band_finish(DeviceCtx *ctx, std::vector<BandCand> &c
     }
 
     int64_t splits = option(kOptBandSplits);
-    if (splits <= 0) splits = (148 * 3 * 8 + bands - 1) / bands;  // about eight waves of blocks
+    if (splits <= 0) {
+        splits = (148 * 3 * 8 + bands - 1) / bands;  // about eight waves of blocks ...
+        // ... but a block should stream at least four times what it stages (a band of x), or the staging shows: a
+        // quarter or an eighth of the power-law matrix (one GPU's share of 4 or 8) ran 2-3 % faster with 2 and 1 blocks
+        // per band than with 4
+        const int64_t stream = covered * (int64_t)(tsz + 2), staged = 4 * (int64_t)bands * width * (int64_t)tsz;
+        splits = std::min<int64_t>(splits, std::max<int64_t>(1, (stream + staged - 1) / staged));
+    }
     splits = std::max<int64_t>(1, std::min<int64_t>(splits, std::max(1, nl / (kBandThreads / kBandLanes))));
     splits = std::min<int64_t>(splits, 65535);
     const int chunk = (int)((nl + splits - 1) / splits);
