@@ -45,6 +45,8 @@ enum Option {
     kOptBinSort,          // 1: the lists of the two longer mid bins are ordered longest row first
     kOptPipeMaxWindows,   // host-vector mv: most row windows the product is cut into (1..16)
     kOptPipeMinPieceKb,   // ... and the smallest piece of y per window, in KB
+    kOptSpmmSplitMin,     // row-major dense-block product: rows above this many elements are multiplied chunk by chunk (0: never)
+    kOptSpmmSplitChunk,   // ... in chunks of this many elements
     kOptSpmmColBlocks,    // column blocks of the row-major dense-block product (0 or 1: one pass)
     kOptCount
 };
@@ -161,6 +163,23 @@ struct SpmmBlocks {
 };
 void spmm_blocks_destroy(SpmmBlocks &b);
 
+// Long rows of the row-major dense-block product (spmm.cu).  One lane group per row is fine until a row holds a
+// hundred thousand elements and its group is still walking it long after every other row is done: rows above
+// `spmm_split_min` elements are left out of the row pass (their end in d_hi_short is their start), cut into chunks of
+// `spmm_split_chunk` elements that the same kernel multiplies as if they were rows, into partial sums, and a last
+// kernel adds each row's partial sums, in chunk order, onto Y.
+struct SpmmSplit {
+    int state = 0;  // 0: not looked at yet, 1: no long rows, 2: tables below are in use
+    int64_t nlong = 0, nchunks = 0;
+    int *d_hi_short = nullptr;                           // rows
+    int *d_chunk_lo = nullptr, *d_chunk_hi = nullptr;    // nchunks
+    int *d_long_row = nullptr, *d_long_first = nullptr;  // nlong, nlong + 1 (first chunk of each long row)
+    int *h_long_row = nullptr, *h_long_first = nullptr;  // host copies: which chunks a row window owns
+    void *d_part = nullptr;                              // partial sums, nchunks x columns
+    size_t part_bytes = 0;
+};
+void spmm_split_destroy(SpmmSplit &s);
+
 struct DeviceCtx {
     uint64_t magic = kCtxMagic;
     int device = 0;
@@ -192,6 +211,7 @@ struct DeviceCtx {
     RowBins bins;                      // row bins of a skewed matrix; active: products run bin by bin
     const int *h_row_ptr = nullptr;    // host copy of the offsets, valid only while the handle is being created
     SpmmBlocks spmm;                   // column blocks of the row-major dense-block product
+    SpmmSplit split;                   // its long rows, cut into chunks
     bool carry_stale = false;          // a run over ALL tiles wrote carries for tiles the schedule leaves out
     BandTables band;                   // long rows taken out of the merge tiles (spmv_band.cu); rows == 0: none
     unsigned *d_chunk_done = nullptr;  // per chunk of kPushChunkTiles tiles (exchange calls only)

@@ -216,6 +216,94 @@ static alphasparse_status_t spmm_blocks_ensure(DeviceCtx *ctx, int blocks, cudaS
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
+// ---- long rows ------------------------------------------------------------------------------------------
+
+void spmm_split_destroy(SpmmSplit &s) {
+    cudaFree(s.d_hi_short), cudaFree(s.d_chunk_lo), cudaFree(s.d_chunk_hi), cudaFree(s.d_long_row), cudaFree(s.d_long_first);
+    cudaFree(s.d_part);
+    free(s.h_long_row), free(s.h_long_first);
+    s = SpmmSplit{};
+}
+
+// Y[row, :] += the row's partial sums in chunk order.  One block per long row, threads over the dense columns.
+template <typename T>
+__global__ void spmm_long_reduce_kernel(const int *__restrict__ long_row, const int *__restrict__ long_first,
+                                        const T *__restrict__ part, int columns, T *__restrict__ Y, long long ldy) {
+    const int row = long_row[blockIdx.x], k0 = long_first[blockIdx.x], k1 = long_first[blockIdx.x + 1];
+    for (int c = threadIdx.x; c < columns; c += blockDim.x) {
+        T acc = T(0);
+        for (int k = k0; k < k1; k++) acc += part[(size_t)k * columns + c];
+        Y[(long long)row * ldy + c] += acc;
+    }
+}
+
+// Looks at the row lengths once (first row-major product of the handle) and builds the chunk tables when some row
+// is longer than spmm_split_min.
+static alphasparse_status_t spmm_split_ensure(DeviceCtx *ctx, cudaStream_t st) {
+    SpmmSplit &sp = ctx->split;
+    if (sp.state != 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+    const int64_t min_len = option(kOptSpmmSplitMin), chunk = std::max<int64_t>(64, option(kOptSpmmSplitChunk));
+    // (only where the rows are uneven: rows that are all long keep every lane group equally busy as they are)
+    if (min_len <= 0 || ctx->max_row_nnz <= min_len || ctx->rows == 0 || (double)ctx->max_row_nnz <= 8.0 * ctx->mean_row_nnz) {
+        sp.state = 1;
+        return ALPHA_SPARSE_STATUS_SUCCESS;
+    }
+    std::vector<int> ptr, hi, clo, chi, lrow, lfirst;
+    try {
+        ptr.resize((size_t)ctx->rows + 1);
+    } catch (...) {
+        return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+    ASB_CUDA_OR(cudaMemcpyAsync(ptr.data(), ctx->d_row_ptr, sizeof(int) * ptr.size(), cudaMemcpyDeviceToHost, st),
+                ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    ASB_CUDA_OR(cudaStreamSynchronize(st), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+    try {
+        hi.resize((size_t)ctx->rows);
+        for (int64_t r = 0; r < ctx->rows; r++) {
+            const int a = ptr[(size_t)r], e = ptr[(size_t)r + 1];
+            hi[(size_t)r] = e;
+            if ((int64_t)e - a <= min_len) continue;
+            hi[(size_t)r] = a;  // nothing of this row in the row pass
+            lrow.push_back((int)r);
+            lfirst.push_back((int)clo.size());
+            for (int64_t k = a; k < e; k += chunk) {
+                clo.push_back((int)k);
+                chi.push_back((int)std::min<int64_t>(e, k + chunk));
+            }
+        }
+        lfirst.push_back((int)clo.size());
+    } catch (...) {
+        return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+    SpmmSplit t;
+    t.nlong = (int64_t)lrow.size(), t.nchunks = (int64_t)clo.size();
+    t.h_long_row = static_cast<int *>(malloc(sizeof(int) * std::max<size_t>(1, lrow.size())));
+    t.h_long_first = static_cast<int *>(malloc(sizeof(int) * lfirst.size()));
+    cudaError_t e = (t.h_long_row && t.h_long_first) ? cudaSuccess : cudaErrorMemoryAllocation;
+    if (e == cudaSuccess) e = device_alloc(&t.d_hi_short, sizeof(int) * hi.size());
+    if (e == cudaSuccess) e = device_alloc(&t.d_chunk_lo, sizeof(int) * clo.size());
+    if (e == cudaSuccess) e = device_alloc(&t.d_chunk_hi, sizeof(int) * chi.size());
+    if (e == cudaSuccess) e = device_alloc(&t.d_long_row, sizeof(int) * lrow.size());
+    if (e == cudaSuccess) e = device_alloc(&t.d_long_first, sizeof(int) * lfirst.size());
+    if (e == cudaSuccess) e = cudaMemcpyAsync(t.d_hi_short, hi.data(), sizeof(int) * hi.size(), cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(t.d_chunk_lo, clo.data(), sizeof(int) * clo.size(), cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(t.d_chunk_hi, chi.data(), sizeof(int) * chi.size(), cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(t.d_long_row, lrow.data(), sizeof(int) * lrow.size(), cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(t.d_long_first, lfirst.data(), sizeof(int) * lfirst.size(), cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);  // the vectors go out of scope
+    if (e != cudaSuccess) {
+        record_cuda_error(e, "long rows of the dense-block product");
+        spmm_split_destroy(t);
+        return ALPHA_SPARSE_STATUS_ALLOC_FAILED;
+    }
+    memcpy(t.h_long_row, lrow.data(), sizeof(int) * lrow.size());
+    memcpy(t.h_long_first, lfirst.data(), sizeof(int) * lfirst.size());
+    t.state = 2;
+    sp = t;
+    ctx->device_bytes += (int64_t)(sizeof(int) * (hi.size() + clo.size() + chi.size() + lrow.size() + lfirst.size()));
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
 // Column blocks are used only when asked for (option spmm_col_blocks > 1).  Measured on B200 with 64 fp32 columns,
 // 2^21 rows of 32 elements and a 537 MB X: 3.51 ms in one pass, 4.08 / 4.60 / 5.16 / 6.37 ms with 4 / 6 / 8 / 12
 // blocks.  Blocking does take the reads of X off HBM, but every stored element still pulls a whole row of X from
@@ -235,12 +323,15 @@ static void launch_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx
     const int64_t first = w ? w->begin : 0, rows = w ? w->count : ctx->rows;
     const unsigned blocks = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
     const T *val = static_cast<const T *>(ctx->d_val);
+    T *const Y0 = Y;
     Y += first * (int64_t)ldy;
-    const int passes = ctx->spmm.d_split ? ctx->spmm.blocks : 1;
+    const SpmmSplit &sp = ctx->split;
+    const bool split = sp.state == 2;
+    const int passes = !split && ctx->spmm.d_split ? ctx->spmm.blocks : 1;
     if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
     for (int p = 0; p < passes; p++) {
         const int *lo = passes > 1 ? ctx->spmm.d_split + (size_t)p * ctx->rows + first : ctx->d_row_ptr + first;
-        const int *hi = passes > 1 ? lo + ctx->rows : lo + 1;
+        const int *hi = passes > 1 ? lo + ctx->rows : split ? sp.d_hi_short + first : lo + 1;
         // the first pass applies beta, the later ones add to what is there
         const T b = p == 0 ? beta : T(1);
         if (b == T(0))
@@ -249,6 +340,24 @@ static void launch_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx
         else
             spmm_row_kernel<T, VEC, LPR, true><<<blocks, 256, 0, st>>>(
                 (int)rows, lo, hi, ctx->d_col, val, X, columns, ldx, Y, ldy, alpha, b);
+    }
+    if (split) {
+        // the long rows of this window: their chunks through the same kernel into partial sums, then onto Y
+        const int *lb = std::lower_bound(sp.h_long_row, sp.h_long_row + sp.nlong, (int)first);
+        const int *le = std::lower_bound(sp.h_long_row, sp.h_long_row + sp.nlong, (int)(first + rows));
+        const int64_t l0 = lb - sp.h_long_row, l1 = le - sp.h_long_row;
+        const int64_t c0 = sp.h_long_first[l0], c1 = sp.h_long_first[l1];
+        if (c1 > c0) {
+            T *part = static_cast<T *>(sp.d_part) + (size_t)c0 * columns;
+            const unsigned cblocks = (unsigned)((c1 - c0 + rows_per_block - 1) / rows_per_block);
+            spmm_row_kernel<T, VEC, LPR, false><<<cblocks, 256, 0, st>>>(
+                (int)(c1 - c0), sp.d_chunk_lo + c0, sp.d_chunk_hi + c0, ctx->d_col, val, X, columns, ldx, part, columns, alpha,
+                T(0));
+            const int threads = std::min(256, (columns + 31) / 32 * 32);
+            spmm_long_reduce_kernel<T><<<(unsigned)(l1 - l0), threads, 0, st>>>(
+                sp.d_long_row + l0, sp.d_long_first + l0, static_cast<const T *>(sp.d_part), columns, Y0, ldy);
+            count_launch(2);
+        }
     }
     if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
     count_launch(passes);
@@ -270,7 +379,21 @@ template <typename T>
 alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx,
                                      T beta, T *Y, int ldy, cudaStream_t st, const RowWindow *w) {
     if (ctx->rows == 0 || columns <= 0 || (w && w->count <= 0)) return ALPHA_SPARSE_STATUS_SUCCESS;
-    alphasparse_status_t bs = spmm_blocks_ensure(ctx, spmm_pick_blocks(ctx, sizeof(T) * (size_t)ctx->cols * (size_t)ldx), st);
+    alphasparse_status_t bs = spmm_split_ensure(ctx, st);
+    if (bs != ALPHA_SPARSE_STATUS_SUCCESS) return bs;
+    if (ctx->split.state == 2) {
+        SpmmSplit &sp = ctx->split;
+        const size_t want = sizeof(T) * (size_t)sp.nchunks * (size_t)columns;
+        if (sp.part_bytes < want) {
+            cudaFree(sp.d_part);
+            ctx->device_bytes -= (int64_t)sp.part_bytes;
+            sp.d_part = nullptr, sp.part_bytes = 0;
+            ASB_CUDA_OR(device_alloc(&sp.d_part, want), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+            sp.part_bytes = want;
+            ctx->device_bytes += (int64_t)want;
+        }
+    }
+    bs = spmm_blocks_ensure(ctx, spmm_pick_blocks(ctx, sizeof(T) * (size_t)ctx->cols * (size_t)ldx), st);
     if (bs != ALPHA_SPARSE_STATUS_SUCCESS) return bs;
     auto fits = [&](int vec) {
         const uintptr_t mask = (uintptr_t)(vec * sizeof(T) - 1);

@@ -62,6 +62,10 @@ alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg);
  *                           0.49 against 0.53 ms per iteration at 4 GPUs, 0.47 against 0.32 ms at 8)
  *   pipe_max_windows (12)   mv with host vectors: the product runs in up to this many row windows (at most 16) that
  *                           overlap the copies of y, each window covering at least pipe_min_piece_kb (4096) KB of y
+ *   spmm_split_min (1024)   row-major dense-block product on a matrix whose longest row exceeds eight times the mean:
+ *                           a row above this many elements is multiplied chunk by chunk (spmm_split_chunk (512)
+ *                           elements per chunk, partial sums added in chunk order), so that one lane group does
+ *                           not walk a hundred thousand elements alone; 0 = never
  *   spmm_col_blocks (0)     row-major dense-block product in this many column blocks (X slab by slab, Y
  *                           accumulated over the passes); 0 or 1 = one pass, which measured faster on B200
  * Unknown names return ALPHA_SPARSE_STATUS_INVALID_VALUE. */

@@ -261,3 +261,78 @@ def test_large_host_operands_take_the_windowed_path(ldy, beta):
     Yd = run_mm("s", A, m, X, columns, ldx, 1.25, beta, Y0, ldy, device=True)
     assert np.array_equal(Y.reshape(rows, ldy)[:, :columns], Yd.reshape(rows, ldy)[:, :columns])  # same kernel, same sums
     spblas.destroy(A)
+
+
+def _with_long_rows(kind, seed, rows, cols, mean, long_rows):
+    """A Poisson(mean) matrix in which the rows named in `long_rows` (row -> length) are replaced by long ones."""
+    base = synth.poisson(kind, seed, rows, cols, mean)
+    rng = np.random.default_rng(seed)
+    lens = np.diff(base.ptr).astype(np.int64)
+    pieces_c, pieces_v = [], []
+    for r in range(rows):
+        if r in long_rows:
+            c = np.sort(rng.choice(cols, long_rows[r], replace=False)).astype(np.int32)
+            pieces_c.append(c)
+            pieces_v.append(rng.uniform(-1, 1, len(c)).astype(base.val.dtype))
+            lens[r] = len(c)
+        else:
+            pieces_c.append(base.col[base.ptr[r]:base.ptr[r + 1]])
+            pieces_v.append(base.val[base.ptr[r]:base.ptr[r + 1]])
+    ptr = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    return synth.Csr(rows, cols, 0, ptr, np.concatenate(pieces_c), np.concatenate(pieces_v))
+
+
+@pytest.mark.parametrize("kind", ["s", "d"])
+def test_long_rows_are_multiplied_in_chunks(kind):
+    """Rows above spmm_split_min elements leave the row pass and are multiplied chunk by chunk into partial sums that
+    a last kernel adds onto Y: same product (fp32 rows stay short enough for the serial fp32 oracle), padding of Y
+    untouched, beta applied once, first / last / neighbouring rows long, every pack width, transposed handle too."""
+    rows, cols = 3000, 4000
+    long_rows = {0: 1400, 1: 700, 1500: 1100, 2999: 900}
+    m = _with_long_rows(kind, 95, rows, cols, 6.0, long_rows)
+    try:
+        assert spblas.set_option("spmm_split_min", 512) == capi.SUCCESS
+        assert spblas.set_option("spmm_split_chunk", 128) == capi.SUCCESS
+        A = make_handle(kind, m)
+        for columns, ldx, ldy, beta in ((64, 64, 64, 0.0), (64, 72, 80, 0.5), (7, 7, 9, 0.5), (1, 1, 1, 0.0), (16, 16, 16, 1.0)):
+            X, Y0 = synth.vector(kind, 95, 1, cols * ldx), synth.vector(kind, 95, 2, rows * ldy)
+            Yref = oracle.gemm(kind, "row", m.rows_start, m.rows_end, m.col, m.val, 1.25, X, columns, ldx, beta, Y0.copy(), ldy)
+            for device in (True, False):
+                Y = run_mm(kind, A, m, X, columns, ldx, 1.25, beta, Y0, ldy, device)
+                compare(kind, m, Y, Yref, X, columns, ldx, 1.25, beta, Y0, ldy, f"long rows {columns}/{ldx}/{ldy} dev={device}")
+        # the same handle transposed: A^T has its own long rows (none here, its columns are short) and its own tables
+        X, Y0 = synth.vector(kind, 96, 1, rows * 8), synth.vector(kind, 96, 2, cols * 8)
+        st = spblas.mm(kind, capi.TRANSPOSE, 1.0, A, spblas.descr(), capi.ROW_MAJOR, torch.from_numpy(X).cuda(), 8, 8, 0.0,
+                       torch.from_numpy(Y0).cuda(), 8)
+        assert st == capi.SUCCESS
+        spblas.destroy(A)
+        # a matrix whose longest row stays under the limit builds no tables and runs the one pass
+        small = synth.poisson(kind, 97, 2000, 2000, 5.0)
+        A = make_handle(kind, small)
+        X, Y0 = synth.vector(kind, 97, 1, 2000 * 8), synth.vector(kind, 97, 2, 2000 * 8)
+        Yref = oracle.gemm(kind, "row", small.rows_start, small.rows_end, small.col, small.val, 1.0, X, 8, 8, 0.0, Y0.copy(), 8)
+        before = spblas.launch_count()
+        Y = run_mm(kind, A, small, X, 8, 8, 1.0, 0.0, Y0, 8, True)
+        assert spblas.launch_count() - before == 1
+        compare(kind, small, Y, Yref, X, 8, 8, 1.0, 0.0, Y0, 8, "no long rows")
+        spblas.destroy(A)
+    finally:
+        spblas.set_option("spmm_split_min", -1)
+        spblas.set_option("spmm_split_chunk", -1)
+
+
+def test_long_rows_in_row_windows():
+    """Host operands above 32 MB run in row windows; each window multiplies the chunks of its own long rows."""
+    rows, cols, columns, ld = 140001, 50000, 64, 64
+    long_rows = {0: 30000, 17500: 20000, 17501: 9000, 70000: 45000, 140000: 12000}
+    m = _with_long_rows("s", 98, rows, cols, 6.0, long_rows)
+    A = make_handle("s", m)          # default limits: rows above 1024 elements, chunks of 512
+    X, Y0 = synth.vector("s", 98, 1, cols * ld), synth.vector("s", 98, 2, rows * ld)
+    # fp32 rows of tens of thousands of elements: compare against the product accumulated in fp64
+    Yref = oracle.gemm("d", "row", m.rows_start, m.rows_end, m.col, m.val.astype(np.float64), 1.25, X.astype(np.float64),
+                       columns, ld, 0.5, Y0.astype(np.float64), ld).astype(np.float32)
+    Y = run_mm("s", A, m, X, columns, ld, 1.25, 0.5, Y0, ld, device=False)
+    compare("s", m, Y, Yref, X, columns, ld, 1.25, 0.5, Y0, ld, "windows")
+    Yd = run_mm("s", A, m, X, columns, ld, 1.25, 0.5, Y0, ld, device=True)
+    assert np.array_equal(Y, Yd)  # same kernels, same chunks, same sums
+    spblas.destroy(A)
