@@ -304,6 +304,23 @@ static alphasparse_status_t spmm_split_ensure(DeviceCtx *ctx, cudaStream_t st) {
     return ALPHA_SPARSE_STATUS_SUCCESS;
 }
 
+// The chunk tables (first product of the handle) and room for the partial sums of a product with `columns` columns.
+static alphasparse_status_t spmm_split_prepare(DeviceCtx *ctx, size_t tsz, int columns, cudaStream_t st) {
+    alphasparse_status_t s = spmm_split_ensure(ctx, st);
+    if (s != ALPHA_SPARSE_STATUS_SUCCESS || ctx->split.state != 2) return s;
+    SpmmSplit &sp = ctx->split;
+    const size_t want = tsz * (size_t)sp.nchunks * (size_t)columns;
+    if (sp.part_bytes < want) {
+        cudaFree(sp.d_part);
+        ctx->device_bytes -= (int64_t)sp.part_bytes;
+        sp.d_part = nullptr, sp.part_bytes = 0;
+        ASB_CUDA_OR(device_alloc(&sp.d_part, want), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+        sp.part_bytes = want;
+        ctx->device_bytes += (int64_t)want;
+    }
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
 // Column blocks are used only when asked for (option spmm_col_blocks > 1).  Measured on B200 with 64 fp32 columns,
 // 2^21 rows of 32 elements and a 537 MB X: 3.51 ms in one pass, 4.08 / 4.60 / 5.16 / 6.37 ms with 4 / 6 / 8 / 12
 // blocks.  Blocking does take the reads of X off HBM, but every stored element still pulls a whole row of X from
@@ -379,20 +396,8 @@ template <typename T>
 alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx,
                                      T beta, T *Y, int ldy, cudaStream_t st, const RowWindow *w) {
     if (ctx->rows == 0 || columns <= 0 || (w && w->count <= 0)) return ALPHA_SPARSE_STATUS_SUCCESS;
-    alphasparse_status_t bs = spmm_split_ensure(ctx, st);
+    alphasparse_status_t bs = spmm_split_prepare(ctx, sizeof(T), columns, st);
     if (bs != ALPHA_SPARSE_STATUS_SUCCESS) return bs;
-    if (ctx->split.state == 2) {
-        SpmmSplit &sp = ctx->split;
-        const size_t want = sizeof(T) * (size_t)sp.nchunks * (size_t)columns;
-        if (sp.part_bytes < want) {
-            cudaFree(sp.d_part);
-            ctx->device_bytes -= (int64_t)sp.part_bytes;
-            sp.d_part = nullptr, sp.part_bytes = 0;
-            ASB_CUDA_OR(device_alloc(&sp.d_part, want), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
-            sp.part_bytes = want;
-            ctx->device_bytes += (int64_t)want;
-        }
-    }
     bs = spmm_blocks_ensure(ctx, spmm_pick_blocks(ctx, sizeof(T) * (size_t)ctx->cols * (size_t)ldx), st);
     if (bs != ALPHA_SPARSE_STATUS_SUCCESS) return bs;
     auto fits = [&](int vec) {
@@ -424,17 +429,17 @@ alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int co
 // blockIdx.y selects the block of KC columns; A is re-read once per block.
 template <typename T, int LANES, int KC, bool HAS_BETA>
 __global__ void __launch_bounds__(256)
-    spmm_col_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
-                    const T *__restrict__ val, const T *__restrict__ X, int columns, long long ldx,
-                    T *__restrict__ Y, long long ldy, T alpha, T beta) {
+    spmm_col_kernel(int rows, const int *__restrict__ row_lo, const int *__restrict__ row_hi,
+                    const int *__restrict__ col, const T *__restrict__ val, const T *__restrict__ X, int columns,
+                    long long ldx, T *__restrict__ Y, long long ldy, T alpha, T beta) {
     constexpr int GROUPS = 256 / LANES;
     const int lane = threadIdx.x % LANES;
     const long long row = (long long)blockIdx.x * GROUPS + threadIdx.x / LANES;
     const int c0 = blockIdx.y * KC;
     int s = 0, e = 0;
-    if (row < rows) {
-        s = __ldg(row_ptr + row);
-        e = __ldg(row_ptr + row + 1);
+    if (row < rows) {  // the whole row, or the chunk of a long row that stands in for a row (see SpmmSplit)
+        s = __ldg(row_lo + row);
+        e = __ldg(row_hi + row);
     }
     T acc[KC];
 #pragma unroll
@@ -463,21 +468,48 @@ __global__ void __launch_bounds__(256)
     }
 }
 
+// Y[c * ldy + row] += the row's partial sums (part[c * nchunks + k]) in chunk order: one thread per (long row, column).
+template <typename T>
+__global__ void spmm_long_reduce_col_kernel(int nlong, const int *__restrict__ long_row, const int *__restrict__ long_first,
+                                            const T *__restrict__ part, long long nchunks, int columns, T *__restrict__ Y,
+                                            long long ldy) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)nlong * columns) return;
+    const int l = (int)(i % nlong), c = (int)(i / nlong);
+    T acc = T(0);
+    for (int k = long_first[l]; k < long_first[l + 1]; k++) acc += part[(long long)c * nchunks + k];
+    Y[(long long)c * ldy + long_row[l]] += acc;
+}
+
 template <typename T, int LANES>
 static void launch_col(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx, T beta, T *Y, int ldy,
                        cudaStream_t st) {
     constexpr int KC = 4;
     const dim3 grid((unsigned)((ctx->rows + 256 / LANES - 1) / (256 / LANES)), (unsigned)((columns + KC - 1) / KC));
     const T *val = static_cast<const T *>(ctx->d_val);
+    const SpmmSplit &sp = ctx->split;
+    const bool split = sp.state == 2;
+    const int *hi = split ? sp.d_hi_short : ctx->d_row_ptr + 1;
     if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
     if (beta == T(0))
-        spmm_col_kernel<T, LANES, KC, false><<<grid, 256, 0, st>>>((int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, X,
+        spmm_col_kernel<T, LANES, KC, false><<<grid, 256, 0, st>>>((int)ctx->rows, ctx->d_row_ptr, hi, ctx->d_col, val, X,
                                                                   columns, ldx, Y, ldy, alpha, beta);
     else
-        spmm_col_kernel<T, LANES, KC, true><<<grid, 256, 0, st>>>((int)ctx->rows, ctx->d_row_ptr, ctx->d_col, val, X,
+        spmm_col_kernel<T, LANES, KC, true><<<grid, 256, 0, st>>>((int)ctx->rows, ctx->d_row_ptr, hi, ctx->d_col, val, X,
                                                                  columns, ldx, Y, ldy, alpha, beta);
-    if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
     count_launch();
+    if (split && sp.nchunks > 0) {
+        // the chunks of the long rows as rows of their own (a warp each) into partial sums, then onto Y
+        T *part = static_cast<T *>(sp.d_part);
+        const dim3 cgrid((unsigned)((sp.nchunks + 7) / 8), grid.y);
+        spmm_col_kernel<T, 32, KC, false><<<cgrid, 256, 0, st>>>((int)sp.nchunks, sp.d_chunk_lo, sp.d_chunk_hi, ctx->d_col, val,
+                                                                X, columns, ldx, part, sp.nchunks, alpha, T(0));
+        const long long cells = (long long)sp.nlong * columns;
+        spmm_long_reduce_col_kernel<T><<<(unsigned)((cells + 255) / 256), 256, 0, st>>>(
+            (int)sp.nlong, sp.d_long_row, sp.d_long_first, part, sp.nchunks, columns, Y, ldy);
+        count_launch(2);
+    }
+    if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
 }
 
 template <typename T>
@@ -485,6 +517,8 @@ alphasparse_status_t launch_spmm_col(DeviceCtx *ctx, T alpha, const T *X, int co
                                      int ldy, cudaStream_t st) {
     if (ctx->rows == 0 || columns <= 0) return ALPHA_SPARSE_STATUS_SUCCESS;
     if ((columns + 3) / 4 > 65535) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
+    const alphasparse_status_t ps = spmm_split_prepare(ctx, sizeof(T), columns, st);
+    if (ps != ALPHA_SPARSE_STATUS_SUCCESS) return ps;
     const double m = ctx->mean_row_nnz;
     if (m <= 8) launch_col<T, 4>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
     else if (m <= 16) launch_col<T, 8>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st);

@@ -300,6 +300,24 @@ def test_long_rows_are_multiplied_in_chunks(kind):
             for device in (True, False):
                 Y = run_mm(kind, A, m, X, columns, ldx, 1.25, beta, Y0, ldy, device)
                 compare(kind, m, Y, Yref, X, columns, ldx, 1.25, beta, Y0, ldy, f"long rows {columns}/{ldx}/{ldy} dev={device}")
+        # column-major operands: the same chunk tables, partial sums laid out column by column
+        for columns, beta in ((6, 0.5), (1, 0.0)):
+            ldx, ldy = cols + 3, rows + 5
+            X, Y0 = synth.vector(kind, 99, 1, ldx * columns), synth.vector(kind, 99, 2, ldy * columns)
+            Yref = oracle.gemm(kind, "col", m.rows_start, m.rows_end, m.col, m.val, 1.25, X, columns, ldx, beta, Y0.copy(), ldy)
+            dX, dY = torch.from_numpy(X).cuda(), torch.from_numpy(Y0).cuda()
+            assert spblas.mm(kind, 0, 1.25, A, spblas.descr(), capi.COLUMN_MAJOR, dX, columns, ldx, beta, dY, ldy) == capi.SUCCESS
+            Y = dY.cpu().numpy()
+            rid = np.repeat(np.arange(rows), np.diff(m.ptr))
+            sc = np.zeros((columns, ldy))
+            for c in range(columns):
+                xs = X[c * ldx:c * ldx + cols].astype(np.float64)
+                sc[c, :rows] = np.abs(beta * Y0[c * ldy:c * ldy + rows]) + 1.25 * np.bincount(
+                    rid, weights=np.abs(m.val.astype(np.float64) * xs[m.col]), minlength=rows)
+            assert_rows_close(kind, Y, Yref, sc.reshape(-1), f"column-major long rows, {columns} columns")
+            pad = np.ones(ldy * columns, bool).reshape(columns, ldy)
+            pad[:, :rows] = False
+            assert np.array_equal(Y[pad.reshape(-1)], Y0[pad.reshape(-1)]), "padding written"
         # the same handle transposed: A^T has its own long rows (none here, its columns are short) and its own tables
         X, Y0 = synth.vector(kind, 96, 1, rows * 8), synth.vector(kind, 96, 2, cols * 8)
         st = spblas.mm(kind, capi.TRANSPOSE, 1.0, A, spblas.descr(), capi.ROW_MAJOR, torch.from_numpy(X).cuda(), 8, 8, 0.0,
