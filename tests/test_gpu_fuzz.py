@@ -98,3 +98,54 @@ def test_random_shapes_and_options(seed):
             for k in opts:
                 spblas.set_option(k, -1)
     assert len(seen) >= 3, seen   # the draws reached several kernel families
+
+
+@pytest.mark.parametrize("seed", [21, 22])
+def test_random_transposed_and_structured_products(seed):
+    """The matrices derived on the device (A^T, kept triangle, mirror image, unit diagonal, diagonal only) from random
+    square matrices, half of them with rows in shuffled column order and diagonals stored twice."""
+    rng = np.random.default_rng(seed)
+    for it in range(8):
+        n = int(rng.integers(1, 40000))
+        shape, s = int(rng.integers(3)), int(rng.integers(1 << 30))
+        if shape == 0:
+            lens = synth.rowlen_zipf(s, n, 1.6 + rng.random(), 1, min(n, int(rng.integers(1, 30000))))
+        elif shape == 1:
+            lens = synth.rowlen_poisson(s, n, rng.random() * 30, n)
+        else:
+            lens = synth.rowlen_poisson(s, n, 2.0, n).copy()
+            for _ in range(3):
+                lens[rng.integers(n)] = min(n, int(rng.integers(50, 30000)))
+        lens = np.minimum(lens, n).astype(np.int32)
+        if lens.sum() > 2_000_000:
+            lens = (lens * (2_000_000 / lens.sum())).astype(np.int32)
+        m = synth.from_lengths("d", s, lens, n)
+        col, val = m.col.copy(), m.val.copy()
+        if rng.random() < 0.5:
+            for r in rng.integers(0, n, 200):
+                a, b = m.ptr[r], m.ptr[r + 1]
+                p = rng.permutation(b - a)
+                col[a:b], val[a:b] = col[a:b][p], val[a:b][p]
+                if b - a >= 2 and rng.random() < 0.5:
+                    col[a] = col[b - 1] = r
+        st, A = spblas.create_csr("d", capi.BASE_ZERO, n, n, m.rows_start, m.rows_end, col, val)
+        assert st == capi.SUCCESS, spblas.last_error()
+        x, y0 = synth.vector("d", it, 1, n), synth.vector("d", it, 2, n)
+        rid = np.repeat(np.arange(n), np.diff(m.ptr))
+        scale = np.abs(0.5 * y0) + 1.25 * (np.bincount(rid, weights=np.abs(val * x[col]), minlength=n) +
+                                           np.bincount(col, weights=np.abs(val * x[rid]), minlength=n) + np.abs(x))
+        cases = [(capi.GENERAL, 0, 0, 1)]
+        for t in (capi.SYMMETRIC, capi.TRIANGULAR, capi.DIAGONAL):
+            cases.append((t, int(rng.integers(2)), int(rng.integers(2)), int(rng.integers(2)) if t == capi.TRIANGULAR else 0))
+        for t, upper, unit, trans in cases:
+            if t == capi.GENERAL:
+                ref = oracle.gemv_trans("d", n, m.rows_start, m.rows_end, col, val, 1.25, x, 0.5, y0.copy())
+                descr = spblas.descr()
+            else:
+                ref = oracle.structured_mv("d", t, upper, unit, trans, m.rows_start, m.rows_end, col, val, 1.25, x, 0.5, y0.copy())
+                descr = spblas.descr(t, upper, unit)
+            dx, dy = torch.from_numpy(x).cuda(), torch.from_numpy(y0).cuda()
+            assert spblas.mv("d", trans, 1.25, A, descr, dx, 0.5, dy) == capi.SUCCESS, spblas.last_error()
+            err = np.abs(dy.cpu().numpy() - ref)
+            assert (err <= TOL["d"] * scale + 1e-300).all(), f"seed {seed} case {it} n {n} type {t} {upper}{unit}{trans}"
+        spblas.destroy(A)
