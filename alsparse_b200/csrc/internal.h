@@ -45,6 +45,8 @@ enum Option {
     kOptBinSort,          // 1: the lists of the two longer mid bins are ordered longest row first
     kOptPipeMaxWindows,   // host-vector mv: most row windows the product is cut into (1..16)
     kOptPipeMinPieceKb,   // ... and the smallest piece of y per window, in KB
+    kOptMvBlockMinKb,     // vector-kernel SpMV: an x above this many KB is multiplied column block by column block (0: never)
+    kOptMvBlockKb,        // ... each block covering at most this many KB of x
     kOptSpmmSplitMin,     // row-major dense-block product: rows above this many elements are multiplied chunk by chunk (0: never)
     kOptSpmmSplitChunk,   // ... in chunks of this many elements
     kOptSpmmColBlocks,    // column blocks of the row-major dense-block product (0 or 1: one pass)
@@ -162,6 +164,10 @@ struct SpmmBlocks {
     int *d_split = nullptr;
 };
 void spmm_blocks_destroy(SpmmBlocks &b);
+struct DeviceCtx;
+// Builds (or drops, blocks <= 1) the table of `b` for `blocks` column blocks of the matrix in `ctx`; leaves
+// b.blocks == 1 when the rows are not in ascending column order.
+alphasparse_status_t col_blocks_ensure(DeviceCtx *ctx, SpmmBlocks &b, int blocks, cudaStream_t st);
 
 // Long rows of the row-major dense-block product (spmm.cu).  One lane group per row is fine until a row holds a
 // hundred thousand elements and its group is still walking it long after every other row is done: rows above
@@ -212,6 +218,7 @@ struct DeviceCtx {
     const int *h_row_ptr = nullptr;    // host copy of the offsets, valid only while the handle is being created
     SpmmBlocks spmm;                   // column blocks of the row-major dense-block product
     SpmmSplit split;                   // its long rows, cut into chunks
+    SpmmBlocks mvb;                    // column blocks of the vector-kernel SpMV, for an x that does not fit L2
     bool carry_stale = false;          // a run over ALL tiles wrote carries for tiles the schedule leaves out
     BandTables band;                   // long rows taken out of the merge tiles (spmv_band.cu); rows == 0: none
     unsigned *d_chunk_done = nullptr;  // per chunk of kPushChunkTiles tiles (exchange calls only)

@@ -171,8 +171,7 @@ void spmm_blocks_destroy(SpmmBlocks &b) {
 
 // Column-block table for `blocks` blocks, built on first use and kept until another count is asked for.
 // Leaves b.blocks == 1 (no blocking) when the rows are not in ascending column order.
-static alphasparse_status_t spmm_blocks_ensure(DeviceCtx *ctx, int blocks, cudaStream_t st) {
-    SpmmBlocks &b = ctx->spmm;
+alphasparse_status_t col_blocks_ensure(DeviceCtx *ctx, SpmmBlocks &b, int blocks, cudaStream_t st) {
     if (b.blocks == blocks || (b.unsorted && blocks > 1)) return ALPHA_SPARSE_STATUS_SUCCESS;
     const int64_t old_bytes = b.d_split ? (int64_t)sizeof(int) * ctx->rows * (b.blocks + 1) : 0;
     spmm_blocks_destroy(b);
@@ -398,7 +397,7 @@ alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int co
     if (ctx->rows == 0 || columns <= 0 || (w && w->count <= 0)) return ALPHA_SPARSE_STATUS_SUCCESS;
     alphasparse_status_t bs = spmm_split_prepare(ctx, sizeof(T), columns, st);
     if (bs != ALPHA_SPARSE_STATUS_SUCCESS) return bs;
-    bs = spmm_blocks_ensure(ctx, spmm_pick_blocks(ctx, sizeof(T) * (size_t)ctx->cols * (size_t)ldx), st);
+    bs = col_blocks_ensure(ctx, ctx->spmm, spmm_pick_blocks(ctx, sizeof(T) * (size_t)ctx->cols * (size_t)ldx), st);
     if (bs != ALPHA_SPARSE_STATUS_SUCCESS) return bs;
     auto fits = [&](int vec) {
         const uintptr_t mask = (uintptr_t)(vec * sizeof(T) - 1);

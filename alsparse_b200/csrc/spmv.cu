@@ -85,9 +85,9 @@ struct VectorShape {
 
 template <typename T, int LANES, int RPG, bool HAS_BETA>
 __global__ void __launch_bounds__(256, VectorShape<LANES>::MIN_BLOCKS)
-    spmv_vector_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ col,
-                       const T *__restrict__ val, const T *__restrict__ x, T *__restrict__ y,
-                       T alpha, T beta) {
+    spmv_vector_kernel(int rows, const int *__restrict__ row_ptr, const int *__restrict__ row_end,
+                       const int *__restrict__ col, const T *__restrict__ val, const T *__restrict__ x,
+                       T *__restrict__ y, T alpha, T beta) {
     constexpr int GROUPS = 256 / LANES;
     const int lane = threadIdx.x % LANES;
     const int grp = threadIdx.x / LANES;
@@ -99,8 +99,8 @@ __global__ void __launch_bounds__(256, VectorShape<LANES>::MIN_BLOCKS)
         const long long r = row0 + (long long)u * GROUPS;
         s[u] = 0, e[u] = 0;
         if (r < rows) {
-            s[u] = __ldg(row_ptr + r);
-            e[u] = __ldg(row_ptr + r + 1);
+            s[u] = __ldg(row_ptr + r);  // the whole row, or its elements inside one column block (see launch_vector)
+            e[u] = __ldg(row_end + r);
         }
     }
 
@@ -972,7 +972,15 @@ alphasparse_status_t ctx_analyse(DeviceCtx *ctx) {
         if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
     }
     ctx->algorithm = alg;
-    return ALPHA_SPARSE_STATUS_SUCCESS;
+    // An x that L2 cannot hold turns most gathers into 32-byte sector reads from HBM (2^24 x 16 in fp64, x = 134 MB:
+    // 3.3 ms against 1.07 ms for the fp32 matrix).  The vector kernel then runs once per column block of at most
+    // mv_block_kb of x; rows in ascending column order need only an offset per row and block for that.
+    int blocks = 1;
+    const int64_t tsz = ctx->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE ? 8 : 4;
+    const int64_t x_kb = ctx->cols * tsz >> 10, min_kb = option(kOptMvBlockMinKb), block_kb = std::max<int64_t>(1, option(kOptMvBlockKb));
+    if (alg == ALPHA_SPARSE_CUDA_ALG_VECTOR && min_kb > 0 && x_kb > min_kb && ctx->nnz > 0)
+        blocks = (int)std::min<int64_t>(64, (x_kb + block_kb - 1) / block_kb);
+    return col_blocks_ensure(ctx, ctx->mvb, blocks, st);
 }
 
 // ---- launchers -----------------------------------------------------------------------------------
@@ -985,15 +993,24 @@ static void launch_vector(DeviceCtx *ctx, T alpha, const T *x, T beta, T *y, cud
     const unsigned blocks = (unsigned)((w.count + rows_per_block - 1) / rows_per_block);
     const T *val = static_cast<const T *>(ctx->d_val);
     if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
-    // a window is just an offset view: offsets stay absolute, so col / val need no shift
-    if (beta == T(0))
-        spmv_vector_kernel<T, LANES, RPG, false><<<blocks, 256, 0, st>>>(
-            (int)w.count, ctx->d_row_ptr + w.begin, ctx->d_col, val, x, y + w.begin, alpha, beta);
-    else
-        spmv_vector_kernel<T, LANES, RPG, true><<<blocks, 256, 0, st>>>(
-            (int)w.count, ctx->d_row_ptr + w.begin, ctx->d_col, val, x, y + w.begin, alpha, beta);
+    // A window is just an offset view: offsets stay absolute, so col / val need no shift.
+    // Column blocks (an x that does not fit L2, see ctx_analyse): one launch per block over the elements of every row
+    // that fall into it, so that the gathers of a launch stay inside a slice of x that L2 holds; the first launch
+    // applies beta, the later ones add to y.
+    const int passes = ctx->mvb.d_split ? ctx->mvb.blocks : 1;
+    for (int p = 0; p < passes; p++) {
+        const int *lo = passes > 1 ? ctx->mvb.d_split + (size_t)p * ctx->rows + w.begin : ctx->d_row_ptr + w.begin;
+        const int *hi = passes > 1 ? lo + ctx->rows : lo + 1;
+        const T b = p == 0 ? beta : T(1);
+        if (b == T(0))
+            spmv_vector_kernel<T, LANES, RPG, false><<<blocks, 256, 0, st>>>((int)w.count, lo, hi, ctx->d_col, val, x,
+                                                                            y + w.begin, alpha, b);
+        else
+            spmv_vector_kernel<T, LANES, RPG, true><<<blocks, 256, 0, st>>>((int)w.count, lo, hi, ctx->d_col, val, x,
+                                                                           y + w.begin, alpha, b);
+    }
     if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
-    count_launch();
+    count_launch(passes);
 }
 
 template <typename T, int IPT, bool HAS_BETA, bool PUSH>
@@ -1156,7 +1173,9 @@ alphasparse_status_t launch_spmv(DeviceCtx *ctx, T alpha, const T *x, T beta, T 
         if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
         pushed = push && !push->after;
     } else {
-        switch (ctx->lanes) {
+        int lanes = ctx->lanes;  // a pass over one of P column blocks sees 1/P of every row
+        for (int p = ctx->mvb.d_split ? ctx->mvb.blocks : 1; p > 1 && lanes > 1; p >>= 1) lanes >>= 1;
+        switch (lanes) {
             case 1: launch_vector<T, 1>(ctx, alpha, x, beta, y, st, w); break;
             case 2: launch_vector<T, 2>(ctx, alpha, x, beta, y, st, w); break;
             case 4: launch_vector<T, 4>(ctx, alpha, x, beta, y, st, w); break;

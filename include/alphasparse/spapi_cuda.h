@@ -62,6 +62,10 @@ alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg);
  *                           0.49 against 0.53 ms per iteration at 4 GPUs, 0.47 against 0.32 ms at 8)
  *   pipe_max_windows (12)   mv with host vectors: the product runs in up to this many row windows (at most 16) that
  *                           overlap the copies of y, each window covering at least pipe_min_piece_kb (4096) KB of y
+ *   mv_block_min_kb (98304) vector-kernel SpMV: when x is larger than this many KB (it no longer fits L2) the product runs
+ *                           column block by column block, each block covering at most mv_block_kb (65536) KB of
+ *                           x, the first launch applying beta and the later ones adding to y; needs rows in
+ *                           ascending column order; 0 = never
  *   spmm_split_min (1024)   row-major dense-block product on a matrix whose longest row exceeds eight times the mean:
  *                           a row above this many elements is multiplied chunk by chunk (spmm_split_chunk (512)
  *                           elements per chunk, partial sums added in chunk order), so that one lane group does

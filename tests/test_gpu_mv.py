@@ -387,6 +387,42 @@ def test_structured_descriptors_on_unsorted_rows_with_repeated_diagonals():
 
 
 @pytest.mark.parametrize("kind", ["s", "d"])
+def test_vector_kernel_in_column_blocks(kind):
+    """An x that does not fit L2 makes the vector kernel run once per column block (limits shrunk here so that a small
+    matrix is cut into 2 .. 64 blocks): every scalar combination, host and device vectors, empty rows, rows with fewer
+    elements than blocks; rows in descending column order must fall back to one launch."""
+    rows, cols = 30011, 40009
+    lens = synth.rowlen_poisson(31, rows, 14.0, cols).copy()
+    lens[::97] = 0
+    m = synth.from_lengths(kind, 31, lens, cols)
+    x, y0 = synth.vector(kind, 31, 1, cols), synth.vector(kind, 31, 2, rows)
+    tsz = 4 if kind == "s" else 8
+    for block_kb in (cols * tsz // 2048 + 1, 16, 1):
+        with _Options(mv_block_min_kb=1, mv_block_kb=block_kb):
+            A = make_handle(kind, m)
+        assert spblas.mat_info(A)[1].algorithm == capi.ALG_VECTOR
+        for alpha, beta in ((1.0, 0.0), (1.5, 0.5), (-0.5, 1.0)):
+            check_mv(kind, m, alpha, beta, A=A)
+            check_mv(kind, m, alpha, beta, A=A, pointers="device")
+        before = spblas.launch_count()
+        dx, dy = torch.from_numpy(x).cuda(), torch.from_numpy(y0).cuda()
+        assert spblas.mv(kind, 0, 1.0, A, spblas.descr(), dx, 0.0, dy) == capi.SUCCESS
+        want = min(64, -(-(cols * tsz // 1024) // block_kb))
+        assert spblas.launch_count() - before == want, (block_kb, want)
+        spblas.destroy(A)
+    col, val = m.col.copy(), m.val.copy()
+    for r in range(rows):
+        col[m.ptr[r]:m.ptr[r + 1]] = col[m.ptr[r]:m.ptr[r + 1]][::-1]
+        val[m.ptr[r]:m.ptr[r + 1]] = val[m.ptr[r]:m.ptr[r + 1]][::-1]
+    mr = synth.Csr(rows, cols, 0, m.ptr, col, val)
+    with _Options(mv_block_min_kb=1, mv_block_kb=16):
+        A = make_handle(kind, mr)
+    before = spblas.launch_count()
+    check_mv(kind, mr, 1.5, 0.5, A=A, pointers="device")
+    spblas.destroy(A)
+
+
+@pytest.mark.parametrize("kind", ["s", "d"])
 def test_large_coo_is_sorted_on_the_device(kind):
     """More than 2^20 COO entries take the GPU radix-sort path of alphasparse_convert_csr; the CSR must be
     the one the reference's conversion produces (bit-exact, duplicates kept in input order)."""
