@@ -47,6 +47,7 @@ enum Option {
     kOptPipeMinPieceKb,   // ... and the smallest piece of y per window, in KB
     kOptMvBlockMinKb,     // vector-kernel SpMV: an x above this many KB is multiplied column block by column block (0: never)
     kOptMvBlockKb,        // ... each block covering at most this many KB of x
+    kOptSpmmNarrow,       // 1: row-major dense blocks with rows of at most 32 bytes go through the narrow kernel
     kOptSpmmSplitMin,     // row-major dense-block product: rows above this many elements are multiplied chunk by chunk (0: never)
     kOptSpmmSplitChunk,   // ... in chunks of this many elements
     kOptSpmmColBlocks,    // column blocks of the row-major dense-block product (0 or 1: one pass)

@@ -128,6 +128,75 @@ __global__ void __launch_bounds__(256, kSpmmMinBlocks)
     }
 }
 
+// ---- narrow dense blocks -------------------------------------------------------------------------------
+//
+// With a handful of dense columns (an X row of at most 32 bytes) the kernel above degenerates: two lanes per row hand
+// their elements round two at a time and every round waits for its own X rows (2^21 rows of 32 elements times 1..8
+// fp32 columns: 0.68..1.24 ms, where an SpMV of the same matrix takes 0.2 ms).  Here the lanes of a group split the
+// ELEMENTS of the row instead, as in the vector SpMV: a lane gathers the whole X row of its element (one or two
+// 16-byte loads when the shapes allow, scalars otherwise), carries KC partial sums, two elements in flight, and the
+// group reduces them by shuffles.  alpha is folded into the stored value before the sum, as in the kernel above.
+template <typename T, int LANES, int KC, bool ALIGNED, bool HAS_BETA>
+__global__ void __launch_bounds__(256)
+    spmm_row_narrow_kernel(int rows, const int *__restrict__ row_lo, const int *__restrict__ row_hi,
+                           const int *__restrict__ col, const T *__restrict__ val, const T *__restrict__ X, int columns,
+                           long long ldx, T *__restrict__ Y, long long ldy, T alpha, T beta) {
+    constexpr int GROUPS = 256 / LANES;
+    constexpr int PER16 = 16 / (int)sizeof(T);  // elements per 16-byte load
+    const int lane = threadIdx.x % LANES;
+    const long long row = (long long)blockIdx.x * GROUPS + threadIdx.x / LANES;
+    int s = 0, e = 0;
+    if (row < rows) {
+        s = __ldg(row_lo + row);
+        e = __ldg(row_hi + row);
+    }
+    T acc[KC];
+#pragma unroll
+    for (int k = 0; k < KC; k++) acc[k] = T(0);
+    auto take = [&](int j) {
+        const int cj = __ldcs(col + j);
+        const T vj = alpha * __ldcs(val + j);
+        const T *xr = X + (long long)cj * ldx;
+        T xv[KC];
+        if (ALIGNED) {  // columns == KC, rows of X on 16-byte boundaries
+#pragma unroll
+            for (int k = 0; k < KC; k += PER16) {
+                using P = typename Pack<T, PER16>::type;
+                const P t = __ldg(reinterpret_cast<const P *>(xr + k));
+                const T *sp = reinterpret_cast<const T *>(&t);
+#pragma unroll
+                for (int i = 0; i < PER16; i++) xv[k + i] = sp[i];
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < KC; k++) xv[k] = k < columns ? __ldg(xr + k) : T(0);
+        }
+#pragma unroll
+        for (int k = 0; k < KC; k++) acc[k] = fma(vj, xv[k], acc[k]);
+    };
+    int j = s + lane;
+    for (; j + LANES < e; j += 2 * LANES) {
+        take(j);
+        take(j + LANES);
+    }
+    if (j < e) take(j);
+#pragma unroll
+    for (int k = 0; k < KC; k++) {
+#pragma unroll
+        for (int o = LANES / 2; o > 0; o >>= 1) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], o);
+    }
+    if (lane == 0 && row < rows) {
+        T *out = Y + row * ldy;
+#pragma unroll
+        for (int k = 0; k < KC; k++)
+            if (k < columns) {
+                T o = acc[k];
+                if (HAS_BETA) o = fma(beta, out[k], o);
+                out[k] = o;
+            }
+    }
+}
+
 // ---- column blocks -----------------------------------------------------------------------------------
 //
 // Every stored element reads one row of X (columns * sizeof(T) bytes).  With unstructured columns and an X far
@@ -391,6 +460,75 @@ static void launch_row_lanes(DeviceCtx *ctx, T alpha, const T *X, int columns, i
     else launch_row<T, VEC, 32>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st, w);
 }
 
+template <typename T, int LANES, int KC, bool ALIGNED>
+static void launch_narrow_as(int rows, const int *lo, const int *hi, DeviceCtx *ctx, T alpha, const T *X, int columns,
+                             int ldx, T beta, T *Y, long long ldy, cudaStream_t st) {
+    const unsigned blocks = (unsigned)(((long long)rows + 256 / LANES - 1) / (256 / LANES));
+    const T *val = static_cast<const T *>(ctx->d_val);
+    if (beta == T(0))
+        spmm_row_narrow_kernel<T, LANES, KC, ALIGNED, false><<<blocks, 256, 0, st>>>(rows, lo, hi, ctx->d_col, val, X, columns,
+                                                                                    ldx, Y, ldy, alpha, beta);
+    else
+        spmm_row_narrow_kernel<T, LANES, KC, ALIGNED, true><<<blocks, 256, 0, st>>>(rows, lo, hi, ctx->d_col, val, X, columns,
+                                                                                   ldx, Y, ldy, alpha, beta);
+    count_launch();
+}
+
+template <typename T, int KC, bool ALIGNED>
+static void launch_narrow_lanes(int lanes, int rows, const int *lo, const int *hi, DeviceCtx *ctx, T alpha, const T *X,
+                                int columns, int ldx, T beta, T *Y, long long ldy, cudaStream_t st) {
+    if (lanes <= 4) launch_narrow_as<T, 4, KC, ALIGNED>(rows, lo, hi, ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+    else if (lanes <= 8) launch_narrow_as<T, 8, KC, ALIGNED>(rows, lo, hi, ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+    else if (lanes <= 16) launch_narrow_as<T, 16, KC, ALIGNED>(rows, lo, hi, ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+    else launch_narrow_as<T, 32, KC, ALIGNED>(rows, lo, hi, ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+}
+
+// One launch of the narrow kernel over `rows` rows (or chunks) in the widest form the shapes allow.
+template <typename T>
+static void launch_narrow_pick(int lanes, int rows, const int *lo, const int *hi, DeviceCtx *ctx, T alpha, const T *X,
+                               int columns, int ldx, T beta, T *Y, long long ldy, cudaStream_t st) {
+    constexpr int PER16 = 16 / (int)sizeof(T), WIDE = 2 * PER16;
+    const bool aligned = ((uintptr_t)X & 15) == 0 && ldx % PER16 == 0;
+    if (aligned && columns == WIDE)
+        launch_narrow_lanes<T, WIDE, true>(lanes, rows, lo, hi, ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+    else if (aligned && columns == PER16)
+        launch_narrow_lanes<T, PER16, true>(lanes, rows, lo, hi, ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+    else if (columns <= PER16)
+        launch_narrow_lanes<T, PER16, false>(lanes, rows, lo, hi, ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+    else
+        launch_narrow_lanes<T, WIDE, false>(lanes, rows, lo, hi, ctx, alpha, X, columns, ldx, beta, Y, ldy, st);
+}
+
+// The row-major product with an X row of at most 32 bytes: windows and long rows as in launch_row.
+template <typename T>
+static void launch_narrow(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx, T beta, T *Y, int ldy, cudaStream_t st,
+                          const RowWindow *w) {
+    const int64_t first = w ? w->begin : 0, rows = w ? w->count : ctx->rows;
+    const SpmmSplit &sp = ctx->split;
+    const bool split = sp.state == 2;
+    const double m = ctx->mean_row_nnz;
+    const int lanes = m <= 8 ? 4 : m <= 16 ? 8 : m <= 32 ? 16 : 32;
+    if (ctx->profile) cudaEventRecord(ctx->ev_start, st);
+    const int *lo = ctx->d_row_ptr + first, *hi = split ? sp.d_hi_short + first : lo + 1;
+    launch_narrow_pick<T>(lanes, (int)rows, lo, hi, ctx, alpha, X, columns, ldx, beta, Y + first * (int64_t)ldy, ldy, st);
+    if (split) {
+        const int *lb = std::lower_bound(sp.h_long_row, sp.h_long_row + sp.nlong, (int)first);
+        const int *le = std::lower_bound(sp.h_long_row, sp.h_long_row + sp.nlong, (int)(first + rows));
+        const int64_t l0 = lb - sp.h_long_row, l1 = le - sp.h_long_row;
+        const int64_t c0 = sp.h_long_first[l0], c1 = sp.h_long_first[l1];
+        if (c1 > c0) {
+            T *part = static_cast<T *>(sp.d_part) + (size_t)c0 * columns;
+            // the partial sums are a dense block of their own: `columns` wide, rows packed
+            launch_narrow_pick<T>(32, (int)(c1 - c0), sp.d_chunk_lo + c0, sp.d_chunk_hi + c0, ctx, alpha, X, columns, ldx, T(0),
+                                  part, columns, st);
+            spmm_long_reduce_kernel<T><<<(unsigned)(l1 - l0), 32, 0, st>>>(sp.d_long_row + l0, sp.d_long_first + l0,
+                                                                         static_cast<const T *>(sp.d_part), columns, Y, ldy);
+            count_launch();
+        }
+    }
+    if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
+}
+
 template <typename T>
 alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx,
                                      T beta, T *Y, int ldy, cudaStream_t st, const RowWindow *w) {
@@ -399,6 +537,11 @@ alphasparse_status_t launch_spmm_row(DeviceCtx *ctx, T alpha, const T *X, int co
     if (bs != ALPHA_SPARSE_STATUS_SUCCESS) return bs;
     bs = col_blocks_ensure(ctx, ctx->spmm, spmm_pick_blocks(ctx, sizeof(T) * (size_t)ctx->cols * (size_t)ldx), st);
     if (bs != ALPHA_SPARSE_STATUS_SUCCESS) return bs;
+    if ((size_t)columns * sizeof(T) <= 32 && option(kOptSpmmNarrow)) {
+        launch_narrow<T>(ctx, alpha, X, columns, ldx, beta, Y, ldy, st, w);
+        ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        return ALPHA_SPARSE_STATUS_SUCCESS;
+    }
     auto fits = [&](int vec) {
         const uintptr_t mask = (uintptr_t)(vec * sizeof(T) - 1);
         return columns % vec == 0 && ldx % vec == 0 && ldy % vec == 0 &&
