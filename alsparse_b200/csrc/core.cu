@@ -66,7 +66,7 @@ struct OptionDef {
 };
 static const OptionDef kOptionDefs[kOptCount] = {
     {"band_enable", 1},       {"band_bytes", 64 * 1024}, {"band_min_seg", 12},      {"band_min_rows", 128},
-    {"band_min_share_pct", 10}, {"band_splits", 0},      {"band_overlap", 0},      {"band_packed", 1},      {"band_variant", 0},     {"bin_enable", 1},        {"bin_short", 16},         {"bin_mid0", 32},          {"bin_mid1", 256},        {"bin_overlap", 1},      {"bin_mid_max", 16384},   {"bin_push_max_peers", 4}, {"bin_sort", 1}, {"pipe_max_windows", 12}, {"pipe_min_piece_kb", 4096}, {"mv_block_min_kb", 98304}, {"mv_block_kb", 65536}, {"spmm_narrow", 1}, {"spmm_split_min", 1024}, {"spmm_split_chunk", 512}, {"spmm_col_blocks", 0},
+    {"band_min_share_pct", 10}, {"band_splits", 0},      {"band_overlap", 0},      {"band_packed", 1},      {"band_variant", 0},     {"bin_enable", 1},        {"bin_short", 16},         {"bin_mid0", 32},          {"bin_mid1", 256},        {"bin_overlap", 1},      {"bin_mid_max", 16384},   {"bin_push_max_peers", 4}, {"bin_sort", 1}, {"pipe_max_windows", 12}, {"pipe_min_piece_kb", 4096}, {"mv_block_min_kb", 98304}, {"mv_block_kb", 65536}, {"spmm_col_via_row", 2}, {"spmm_narrow", 1}, {"spmm_split_min", 1024}, {"spmm_split_chunk", 512}, {"spmm_col_blocks", 0},
 };
 static std::atomic<int64_t> g_options[kOptCount];
 static std::once_flag g_options_once;
@@ -139,6 +139,8 @@ void ctx_destroy(DeviceCtx *c) {
     spmm_blocks_destroy(c->spmm);
     spmm_split_destroy(c->split);
     spmm_blocks_destroy(c->mvb);
+    cudaFree(c->d_cm_x);
+    cudaFree(c->d_cm_y);
     cudaFree(c->d_x_stage);
     cudaFree(c->d_y_stage);
     cudaFree(c->d_status);

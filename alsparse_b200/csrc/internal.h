@@ -47,6 +47,7 @@ enum Option {
     kOptPipeMinPieceKb,   // ... and the smallest piece of y per window, in KB
     kOptMvBlockMinKb,     // vector-kernel SpMV: an x above this many KB is multiplied column block by column block (0: never)
     kOptMvBlockKb,        // ... each block covering at most this many KB of x
+    kOptSpmmColViaRow,    // column-major dense blocks of at least this many columns are transposed and go through the row-major kernels (0: never)
     kOptSpmmNarrow,       // 1: row-major dense blocks with rows of at most 32 bytes go through the narrow kernel
     kOptSpmmSplitMin,     // row-major dense-block product: rows above this many elements are multiplied chunk by chunk (0: never)
     kOptSpmmSplitChunk,   // ... in chunks of this many elements
@@ -219,6 +220,8 @@ struct DeviceCtx {
     const int *h_row_ptr = nullptr;    // host copy of the offsets, valid only while the handle is being created
     SpmmBlocks spmm;                   // column blocks of the row-major dense-block product
     SpmmSplit split;                   // its long rows, cut into chunks
+    void *d_cm_x = nullptr, *d_cm_y = nullptr;  // row-major copies of column-major dense operands (spmm.cu), grown on demand
+    size_t cm_x_bytes = 0, cm_y_bytes = 0;
     SpmmBlocks mvb;                    // column blocks of the vector-kernel SpMV, for an x that does not fit L2
     bool carry_stale = false;          // a run over ALL tiles wrote carries for tiles the schedule leaves out
     BandTables band;                   // long rows taken out of the merge tiles (spmv_band.cu); rows == 0: none

@@ -654,10 +654,75 @@ static void launch_col(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx
     if (ctx->profile) cudaEventRecord(ctx->ev_stop, st);
 }
 
+// B[f * ld_b + s] = A[s * ld_a + f] for f < n_fast, s < n_slow: a column-major operand (f = row, s = dense column)
+// into a row-major one, or back (f = dense column, s = row).  32 x 32 tiles through shared memory; the tiles along the
+// longer of the two extents are numbered by blockIdx.x (`slow_on_x`), whose range is the wide one.
+template <typename T>
+__global__ void __launch_bounds__(256) dense_transpose_kernel(long long n_fast, long long n_slow, const T *__restrict__ A,
+                                                              long long ld_a, T *__restrict__ B, long long ld_b,
+                                                              int slow_on_x) {
+    __shared__ T tile[32][33];
+    const long long f0 = (long long)(slow_on_x ? blockIdx.y : blockIdx.x) * 32;
+    const long long s0 = (long long)(slow_on_x ? blockIdx.x : blockIdx.y) * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+#pragma unroll
+    for (int k = 0; k < 32; k += 8) {
+        const long long f = f0 + tx, sl = s0 + ty + k;
+        if (f < n_fast && sl < n_slow) tile[ty + k][tx] = A[sl * ld_a + f];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 32; k += 8) {
+        const long long f = f0 + ty + k, sl = s0 + tx;
+        if (f < n_fast && sl < n_slow) B[f * ld_b + sl] = tile[tx][ty + k];
+    }
+}
+
+template <typename T>
+static void dense_transpose(long long n_fast, long long n_slow, const T *A, long long ld_a, T *B, long long ld_b,
+                            cudaStream_t st) {
+    const long long tf = (n_fast + 31) / 32, ts = (n_slow + 31) / 32;
+    const int slow_on_x = ts > tf;
+    const dim3 grid((unsigned)(slow_on_x ? ts : tf), (unsigned)(slow_on_x ? tf : ts));
+    dense_transpose_kernel<T><<<grid, 256, 0, st>>>(n_fast, n_slow, A, ld_a, B, ld_b, slow_on_x);
+    count_launch();
+}
+
+static alphasparse_status_t grow_scratch(DeviceCtx *ctx, void **buf, size_t *have, size_t want) {
+    if (*have >= want) return ALPHA_SPARSE_STATUS_SUCCESS;
+    cudaFree(*buf);
+    ctx->device_bytes -= (int64_t)*have;
+    *buf = nullptr, *have = 0;
+    ASB_CUDA_OR(device_alloc(buf, want), ALPHA_SPARSE_STATUS_ALLOC_FAILED);
+    *have = want;
+    ctx->device_bytes += (int64_t)want;
+    return ALPHA_SPARSE_STATUS_SUCCESS;
+}
+
 template <typename T>
 alphasparse_status_t launch_spmm_col(DeviceCtx *ctx, T alpha, const T *X, int columns, int ldx, T beta, T *Y,
                                      int ldy, cudaStream_t st) {
     if (ctx->rows == 0 || columns <= 0) return ALPHA_SPARSE_STATUS_SUCCESS;
+    // The kernel below gathers one x element per (stored element, dense column): four L2 requests per element and
+    // pass of four columns, where the row-major kernels take a whole X row with one or two (2^21 rows of 32 elements
+    // times 8 / 64 fp32 columns: 2.0 / 16.2 ms column-major against 0.6 / 3.5 ms row-major).  From spmm_col_via_row
+    // columns on the operands are therefore transposed into row-major copies kept with the handle (X, and Y when
+    // beta != 0), multiplied there, and Y is transposed back.
+    const int64_t via = option(kOptSpmmColViaRow);
+    if (via > 0 && columns >= via && columns <= 32 * 65535) {
+        const size_t xb = sizeof(T) * (size_t)ctx->cols * (size_t)columns, yb = sizeof(T) * (size_t)ctx->rows * (size_t)columns;
+        alphasparse_status_t s = grow_scratch(ctx, &ctx->d_cm_x, &ctx->cm_x_bytes, xb);
+        if (s == ALPHA_SPARSE_STATUS_SUCCESS) s = grow_scratch(ctx, &ctx->d_cm_y, &ctx->cm_y_bytes, yb);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        T *xt = static_cast<T *>(ctx->d_cm_x), *yt = static_cast<T *>(ctx->d_cm_y);
+        dense_transpose<T>(ctx->cols, columns, X, ldx, xt, columns, st);
+        if (beta != T(0)) dense_transpose<T>(ctx->rows, columns, Y, ldy, yt, columns, st);
+        s = launch_spmm_row<T>(ctx, alpha, xt, columns, columns, beta, yt, columns, st, nullptr);
+        if (s != ALPHA_SPARSE_STATUS_SUCCESS) return s;
+        dense_transpose<T>(columns, ctx->rows, yt, columns, Y, ldy, st);
+        ASB_CUDA_OR(cudaGetLastError(), ALPHA_SPARSE_STATUS_EXECUTION_FAILED);
+        return ALPHA_SPARSE_STATUS_SUCCESS;
+    }
     if ((columns + 3) / 4 > 65535) return ALPHA_SPARSE_STATUS_NOT_SUPPORTED;
     const alphasparse_status_t ps = spmm_split_prepare(ctx, sizeof(T), columns, st);
     if (ps != ALPHA_SPARSE_STATUS_SUCCESS) return ps;

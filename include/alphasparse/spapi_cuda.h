@@ -66,6 +66,9 @@ alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg);
  *                           column block by column block, each block covering at most mv_block_kb (65536) KB of
  *                           x, the first launch applying beta and the later ones adding to y; needs rows in
  *                           ascending column order; 0 = never
+ *   spmm_col_via_row (2)    column-major dense blocks of at least this many columns are transposed into row-major copies
+ *                           kept with the handle (X, and Y when beta != 0), multiplied by the row-major kernels
+ *                           and transposed back: device memory for one more X and Y; 0 = never
  *   spmm_narrow (1)         row-major dense blocks whose rows take at most 32 bytes (8 fp32 / 4 fp64 columns) go through
  *                           a kernel whose lanes split the elements of a sparse row instead of the dense columns
  *   spmm_split_min (1024)   row-major dense-block product on a matrix whose longest row exceeds eight times the mean:
