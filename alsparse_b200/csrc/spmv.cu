@@ -827,7 +827,12 @@ static alphasparse_status_t try_row_bins(DeviceCtx *ctx, cudaStream_t st) {
         h_ptr = fetched.data();
     }
     const int64_t long_min = option(kOptBandEnable) ? band_long_min(ctx) : INT64_MAX;
-    const int64_t mid_max = option(kOptBinMidMax);
+    // With many column bands (a wide matrix) the rows that are long enough for the band kernel start far above
+    // bin_mid_max; the 32-lane list then takes the rows in between as well, up to eight times the limit (its rows are
+    // ordered longest first), rather than the whole matrix falling back to merge tiles for them (power-law, 2^24 rows:
+    // long rows start at 24,576 elements).
+    int64_t mid_max = option(kOptBinMidMax);
+    if (long_min != INT64_MAX) mid_max = std::max(mid_max, std::min(long_min - 1, 8 * mid_max));
     for (int64_t r = 0; r < ctx->rows; r++) {
         const int64_t n = (int64_t)h_ptr[r + 1] - h_ptr[r];
         if (n > mid_max && n < long_min) return ALPHA_SPARSE_STATUS_SUCCESS;
@@ -978,7 +983,8 @@ alphasparse_status_t ctx_analyse(DeviceCtx *ctx) {
     int blocks = 1;
     const int64_t tsz = ctx->datatype == ALPHA_SPARSE_DATATYPE_DOUBLE ? 8 : 4;
     const int64_t x_kb = ctx->cols * tsz >> 10, min_kb = option(kOptMvBlockMinKb), block_kb = std::max<int64_t>(1, option(kOptMvBlockKb));
-    if (alg == ALPHA_SPARSE_CUDA_ALG_VECTOR && min_kb > 0 && x_kb > min_kb && ctx->nnz > 0)
+    if ((alg == ALPHA_SPARSE_CUDA_ALG_VECTOR || (alg == ALPHA_SPARSE_CUDA_ALG_MERGE && ctx->bins.active)) && min_kb > 0 &&
+        x_kb > min_kb && ctx->nnz > 0)  // (of a binned handle the lists of mid rows run block by block)
         blocks = (int)std::min<int64_t>(64, (x_kb + block_kb - 1) / block_kb);
     return col_blocks_ensure(ctx, ctx->mvb, blocks, st);
 }

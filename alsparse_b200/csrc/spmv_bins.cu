@@ -126,8 +126,9 @@ __device__ __forceinline__ T bin_quad_dot(const int4 c, const BinQuad<T> &v, int
 template <typename T, int LANES, int R, int U, bool HAS_BETA, bool PUSH>
 __global__ void __launch_bounds__(256)
     spmv_rowlist_kernel(int count, const int *__restrict__ list, const int *__restrict__ row_ptr,
-                        const int *__restrict__ col, const T *__restrict__ val, const T *__restrict__ x,
-                        T *__restrict__ y, T alpha, T beta, const __grid_constant__ BinPushArg<PUSH> push) {
+                        const int *__restrict__ row_end, const int *__restrict__ col, const T *__restrict__ val,
+                        const T *__restrict__ x, T *__restrict__ y, T alpha, T beta,
+                        const __grid_constant__ BinPushArg<PUSH> push) {
     constexpr int GROUPS = 256 / LANES;
     const int lane = threadIdx.x % LANES, grp = threadIdx.x / LANES;
     const long long i0 = (long long)blockIdx.x * (GROUPS * R) + grp;
@@ -139,8 +140,8 @@ __global__ void __launch_bounds__(256)
         row[u] = -1, s[u] = 0, e[u] = 0, sum[u] = T(0);
         if (i < count) {
             row[u] = __ldg(list + i);
-            s[u] = __ldg(row_ptr + row[u]);
-            e[u] = __ldg(row_ptr + row[u] + 1);
+            s[u] = __ldg(row_ptr + row[u]);  // the whole row, or its elements inside one column block (launch_list)
+            e[u] = __ldg(row_end + row[u]);
         }
         q[u] = (s[u] >> 2) + lane;
     }
@@ -295,13 +296,30 @@ static void launch_list(DeviceCtx *ctx, int k, T alpha, const T *x, T beta, T *y
     constexpr int per_block = (256 / LANES) * R;
     const unsigned blocks = (unsigned)((b.count[k] + per_block - 1) / per_block);
     const T *val = static_cast<const T *>(ctx->d_val);
-    if (beta == T(0))
-        spmv_rowlist_kernel<T, LANES, R, U, false, PUSH><<<blocks, 256, 0, st>>>(
-            (int)b.count[k], b.d_list + b.offset[k], ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta, push);
-    else
-        spmv_rowlist_kernel<T, LANES, R, U, true, PUSH><<<blocks, 256, 0, st>>>(
-            (int)b.count[k], b.d_list + b.offset[k], ctx->d_row_ptr, ctx->d_col, val, x, y, alpha, beta, push);
-    count_launch();
+    const int *list = b.d_list + b.offset[k];
+    // Column blocks (an x that does not fit L2, see ctx_analyse): one launch per block over the elements of the listed
+    // rows that fall into it; the first applies beta, the later ones add to y, the last one delivers (exchange calls).
+    const int passes = ctx->mvb.d_split ? ctx->mvb.blocks : 1;
+    for (int p = 0; p < passes; p++) {
+        const int *lo = passes > 1 ? ctx->mvb.d_split + (size_t)p * ctx->rows : ctx->d_row_ptr;
+        const int *hi = passes > 1 ? lo + ctx->rows : lo + 1;
+        const T bp = p == 0 ? beta : T(1);
+        if (PUSH && p + 1 < passes) {
+            if (bp == T(0))
+                spmv_rowlist_kernel<T, LANES, R, U, false, false><<<blocks, 256, 0, st>>>((int)b.count[k], list, lo, hi, ctx->d_col,
+                                                                                         val, x, y, alpha, bp, BinNoPush{});
+            else
+                spmv_rowlist_kernel<T, LANES, R, U, true, false><<<blocks, 256, 0, st>>>((int)b.count[k], list, lo, hi, ctx->d_col,
+                                                                                        val, x, y, alpha, bp, BinNoPush{});
+        } else if (bp == T(0)) {
+            spmv_rowlist_kernel<T, LANES, R, U, false, PUSH><<<blocks, 256, 0, st>>>((int)b.count[k], list, lo, hi, ctx->d_col, val,
+                                                                                    x, y, alpha, bp, push);
+        } else {
+            spmv_rowlist_kernel<T, LANES, R, U, true, PUSH><<<blocks, 256, 0, st>>>((int)b.count[k], list, lo, hi, ctx->d_col, val,
+                                                                                   x, y, alpha, bp, push);
+        }
+    }
+    count_launch(passes);
 }
 
 template <typename T, bool PUSH>

@@ -53,7 +53,8 @@ alphasparse_status_t alphasparse_cuda_set_algorithm(alphasparse_cuda_alg_t alg);
  *   bin_enable (1)          skewed matrices are multiplied bin by bin: thread per row up to bin_short (16)
  *                           elements, a lane group (4 / 16 / 32 lanes for rows up to bin_mid0 (32) / bin_mid1 (256) /
  *                           longer) per row above, the column-band kernel for long rows; merge
- *                           tiles remain for matrices with rows above bin_mid_max (16384) that are not long
+ *                           tiles remain for matrices with rows above bin_mid_max (16384; eight times that when the band
+ *                           kernel's own threshold lies higher, as it does for wide matrices) that are not long
  *                           enough for the band kernel, with too few long rows, or with unsorted long rows
  *   bin_sort (1)            the two lists of rows above bin_mid0 elements are ordered longest row first, so that the
  *                           rows of one thread block are of about one length; 0 = row order

@@ -59,6 +59,44 @@ def test_single_rank_push_matches_oracle(kind, after):
         spblas.destroy(A)
 
 
+@pytest.mark.parametrize("kind", ["s", "d"])
+def test_single_rank_push_with_column_blocks(kind):
+    """Handles whose x counts as too large for L2 (limit shrunk): the vector kernel and the lists of a binned handle run
+    column block by column block, and only the last launch of a list delivers to the peers."""
+    opts = dict(mv_block_min_kb=1, mv_block_kb=32, band_bytes=4096, band_min_seg=2, band_min_rows=1, band_min_share_pct=0,
+                bin_short=2, bin_mid0=8, bin_mid1=64)
+    hi = 20000 if kind == "d" else 1500
+    cases = [("binned", synth.zipf(kind, 5, 30000, 30000, 1.8, 1, hi)), ("vector", synth.uniform_fixed(kind, 6, 20000, 20000, 16))]
+    for name, m in cases:
+        try:
+            for k, v in opts.items():
+                assert spblas.set_option(k, v) == capi.SUCCESS
+            A = make_handle(kind, m)
+        finally:
+            for k in opts:
+                spblas.set_option(k, -1)
+        info = spblas.mat_info(A)[1]
+        assert (info.binned == 1) == (name == "binned"), (name, info.binned, info.algorithm)
+        ex = multi.FusedExchange(kind, np.array([0, m.nrows], np.int32), 0, 1, deliver_after=False)
+        x_ref = synth.vector(kind, 5, 1, m.cols)
+        ex.x_tensor().copy_(torch.from_numpy(x_ref))
+        y_ref = synth.vector(kind, 5, 2, m.nrows)
+        y = torch.from_numpy(y_ref).cuda()
+        for it in range(3):
+            alpha, beta = (0.125, 0.5) if it % 2 else (0.25, 0.0)
+            assert ex.step(alpha, A, beta, y) == capi.SUCCESS
+            scale = row_scale(m.ptr, m.col, m.val, x_ref, alpha, beta, y_ref)
+            want = oracle.gemv(kind, m.rows_start, m.rows_end, m.col, m.val, alpha, x_ref, beta, y_ref)
+            got_y, got_x = y.cpu().numpy(), ex.x_tensor().cpu().numpy()
+            assert np.array_equal(got_y, got_x), f"{name}: pushed x differs from y"
+            err = np.abs(got_y.astype(np.float64) - want)
+            assert (err <= (it + 1) * TOL[kind] * scale + 1e-300).all(), (name, it, float(np.max(err / np.maximum(scale, 1e-300))))
+            x_ref, y_ref = got_y.copy(), got_y.copy()
+        assert ex.status() == (capi.SUCCESS, 0)
+        ex.destroy()
+        spblas.destroy(A)
+
+
 def test_single_rank_load_x():
     """alphasparse_cuda_exchange_load_x with one rank: the piece is the whole vector; buffers swap as after a product."""
     m = synth.uniform_fixed("s", 4, 5000, 5000, 8)

@@ -686,11 +686,11 @@ def test_row_bins_and_the_column_band_path(kind, overlap, mode):
 @pytest.mark.parametrize("kind", ["s", "d"])
 def test_row_bins_without_long_rows_and_declined_bins(kind):
     """A skewed matrix whose longest rows stay below the column-band kernel's threshold is binned without that kernel;
-    a row longer than the lane-group kernels may take (bin_mid_max) but too short for the band kernel keeps the handle
-    on merge tiles."""
+    a row longer than the lane-group kernels may take (eight times bin_mid_max when the band kernel's threshold lies
+    above that) but too short for the band kernel keeps the handle on merge tiles."""
     lens = np.concatenate([synth.rowlen_zipf(3, 20000, 1.8, 1, 2500), np.zeros(50), [2999, 1]]).astype(np.int32)
     m = synth.from_lengths(kind, 3, lens, 1 << 23)              # 512 / 1024 bands: a row is long from 4096 / 8192 elements
-    for mid_max, expect in ((16384, 1), (2000, 0)):
+    for mid_max, expect in ((16384, 1), (2000, 1), (300, 0)):
         with _Options(bin_mid_max=mid_max):
             spblas.set_algorithm(capi.ALG_MERGE)
             try:
